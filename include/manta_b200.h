@@ -1,0 +1,173 @@
+/*
+ * manta_b200.h -- C ABI of the B200-native score/select path for Manta's CUDA backend.
+ *
+ * This is the boundary the Go side binds with cgo in place of the C preamble of
+ * runtime/backends/cuda/native_linux.go (reference paths are inside odvcencio/manta).
+ * Conventions kept from that preamble (native_linux.go:30-75, 385-402, 620-624):
+ *   - every call returns int: 0 = ok, 1 = failure;
+ *   - on failure *err receives a malloc'd, NUL-terminated message that the caller releases with
+ *     manta_b200_free_cstring (the reference's mantaCudaFreeCString); err may be NULL;
+ *   - the device is made current at the top of every call (goroutines migrate between threads);
+ *   - host pointers are borrowed for the duration of the call only; calls are synchronous unless
+ *     the name ends in _device and sync == 0;
+ *   - nothing aborts or traps; a runtime handle serialises its calls with an internal mutex.
+ *
+ * Differences from the reference's device path, by design:
+ *   - candidates are bound once and stay resident in HBM in their packed form (the reference
+ *     uploads all docs as fp32 on every call, native_linux.go:1705-1714);
+ *   - score -> topk -> gather(scores, ids) runs as one fused device pass (the reference runs topk
+ *     and gather on the host, runtime/backend/tensor_ops.go:119-135, 1523-1592);
+ *   - a batch of queries against ONE shared candidate matrix is supported ([Q,D] x [N,D]).
+ *
+ * There is no CPU fallback behind any of these entry points.
+ */
+#ifndef MANTA_B200_H_
+#define MANTA_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct MantaB200Runtime MantaB200Runtime;       /* replaces MantaCudaRuntime, native_linux.go:16-23 */
+typedef struct MantaB200Candidates MantaB200Candidates; /* replaces the per-call docs buffer, native_linux.go:1710 */
+
+/* Candidate layouts.  Row-major [rows, cols].
+ *   F16        : IEEE half bits, 2*cols bytes per row.
+ *   Q8_ROW_F32 : int8 codes, cols bytes per row + one f32 scale per row; value = code * scale;
+ *                scale = max|x|/127, code = round-half-away(x/scale) clamped to +-127
+ *                (the rule of runtime/embedding_trainer.go:3730-3763 applied per row).
+ *   Q4_B32_F16 : cols/32 blocks per row; block = 16 bytes, element 2j in the low nibble of byte j and
+ *                element 2j+1 in the high nibble, 4-bit two's complement codes in [-7,7]; one f16
+ *                scale per block (scales array [rows, cols/32]); value = code * scale; cols % 32 == 0.
+ */
+enum {
+    MANTA_B200_LAYOUT_F16 = 0,
+    MANTA_B200_LAYOUT_Q8_ROW_F32 = 1,
+    MANTA_B200_LAYOUT_Q4_B32_F16 = 2
+};
+
+/* Score builtins of compiler/compiler.go:803-842 / runtime/backend/tensor_ops.go:1366-1490. */
+enum {
+    MANTA_B200_METRIC_DOT = 0,
+    MANTA_B200_METRIC_COSINE = 1,
+    MANTA_B200_METRIC_L2_DISTANCE = 2
+};
+
+/* LARGEST is topKTensor's order (value descending, ties to the lower row id,
+ * runtime/backend/tensor_ops.go:1539-1552).  SMALLEST is the build's extension for
+ * "k smallest distance": ascending value, ties to the lower row id. */
+enum {
+    MANTA_B200_ORDER_LARGEST = 0,
+    MANTA_B200_ORDER_SMALLEST = 1
+};
+
+/* Where the pointers passed to manta_b200_candidates_bind live. */
+enum {
+    MANTA_B200_MEM_HOST = 0,        /* host memory: copied to the device */
+    MANTA_B200_MEM_DEVICE_COPY = 1, /* device memory: copied into storage the set owns */
+    MANTA_B200_MEM_DEVICE_ADOPT = 2 /* device memory: used in place, caller keeps it alive; needs 16-byte
+                                       aligned base and a row size that is a multiple of 16 bytes */
+};
+
+typedef struct {
+    uint64_t bind_calls;         /* counterparts of MatMulAcceleratorStats, runtime/backend/backend.go:92-107 */
+    uint64_t bound_bytes;
+    uint64_t score_calls;
+    uint64_t score_topk_calls;
+    uint64_t kernel_launches;    /* launches of this library's kernels */
+    uint64_t h2d_bytes;
+    uint64_t d2h_bytes;
+    uint64_t chunked_reruns;     /* fused passes that overflowed the candidate pool and were redone in chunks */
+    uint64_t mma_passes;         /* fused passes that ran on the tcgen05 tensor-core kernel */
+    uint64_t gemv_passes;        /* fused passes that ran on the streaming (GEMV) kernel */
+} MantaB200Stats;
+
+/* mantaCudaRuntimeCreate, native_linux.go:108-169.  device: CUDA ordinal (the reference hard-codes 0).
+ * stream: a cudaStream_t to launch on, or NULL to let the runtime create its own. */
+int manta_b200_runtime_create(int device, void* stream, MantaB200Runtime** out, char** err);
+/* mantaCudaRuntimeDestroy, native_linux.go:171-189. */
+int manta_b200_runtime_destroy(MantaB200Runtime* rt, char** err);
+/* mantaCudaFreeCString, native_linux.go:620-624. */
+void manta_b200_free_cstring(char* s);
+/* The stream all work of this runtime is issued on (cudaStream_t). */
+int manta_b200_runtime_stream(MantaB200Runtime* rt, void** out_stream, char** err);
+/* mantaCudaSynchronize-equivalent for the runtime's stream (native_linux.go:385-402 syncs after each launch). */
+int manta_b200_runtime_synchronize(MantaB200Runtime* rt, char** err);
+int manta_b200_runtime_stats(MantaB200Runtime* rt, MantaB200Stats* out, char** err);
+/* Device-time accounting of the scan kernels (the counterpart of RunNanos in MatMulAcceleratorStats,
+ * runtime/backend/backend.go:92-107).  While enabled, every fused pass brackets its scan kernel(s) with CUDA
+ * events on the runtime's stream (at most 256 passes are kept).  scan_time synchronises the stream, returns the
+ * summed device milliseconds and the number of passes measured since the last call, and clears the record. */
+int manta_b200_runtime_profile(MantaB200Runtime* rt, int enable, char** err);
+int manta_b200_runtime_scan_time(MantaB200Runtime* rt, double* total_ms, int* passes, char** err);
+/* Number of kernels this library has launched in this process (all runtimes). */
+uint64_t manta_b200_kernel_launch_count(void);
+
+/* Binds a packed candidate matrix: replaces uploadFloat32(docs.F32) of runScoreKernel
+ * (native_linux.go:1710, 1775-1785) and bindResidentMatMulParams' residency (cuda.go:129-196).
+ * data/scales are laid out as described at the layout enum; scales is NULL for F16.
+ * row_base is added to local row numbers to form the ids a fused pass returns (shard offset);
+ * row_base + rows must fit int32 (topKTensor returns int32 ids, tensor_ops.go:1553).
+ * Row statistics (sum of squares per row) are computed on the device at bind time. */
+int manta_b200_candidates_bind(MantaB200Runtime* rt, int layout, int64_t rows, int cols, const void* data,
+                               const void* scales, int64_t row_base, int mem, MantaB200Candidates** out,
+                               char** err);
+int manta_b200_candidates_unbind(MantaB200Runtime* rt, MantaB200Candidates* set, char** err);
+/* Stored bytes of a bound set (codes + scales), the figure memory planning budgets
+ * (runtime/memory_plan.go:381-406 counts codes only). */
+int64_t manta_b200_candidates_bytes(const MantaB200Candidates* set);
+
+/* Quantisers for the packed layouts: quantizeBufferInPlace + manta_forward_quantize_in_place
+ * (native_linux.go:2588-2619, 641-661) applied per row (q8) / per 32-element block (q4), codes kept
+ * instead of being multiplied back.  Host in, host out; the work runs on the device. */
+int manta_b200_pack_q8_rows(MantaB200Runtime* rt, const float* src, int64_t rows, int cols, int8_t* codes,
+                            float* scales, char** err);
+int manta_b200_pack_q4_b32(MantaB200Runtime* rt, const float* src, int64_t rows, int cols, uint8_t* codes,
+                           uint16_t* scales, char** err);
+/* Same, device in / device out, asynchronous on the runtime's stream. src_is_f16: rows are half bits. */
+int manta_b200_pack_q8_rows_device(MantaB200Runtime* rt, const void* d_src, int src_is_f16, int64_t rows, int cols,
+                                   int8_t* d_codes, float* d_scales, char** err);
+int manta_b200_pack_q4_b32_device(MantaB200Runtime* rt, const void* d_src, int src_is_f16, int64_t rows, int cols,
+                                  uint8_t* d_codes, uint16_t* d_scales, char** err);
+
+/* Full score vector: runScoreKernel + mantaCudaLaunchScore (native_linux.go:1694-1732, 419-422).
+ * queries: nq x cols IEEE half bits (nq == 1 is the reference's [D] x [N,D] form).
+ * out_scores: host, nq x rows f32. */
+int manta_b200_score(MantaB200Runtime* rt, const MantaB200Candidates* set, int metric, const uint16_t* queries,
+                     int nq, float* out_scores, char** err);
+
+/* Fused score -> topk -> gather(scores, ids): the three plan steps of compiler/compiler.go:1628-1661
+ * executed as one device pass.  out_ids: host int32 [nq, k] (row_base + local row), out_scores: host f32
+ * [nq, k], best first.  Fails like topKTensor (tensor_ops.go:1532) when k <= 0 or k > rows. */
+int manta_b200_score_topk(MantaB200Runtime* rt, const MantaB200Candidates* set, int metric, int order,
+                          const uint16_t* queries, int nq, int k, int32_t* out_ids, float* out_scores,
+                          char** err);
+/* Same with device buffers; asynchronous on the runtime's stream when sync == 0. */
+int manta_b200_score_topk_device(MantaB200Runtime* rt, const MantaB200Candidates* set, int metric, int order,
+                                 const void* d_queries, int nq, int k, int32_t* d_out_ids, float* d_out_scores,
+                                 int sync, char** err);
+
+/* Merges `lists` per-shard results (device, each [nq, k] ids + scores, concatenated list-major) into the
+ * global best k per query with the same ordering rule.  Used after the shards' lists are gathered. */
+int manta_b200_topk_merge_device(MantaB200Runtime* rt, int order, const int32_t* d_ids, const float* d_scores,
+                                 int lists, int nq, int k, int32_t* d_out_ids, float* d_out_scores, int sync,
+                                 char** err);
+
+/* gatherTensor on a rank-2 table (tensor_ops.go:794-827) for the bound set: de-quantised rows
+ * out[i, :] = value(ids[i] - row_base, :) as f32 (the reference keeps them as float32 labelled q4).
+ * Any id outside the set fails with "gather index %d out of range". */
+int manta_b200_gather_rows(MantaB200Runtime* rt, const MantaB200Candidates* set, const int32_t* ids, int64_t n,
+                           float* out, char** err);
+
+/* Integer accumulators of the packed q8 path for one query: out_acc int32 [rows, 3] =
+ * (sum hi*code, sum lo*code, sum code*code) where hi/lo are the two int8 planes the query is split into.
+ * Exists so that parity tests can demand bit equality of the integer work. */
+int manta_b200_q8_accumulators(MantaB200Runtime* rt, const MantaB200Candidates* set, const uint16_t* query,
+                               int32_t* out_acc, char** err);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MANTA_B200_H_ */

@@ -1,0 +1,814 @@
+// C ABI of the library (include/manta_b200.h): runtime, resident candidate sets, fused score/select.
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <new>
+
+#include "kernels.h"
+#include "mma.h"
+
+namespace mb200 {
+
+static std::atomic<uint64_t> g_launches{0};
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+cudaError_t launch_gemv_f16(cudaStream_t st, int sm_count, const GemvArgs& a, int mode);
+cudaError_t launch_gemv_q8(cudaStream_t st, int sm_count, const GemvArgs& a, int mode);
+cudaError_t launch_gemv_q4(cudaStream_t st, int sm_count, const GemvArgs& a, int mode);
+
+int gemv_grid_size(int sm_count) { return sm_count * 2; }
+int gemv_bucket_count(int sm_count) { return gemv_grid_size(sm_count) * kWarpsPerCta; }
+int gemv_first_burst_rows(int sm_count, int chunks) {
+    GemvShape s;
+    if (!pick_gemv_shape(chunks, &s)) return 0;
+    return gemv_bucket_count(sm_count) * (32 / s.lpr) * s.u * 4;
+}
+
+cudaError_t launch_gemv(cudaStream_t st, int sm_count, const GemvArgs& a, int mode) {
+    switch (a.cv.layout) {
+        case MANTA_B200_LAYOUT_F16: return launch_gemv_f16(st, sm_count, a, mode);
+        case MANTA_B200_LAYOUT_Q8_ROW_F32: return launch_gemv_q8(st, sm_count, a, mode);
+        case MANTA_B200_LAYOUT_Q4_B32_F16: return launch_gemv_q4(st, sm_count, a, mode);
+    }
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace mb200
+
+using namespace mb200;
+
+// ---- error plumbing (int rc + malloc'd message, as the reference's cgo preamble) -----------------------
+static int fail(char** err, const char* fmt, ...) {
+    if (err) {
+        char buf[512];
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(buf, sizeof buf, fmt, ap);
+        va_end(ap);
+        size_t n = strlen(buf) + 1;
+        char* out = (char*)malloc(n);
+        if (out) memcpy(out, buf, n);
+        *err = out;
+    }
+    return 1;
+}
+
+static int fail_cuda(char** err, const char* what, cudaError_t e) {
+    return fail(err, "%s: %s (%s)", what, cudaGetErrorName(e), cudaGetErrorString(e));
+}
+
+#define CU_TRY(call)                                       \
+    do {                                                   \
+        cudaError_t e_ = (call);                           \
+        if (e_ != cudaSuccess) return fail_cuda(err, #call, e_); \
+    } while (0)
+
+// ---- handles -----------------------------------------------------------------------------------------
+struct DevBuf {
+    void* p = nullptr;
+    size_t bytes = 0;
+};
+
+struct MantaB200Runtime {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    bool owns_stream = false;
+    int sm_count = 0;
+    std::mutex mu;
+    MantaB200Stats stats{};
+    // grow-only device buffers
+    DevBuf queries, headers, qf32, plane_hi, plane_lo, pool, count, thr, bucket, flags, out_ids, out_scores, misc;
+    // pinned host staging
+    void* h_stage = nullptr;
+    size_t h_stage_bytes = 0;
+    uint32_t* h_flags = nullptr;
+    mb200::MmaState* mma = nullptr;
+    // device-time accounting of the scan kernels
+    bool profiling = false;
+    static constexpr int kMaxProf = 256;
+    cudaEvent_t prof_ev[2 * kMaxProf];
+    int prof_created = 0;
+    int prof_used = 0;
+};
+
+static void prof_mark(MantaB200Runtime* rt, int which) {
+    if (!rt->profiling || rt->prof_used >= MantaB200Runtime::kMaxProf) return;
+    const int idx = 2 * rt->prof_used + which;
+    while (rt->prof_created <= idx) {
+        if (cudaEventCreate(&rt->prof_ev[rt->prof_created]) != cudaSuccess) return;
+        rt->prof_created++;
+    }
+    cudaEventRecord(rt->prof_ev[idx], rt->stream);
+    if (which == 1) rt->prof_used++;
+}
+
+struct MantaB200Candidates {
+    CandView cv{};
+    void* owned_data = nullptr;
+    void* owned_scales = nullptr;
+    void* owned_stats = nullptr;
+    int64_t stored_bytes = 0;
+    int device = 0;
+};
+
+static int ensure(MantaB200Runtime* rt, DevBuf& b, size_t bytes, char** err) {
+    if (bytes <= b.bytes) return 0;
+    if (b.p) {
+        CU_TRY(cudaStreamSynchronize(rt->stream));
+        CU_TRY(cudaFree(b.p));
+        b.p = nullptr;
+        b.bytes = 0;
+    }
+    size_t want = bytes + bytes / 4 + 256;
+    CU_TRY(cudaMalloc(&b.p, want));
+    b.bytes = want;
+    return 0;
+}
+
+static int ensure_host(MantaB200Runtime* rt, size_t bytes, char** err) {
+    if (bytes <= rt->h_stage_bytes) return 0;
+    if (rt->h_stage) {
+        CU_TRY(cudaStreamSynchronize(rt->stream));
+        CU_TRY(cudaFreeHost(rt->h_stage));
+        rt->h_stage = nullptr;
+        rt->h_stage_bytes = 0;
+    }
+    size_t want = bytes * 2 + 4096;
+    CU_TRY(cudaMallocHost(&rt->h_stage, want));
+    rt->h_stage_bytes = want;
+    return 0;
+}
+
+static void free_buf(DevBuf& b) {
+    if (b.p) cudaFree(b.p);
+    b.p = nullptr;
+    b.bytes = 0;
+}
+
+static const char* metric_name(int m) {
+    return m == MANTA_B200_METRIC_DOT ? "dot" : m == MANTA_B200_METRIC_COSINE ? "cosine" : "l2_distance";
+}
+
+extern "C" {
+
+void manta_b200_free_cstring(char* s) { free(s); }
+
+uint64_t manta_b200_kernel_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int manta_b200_runtime_create(int device, void* stream, MantaB200Runtime** out, char** err) {
+    if (!out) return fail(err, "runtime_create: out is NULL");
+    *out = nullptr;
+    int ndev = 0;
+    CU_TRY(cudaGetDeviceCount(&ndev));
+    if (device < 0 || device >= ndev) return fail(err, "runtime_create: device %d out of range (%d devices)", device, ndev);
+    CU_TRY(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    CU_TRY(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10) {
+        return fail(err, "runtime_create: device %d is sm_%d%d; this library carries sm_100a code only", device,
+                    prop.major, prop.minor);
+    }
+    MantaB200Runtime* rt = new (std::nothrow) MantaB200Runtime();
+    if (!rt) return fail(err, "runtime_create: out of host memory");
+    rt->device = device;
+    rt->sm_count = prop.multiProcessorCount;
+    if (stream) {
+        rt->stream = (cudaStream_t)stream;
+    } else {
+        cudaError_t e = cudaStreamCreateWithFlags(&rt->stream, cudaStreamNonBlocking);
+        if (e != cudaSuccess) {
+            delete rt;
+            return fail_cuda(err, "cudaStreamCreateWithFlags", e);
+        }
+        rt->owns_stream = true;
+    }
+    cudaError_t e = cudaMallocHost((void**)&rt->h_flags, 64);
+    if (e != cudaSuccess) {
+        if (rt->owns_stream) cudaStreamDestroy(rt->stream);
+        delete rt;
+        return fail_cuda(err, "cudaMallocHost", e);
+    }
+    *out = rt;
+    return 0;
+}
+
+int manta_b200_runtime_destroy(MantaB200Runtime* rt, char** err) {
+    if (!rt) return 0;
+    cudaSetDevice(rt->device);
+    cudaError_t e = cudaStreamSynchronize(rt->stream);
+    DevBuf* bufs[] = {&rt->queries, &rt->headers, &rt->qf32, &rt->plane_hi, &rt->plane_lo, &rt->pool, &rt->count,
+                      &rt->thr, &rt->bucket, &rt->flags, &rt->out_ids, &rt->out_scores, &rt->misc};
+    for (DevBuf* b : bufs) free_buf(*b);
+    mma_state_destroy(rt->mma);
+    for (int i = 0; i < rt->prof_created; ++i) cudaEventDestroy(rt->prof_ev[i]);
+    if (rt->h_stage) cudaFreeHost(rt->h_stage);
+    if (rt->h_flags) cudaFreeHost(rt->h_flags);
+    if (rt->owns_stream) cudaStreamDestroy(rt->stream);
+    delete rt;
+    if (e != cudaSuccess) return fail_cuda(err, "cudaStreamSynchronize", e);
+    return 0;
+}
+
+int manta_b200_runtime_stream(MantaB200Runtime* rt, void** out_stream, char** err) {
+    if (!rt || !out_stream) return fail(err, "runtime_stream: NULL argument");
+    *out_stream = (void*)rt->stream;
+    return 0;
+}
+
+int manta_b200_runtime_synchronize(MantaB200Runtime* rt, char** err) {
+    if (!rt) return fail(err, "runtime_synchronize: NULL runtime");
+    std::lock_guard<std::mutex> lk(rt->mu);
+    CU_TRY(cudaSetDevice(rt->device));
+    CU_TRY(cudaStreamSynchronize(rt->stream));
+    return 0;
+}
+
+int manta_b200_runtime_stats(MantaB200Runtime* rt, MantaB200Stats* out, char** err) {
+    if (!rt || !out) return fail(err, "runtime_stats: NULL argument");
+    std::lock_guard<std::mutex> lk(rt->mu);
+    *out = rt->stats;
+    return 0;
+}
+
+int manta_b200_runtime_profile(MantaB200Runtime* rt, int enable, char** err) {
+    if (!rt) return fail(err, "runtime_profile: NULL runtime");
+    std::lock_guard<std::mutex> lk(rt->mu);
+    CU_TRY(cudaSetDevice(rt->device));
+    CU_TRY(cudaStreamSynchronize(rt->stream));
+    rt->profiling = enable != 0;
+    rt->prof_used = 0;
+    return 0;
+}
+
+int manta_b200_runtime_scan_time(MantaB200Runtime* rt, double* total_ms, int* passes, char** err) {
+    if (!rt || !total_ms || !passes) return fail(err, "runtime_scan_time: NULL argument");
+    std::lock_guard<std::mutex> lk(rt->mu);
+    CU_TRY(cudaSetDevice(rt->device));
+    CU_TRY(cudaStreamSynchronize(rt->stream));
+    double sum = 0.0;
+    for (int i = 0; i < rt->prof_used; ++i) {
+        float ms = 0.0f;
+        CU_TRY(cudaEventElapsedTime(&ms, rt->prof_ev[2 * i], rt->prof_ev[2 * i + 1]));
+        sum += ms;
+    }
+    *total_ms = sum;
+    *passes = rt->prof_used;
+    rt->prof_used = 0;
+    return 0;
+}
+
+// ---- candidates ------------------------------------------------------------------------------------------
+static int layout_geometry(int layout, int cols, int* elem_row_bytes, int* chunks, int* scale_row_bytes, char** err) {
+    if (cols <= 0 || cols > kMaxCols) return fail(err, "candidates: cols %d out of range (1..%d)", cols, kMaxCols);
+    switch (layout) {
+        case MANTA_B200_LAYOUT_F16:
+            *elem_row_bytes = cols * 2;
+            *chunks = (cols + 7) / 8;
+            *scale_row_bytes = 0;
+            return 0;
+        case MANTA_B200_LAYOUT_Q8_ROW_F32:
+            *elem_row_bytes = cols;
+            *chunks = (cols + 15) / 16;
+            *scale_row_bytes = 4;
+            return 0;
+        case MANTA_B200_LAYOUT_Q4_B32_F16:
+            if (cols % 32) return fail(err, "candidates: q4 block32 layout needs cols %% 32 == 0, got %d", cols);
+            *elem_row_bytes = cols / 2;
+            *chunks = cols / 32;
+            *scale_row_bytes = (cols / 32) * 2;
+            return 0;
+    }
+    return fail(err, "candidates: unknown layout %d", layout);
+}
+
+int manta_b200_candidates_bind(MantaB200Runtime* rt, int layout, int64_t rows, int cols, const void* data,
+                               const void* scales, int64_t row_base, int mem, MantaB200Candidates** out,
+                               char** err) {
+    if (!rt || !out) return fail(err, "candidates_bind: NULL argument");
+    *out = nullptr;
+    int elem_row_bytes = 0, chunks = 0, scale_row_bytes = 0;
+    if (layout_geometry(layout, cols, &elem_row_bytes, &chunks, &scale_row_bytes, err)) return 1;
+    if (rows < 0) return fail(err, "candidates_bind: negative row count");
+    if (row_base < 0 || row_base + rows > (int64_t)INT32_MAX)
+        return fail(err, "candidates_bind: row ids [%lld, %lld) do not fit int32", (long long)row_base,
+                    (long long)(row_base + rows));
+    if (rows > 0 && (!data || (scale_row_bytes && !scales))) return fail(err, "candidates_bind: NULL data or scales");
+    if (!pick_gemv_shape(chunks, nullptr))
+        return fail(err, "candidates_bind: row of %d columns is wider than the kernels support for this layout", cols);
+
+    std::lock_guard<std::mutex> lk(rt->mu);
+    CU_TRY(cudaSetDevice(rt->device));
+    MantaB200Candidates* set = new (std::nothrow) MantaB200Candidates();
+    if (!set) return fail(err, "candidates_bind: out of host memory");
+    set->device = rt->device;
+    CandView& cv = set->cv;
+    cv.layout = layout;
+    cv.rows = rows;
+    cv.cols = cols;
+    cv.row_base = row_base;
+    cv.chunks = chunks;
+    cv.row_bytes = chunks * 16;
+    const size_t data_bytes = (size_t)rows * cv.row_bytes;
+    const size_t scale_bytes = (size_t)rows * scale_row_bytes;
+    set->stored_bytes = (int64_t)((size_t)rows * elem_row_bytes + scale_bytes);
+    auto cleanup = [&]() {
+        if (set->owned_data) cudaFree(set->owned_data);
+        if (set->owned_scales) cudaFree(set->owned_scales);
+        if (set->owned_stats) cudaFree(set->owned_stats);
+        delete set;
+    };
+#define BIND_TRY(call)                                 \
+    do {                                               \
+        cudaError_t e_ = (call);                       \
+        if (e_ != cudaSuccess) {                       \
+            cleanup();                                 \
+            return fail_cuda(err, #call, e_);          \
+        }                                              \
+    } while (0)
+
+    if (rows > 0) {
+        if (mem == MANTA_B200_MEM_DEVICE_ADOPT) {
+            if (cv.row_bytes != elem_row_bytes || ((uintptr_t)data & 15)) {
+                cleanup();
+                return fail(err, "candidates_bind: adopt needs a 16-byte aligned base and a row size that is a multiple of 16 bytes");
+            }
+            cv.data = (const uint8_t*)data;
+            cv.scales = scales;
+        } else if (mem == MANTA_B200_MEM_HOST || mem == MANTA_B200_MEM_DEVICE_COPY) {
+            const cudaMemcpyKind kind = (mem == MANTA_B200_MEM_HOST) ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToDevice;
+            BIND_TRY(cudaMalloc(&set->owned_data, data_bytes));
+            if (cv.row_bytes != elem_row_bytes) BIND_TRY(cudaMemsetAsync(set->owned_data, 0, data_bytes, rt->stream));
+            BIND_TRY(cudaMemcpy2DAsync(set->owned_data, cv.row_bytes, data, elem_row_bytes, elem_row_bytes, rows, kind,
+                                       rt->stream));
+            if (scale_bytes) {
+                BIND_TRY(cudaMalloc(&set->owned_scales, scale_bytes));
+                BIND_TRY(cudaMemcpyAsync(set->owned_scales, scales, scale_bytes, kind, rt->stream));
+            }
+            cv.data = (const uint8_t*)set->owned_data;
+            cv.scales = set->owned_scales;
+            if (mem == MANTA_B200_MEM_HOST) rt->stats.h2d_bytes += (uint64_t)rows * elem_row_bytes + scale_bytes;
+        } else {
+            cleanup();
+            return fail(err, "candidates_bind: unknown mem kind %d", mem);
+        }
+        BIND_TRY(cudaMalloc(&set->owned_stats, (size_t)rows * 4));
+        cv.stats = set->owned_stats;
+        launch_row_stats(rt->stream, cv, set->owned_stats);
+        rt->stats.kernel_launches++;
+        BIND_TRY(cudaGetLastError());
+        BIND_TRY(cudaStreamSynchronize(rt->stream));
+    }
+#undef BIND_TRY
+    rt->stats.bind_calls++;
+    rt->stats.bound_bytes += (uint64_t)set->stored_bytes;
+    *out = set;
+    return 0;
+}
+
+int manta_b200_candidates_unbind(MantaB200Runtime* rt, MantaB200Candidates* set, char** err) {
+    if (!set) return 0;
+    if (!rt) return fail(err, "candidates_unbind: NULL runtime");
+    std::lock_guard<std::mutex> lk(rt->mu);
+    CU_TRY(cudaSetDevice(rt->device));
+    CU_TRY(cudaStreamSynchronize(rt->stream));
+    if (set->owned_data) cudaFree(set->owned_data);
+    if (set->owned_scales) cudaFree(set->owned_scales);
+    if (set->owned_stats) cudaFree(set->owned_stats);
+    delete set;
+    return 0;
+}
+
+int64_t manta_b200_candidates_bytes(const MantaB200Candidates* set) { return set ? set->stored_bytes : 0; }
+
+// ---- quantisers --------------------------------------------------------------------------------------------
+int manta_b200_pack_q8_rows_device(MantaB200Runtime* rt, const void* d_src, int src_is_f16, int64_t rows, int cols,
+                                   int8_t* d_codes, float* d_scales, char** err) {
+    if (!rt) return fail(err, "pack_q8_rows: NULL runtime");
+    if (rows < 0 || cols <= 0) return fail(err, "pack_q8_rows: bad shape");
+    std::lock_guard<std::mutex> lk(rt->mu);
+    CU_TRY(cudaSetDevice(rt->device));
+    launch_pack_q8(rt->stream, d_src, src_is_f16 != 0, rows, cols, cols, d_codes, d_scales);
+    rt->stats.kernel_launches++;
+    CU_TRY(cudaGetLastError());
+    return 0;
+}
+
+int manta_b200_pack_q4_b32_device(MantaB200Runtime* rt, const void* d_src, int src_is_f16, int64_t rows, int cols,
+                                  uint8_t* d_codes, uint16_t* d_scales, char** err) {
+    if (!rt) return fail(err, "pack_q4_b32: NULL runtime");
+    if (rows < 0 || cols <= 0 || cols % 32) return fail(err, "pack_q4_b32: cols must be a positive multiple of 32");
+    std::lock_guard<std::mutex> lk(rt->mu);
+    CU_TRY(cudaSetDevice(rt->device));
+    launch_pack_q4(rt->stream, d_src, src_is_f16 != 0, rows, cols, d_codes, d_scales);
+    rt->stats.kernel_launches++;
+    CU_TRY(cudaGetLastError());
+    return 0;
+}
+
+static int pack_host(MantaB200Runtime* rt, int which, const float* src, int64_t rows, int cols, void* codes,
+                     void* scales, char** err) {
+    if (!rt || !src || !codes || !scales) return fail(err, "pack: NULL argument");
+    if (rows < 0 || cols <= 0 || (which == 4 && cols % 32)) return fail(err, "pack: bad shape");
+    if (rows == 0) return 0;
+    const size_t src_bytes = (size_t)rows * cols * 4;
+    const size_t code_bytes = (which == 8) ? (size_t)rows * cols : (size_t)rows * cols / 2;
+    const size_t scale_bytes = (which == 8) ? (size_t)rows * 4 : (size_t)rows * (cols / 32) * 2;
+    void *d_src = nullptr, *d_codes = nullptr, *d_scales = nullptr;
+    {
+        std::lock_guard<std::mutex> lk(rt->mu);
+        CU_TRY(cudaSetDevice(rt->device));
+        cudaError_t e = cudaMalloc(&d_src, src_bytes);
+        if (e == cudaSuccess) e = cudaMalloc(&d_codes, code_bytes);
+        if (e == cudaSuccess) e = cudaMalloc(&d_scales, scale_bytes);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(d_src, src, src_bytes, cudaMemcpyHostToDevice, rt->stream);
+        if (e == cudaSuccess) {
+            if (which == 8)
+                launch_pack_q8(rt->stream, d_src, false, rows, cols, cols, (int8_t*)d_codes, (float*)d_scales);
+            else
+                launch_pack_q4(rt->stream, d_src, false, rows, cols, (uint8_t*)d_codes, (uint16_t*)d_scales);
+            rt->stats.kernel_launches++;
+            e = cudaGetLastError();
+        }
+        if (e == cudaSuccess) e = cudaMemcpyAsync(codes, d_codes, code_bytes, cudaMemcpyDeviceToHost, rt->stream);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(scales, d_scales, scale_bytes, cudaMemcpyDeviceToHost, rt->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(rt->stream);
+        cudaFree(d_src);
+        cudaFree(d_codes);
+        cudaFree(d_scales);
+        if (e != cudaSuccess) return fail_cuda(err, "pack", e);
+        rt->stats.h2d_bytes += src_bytes;
+        rt->stats.d2h_bytes += code_bytes + scale_bytes;
+    }
+    return 0;
+}
+
+int manta_b200_pack_q8_rows(MantaB200Runtime* rt, const float* src, int64_t rows, int cols, int8_t* codes,
+                            float* scales, char** err) {
+    return pack_host(rt, 8, src, rows, cols, codes, scales, err);
+}
+
+int manta_b200_pack_q4_b32(MantaB200Runtime* rt, const float* src, int64_t rows, int cols, uint8_t* codes,
+                           uint16_t* scales, char** err) {
+    return pack_host(rt, 4, src, rows, cols, codes, scales, err);
+}
+
+// ---- scoring ---------------------------------------------------------------------------------------------------
+static int plane_stride_for(const CandView& cv) {
+    int bytes = (cv.layout == MANTA_B200_LAYOUT_Q4_B32_F16) ? cv.chunks * 32 : cv.chunks * 16;
+    return (bytes + 127) / 128 * 128;
+}
+
+// Pool capacity per query for the optimistic single-launch pass.
+static uint32_t pool_cap_for(const MantaB200Runtime* rt, const CandView& cv, int nq, int k) {
+    int64_t rows = cv.rows;
+    int64_t cap = mma_supported(cv, nq) ? (int64_t)mma_first_burst_rows(rt->sm_count) * 2
+                                        : (int64_t)gemv_first_burst_rows(rt->sm_count, cv.chunks) * 2;
+    if (cap < 32ll * k) cap = 32ll * k;
+    if (cap < 16384) cap = 16384;
+    if (cap > rows) cap = rows;  // a pool as large as the set cannot overflow
+    if (cap < k) cap = k;
+    return (uint32_t)cap;
+}
+
+static int prepare_queries(MantaB200Runtime* rt, const CandView& cv, const void* d_queries, int nq, const SelectWs& ws,
+                           int reset_ws, QueryPrep* qp, char** err) {
+    const int ps = plane_stride_for(cv);
+    if (ensure(rt, rt->headers, (size_t)nq * sizeof(QueryHeader), err)) return 1;
+    if (ensure(rt, rt->qf32, (size_t)nq * cv.cols * 4, err)) return 1;
+    if (ensure(rt, rt->plane_hi, (size_t)nq * ps, err)) return 1;
+    if (ensure(rt, rt->plane_lo, (size_t)nq * ps, err)) return 1;
+    launch_query_prep(rt->stream, d_queries, nq, cv.cols, cv.layout, ps, (QueryHeader*)rt->headers.p, (float*)rt->qf32.p,
+                      (int8_t*)rt->plane_hi.p, (int8_t*)rt->plane_lo.p, ws, reset_ws);
+    rt->stats.kernel_launches++;
+    CU_TRY(cudaGetLastError());
+    qp->headers = (const QueryHeader*)rt->headers.p;
+    qp->qf32 = (const float*)rt->qf32.p;
+    qp->plane_hi = (const int8_t*)rt->plane_hi.p;
+    qp->plane_lo = (const int8_t*)rt->plane_lo.p;
+    qp->plane_stride = ps;
+    qp->nq = nq;
+    return 0;
+}
+
+static int ensure_select_ws(MantaB200Runtime* rt, int nq, uint32_t cap, uint32_t nb, SelectWs* ws, char** err) {
+    if (ensure(rt, rt->pool, (size_t)nq * cap * 8, err)) return 1;
+    if (ensure(rt, rt->count, (size_t)nq * 4, err)) return 1;
+    if (ensure(rt, rt->thr, (size_t)nq * 4, err)) return 1;
+    if (ensure(rt, rt->bucket, (size_t)nq * nb * 4, err)) return 1;
+    if (ensure(rt, rt->flags, kNumFlags * 4, err)) return 1;
+    ws->pool = (uint64_t*)rt->pool.p;
+    ws->count = (uint32_t*)rt->count.p;
+    ws->thr = (uint32_t*)rt->thr.p;
+    ws->bucket = (uint32_t*)rt->bucket.p;
+    ws->flags = (uint32_t*)rt->flags.p;
+    ws->cap = cap;
+    ws->nb = nb;
+    return 0;
+}
+
+static int check_score_args(const MantaB200Runtime* rt, const MantaB200Candidates* set, int metric, int nq, char** err) {
+    if (!rt || !set) return fail(err, "score: NULL runtime or candidate set");
+    if (set->device != rt->device) return fail(err, "score: candidate set lives on device %d, runtime on %d", set->device, rt->device);
+    if (metric < 0 || metric > 2) return fail(err, "score: unknown metric %d", metric);
+    if (nq <= 0) return fail(err, "score: query count %d out of range", nq);
+    return 0;
+}
+
+// Streams the row range [r0, r1) through the scoring kernels for all queries (no reset, no selection).
+static int scan_rows(MantaB200Runtime* rt, const CandView& cv, const QueryPrep& qp, int metric, int order, int k,
+                     int64_t r0, int64_t r1, const SelectWs& ws, int nq, bool allow_mma, char** err) {
+    if (allow_mma && mma_supported(cv, nq)) {
+        MmaArgs m;
+        m.cv = cv;
+        m.qp = qp;
+        m.metric = metric;
+        m.order = order;
+        m.k = k;
+        m.row_begin = r0;
+        m.row_end = r1;
+        m.ws = ws;
+        m.nq = nq;
+        int launches = 0;
+        const char* why = nullptr;
+        cudaError_t e = launch_mma_topk(rt->stream, rt->sm_count, &rt->mma, m, &launches, &why);
+        rt->stats.kernel_launches += launches;
+        if (e != cudaSuccess) return fail(err, "score_topk(%s): tensor-core pass: %s (%s)", metric_name(metric), why ? why : "launch failed", cudaGetErrorName(e));
+        rt->stats.mma_passes++;
+        return 0;
+    }
+    for (int q0 = 0; q0 < nq;) {
+        int left = nq - q0;
+        int qt = left >= 4 ? 4 : (left >= 2 ? 2 : 1);
+        GemvShape s;
+        pick_gemv_shape(cv.chunks, &s);
+        if (s.cpl == 8) qt = 1;
+        GemvArgs a{};
+        a.cv = cv;
+        a.qp = qp;
+        a.q0 = q0;
+        a.qt = qt;
+        a.metric = metric;
+        a.order = order;
+        a.k = k;
+        a.row_begin = r0;
+        a.row_end = r1;
+        a.ws = ws;
+        cudaError_t e = launch_gemv(rt->stream, rt->sm_count, a, kModeTopk);
+        rt->stats.kernel_launches++;
+        if (e != cudaSuccess) return fail_cuda(err, "launch score kernel", e);
+        q0 += qt;
+    }
+    rt->stats.gemv_passes++;
+    return 0;
+}
+
+static int score_topk_locked(MantaB200Runtime* rt, const MantaB200Candidates* set, int metric, int order,
+                             const void* d_queries, int nq, int k, int32_t* d_out_ids, float* d_out_scores, int sync,
+                             char** err) {
+    const CandView& cv = set->cv;
+    const uint32_t nb = (uint32_t)std::max(gemv_bucket_count(rt->sm_count), mma_bucket_count(rt->sm_count));
+    uint32_t cap = pool_cap_for(rt, cv, nq, k);
+    SelectWs ws;
+    if (ensure_select_ws(rt, nq, cap, nb, &ws, err)) return 1;
+    QueryPrep qp;
+    if (prepare_queries(rt, cv, d_queries, nq, ws, 1, &qp, err)) return 1;
+    prof_mark(rt, 0);
+    if (scan_rows(rt, cv, qp, metric, order, k, 0, cv.rows, ws, nq, true, err)) return 1;
+    prof_mark(rt, 1);
+    SelectArgs sa{};
+    sa.ws = ws;
+    sa.nq = nq;
+    sa.k = k;
+    sa.order = order;
+    sa.write_back = 0;
+    sa.out_ids = d_out_ids;
+    sa.out_scores = d_out_scores;
+    cudaError_t e = launch_select(rt->stream, sa);
+    rt->stats.kernel_launches++;
+    if (e != cudaSuccess) return fail_cuda(err, "launch select kernel", e);
+    CU_TRY(cudaMemcpyAsync(rt->h_flags, ws.flags, kNumFlags * 4, cudaMemcpyDeviceToHost, rt->stream));
+    if (!sync) return 0;
+    CU_TRY(cudaStreamSynchronize(rt->stream));
+    if (rt->h_flags[kFlagTimeout]) return fail(err, "score_topk(%s): a bounded device wait gave up", metric_name(metric));
+    if (!rt->h_flags[kFlagOverflow]) {
+        if (rt->h_flags[kFlagInternal]) return fail(err, "score_topk(%s): selection found fewer than k candidates", metric_name(metric));
+        return 0;
+    }
+    // The candidate pool overflowed (scores arrive in an order that keeps beating the threshold).  Redo the
+    // pass in row chunks that cannot overflow, compacting the pool to the best k between chunks.
+    rt->stats.chunked_reruns++;
+    int64_t chunk = std::min<int64_t>(cv.rows, (int64_t)1 << 20);
+    cap = (uint32_t)(chunk + k);
+    if (ensure_select_ws(rt, nq, cap, nb, &ws, err)) return 1;
+    if (prepare_queries(rt, cv, d_queries, nq, ws, 1, &qp, err)) return 1;
+    for (int64_t r0 = 0; r0 < cv.rows; r0 += chunk) {
+        int64_t r1 = std::min(cv.rows, r0 + chunk);
+        if (scan_rows(rt, cv, qp, metric, order, k, r0, r1, ws, nq, false, err)) return 1;
+        sa.ws = ws;
+        sa.write_back = (r1 < cv.rows) ? 1 : 0;
+        sa.out_ids = sa.write_back ? nullptr : d_out_ids;
+        sa.out_scores = sa.write_back ? nullptr : d_out_scores;
+        e = launch_select(rt->stream, sa);
+        rt->stats.kernel_launches++;
+        if (e != cudaSuccess) return fail_cuda(err, "launch select kernel", e);
+    }
+    CU_TRY(cudaMemcpyAsync(rt->h_flags, ws.flags, kNumFlags * 4, cudaMemcpyDeviceToHost, rt->stream));
+    CU_TRY(cudaStreamSynchronize(rt->stream));
+    if (rt->h_flags[kFlagOverflow] || rt->h_flags[kFlagInternal])
+        return fail(err, "score_topk(%s): chunked selection failed (flags %u %u)", metric_name(metric),
+                    rt->h_flags[kFlagOverflow], rt->h_flags[kFlagInternal]);
+    return 0;
+}
+
+static int check_topk_args(const MantaB200Candidates* set, int order, int k, char** err) {
+    if (order != MANTA_B200_ORDER_LARGEST && order != MANTA_B200_ORDER_SMALLEST) return fail(err, "score_topk: unknown order %d", order);
+    // message of topKTensor, runtime/backend/tensor_ops.go:1532
+    if (k <= 0 || k > set->cv.rows) return fail(err, "topk limit %d out of range for %lld scores", k, (long long)set->cv.rows);
+    if (k > kMaxK) return fail(err, "topk limit %d exceeds the fused pass maximum %d", k, kMaxK);
+    return 0;
+}
+
+int manta_b200_score_topk_device(MantaB200Runtime* rt, const MantaB200Candidates* set, int metric, int order,
+                                 const void* d_queries, int nq, int k, int32_t* d_out_ids, float* d_out_scores,
+                                 int sync, char** err) {
+    if (check_score_args(rt, set, metric, nq, err)) return 1;
+    if (check_topk_args(set, order, k, err)) return 1;
+    if (!d_queries || !d_out_ids || !d_out_scores) return fail(err, "score_topk: NULL buffer");
+    std::lock_guard<std::mutex> lk(rt->mu);
+    CU_TRY(cudaSetDevice(rt->device));
+    rt->stats.score_topk_calls++;
+    return score_topk_locked(rt, set, metric, order, d_queries, nq, k, d_out_ids, d_out_scores, sync, err);
+}
+
+int manta_b200_score_topk(MantaB200Runtime* rt, const MantaB200Candidates* set, int metric, int order,
+                          const uint16_t* queries, int nq, int k, int32_t* out_ids, float* out_scores, char** err) {
+    if (check_score_args(rt, set, metric, nq, err)) return 1;
+    if (check_topk_args(set, order, k, err)) return 1;
+    if (!queries || !out_ids || !out_scores) return fail(err, "score_topk: NULL buffer");
+    std::lock_guard<std::mutex> lk(rt->mu);
+    CU_TRY(cudaSetDevice(rt->device));
+    rt->stats.score_topk_calls++;
+    const size_t qbytes = (size_t)nq * set->cv.cols * 2;
+    const size_t obytes = (size_t)nq * k * 4;
+    if (ensure(rt, rt->queries, qbytes, err)) return 1;
+    if (ensure(rt, rt->out_ids, obytes, err)) return 1;
+    if (ensure(rt, rt->out_scores, obytes, err)) return 1;
+    const size_t qpad = (qbytes + 255) / 256 * 256, opad = (obytes + 255) / 256 * 256;
+    if (ensure_host(rt, qpad + 2 * opad, err)) return 1;
+    char* hq = (char*)rt->h_stage;
+    char* hi = hq + qpad;
+    char* hs = hi + opad;
+    memcpy(hq, queries, qbytes);
+    CU_TRY(cudaMemcpyAsync(rt->queries.p, hq, qbytes, cudaMemcpyHostToDevice, rt->stream));
+    rt->stats.h2d_bytes += qbytes;
+    int rc = score_topk_locked(rt, set, metric, order, rt->queries.p, nq, k, (int32_t*)rt->out_ids.p,
+                               (float*)rt->out_scores.p, 1, err);
+    if (rc) return rc;
+    CU_TRY(cudaMemcpyAsync(hi, rt->out_ids.p, obytes, cudaMemcpyDeviceToHost, rt->stream));
+    CU_TRY(cudaMemcpyAsync(hs, rt->out_scores.p, obytes, cudaMemcpyDeviceToHost, rt->stream));
+    CU_TRY(cudaStreamSynchronize(rt->stream));
+    memcpy(out_ids, hi, obytes);
+    memcpy(out_scores, hs, obytes);
+    rt->stats.d2h_bytes += 2 * obytes;
+    return 0;
+}
+
+int manta_b200_score(MantaB200Runtime* rt, const MantaB200Candidates* set, int metric, const uint16_t* queries,
+                     int nq, float* out_scores, char** err) {
+    if (check_score_args(rt, set, metric, nq, err)) return 1;
+    if (!queries || !out_scores) return fail(err, "score: NULL buffer");
+    std::lock_guard<std::mutex> lk(rt->mu);
+    CU_TRY(cudaSetDevice(rt->device));
+    rt->stats.score_calls++;
+    const CandView& cv = set->cv;
+    if (cv.rows == 0) return 0;
+    const size_t qbytes = (size_t)nq * cv.cols * 2;
+    const size_t obytes = (size_t)nq * cv.rows * 4;
+    if (ensure(rt, rt->queries, qbytes, err)) return 1;
+    if (ensure(rt, rt->misc, obytes, err)) return 1;
+    CU_TRY(cudaMemcpyAsync(rt->queries.p, queries, qbytes, cudaMemcpyHostToDevice, rt->stream));
+    SelectWs ws{};
+    QueryPrep qp;
+    if (prepare_queries(rt, cv, rt->queries.p, nq, ws, 0, &qp, err)) return 1;
+    for (int q0 = 0; q0 < nq;) {
+        int left = nq - q0;
+        int qt = left >= 4 ? 4 : (left >= 2 ? 2 : 1);
+        GemvShape s;
+        pick_gemv_shape(cv.chunks, &s);
+        if (s.cpl == 8) qt = 1;
+        GemvArgs a{};
+        a.cv = cv;
+        a.qp = qp;
+        a.q0 = q0;
+        a.qt = qt;
+        a.metric = metric;
+        a.row_begin = 0;
+        a.row_end = cv.rows;
+        a.out_scores = (float*)rt->misc.p;
+        cudaError_t e = launch_gemv(rt->stream, rt->sm_count, a, kModeScores);
+        rt->stats.kernel_launches++;
+        if (e != cudaSuccess) return fail_cuda(err, "launch score kernel", e);
+        q0 += qt;
+    }
+    CU_TRY(cudaMemcpyAsync(out_scores, rt->misc.p, obytes, cudaMemcpyDeviceToHost, rt->stream));
+    CU_TRY(cudaStreamSynchronize(rt->stream));
+    rt->stats.h2d_bytes += qbytes;
+    rt->stats.d2h_bytes += obytes;
+    return 0;
+}
+
+int manta_b200_q8_accumulators(MantaB200Runtime* rt, const MantaB200Candidates* set, const uint16_t* query,
+                               int32_t* out_acc, char** err) {
+    if (check_score_args(rt, set, MANTA_B200_METRIC_DOT, 1, err)) return 1;
+    if (set->cv.layout != MANTA_B200_LAYOUT_Q8_ROW_F32) return fail(err, "q8_accumulators: candidate set is not q8");
+    if (!query || !out_acc) return fail(err, "q8_accumulators: NULL buffer");
+    std::lock_guard<std::mutex> lk(rt->mu);
+    CU_TRY(cudaSetDevice(rt->device));
+    const CandView& cv = set->cv;
+    if (cv.rows == 0) return 0;
+    const size_t qbytes = (size_t)cv.cols * 2;
+    const size_t obytes = (size_t)cv.rows * 12;
+    if (ensure(rt, rt->queries, qbytes, err)) return 1;
+    if (ensure(rt, rt->misc, obytes, err)) return 1;
+    CU_TRY(cudaMemcpyAsync(rt->queries.p, query, qbytes, cudaMemcpyHostToDevice, rt->stream));
+    SelectWs ws{};
+    QueryPrep qp;
+    if (prepare_queries(rt, cv, rt->queries.p, 1, ws, 0, &qp, err)) return 1;
+    GemvArgs a{};
+    a.cv = cv;
+    a.qp = qp;
+    a.q0 = 0;
+    a.qt = 1;
+    a.metric = MANTA_B200_METRIC_COSINE;
+    a.row_begin = 0;
+    a.row_end = cv.rows;
+    a.out_acc = (int32_t*)rt->misc.p;
+    cudaError_t e = launch_gemv(rt->stream, rt->sm_count, a, kModeAccum);
+    rt->stats.kernel_launches++;
+    if (e != cudaSuccess) return fail_cuda(err, "launch score kernel", e);
+    CU_TRY(cudaMemcpyAsync(out_acc, rt->misc.p, obytes, cudaMemcpyDeviceToHost, rt->stream));
+    CU_TRY(cudaStreamSynchronize(rt->stream));
+    return 0;
+}
+
+int manta_b200_topk_merge_device(MantaB200Runtime* rt, int order, const int32_t* d_ids, const float* d_scores,
+                                 int lists, int nq, int k, int32_t* d_out_ids, float* d_out_scores, int sync,
+                                 char** err) {
+    if (!rt || !d_ids || !d_scores || !d_out_ids || !d_out_scores) return fail(err, "topk_merge: NULL argument");
+    if (lists <= 0 || nq <= 0 || k <= 0 || k > kMaxK) return fail(err, "topk_merge: bad shape (lists %d, nq %d, k %d)", lists, nq, k);
+    std::lock_guard<std::mutex> lk(rt->mu);
+    CU_TRY(cudaSetDevice(rt->device));
+    SelectWs ws;
+    if (ensure_select_ws(rt, nq, (uint32_t)(lists * k), 1, &ws, err)) return 1;
+    cudaError_t e = launch_lists_to_pool(rt->stream, d_ids, d_scores, lists, nq, k, order, ws);
+    rt->stats.kernel_launches++;
+    if (e != cudaSuccess) return fail_cuda(err, "launch lists_to_pool", e);
+    SelectArgs sa{};
+    sa.ws = ws;
+    sa.nq = nq;
+    sa.k = k;
+    sa.order = order;
+    sa.out_ids = d_out_ids;
+    sa.out_scores = d_out_scores;
+    e = launch_select(rt->stream, sa);
+    rt->stats.kernel_launches++;
+    if (e != cudaSuccess) return fail_cuda(err, "launch select kernel", e);
+    if (sync) CU_TRY(cudaStreamSynchronize(rt->stream));
+    return 0;
+}
+
+int manta_b200_gather_rows(MantaB200Runtime* rt, const MantaB200Candidates* set, const int32_t* ids, int64_t n,
+                           float* out, char** err) {
+    if (!rt || !set) return fail(err, "gather: NULL runtime or candidate set");
+    if (n < 0 || (n > 0 && (!ids || !out))) return fail(err, "gather: NULL buffer");
+    if (n == 0) return 0;
+    std::lock_guard<std::mutex> lk(rt->mu);
+    CU_TRY(cudaSetDevice(rt->device));
+    const CandView& cv = set->cv;
+    const size_t ibytes = (size_t)n * 4, obytes = (size_t)n * cv.cols * 4;
+    if (ensure(rt, rt->out_ids, ibytes + 64, err)) return 1;
+    if (ensure(rt, rt->misc, obytes, err)) return 1;
+    if (ensure(rt, rt->flags, kNumFlags * 4, err)) return 1;
+    // out_ids: [n ids][pad][bad id]; flags[3] doubles as the "bad id seen" word
+    int32_t* d_ids = (int32_t*)rt->out_ids.p;
+    int32_t* d_bad = d_ids + n + 8;
+    uint32_t* d_flag = (uint32_t*)rt->flags.p + 3;
+    CU_TRY(cudaMemcpyAsync(d_ids, ids, ibytes, cudaMemcpyHostToDevice, rt->stream));
+    CU_TRY(cudaMemsetAsync(d_flag, 0, 4, rt->stream));
+    launch_gather_rows(rt->stream, cv, d_ids, n, (float*)rt->misc.p, d_bad, d_flag);
+    rt->stats.kernel_launches++;
+    CU_TRY(cudaGetLastError());
+    CU_TRY(cudaMemcpyAsync(&rt->h_flags[8], d_flag, 4, cudaMemcpyDeviceToHost, rt->stream));
+    CU_TRY(cudaMemcpyAsync(&rt->h_flags[9], d_bad, 4, cudaMemcpyDeviceToHost, rt->stream));
+    CU_TRY(cudaMemcpyAsync(out, rt->misc.p, obytes, cudaMemcpyDeviceToHost, rt->stream));
+    CU_TRY(cudaStreamSynchronize(rt->stream));
+    if (rt->h_flags[8]) return fail(err, "gather index %d out of range", (int32_t)rt->h_flags[9]);  // tensor_ops.go:803
+    rt->stats.h2d_bytes += ibytes;
+    rt->stats.d2h_bytes += obytes;
+    return 0;
+}
+
+}  // extern "C"

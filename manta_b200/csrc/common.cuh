@@ -1,0 +1,154 @@
+// Shared declarations of the score/select kernels: parameter blocks, key encoding, small device helpers.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/manta_b200.h"
+
+namespace mb200 {
+
+constexpr int kMaxK = 2048;          // largest k the fused pass accepts
+constexpr int kMaxCols = 8192;       // largest row width (elements)
+constexpr int kThreads = 256;        // threads per CTA of the streaming kernels
+constexpr int kWarpsPerCta = kThreads / 32;
+
+// ---- ordering -------------------------------------------------------------------------------------
+// A candidate is ranked by "goodness" g: g = score for LARGEST, g = -score for SMALLEST.  ord(g) is a
+// monotone map float -> uint32 (0 is below every finite value and marks "empty").  The 64-bit key
+// (ord(g) << 32) | ~id is unique per row and orders by goodness descending, then id ascending, which is
+// the comparator of topKTensor.
+__host__ __device__ inline uint32_t ord_from_float(float g) {
+    uint32_t u = __builtin_bit_cast(uint32_t, g);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__host__ __device__ inline float float_from_ord(uint32_t o) {
+    uint32_t u = (o & 0x80000000u) ? (o & 0x7fffffffu) : ~o;
+    return __builtin_bit_cast(float, u);
+}
+__host__ __device__ inline uint64_t make_key(float g, int32_t id) {
+    return ((uint64_t)ord_from_float(g) << 32) | (uint64_t)(~(uint32_t)id);
+}
+__host__ __device__ inline int32_t key_id(uint64_t key) { return (int32_t)(~(uint32_t)(key & 0xffffffffu)); }
+__host__ __device__ inline float key_goodness(uint64_t key) { return float_from_ord((uint32_t)(key >> 32)); }
+
+// ---- per-query constants produced by the query-prep kernel -----------------------------------------
+struct QueryHeader {
+    float s_hi;   // scale of the high int8 plane (q8/q4 candidates)
+    float s_lo;   // scale of the low int8 plane
+    float qn;     // ||q|| (f32 of the f64 root)
+    float qn2;    // ||q||^2 (f32 of the f64 sum)
+};
+
+// ---- selection workspace ------------------------------------------------------------------------------
+// Per query: pool of candidate keys (append-only within a pass), its fill count, the current filter
+// threshold (ord space, only ever raised) and one running maximum per bucket (a bucket is a disjoint
+// subset of rows; the k-th largest bucket maximum is a valid lower bound of the k-th best score).
+struct SelectWs {
+    uint64_t* pool;       // [nq][cap]
+    uint32_t* count;      // [nq]
+    uint32_t* thr;        // [nq]
+    uint32_t* bucket;     // [nq][nb]
+    uint32_t* flags;      // [0] pool overflow, [1] bounded wait gave up, [2] internal check failed
+    uint32_t cap;
+    uint32_t nb;
+};
+
+enum { kFlagOverflow = 0, kFlagTimeout = 1, kFlagInternal = 2, kNumFlags = 4 };
+
+struct CandView {
+    const uint8_t* data;     // packed rows
+    const void* scales;      // f32 per row (q8) or f16 per block (q4); null for f16
+    const void* stats;       // per row: int32 sum code^2 (q8) or f32 sum value^2 (q4, f16)
+    int64_t rows;
+    int64_t row_base;
+    int cols;
+    int row_bytes;           // stride between rows in data
+    int chunks;              // 16-byte chunks per row that carry data
+    int layout;
+};
+
+// score epilogues -----------------------------------------------------------------------------------------
+// q8: t = s_hi*I_hi + s_lo*I_lo is q . codes (without the row scale).  Fixed operation order, every
+// operation correctly rounded, so a CPU model can reproduce the bits.
+__device__ __forceinline__ float q8_finish(int metric, int ih, int il, int nn, float sd, const QueryHeader& h) {
+    float a = __fmul_rn((float)ih, h.s_hi);
+    float t = __fmaf_rn((float)il, h.s_lo, a);
+    float res;
+    if (metric == MANTA_B200_METRIC_DOT) {
+        res = __fmul_rn(t, sd);
+    } else if (metric == MANTA_B200_METRIC_COSINE) {
+        if (nn == 0 || h.qn == 0.0f) {
+            res = 0.0f;
+        } else {
+            res = __fdiv_rn(t, __fmul_rn(h.qn, __fsqrt_rn((float)nn)));
+        }
+    } else {
+        float dotv = __fmul_rn(t, sd);
+        float dn2 = __fmul_rn(__fmul_rn(sd, sd), (float)nn);
+        float x = __fmaf_rn(-2.0f, dotv, __fadd_rn(h.qn2, dn2));
+        res = __fsqrt_rn(fmaxf(x, 0.0f));
+    }
+    return res + 0.0f;  // -0 -> +0 so equal scores have equal bits
+}
+
+// float layouts (f16, q4): dotv = q . d, dn2 = ||d||^2 from the bind-time statistics.
+__device__ __forceinline__ float float_finish(int metric, float dotv, float dn2, const QueryHeader& h) {
+    float res;
+    if (metric == MANTA_B200_METRIC_DOT) {
+        res = dotv;
+    } else if (metric == MANTA_B200_METRIC_COSINE) {
+        float den = __fmul_rn(h.qn, __fsqrt_rn(dn2));
+        res = (den == 0.0f) ? 0.0f : __fdiv_rn(dotv, den);
+    } else {
+        float x = __fmaf_rn(-2.0f, dotv, __fadd_rn(h.qn2, dn2));
+        res = __fsqrt_rn(fmaxf(x, 0.0f));
+    }
+    return res + 0.0f;
+}
+
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.L2::128B.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ uint32_t ld_relaxed_u32(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ void st_relaxed_u32(uint32_t* p, uint32_t v) {
+    asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v));
+}
+
+// Appends one candidate to a query's pool.  Overflow only raises a flag: the host redoes the pass in
+// row chunks small enough that the pool cannot overflow.
+__device__ __forceinline__ void pool_append(const SelectWs& ws, int q, uint64_t key) {
+    uint32_t pos = atomicAdd(&ws.count[q], 1u);
+    if (pos < ws.cap) {
+        ws.pool[(size_t)q * ws.cap + pos] = key;
+    } else {
+        ws.flags[kFlagOverflow] = 1u;
+    }
+}
+
+// One warp: largest t such that at least k of the nb bucket maxima of query q are >= t (0 if fewer than k
+// buckets have reported).  Built bit by bit from the top; 32 counting passes over nb values.
+__device__ __forceinline__ uint32_t warp_kth_largest_bucket(const uint32_t* bucket, uint32_t nb, uint32_t k, int lane) {
+    uint32_t t = 0;
+    for (int bit = 31; bit >= 0; --bit) {
+        uint32_t cand = t | (1u << bit);
+        uint32_t cnt = 0;
+        for (uint32_t i = lane; i < nb; i += 32) cnt += (ld_relaxed_u32(bucket + i) >= cand) ? 1u : 0u;
+        cnt = __reduce_add_sync(0xffffffffu, cnt);
+        if (cnt >= k) t = cand;
+    }
+    return t;
+}
+
+}  // namespace mb200

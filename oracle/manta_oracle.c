@@ -459,13 +459,20 @@ int mo_unpack_q4_b32(const uint8_t* codes, const uint16_t* scales, int64_t rows,
 void mo_q8_query_planes(const float* q, int64_t cols, int8_t* hi, int8_t* lo, float* s_hi, float* s_lo,
                         float* qn, float* qn2) {
     float amax = 0.0f;
-    double n2 = 0.0;
+    /* device order of the f64 sum of squares: 32 lane-strided partial sums, then an xor butterfly */
+    double part[32], tmp[32];
+    for (int l = 0; l < 32; l++) part[l] = 0.0;
     for (int64_t c = 0; c < cols; c++) {
         float a = fabsf(q[c]);
         if (a > amax) amax = a;
         double v = (double)q[c];
-        n2 += v * v;
+        part[c & 31] += v * v;
     }
+    for (int off = 16; off > 0; off >>= 1) {
+        for (int l = 0; l < 32; l++) tmp[l] = part[l] + part[l ^ off];
+        for (int l = 0; l < 32; l++) part[l] = tmp[l];
+    }
+    double n2 = part[0];
     *qn2 = (float)n2;
     *qn = (float)sqrt(n2);
     if (amax == 0.0f) {
