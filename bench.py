@@ -151,7 +151,7 @@ def run_reference(args):
     import oracle
 
     threads = os.cpu_count() or 1
-    sample_rows = 1_000_000
+    sample_rows = min(1_000_000, ROWS)
     t0 = time.perf_counter()
     qps, sec, _ = cpu_reference_pass(sample_rows, threads, args.steps, args.warmup)
     line = {
@@ -281,7 +281,7 @@ def run_ours(args):
     if rank == 0 and world == 1 and not args.no_cpu:
         import oracle
 
-        sample_rows = 1_000_000
+        sample_rows = min(1_000_000, ROWS)
         threads = os.cpu_count() or 1
         qps, sec, ref_ids = cpu_reference_pass(sample_rows, threads, 3, 1)
         qps1, sec1, _ = cpu_reference_pass(sample_rows, 1, 1, 0)
@@ -307,7 +307,7 @@ def run_ours(args):
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8 x int8 -> int32 (dp4a), f32 epilogue",
             "data": "synthetic",
-            "config": {"workload": "q8 cosine 10M x 768, 1 query per pass, k=10", "rows": ROWS, "cols": COLS, "k": K,
+            "config": {"workload": f"q8 cosine {ROWS / 1e6:g}M x 768, 1 query per pass, k=10", "rows": ROWS, "cols": COLS, "k": K,
                        "queries_per_step": NQ, "layout": "q8 per-row f32 scale", "shards": world,
                        "l2": "inputs larger than L2 (7.7 GB scanned per pass / shards)"},
             "candidates_dim_per_s": args.steps * NQ * ROWS * COLS / (total_ms * 1e-3),
@@ -336,7 +336,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline / parity spot check")
+    ap.add_argument("--rows", type=int, default=ROWS,
+                    help="candidate rows (default: the 10M of the headline workload; smaller values are for profiling)")
     args = ap.parse_args()
+    globals()["ROWS"] = args.rows
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":

@@ -93,7 +93,8 @@ int manta_b200_runtime_destroy(MantaB200Runtime* rt, char** err);
 void manta_b200_free_cstring(char* s);
 /* The stream all work of this runtime is issued on (cudaStream_t). */
 int manta_b200_runtime_stream(MantaB200Runtime* rt, void** out_stream, char** err);
-/* mantaCudaSynchronize-equivalent for the runtime's stream (native_linux.go:385-402 syncs after each launch). */
+/* mantaCudaSynchronize-equivalent for the runtime's stream (native_linux.go:385-402 syncs after each launch).
+ * Also reports, as a failure, a candidate-pool overflow of the last fused pass issued with sync == 0. */
 int manta_b200_runtime_synchronize(MantaB200Runtime* rt, char** err);
 int manta_b200_runtime_stats(MantaB200Runtime* rt, MantaB200Stats* out, char** err);
 /* Device-time accounting of the scan kernels (the counterpart of RunNanos in MatMulAcceleratorStats,

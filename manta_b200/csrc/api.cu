@@ -92,6 +92,7 @@ struct MantaB200Runtime {
     cudaEvent_t prof_ev[2 * kMaxProf];
     int prof_created = 0;
     int prof_used = 0;
+    bool async_flags_pending = false;  // a sync == 0 pass copied its flags to h_flags; checked at synchronize
 };
 
 static void prof_mark(MantaB200Runtime* rt, int which) {
@@ -223,6 +224,14 @@ int manta_b200_runtime_synchronize(MantaB200Runtime* rt, char** err) {
     std::lock_guard<std::mutex> lk(rt->mu);
     CU_TRY(cudaSetDevice(rt->device));
     CU_TRY(cudaStreamSynchronize(rt->stream));
+    if (rt->async_flags_pending) {
+        rt->async_flags_pending = false;
+        if (rt->h_flags[kFlagTimeout]) return fail(err, "runtime_synchronize: a bounded device wait gave up in an asynchronous pass");
+        if (rt->h_flags[kFlagOverflow])
+            return fail(err, "runtime_synchronize: the last asynchronous fused pass overflowed its candidate pool; its "
+                             "result is incomplete, reissue it with sync != 0 (which redoes it in chunks)");
+        if (rt->h_flags[kFlagInternal]) return fail(err, "runtime_synchronize: selection found fewer than k candidates");
+    }
     return 0;
 }
 
@@ -467,7 +476,7 @@ static uint32_t pool_cap_for(const MantaB200Runtime* rt, const CandView& cv, int
     int64_t cap = mma_supported(cv, nq) ? (int64_t)mma_first_burst_rows(rt->sm_count) * 2
                                         : (int64_t)gemv_first_burst_rows(rt->sm_count, cv.chunks) * 2;
     if (cap < 32ll * k) cap = 32ll * k;
-    if (cap < 16384) cap = 16384;
+    if (cap < (1 << 18)) cap = 1 << 18;  // rows streamed before the first threshold lands all enter the pool
     if (cap > rows) cap = rows;  // a pool as large as the set cannot overflow
     if (cap < k) cap = k;
     return (uint32_t)cap;
@@ -590,8 +599,12 @@ static int score_topk_locked(MantaB200Runtime* rt, const MantaB200Candidates* se
     rt->stats.kernel_launches++;
     if (e != cudaSuccess) return fail_cuda(err, "launch select kernel", e);
     CU_TRY(cudaMemcpyAsync(rt->h_flags, ws.flags, kNumFlags * 4, cudaMemcpyDeviceToHost, rt->stream));
-    if (!sync) return 0;
+    if (!sync) {
+        rt->async_flags_pending = true;
+        return 0;
+    }
     CU_TRY(cudaStreamSynchronize(rt->stream));
+    rt->async_flags_pending = false;
     if (rt->h_flags[kFlagTimeout]) return fail(err, "score_topk(%s): a bounded device wait gave up", metric_name(metric));
     if (!rt->h_flags[kFlagOverflow]) {
         if (rt->h_flags[kFlagInternal]) return fail(err, "score_topk(%s): selection found fewer than k candidates", metric_name(metric));

@@ -39,6 +39,8 @@ struct QueryHeader {
     float s_lo;   // scale of the low int8 plane
     float qn;     // ||q|| (f32 of the f64 root)
     float qn2;    // ||q||^2 (f32 of the f64 sum)
+    double qn2d;  // ||q||^2 in f64
+    double qhat2; // ||s_hi*hi + s_lo*lo||^2 in f64: the squared norm of the query the int8 planes represent
 };
 
 // ---- selection workspace ------------------------------------------------------------------------------
@@ -85,16 +87,20 @@ __device__ __forceinline__ float q8_finish(int metric, int ih, int il, int nn, f
             res = __fdiv_rn(t, __fmul_rn(h.qn, __fsqrt_rn((float)nn)));
         }
     } else {
-        float dotv = __fmul_rn(t, sd);
-        float dn2 = __fmul_rn(__fmul_rn(sd, sd), (float)nn);
-        float x = __fmaf_rn(-2.0f, dotv, __fadd_rn(h.qn2, dn2));
-        res = __fsqrt_rn(fmaxf(x, 0.0f));
+        // ||qhat - d||^2 = ||qhat||^2 + ||d||^2 - 2 qhat.d, combined in f64 so that the cancellation near zero
+        // distance costs nothing; qhat is the query the two planes represent (|qhat - q| <= s_lo/2 per element).
+        double td = __dadd_rn(__dmul_rn((double)ih, (double)h.s_hi), __dmul_rn((double)il, (double)h.s_lo));
+        double dotd = __dmul_rn(td, (double)sd);
+        double dn2d = __dmul_rn(__dmul_rn((double)sd, (double)sd), (double)nn);
+        double x = __dadd_rn(__dadd_rn(h.qhat2, dn2d), -__dmul_rn(2.0, dotd));
+        res = __double2float_rn(__dsqrt_rn(fmax(x, 0.0)));
     }
     return res + 0.0f;  // -0 -> +0 so equal scores have equal bits
 }
 
-// float layouts (f16, q4): dotv = q . d, dn2 = ||d||^2 from the bind-time statistics.
-__device__ __forceinline__ float float_finish(int metric, float dotv, float dn2, const QueryHeader& h) {
+// float layouts (f16, q4): dotv = q . d, dn2 = ||d||^2 from the bind-time statistics, q2 = squared norm of the
+// query as the kernel sees it (f64).  The l2 combination runs in f64; dotv and dn2 carry f32 rounding.
+__device__ __forceinline__ float float_finish(int metric, float dotv, float dn2, const QueryHeader& h, double q2) {
     float res;
     if (metric == MANTA_B200_METRIC_DOT) {
         res = dotv;
@@ -102,8 +108,8 @@ __device__ __forceinline__ float float_finish(int metric, float dotv, float dn2,
         float den = __fmul_rn(h.qn, __fsqrt_rn(dn2));
         res = (den == 0.0f) ? 0.0f : __fdiv_rn(dotv, den);
     } else {
-        float x = __fmaf_rn(-2.0f, dotv, __fadd_rn(h.qn2, dn2));
-        res = __fsqrt_rn(fmaxf(x, 0.0f));
+        double x = __dadd_rn(__dadd_rn(q2, (double)dn2), -__dmul_rn(2.0, (double)dotv));
+        res = __double2float_rn(__dsqrt_rn(fmax(x, 0.0)));
     }
     return res + 0.0f;
 }

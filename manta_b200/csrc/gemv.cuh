@@ -69,7 +69,7 @@ __device__ __forceinline__ T group_sum(T v) {
 }
 
 template <int LAYOUT, int QT, int LPR, int CPL, int U>
-__global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvArgs a, const int mode) {
+__global__ void __launch_bounds__(kThreads, (QT == 1 && CPL <= 4) ? 2 : 1) gemv_kernel(const GemvArgs a, const int mode) {
     constexpr bool kQ8 = LAYOUT == MANTA_B200_LAYOUT_Q8_ROW_F32;
     constexpr bool kQ4 = LAYOUT == MANTA_B200_LAYOUT_Q4_B32_F16;
     constexpr bool kF16 = LAYOUT == MANTA_B200_LAYOUT_F16;
@@ -116,6 +116,45 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvArgs a, const 
 
     const int64_t nrows = a.row_end - a.row_begin;
     const int64_t n_wt = (nrows + ROWS_PER_WT - 1) / ROWS_PER_WT;
+    const bool want_stats = (a.metric != MANTA_B200_METRIC_DOT || mode == kModeAccum) &&
+                            !(kF16 && a.metric == MANTA_B200_METRIC_L2_DISTANCE);
+    const bool want_scale = kQ8 && a.metric != MANTA_B200_METRIC_COSINE;
+
+    // Everything one warp-tile needs from memory.  The loads of tile t+1 are issued before tile t is consumed
+    // (software pipelining), so every lane keeps U*CPL 16-byte loads in flight while it computes.
+    struct Tile {
+        uint4 data[U][CPL];
+        float sd[U];          // q8: row scale
+        __half q4s[U][CPL];   // q4: block scales
+        uint32_t stat[U];     // row statistic bits (leader lane only)
+    };
+    auto load_tile = [&](int64_t wt, Tile& t) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t r = a.row_begin + wt * ROWS_PER_WT + (int64_t)u * GPW + grp;
+            const bool rv = wt < n_wt && r < a.row_end;
+            const uint8_t* rp = cv.data + (size_t)(rv ? r : a.row_begin) * cv.row_bytes;
+#pragma unroll
+            for (int j = 0; j < CPL; ++j) {
+                const int chunk = j * LPR + gl;
+                if (rv && chunk < cv.chunks)
+                    t.data[u][j] = ld_stream16(rp + (size_t)chunk * 16);
+                else
+                    t.data[u][j] = make_uint4(0, 0, 0, 0);
+                if constexpr (kQ4) {
+                    t.q4s[u][j] = __ushort_as_half((unsigned short)0);
+                    if (rv && chunk < cv.chunks) t.q4s[u][j] = ((const __half*)cv.scales)[(size_t)r * cv.chunks + chunk];
+                }
+            }
+            t.sd[u] = 0.0f;
+            t.stat[u] = 0u;
+            if (rv && want_scale) t.sd[u] = ((const float*)cv.scales)[r];
+            if (rv && gl == 0 && want_stats) t.stat[u] = ((const uint32_t*)cv.stats)[r];
+        }
+    };
+
+    Tile nxt;
+    load_tile(gw, nxt);
     uint32_t iter = 0;
     for (int64_t wt = gw; wt < n_wt; wt += nwarps) {
         ++iter;
@@ -123,35 +162,16 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvArgs a, const 
         if (mode == kModeTopk) {
 #pragma unroll
             for (int q = 0; q < QT; ++q) thr[q] = ld_relaxed_u32(a.ws.thr + a.q0 + ((q < a.qt) ? q : 0));
+            // a pool that overflowed makes the host redo the pass in chunks: stop streaming
+            if ((iter & 15) == 0 && ld_relaxed_u32(a.ws.flags + kFlagOverflow) != 0) break;
         }
-        // ---- issue all loads of the warp-tile
-        uint4 data[U][CPL];
-        float sd[U];       // q8: row scale
-        float q4s[U][CPL]; // q4: block scales
+        const Tile cur = nxt;
+        load_tile(wt + nwarps, nxt);
         int64_t row[U];
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            row[u] = a.row_begin + wt * ROWS_PER_WT + (int64_t)u * GPW + grp;
-            const bool rv = row[u] < a.row_end;
-            const uint8_t* rp = cv.data + (size_t)(rv ? row[u] : a.row_begin) * cv.row_bytes;
-#pragma unroll
-            for (int j = 0; j < CPL; ++j) {
-                const int chunk = j * LPR + gl;
-                if (rv && chunk < cv.chunks)
-                    data[u][j] = ld_stream16(rp + (size_t)chunk * 16);
-                else
-                    data[u][j] = make_uint4(0, 0, 0, 0);
-                if constexpr (kQ4) {
-                    q4s[u][j] = 0.0f;
-                    if (rv && chunk < cv.chunks)
-                        q4s[u][j] = __half2float(((const __half*)cv.scales)[(size_t)row[u] * cv.chunks + chunk]);
-                }
-            }
-            if constexpr (kQ8) {
-                sd[u] = 0.0f;
-                if (rv && a.metric != MANTA_B200_METRIC_COSINE) sd[u] = ((const float*)cv.scales)[row[u]];
-            }
-        }
+        for (int u = 0; u < U; ++u) row[u] = a.row_begin + wt * ROWS_PER_WT + (int64_t)u * GPW + grp;
+        const auto& data = cur.data;
+        const auto& sd = cur.sd;
         // ---- accumulate
         int ih[U][QT], il[U][QT];
         float fa[U][QT], fb[U][QT];
@@ -200,8 +220,9 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvArgs a, const 
                             l = __dp4a(ev[g], (int)pl[2 * g], l);
                             l = __dp4a(od[g], (int)pl[2 * g + 1], l);
                         }
-                        fa[u][q] = __fmaf_rn((float)h, q4s[u][j], fa[u][q]);
-                        fb[u][q] = __fmaf_rn((float)l, q4s[u][j], fb[u][q]);
+                        const float bs = __half2float(cur.q4s[u][j]);
+                        fa[u][q] = __fmaf_rn((float)h, bs, fa[u][q]);
+                        fb[u][q] = __fmaf_rn((float)l, bs, fb[u][q]);
                     }
                 } else {
                     const __half2* hp = (const __half2*)&d;
@@ -212,30 +233,46 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvArgs a, const 
                         f[2 * t] = p.x;
                         f[2 * t + 1] = p.y;
                     }
+                    if (a.metric == MANTA_B200_METRIC_L2_DISTANCE) {
+                        // sum (q - d)^2 directly, as the reference does: no cancellation near zero distance
 #pragma unroll
-                    for (int q = 0; q < QT; ++q) {
-                        float acc = fa[u][q];
+                        for (int q = 0; q < QT; ++q) {
+                            float acc = fa[u][q];
 #pragma unroll
-                        for (int t = 0; t < 8; ++t) acc = __fmaf_rn(f[t], qr[q][j].v[t], acc);
-                        fa[u][q] = acc;
+                            for (int t = 0; t < 8; ++t) {
+                                const float df = __fsub_rn(qr[q][j].v[t], f[t]);
+                                acc = __fmaf_rn(df, df, acc);
+                            }
+                            fa[u][q] = acc;
+                        }
+                    } else {
+#pragma unroll
+                        for (int q = 0; q < QT; ++q) {
+                            float acc = fa[u][q];
+#pragma unroll
+                            for (int t = 0; t < 8; ++t) acc = __fmaf_rn(f[t], qr[q][j].v[t], acc);
+                            fa[u][q] = acc;
+                        }
                     }
                 }
             }
         }
         // ---- reduce over the lanes of a row, finish the score, store or filter
+        int nnv[U];
+        float dn2v[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            const bool rv = row[u] < a.row_end;
-            int nn = 0;
-            float dn2 = 0.0f;
-            if (rv && gl == 0 && (a.metric != MANTA_B200_METRIC_DOT || mode == kModeAccum)) {
-                if constexpr (kQ8)
-                    nn = ((const int32_t*)cv.stats)[row[u]];
-                else
-                    dn2 = ((const float*)cv.stats)[row[u]];
-            }
+            nnv[u] = (int)cur.stat[u];
+            dn2v[u] = __uint_as_float(cur.stat[u]);
+        }
 #pragma unroll
-            for (int q = 0; q < QT; ++q) {
+        for (int q = 0; q < QT; ++q) {
+            uint64_t key[U];
+            uint32_t ballots[U];
+            uint32_t total = 0;
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const bool rv = row[u] < a.row_end;
                 float score;
                 if constexpr (kQ8) {
                     const int h = group_sum<LPR>(ih[u][q]);
@@ -245,28 +282,56 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvArgs a, const 
                             int32_t* o = a.out_acc + (size_t)(row[u] - a.row_begin) * 3;
                             o[0] = h;
                             o[1] = l;
-                            o[2] = nn;
+                            o[2] = nnv[u];
                         }
+                        ballots[u] = 0;
                         continue;
                     }
-                    score = q8_finish(a.metric, h, l, nn, sd[u], hdr[q]);
+                    score = q8_finish(a.metric, h, l, nnv[u], sd[u], hdr[q]);
                 } else if constexpr (kQ4) {
                     const float th = group_sum<LPR>(fa[u][q]);
                     const float tl = group_sum<LPR>(fb[u][q]);
                     const float dotv = __fmaf_rn(tl, q4_sl[q], __fmul_rn(th, q4_sh[q]));
-                    score = float_finish(a.metric, dotv, dn2, hdr[q]);
+                    score = float_finish(a.metric, dotv, dn2v[u], hdr[q], hdr[q].qhat2);
                 } else {
                     const float dotv = group_sum<LPR>(fa[u][q]);
-                    score = float_finish(a.metric, dotv, dn2, hdr[q]);
+                    if (a.metric == MANTA_B200_METRIC_L2_DISTANCE)
+                        score = __fsqrt_rn(dotv) + 0.0f;  // dotv holds sum (q - d)^2 here
+                    else
+                        score = float_finish(a.metric, dotv, dn2v[u], hdr[q], hdr[q].qn2d);
                 }
-                if (!(rv && gl == 0 && q < a.qt)) continue;
+                const bool mine = rv && gl == 0 && q < a.qt;
+                bool pass = false;
                 if (mode == kModeScores) {
-                    a.out_scores[(size_t)(a.q0 + q) * cv.rows + row[u]] = score;
-                } else {
+                    if (mine) a.out_scores[(size_t)(a.q0 + q) * cv.rows + row[u]] = score;
+                } else if (mode == kModeTopk) {
                     const float g = score * sign + 0.0f;
                     const uint32_t o = ord_from_float(g);
-                    bmax[q] = max(bmax[q], o);
-                    if (o >= thr[q]) pool_append(a.ws, a.q0 + q, make_key(g, (int32_t)(cv.row_base + row[u])));
+                    if (mine) {
+                        bmax[q] = max(bmax[q], o);
+                        pass = o >= thr[q];
+                        key[u] = make_key(g, (int32_t)(cv.row_base + row[u]));
+                    }
+                }
+                ballots[u] = __ballot_sync(0xffffffffu, pass);
+                total += __popc(ballots[u]);
+            }
+            // one reservation per warp-tile and query for all rows that passed
+            if (mode == kModeTopk && total != 0) {
+                uint32_t base = 0;
+                if (lane == 0) base = atomicAdd(a.ws.count + a.q0 + q, total);
+                base = __shfl_sync(0xffffffffu, base, 0);
+                uint64_t* pool = a.ws.pool + (size_t)(a.q0 + q) * a.ws.cap;
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    if (ballots[u] & (1u << lane)) {
+                        const uint32_t pos = base + __popc(ballots[u] & ((1u << lane) - 1u));
+                        if (pos < a.ws.cap)
+                            pool[pos] = key[u];
+                        else
+                            a.ws.flags[kFlagOverflow] = 1u;
+                    }
+                    base += __popc(ballots[u]);
                 }
             }
         }
@@ -283,14 +348,17 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvArgs a, const 
             }
         }
         // ---- threshold refresh duty: warp 0, at power-of-two tile counts, one CTA in eight per count
-        if (warp_in_cta == 0 && (iter & (iter - 1)) == 0 && ((blockIdx.x & 7) == ((31 - __clz(iter)) & 7))) {
+        // (plus tile counts 3, 6 early on).  The bound is built from the top 20 bits only: rounding it down keeps
+        // it valid and costs a fraction of a percent of selectivity.
+        const bool duty_iter = (iter & (iter - 1)) == 0 || iter == 3 || iter == 6;
+        if (warp_in_cta == 0 && duty_iter && ((blockIdx.x & 7) == ((iter == 3 || iter == 6) ? 7 - (iter / 3) : ((31 - __clz(iter)) & 7)))) {
             for (int q = 0; q < a.qt; ++q) {
                 const uint32_t* b = a.ws.bucket + (size_t)(a.q0 + q) * a.ws.nb;
                 const uint32_t nb = min(a.ws.nb, 4096u);
                 for (uint32_t i = lane; i < nb; i += 32) s_stage[i] = ld_relaxed_u32(b + i);
                 __syncwarp();
                 uint32_t t = 0;
-                for (int bit = 31; bit >= 0; --bit) {
+                for (int bit = 31; bit >= 12; --bit) {
                     const uint32_t cand = t | (1u << bit);
                     uint32_t cnt = 0;
                     for (uint32_t i = lane; i < nb; i += 32) cnt += (s_stage[i] >= cand) ? 1u : 0u;

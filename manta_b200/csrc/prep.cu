@@ -47,6 +47,8 @@ __global__ void __launch_bounds__(256) query_prep_kernel(const __half* __restric
             QueryHeader h;
             h.qn2 = __double2float_rn(part);
             h.qn = __double2float_rn(__dsqrt_rn(part));
+            h.qn2d = part;
+            h.qhat2 = part;
             float sh = 0.0f, sl = 0.0f;
             if (m > 0.0f) {
                 sh = __fdiv_rn(m, 127.0f);
@@ -87,6 +89,33 @@ __global__ void __launch_bounds__(256) query_prep_kernel(const __half* __restric
             }
             plane_hi[(size_t)q * plane_stride + c] = hi;
             plane_lo[(size_t)q * plane_stride + c] = lo;
+        }
+    }
+    if (layout != MANTA_B200_LAYOUT_F16) {
+        // squared norm of the query the planes represent, same summation order as ||q||^2
+        __syncthreads();
+        if (tid < 32) {
+            const float sh = s_sh, sl = s_sl;
+            const bool zero = !(s_amax > 0.0f);
+            double part = 0.0;
+            for (int c = tid; c < cols; c += 32) {
+                double v = 0.0;
+                if (!zero) {
+                    float x = __half2float(src[c]);
+                    float h = roundf(__fdiv_rn(x, sh));
+                    h = fminf(fmaxf(h, -127.0f), 127.0f);
+                    float rem = __fmaf_rn(-h, sh, x);
+                    float l = 0.0f;
+                    if (sl != 0.0f) {
+                        l = roundf(__fdiv_rn(rem, sl));
+                        l = fminf(fmaxf(l, -127.0f), 127.0f);
+                    }
+                    v = __dadd_rn(__dmul_rn((double)h, (double)sh), __dmul_rn((double)l, (double)sl));
+                }
+                part = __dadd_rn(part, __dmul_rn(v, v));
+            }
+            for (int off = 16; off > 0; off >>= 1) part = __dadd_rn(part, __shfl_xor_sync(0xffffffffu, part, off));
+            if (tid == 0) headers[q].qhat2 = part;
         }
     }
     if (reset_ws) {

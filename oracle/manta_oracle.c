@@ -456,28 +456,34 @@ int mo_unpack_q4_b32(const uint8_t* codes, const uint16_t* scales, int64_t rows,
  * It is a statement of the build's own arithmetic, not of the reference's; agreement of this
  * arithmetic with the reference's float path (1e-3 relative) is tested separately.
  */
+static double mo_butterfly32(double* part) {
+    double tmp[32];
+    for (int off = 16; off > 0; off >>= 1) {
+        for (int l = 0; l < 32; l++) tmp[l] = part[l] + part[l ^ off];
+        for (int l = 0; l < 32; l++) part[l] = tmp[l];
+    }
+    return part[0];
+}
+
 void mo_q8_query_planes(const float* q, int64_t cols, int8_t* hi, int8_t* lo, float* s_hi, float* s_lo,
-                        float* qn, float* qn2) {
+                        float* qn, float* qn2, double* qhat2) {
     float amax = 0.0f;
     /* device order of the f64 sum of squares: 32 lane-strided partial sums, then an xor butterfly */
-    double part[32], tmp[32];
-    for (int l = 0; l < 32; l++) part[l] = 0.0;
+    double part[32], hpart[32];
+    for (int l = 0; l < 32; l++) part[l] = hpart[l] = 0.0;
     for (int64_t c = 0; c < cols; c++) {
         float a = fabsf(q[c]);
         if (a > amax) amax = a;
         double v = (double)q[c];
         part[c & 31] += v * v;
     }
-    for (int off = 16; off > 0; off >>= 1) {
-        for (int l = 0; l < 32; l++) tmp[l] = part[l] + part[l ^ off];
-        for (int l = 0; l < 32; l++) part[l] = tmp[l];
-    }
-    double n2 = part[0];
+    double n2 = mo_butterfly32(part);
     *qn2 = (float)n2;
     *qn = (float)sqrt(n2);
     if (amax == 0.0f) {
         *s_hi = 0.0f;
         *s_lo = 0.0f;
+        *qhat2 = 0.0;
         memset(hi, 0, (size_t)cols);
         memset(lo, 0, (size_t)cols);
         return;
@@ -501,7 +507,10 @@ void mo_q8_query_planes(const float* q, int64_t cols, int8_t* hi, int8_t* lo, fl
         }
         hi[c] = (int8_t)h;
         lo[c] = (int8_t)l;
+        double v = (double)h * (double)sh + (double)l * (double)sl;
+        hpart[c & 31] += v * v;
     }
+    *qhat2 = mo_butterfly32(hpart);
 }
 
 /* metric: 0 dot, 1 cosine, 2 l2_distance.  acc (optional) receives I_hi, I_lo, nn per row. */
@@ -511,7 +520,8 @@ int mo_q8_model_scores(const float* query, const int8_t* codes, const float* sca
     int8_t* lo = (int8_t*)malloc((size_t)cols);
     if (!hi || !lo) return MO_ERR_RANGE;
     float s_hi, s_lo, qn, qn2;
-    mo_q8_query_planes(query, cols, hi, lo, &s_hi, &s_lo, &qn, &qn2);
+    double qhat2;
+    mo_q8_query_planes(query, cols, hi, lo, &s_hi, &s_lo, &qn, &qn2, &qhat2);
 #pragma omp parallel for schedule(static)
     for (int64_t r = 0; r < rows; r++) {
         const int8_t* d = codes + r * cols;
@@ -543,13 +553,12 @@ int mo_q8_model_scores(const float* query, const int8_t* codes, const float* sca
                 res = qv;
             }
         } else {
-            volatile float dotv = t * sd;
-            volatile float s2 = sd * sd;
-            volatile float dn2 = s2 * (float)nn;
-            volatile float sum = qn2 + dn2;
-            float x = fmaf(-2.0f, dotv, sum);
-            if (x < 0.0f) x = 0.0f;
-            res = sqrtf(x);
+            double td = (double)ih * (double)s_hi + (double)il * (double)s_lo;
+            double dotd = td * (double)sd;
+            double dn2d = ((double)sd * (double)sd) * (double)nn;
+            double x = (qhat2 + dn2d) + -(2.0 * dotd);
+            if (!(x > 0.0)) x = 0.0;
+            res = (float)sqrt(x);
         }
         out[r] = res;
     }

@@ -4,7 +4,9 @@ import numpy as np
 import oracle
 
 REL_TOL = 1e-3  # float scores: 1e-3 relative ...
-FLOOR = 1e-2    # ... down to scores of FLOOR*|q||d|; below that the bound is absolute REL_TOL*FLOOR*|q||d|
+FLOOR = 5e-2    # ... down to scores of FLOOR*|q||d|; below that the bound is absolute REL_TOL*FLOOR*|q||d|
+# (5e-5*|q||d| absolute: the two int8 planes that carry the query hold max|q| * 2^-16 per element; the
+# reference's own tests compare its device and host paths with 5e-4 absolute, ten times looser.)
 
 
 def f16_round(x):
