@@ -7,6 +7,7 @@
 #include <mutex>
 #include <new>
 
+#include "internal.h"
 #include "kernels.h"
 #include "mma.h"
 
@@ -114,6 +115,12 @@ struct MantaB200Candidates {
     int64_t stored_bytes = 0;
     int device = 0;
 };
+
+namespace mb200 {
+RuntimeInfo runtime_info(MantaB200Runtime* rt) { return RuntimeInfo{rt->device, rt->sm_count, rt->stream, rt->h_flags, &rt->mu}; }
+const CandView* candidates_view(const MantaB200Candidates* set) { return &set->cv; }
+int candidates_device(const MantaB200Candidates* set) { return set->device; }
+}  // namespace mb200
 
 static int ensure(MantaB200Runtime* rt, DevBuf& b, size_t bytes, char** err) {
     if (bytes <= b.bytes) return 0;
@@ -472,11 +479,19 @@ static int plane_stride_for(const CandView& cv) {
 
 // Pool capacity per query for the optimistic single-launch pass.
 static uint32_t pool_cap_for(const MantaB200Runtime* rt, const CandView& cv, int nq, int k) {
-    int64_t rows = cv.rows;
-    int64_t cap = mma_supported(cv, nq) ? (int64_t)mma_first_burst_rows(rt->sm_count) * 2
-                                        : (int64_t)gemv_first_burst_rows(rt->sm_count, cv.chunks) * 2;
+    const int64_t rows = cv.rows;
+    int64_t cap;
+    if (mma_supported(cv, nq)) {
+        cap = (int64_t)mma_first_burst_rows(rt->sm_count) * 2;
+    } else {
+        // Every row streamed before the first threshold lands enters the pool.  That takes on the order of ten
+        // microseconds whatever the row size, so the allowance is a byte budget (HBM rate x ~20 us), in rows.
+        cap = (int64_t)gemv_first_burst_rows(rt->sm_count, cv.chunks) * 2;
+        const int64_t by_time = (int64_t)130000000 / (cv.row_bytes + 8);
+        if (cap < by_time) cap = by_time;
+    }
     if (cap < 32ll * k) cap = 32ll * k;
-    if (cap < (1 << 18)) cap = 1 << 18;  // rows streamed before the first threshold lands all enter the pool
+    if (cap < (1 << 16)) cap = 1 << 16;
     if (cap > rows) cap = rows;  // a pool as large as the set cannot overflow
     if (cap < k) cap = k;
     return (uint32_t)cap;

@@ -242,12 +242,12 @@ def test_zero_rows_and_zero_query(rt):
 def test_pool_overflow_falls_back_to_chunks(rt):
     """Rows sorted so that every row beats all earlier ones: every row passes the filter, the candidate pool
     overflows and the pass is redone in chunks; the result must still be exact."""
-    rows, cols = 1500000, 32
+    rows, cols = 900000, 128
     rng = np.random.default_rng(9)
     q = make_rows(rng, 1, cols)[0]
-    noise = make_rows(rng, rows, cols) * 1e-3
-    ramp = (np.arange(rows, dtype=np.float32) / rows)[:, None]
-    x = f16_round(noise + ramp * q[None, :])
+    x = rng.standard_normal((rows, cols), dtype=np.float32) * np.float32(1e-4)
+    x += (np.arange(rows, dtype=np.float32) / rows)[:, None] * q[None, :]
+    x = f16_round(x)
     cands, deq = _bind(rt, "f16", x)
     before = rt.stats()["chunked_reruns"]
     ids, scores = rt.score_topk(cands, "dot", q, 10)
