@@ -150,6 +150,21 @@ int manta_b200_score_topk_device(MantaB200Runtime* rt, const MantaB200Candidates
                                  const void* d_queries, int nq, int k, int32_t* d_out_ids, float* d_out_scores,
                                  int sync, char** err);
 
+/* Same pass as manta_b200_score_topk_device for callers that cannot allocate device memory when they score
+ * (all HBM already handed out, a no-allocation rule after start-up, another stream being captured).  It has no
+ * counterpart in the reference.  It never calls cudaMalloc/cudaFree or any allocating routine: all scratch lives in
+ * one fixed array inside the library image (about 4.4 MB, held by every GPU that loads the library until exit).
+ * Limits, rejected with an error beyond them: at most 4 queries, k <= 256, cols <= 4096 per call.  The candidate
+ * pool holds 131072 keys per query, so rows are scanned in chunks of (131072 - k) rows with the pool compacted to
+ * the best k between chunks: the result is exact for any row order, but large sets take more launches than the
+ * allocating entry points need.
+ * The first call on a device looks up the array's device address; make that call before any stream capture.
+ * All calls share the array, which keeps the previous call's contents (what must start at zero is cleared by
+ * the pass itself): two calls whose device work overlaps, from any runtimes or threads, race. */
+int manta_b200_score_topk_static(MantaB200Runtime* rt, const MantaB200Candidates* set, int metric, int order,
+                                 const void* d_queries, int nq, int k, int32_t* d_out_ids, float* d_out_scores,
+                                 int sync, char** err);
+
 /* Merges `lists` per-shard results (device, each [nq, k] ids + scores, concatenated list-major) into the
  * global best k per query with the same ordering rule.  Used after the shards' lists are gathered. */
 int manta_b200_topk_merge_device(MantaB200Runtime* rt, int order, const int32_t* d_ids, const float* d_scores,

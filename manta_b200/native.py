@@ -32,7 +32,7 @@ EXPORTS = [
     "manta_b200_candidates_bytes", "manta_b200_pack_q8_rows", "manta_b200_pack_q4_b32",
     "manta_b200_pack_q8_rows_device", "manta_b200_pack_q4_b32_device", "manta_b200_score",
     "manta_b200_score_topk", "manta_b200_score_topk_device", "manta_b200_topk_merge_device",
-    "manta_b200_gather_rows", "manta_b200_q8_accumulators",
+    "manta_b200_gather_rows", "manta_b200_q8_accumulators", "manta_b200_score_topk_static",
 ]
 
 
@@ -84,6 +84,8 @@ def load() -> ctypes.CDLL:
         "manta_b200_score": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, E],
         "manta_b200_score_topk": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, E],
         "manta_b200_score_topk_device": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p,
+                                         c_void_p, c_int, E],
+        "manta_b200_score_topk_static": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p,
                                          c_void_p, c_int, E],
         "manta_b200_topk_merge_device": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
                                          c_void_p, c_int, E],
@@ -282,6 +284,13 @@ class Runtime:
     def score_topk_device(self, cands: Candidates, metric: str, d_queries, nq: int, k: int, d_ids, d_scores,
                           smallest: bool = False, sync: bool = False):
         call("manta_b200_score_topk_device", self.handle, cands.handle, c_int(METRICS[metric]),
+             c_int(ORDER_SMALLEST if smallest else ORDER_LARGEST), _ptr(d_queries), c_int(nq), c_int(k), _ptr(d_ids),
+             _ptr(d_scores), c_int(1 if sync else 0))
+
+    def score_topk_static(self, cands: Candidates, metric: str, d_queries, nq: int, k: int, d_ids, d_scores,
+                          smallest: bool = False, sync: bool = True):
+        """The fused pass on the library's fixed scratch array: no device allocation happens in this call."""
+        call("manta_b200_score_topk_static", self.handle, cands.handle, c_int(METRICS[metric]),
              c_int(ORDER_SMALLEST if smallest else ORDER_LARGEST), _ptr(d_queries), c_int(nq), c_int(k), _ptr(d_ids),
              _ptr(d_scores), c_int(1 if sync else 0))
 
