@@ -61,6 +61,19 @@ struct QChunk<MANTA_B200_LAYOUT_F16> {
     }
 };
 
+constexpr int kStages = 3;        // ring depth of the asynchronous copies (kStages-1 warp-tiles in flight)
+constexpr int kStageWords = 2560; // bucket maxima a threshold refresh can stage in shared memory
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global.L2::128B [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
 template <int LPR, typename T>
 __device__ __forceinline__ T group_sum(T v) {
 #pragma unroll
@@ -68,20 +81,45 @@ __device__ __forceinline__ T group_sum(T v) {
     return v;
 }
 
+// Sums v[0..V) over the LPR lanes of a row group and leaves the total of v[i] on the lanes whose position in
+// the group, gl, satisfies gl / (LPR / V) == i (returned value).  Values are exchanged half at a time, so the
+// whole reduction costs V - 1 + log2(LPR / V) shuffles instead of V * log2(LPR).
+template <int LPR, int V, typename T>
+__device__ __forceinline__ T reduce_scatter(T (&v)[V], int gl) {
+    static_assert((V & (V - 1)) == 0 && V <= LPR, "V must be a power of two not above LPR");
+    int off = LPR / 2;
+#pragma unroll
+    for (int n = V / 2; n >= 1; n >>= 1, off >>= 1) {
+        const bool upper = (gl & off) != 0;
+#pragma unroll
+        for (int i = 0; i < n; ++i) {
+            const T send = upper ? v[i] : v[i + n];
+            const T keep = upper ? v[i + n] : v[i];
+            v[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+        }
+    }
+#pragma unroll
+    for (; off > 0; off >>= 1) v[0] += __shfl_xor_sync(0xffffffffu, v[0], off);
+    return v[0];
+}
+
 template <int LAYOUT, int QT, int LPR, int CPL, int U>
 __global__ void __launch_bounds__(kThreads, (QT == 1 && CPL <= 4) ? 2 : 1) gemv_kernel(const GemvArgs a, const int mode) {
     constexpr bool kQ8 = LAYOUT == MANTA_B200_LAYOUT_Q8_ROW_F32;
     constexpr bool kQ4 = LAYOUT == MANTA_B200_LAYOUT_Q4_B32_F16;
     constexpr bool kF16 = LAYOUT == MANTA_B200_LAYOUT_F16;
-    constexpr int GPW = 32 / LPR;
-    constexpr int ROWS_PER_WT = GPW * U;
-
-    __shared__ uint32_t s_stage[4096];
+    constexpr int GPW = 32 / LPR;             // row groups per warp
+    constexpr int ROWS_PER_WT = GPW * U;      // rows per warp-tile
+    constexpr int OWN = LPR / U;              // lanes of a group that end up holding the same row's sums
+    constexpr int SLOTS = U * CPL;
 
     const int lane = threadIdx.x & 31;
     const int warp_in_cta = threadIdx.x >> 5;
     const int gl = lane % LPR;
     const int grp = lane / LPR;
+    const int own_u = gl / OWN;               // the row of the tile (within the group) this lane finishes
+    const bool leader = (gl % OWN) == 0;
+    const int own_off = own_u * GPW + grp;    // row offset inside the warp-tile
     const int64_t gw = (int64_t)blockIdx.x * kWarpsPerCta + warp_in_cta;
     const int64_t nwarps = (int64_t)gridDim.x * kWarpsPerCta;
     const CandView& cv = a.cv;
@@ -89,6 +127,9 @@ __global__ void __launch_bounds__(kThreads, (QT == 1 && CPL <= 4) ? 2 : 1) gemv_
     // query registers and per-query constants
     QChunk<LAYOUT> qr[QT][CPL];
     QueryHeader hdr[QT];
+    bool cvalid[CPL];
+#pragma unroll
+    for (int j = 0; j < CPL; ++j) cvalid[j] = (j * LPR + gl) < cv.chunks;
 #pragma unroll
     for (int q = 0; q < QT; ++q) {
         const int qi = a.q0 + ((q < a.qt) ? q : 0);  // unused slots repeat query 0 of the pass
@@ -97,9 +138,9 @@ __global__ void __launch_bounds__(kThreads, (QT == 1 && CPL <= 4) ? 2 : 1) gemv_
         for (int j = 0; j < CPL; ++j) {
             const int chunk = j * LPR + gl;
             if constexpr (kF16)
-                qr[q][j].load(a.qp, qi, chunk, chunk < cv.chunks, cv.cols);
+                qr[q][j].load(a.qp, qi, chunk, cvalid[j], cv.cols);
             else
-                qr[q][j].load(a.qp, qi, chunk, chunk < cv.chunks);
+                qr[q][j].load(a.qp, qi, chunk, cvalid[j]);
         }
     }
     float q4_sh[QT], q4_sl[QT];
@@ -120,42 +161,68 @@ __global__ void __launch_bounds__(kThreads, (QT == 1 && CPL <= 4) ? 2 : 1) gemv_
                             !(kF16 && a.metric == MANTA_B200_METRIC_L2_DISTANCE);
     const bool want_scale = kQ8 && a.metric != MANTA_B200_METRIC_COSINE;
 
-    // Everything one warp-tile needs from memory.  The loads of tile t+1 are issued before tile t is consumed
-    // (software pipelining), so every lane keeps U*CPL 16-byte loads in flight while it computes.
-    struct Tile {
-        uint4 data[U][CPL];
-        float sd[U];          // q8: row scale
-        __half q4s[U][CPL];   // q4: block scales
-        uint32_t stat[U];     // row statistic bits (leader lane only)
-    };
-    auto load_tile = [&](int64_t wt, Tile& t) {
+    // Candidate bytes travel global -> shared memory with 16-byte asynchronous copies (cp.async.cg, no registers
+    // held while in flight): every lane copies exactly the chunks it will consume itself into its own slots of a
+    // kStages-deep ring, so no barrier is needed; kStages-1 warp-tiles are in flight per lane while one is
+    // consumed.  The small per-row values (scale, block scales, statistic) are prefetched one tile ahead in
+    // registers, by the lane that will finish that row.
+    extern __shared__ __align__(16) unsigned char dyn_smem[];
+    uint4* ring = reinterpret_cast<uint4*>(dyn_smem);
+    uint32_t* s_stage = reinterpret_cast<uint32_t*>(dyn_smem + (size_t)kStages * SLOTS * kThreads * 16);
+    auto slot = [&](int stage, int i) -> uint4* { return ring + ((size_t)(stage * SLOTS + i) * kThreads + threadIdx.x); };
+    const size_t tile_stride = (size_t)ROWS_PER_WT * cv.row_bytes;
+    // address of this lane's first chunk of row `grp` of warp-tile `gw`
+    const uint8_t* lane_base = cv.data + (size_t)(a.row_begin + gw * ROWS_PER_WT + grp) * cv.row_bytes + (size_t)gl * 16;
+    const size_t u_stride = (size_t)GPW * cv.row_bytes;
+    auto issue_tile = [&](int64_t wt, int stage) {
+        const int64_t left = nrows - wt * ROWS_PER_WT;  // rows of the range at or after this tile's first row
+        const uint8_t* tp = lane_base + (size_t)(wt - gw) * tile_stride;
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            const int64_t r = a.row_begin + wt * ROWS_PER_WT + (int64_t)u * GPW + grp;
-            const bool rv = wt < n_wt && r < a.row_end;
-            const uint8_t* rp = cv.data + (size_t)(rv ? r : a.row_begin) * cv.row_bytes;
+            const bool rv = (int64_t)(u * GPW + grp) < left;
 #pragma unroll
             for (int j = 0; j < CPL; ++j) {
-                const int chunk = j * LPR + gl;
-                if (rv && chunk < cv.chunks)
-                    t.data[u][j] = ld_stream16(rp + (size_t)chunk * 16);
+                if (rv && cvalid[j])
+                    cp_async16(slot(stage, u * CPL + j), tp + u * u_stride + (size_t)j * LPR * 16);
                 else
-                    t.data[u][j] = make_uint4(0, 0, 0, 0);
-                if constexpr (kQ4) {
+                    *slot(stage, u * CPL + j) = make_uint4(0, 0, 0, 0);
+            }
+        }
+        cp_async_commit();
+    };
+    struct Meta {
+        float sd;             // q8: scale of the row this lane finishes
+        uint32_t stat;        // statistic bits of that row
+        __half q4s[U][CPL];   // q4: block scales of the chunks this lane accumulates
+    };
+    auto load_meta = [&](int64_t wt, Meta& t) {
+        const int64_t first = a.row_begin + wt * ROWS_PER_WT;
+        if constexpr (kQ4) {
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int64_t r = first + u * GPW + grp;
+                const bool rv = wt < n_wt && r < a.row_end;
+#pragma unroll
+                for (int j = 0; j < CPL; ++j) {
                     t.q4s[u][j] = __ushort_as_half((unsigned short)0);
-                    if (rv && chunk < cv.chunks) t.q4s[u][j] = ((const __half*)cv.scales)[(size_t)r * cv.chunks + chunk];
+                    if (rv && cvalid[j]) t.q4s[u][j] = ((const __half*)cv.scales)[(size_t)r * cv.chunks + j * LPR + gl];
                 }
             }
-            t.sd[u] = 0.0f;
-            t.stat[u] = 0u;
-            if (rv && want_scale) t.sd[u] = ((const float*)cv.scales)[r];
-            if (rv && gl == 0 && want_stats) t.stat[u] = ((const uint32_t*)cv.stats)[r];
         }
+        const int64_t r = first + own_off;
+        const bool rv = leader && wt < n_wt && r < a.row_end;
+        t.sd = 0.0f;
+        t.stat = 0u;
+        if (rv && want_scale) t.sd = ((const float*)cv.scales)[r];
+        if (rv && want_stats) t.stat = ((const uint32_t*)cv.stats)[r];
     };
 
-    Tile nxt;
-    load_tile(gw, nxt);
+#pragma unroll
+    for (int p = 0; p < kStages - 1; ++p) issue_tile(gw + (int64_t)p * nwarps, p);
+    Meta nxt;
+    load_meta(gw, nxt);
     uint32_t iter = 0;
+    int stage = 0;
     for (int64_t wt = gw; wt < n_wt; wt += nwarps) {
         ++iter;
         uint32_t thr[QT];
@@ -165,22 +232,27 @@ __global__ void __launch_bounds__(kThreads, (QT == 1 && CPL <= 4) ? 2 : 1) gemv_
             // a pool that overflowed makes the host redo the pass in chunks: stop streaming
             if ((iter & 15) == 0 && ld_relaxed_u32(a.ws.flags + kFlagOverflow) != 0) break;
         }
-        const Tile cur = nxt;
-        load_tile(wt + nwarps, nxt);
-        int64_t row[U];
+        cp_async_wait<kStages - 2>();  // the copies of this tile have landed
+        // refill the stage that was consumed in the previous iteration
+        issue_tile(wt + (int64_t)(kStages - 1) * nwarps, (stage == 0) ? kStages - 1 : stage - 1);
+        uint4 data[U][CPL];
 #pragma unroll
-        for (int u = 0; u < U; ++u) row[u] = a.row_begin + wt * ROWS_PER_WT + (int64_t)u * GPW + grp;
-        const auto& data = cur.data;
-        const auto& sd = cur.sd;
-        // ---- accumulate
-        int ih[U][QT], il[U][QT];
-        float fa[U][QT], fb[U][QT];
+        for (int u = 0; u < U; ++u)
+#pragma unroll
+            for (int j = 0; j < CPL; ++j) data[u][j] = *slot(stage, u * CPL + j);
+        stage = (stage + 1 == kStages) ? 0 : stage + 1;
+        const Meta cur = nxt;
+        load_meta(wt + nwarps, nxt);
+
+        // ---- accumulate: ih/il int32 (q8), fa/fb f32 (q4: hi/lo planes; f16: fa only)
+        int ih[QT][U], il[QT][U];
+        float fa[QT][U], fb[QT][U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
 #pragma unroll
             for (int q = 0; q < QT; ++q) {
-                ih[u][q] = il[u][q] = 0;
-                fa[u][q] = fb[u][q] = 0.0f;
+                ih[q][u] = il[q][u] = 0;
+                fa[q][u] = fb[q][u] = 0.0f;
             }
 #pragma unroll
             for (int j = 0; j < CPL; ++j) {
@@ -188,7 +260,7 @@ __global__ void __launch_bounds__(kThreads, (QT == 1 && CPL <= 4) ? 2 : 1) gemv_
                 if constexpr (kQ8) {
 #pragma unroll
                     for (int q = 0; q < QT; ++q) {
-                        int h = ih[u][q], l = il[u][q];
+                        int h = ih[q][u], l = il[q][u];
                         h = __dp4a((int)d.x, (int)qr[q][j].hi.x, h);
                         h = __dp4a((int)d.y, (int)qr[q][j].hi.y, h);
                         h = __dp4a((int)d.z, (int)qr[q][j].hi.z, h);
@@ -197,8 +269,8 @@ __global__ void __launch_bounds__(kThreads, (QT == 1 && CPL <= 4) ? 2 : 1) gemv_
                         l = __dp4a((int)d.y, (int)qr[q][j].lo.y, l);
                         l = __dp4a((int)d.z, (int)qr[q][j].lo.z, l);
                         l = __dp4a((int)d.w, (int)qr[q][j].lo.w, l);
-                        ih[u][q] = h;
-                        il[u][q] = l;
+                        ih[q][u] = h;
+                        il[q][u] = l;
                     }
                 } else if constexpr (kQ4) {
                     const uint32_t w[4] = {d.x, d.y, d.z, d.w};
@@ -208,6 +280,7 @@ __global__ void __launch_bounds__(kThreads, (QT == 1 && CPL <= 4) ? 2 : 1) gemv_
                         ev[g] = (int)((w[g] << 4) & 0xF0F0F0F0u);
                         od[g] = (int)(w[g] & 0xF0F0F0F0u);
                     }
+                    const float bs = __half2float(cur.q4s[u][j]);
 #pragma unroll
                     for (int q = 0; q < QT; ++q) {
                         const uint32_t* ph = (const uint32_t*)qr[q][j].hi;
@@ -220,9 +293,8 @@ __global__ void __launch_bounds__(kThreads, (QT == 1 && CPL <= 4) ? 2 : 1) gemv_
                             l = __dp4a(ev[g], (int)pl[2 * g], l);
                             l = __dp4a(od[g], (int)pl[2 * g + 1], l);
                         }
-                        const float bs = __half2float(cur.q4s[u][j]);
-                        fa[u][q] = __fmaf_rn((float)h, bs, fa[u][q]);
-                        fb[u][q] = __fmaf_rn((float)l, bs, fb[u][q]);
+                        fa[q][u] = __fmaf_rn((float)h, bs, fa[q][u]);
+                        fb[q][u] = __fmaf_rn((float)l, bs, fb[q][u]);
                     }
                 } else {
                     const __half2* hp = (const __half2*)&d;
@@ -237,101 +309,85 @@ __global__ void __launch_bounds__(kThreads, (QT == 1 && CPL <= 4) ? 2 : 1) gemv_
                         // sum (q - d)^2 directly, as the reference does: no cancellation near zero distance
 #pragma unroll
                         for (int q = 0; q < QT; ++q) {
-                            float acc = fa[u][q];
+                            float acc = fa[q][u];
 #pragma unroll
                             for (int t = 0; t < 8; ++t) {
                                 const float df = __fsub_rn(qr[q][j].v[t], f[t]);
                                 acc = __fmaf_rn(df, df, acc);
                             }
-                            fa[u][q] = acc;
+                            fa[q][u] = acc;
                         }
                     } else {
 #pragma unroll
                         for (int q = 0; q < QT; ++q) {
-                            float acc = fa[u][q];
+                            float acc = fa[q][u];
 #pragma unroll
                             for (int t = 0; t < 8; ++t) acc = __fmaf_rn(f[t], qr[q][j].v[t], acc);
-                            fa[u][q] = acc;
+                            fa[q][u] = acc;
                         }
                     }
                 }
             }
         }
-        // ---- reduce over the lanes of a row, finish the score, store or filter
-        int nnv[U];
-        float dn2v[U];
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            nnv[u] = (int)cur.stat[u];
-            dn2v[u] = __uint_as_float(cur.stat[u]);
-        }
+
+        // ---- reduce over the lanes of a row; afterwards lane (own_u, leader) holds the sums of row own_u of its
+        // group, so one pass of the epilogue finishes all GPW*U rows of the warp-tile at once
+        const int64_t my_row = a.row_begin + wt * ROWS_PER_WT + own_off;
+        const bool rv = leader && my_row < a.row_end;
+        const int nn = (int)cur.stat;
+        const float dn2 = __uint_as_float(cur.stat);
 #pragma unroll
         for (int q = 0; q < QT; ++q) {
-            uint64_t key[U];
-            uint32_t ballots[U];
-            uint32_t total = 0;
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const bool rv = row[u] < a.row_end;
-                float score;
-                if constexpr (kQ8) {
-                    const int h = group_sum<LPR>(ih[u][q]);
-                    const int l = group_sum<LPR>(il[u][q]);
-                    if (mode == kModeAccum) {
-                        if (rv && gl == 0 && q == 0) {
-                            int32_t* o = a.out_acc + (size_t)(row[u] - a.row_begin) * 3;
-                            o[0] = h;
-                            o[1] = l;
-                            o[2] = nnv[u];
-                        }
-                        ballots[u] = 0;
-                        continue;
+            float score;
+            if constexpr (kQ8) {
+                const int h = reduce_scatter<LPR, U>(ih[q], gl);
+                const int l = reduce_scatter<LPR, U>(il[q], gl);
+                if (mode == kModeAccum) {
+                    if (rv && q == 0) {
+                        int32_t* o = a.out_acc + (size_t)(my_row - a.row_begin) * 3;
+                        o[0] = h;
+                        o[1] = l;
+                        o[2] = nn;
                     }
-                    score = q8_finish(a.metric, h, l, nnv[u], sd[u], hdr[q]);
-                } else if constexpr (kQ4) {
-                    const float th = group_sum<LPR>(fa[u][q]);
-                    const float tl = group_sum<LPR>(fb[u][q]);
-                    const float dotv = __fmaf_rn(tl, q4_sl[q], __fmul_rn(th, q4_sh[q]));
-                    score = float_finish(a.metric, dotv, dn2v[u], hdr[q], hdr[q].qhat2);
-                } else {
-                    const float dotv = group_sum<LPR>(fa[u][q]);
-                    if (a.metric == MANTA_B200_METRIC_L2_DISTANCE)
-                        score = __fsqrt_rn(dotv) + 0.0f;  // dotv holds sum (q - d)^2 here
-                    else
-                        score = float_finish(a.metric, dotv, dn2v[u], hdr[q], hdr[q].qn2d);
+                    continue;
                 }
-                const bool mine = rv && gl == 0 && q < a.qt;
-                bool pass = false;
-                if (mode == kModeScores) {
-                    if (mine) a.out_scores[(size_t)(a.q0 + q) * cv.rows + row[u]] = score;
-                } else if (mode == kModeTopk) {
-                    const float g = score * sign + 0.0f;
-                    const uint32_t o = ord_from_float(g);
-                    if (mine) {
-                        bmax[q] = max(bmax[q], o);
-                        pass = o >= thr[q];
-                        key[u] = make_key(g, (int32_t)(cv.row_base + row[u]));
-                    }
-                }
-                ballots[u] = __ballot_sync(0xffffffffu, pass);
-                total += __popc(ballots[u]);
+                score = q8_finish(a.metric, h, l, nn, cur.sd, hdr[q]);
+            } else if constexpr (kQ4) {
+                const float th = reduce_scatter<LPR, U>(fa[q], gl);
+                const float tl = reduce_scatter<LPR, U>(fb[q], gl);
+                const float dotv = __fmaf_rn(tl, q4_sl[q], __fmul_rn(th, q4_sh[q]));
+                score = float_finish(a.metric, dotv, dn2, hdr[q], hdr[q].qhat2);
+            } else {
+                const float dotv = reduce_scatter<LPR, U>(fa[q], gl);
+                if (a.metric == MANTA_B200_METRIC_L2_DISTANCE)
+                    score = __fsqrt_rn(dotv) + 0.0f;  // dotv holds sum (q - d)^2 here
+                else
+                    score = float_finish(a.metric, dotv, dn2, hdr[q], hdr[q].qn2d);
             }
-            // one reservation per warp-tile and query for all rows that passed
-            if (mode == kModeTopk && total != 0) {
-                uint32_t base = 0;
-                if (lane == 0) base = atomicAdd(a.ws.count + a.q0 + q, total);
-                base = __shfl_sync(0xffffffffu, base, 0);
-                uint64_t* pool = a.ws.pool + (size_t)(a.q0 + q) * a.ws.cap;
-#pragma unroll
-                for (int u = 0; u < U; ++u) {
-                    if (ballots[u] & (1u << lane)) {
-                        const uint32_t pos = base + __popc(ballots[u] & ((1u << lane) - 1u));
+            const bool mine = rv && q < a.qt;
+            if (mode == kModeScores) {
+                if (mine) a.out_scores[(size_t)(a.q0 + q) * cv.rows + my_row] = score;
+            } else if (mode == kModeTopk) {
+                const float g = score * sign + 0.0f;
+                const uint32_t o = ord_from_float(g);
+                bool pass = false;
+                if (mine) {
+                    bmax[q] = max(bmax[q], o);
+                    pass = o >= thr[q];
+                }
+                // one reservation per warp-tile and query for all rows that passed
+                const uint32_t ballot = __ballot_sync(0xffffffffu, pass);
+                if (ballot != 0) {
+                    uint32_t base = 0;
+                    if (lane == 0) base = atomicAdd(a.ws.count + a.q0 + q, (uint32_t)__popc(ballot));
+                    base = __shfl_sync(0xffffffffu, base, 0);
+                    if (pass) {
+                        const uint32_t pos = base + __popc(ballot & ((1u << lane) - 1u));
                         if (pos < a.ws.cap)
-                            pool[pos] = key[u];
+                            a.ws.pool[(size_t)(a.q0 + q) * a.ws.cap + pos] = make_key(g, (int32_t)(cv.row_base + my_row));
                         else
                             a.ws.flags[kFlagOverflow] = 1u;
                     }
-                    base += __popc(ballots[u]);
                 }
             }
         }
@@ -339,7 +395,7 @@ __global__ void __launch_bounds__(kThreads, (QT == 1 && CPL <= 4) ? 2 : 1) gemv_
         // ---- publish this warp's running maxima when they changed
 #pragma unroll
         for (int q = 0; q < QT; ++q) {
-            uint32_t m = (gl == 0) ? bmax[q] : 0u;
+            uint32_t m = bmax[q];
             if (__any_sync(0xffffffffu, m > published[q])) {
                 m = __reduce_max_sync(0xffffffffu, m);
                 published[q] = m;
@@ -354,7 +410,7 @@ __global__ void __launch_bounds__(kThreads, (QT == 1 && CPL <= 4) ? 2 : 1) gemv_
         if (warp_in_cta == 0 && duty_iter && ((blockIdx.x & 7) == ((iter == 3 || iter == 6) ? 7 - (iter / 3) : ((31 - __clz(iter)) & 7)))) {
             for (int q = 0; q < a.qt; ++q) {
                 const uint32_t* b = a.ws.bucket + (size_t)(a.q0 + q) * a.ws.nb;
-                const uint32_t nb = min(a.ws.nb, 4096u);
+                const uint32_t nb = min(a.ws.nb, (uint32_t)kStageWords);
                 for (uint32_t i = lane; i < nb; i += 32) s_stage[i] = ld_relaxed_u32(b + i);
                 __syncwarp();
                 uint32_t t = 0;
@@ -370,12 +426,23 @@ __global__ void __launch_bounds__(kThreads, (QT == 1 && CPL <= 4) ? 2 : 1) gemv_
             }
         }
     }
+    cp_async_wait<0>();
 }
 
 template <int LAYOUT, int QT, int LPR, int CPL>
 cudaError_t launch_gemv_shape(cudaStream_t st, int grid, const GemvArgs& a, int mode) {
     constexpr int U = (CPL == 1) ? 8 : (CPL == 2) ? 4 : (CPL <= 4) ? 2 : 1;
-    gemv_kernel<LAYOUT, QT, LPR, CPL, U><<<grid, kThreads, 0, st>>>(a, mode);
+    constexpr size_t smem = (size_t)kStages * U * CPL * kThreads * 16 + (size_t)kStageWords * 4;
+    static bool configured[64] = {};  // one attribute call per instantiation and device
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(gemv_kernel<LAYOUT, QT, LPR, CPL, U>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    gemv_kernel<LAYOUT, QT, LPR, CPL, U><<<grid, kThreads, smem, st>>>(a, mode);
     count_launch();
     return cudaGetLastError();
 }
