@@ -580,6 +580,8 @@ static int scan_rows(MantaB200Runtime* rt, const CandView& cv, const QueryPrep& 
         a.row_begin = r0;
         a.row_end = r1;
         a.ws = ws;
+        static const bool no_wait = getenv("MANTA_B200_NO_STARTUP_WAIT") != nullptr;  // debugging switch
+        a.no_startup_wait = no_wait ? 1 : 0;
         cudaError_t e = launch_gemv(rt->stream, rt->sm_count, a, kModeTopk);
         rt->stats.kernel_launches++;
         if (e != cudaSuccess) return fail_cuda(err, "launch score kernel", e);

@@ -231,6 +231,18 @@ __global__ void __launch_bounds__(kThreads, (QT == 1 && CPL <= 4) ? 2 : 1) gemv_
             for (int q = 0; q < QT; ++q) thr[q] = ld_relaxed_u32(a.ws.thr + a.q0 + ((q < a.qt) ? q : 0));
             // a pool that overflowed makes the host redo the pass in chunks: stop streaming
             if ((iter & 15) == 0 && ld_relaxed_u32(a.ws.flags + kFlagOverflow) != 0) break;
+            // Two tiles per warp have entered the pool unfiltered.  Before streaming on, let the first bound
+            // arrive (the warps on refresh duty at tile counts 2 and 3 are computing it), so that the number of
+            // unfiltered rows does not depend on timing.  The wait is bounded; giving up only costs pool space.
+            if (iter == 3 && !a.no_startup_wait && !(warp_in_cta == 0 && (blockIdx.x & 7) == 6)) {
+#pragma unroll
+                for (int q = 0; q < QT; ++q) {
+                    for (int spin = 0; thr[q] == 0 && spin < 2000; ++spin) {
+                        __nanosleep(32);
+                        thr[q] = ld_relaxed_u32(a.ws.thr + a.q0 + ((q < a.qt) ? q : 0));
+                    }
+                }
+            }
         }
         cp_async_wait<kStages - 2>();  // the copies of this tile have landed
         // refill the stage that was consumed in the previous iteration
@@ -433,15 +445,23 @@ template <int LAYOUT, int QT, int LPR, int CPL>
 cudaError_t launch_gemv_shape(cudaStream_t st, int grid, const GemvArgs& a, int mode) {
     constexpr int U = (CPL == 1) ? 8 : (CPL == 2) ? 4 : (CPL <= 4) ? 2 : 1;
     constexpr size_t smem = (size_t)kStages * U * CPL * kThreads * 16 + (size_t)kStageWords * 4;
-    static bool configured[64] = {};  // one attribute call per instantiation and device
+    // One attribute call and one occupancy query per instantiation and device.  The grid is exactly what is
+    // resident at once (every warp is a bucket and the start-up wait relies on all of them running).
+    static int resident[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 64 || !configured[dev]) {
+    int occ = (dev >= 0 && dev < 64) ? resident[dev] : 0;
+    if (occ == 0) {
         cudaError_t e = cudaFuncSetAttribute(gemv_kernel<LAYOUT, QT, LPR, CPL, U>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
-        if (dev >= 0 && dev < 64) configured[dev] = true;
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, gemv_kernel<LAYOUT, QT, LPR, CPL, U>, kThreads, smem);
+        if (e != cudaSuccess) return e;
+        if (occ < 1) return cudaErrorLaunchOutOfResources;
+        if (occ > 2) occ = 2;
+        if (dev >= 0 && dev < 64) resident[dev] = occ;
     }
+    grid = (grid / 2) * occ;  // the caller passes 2 CTAs per SM, the bucket layout's upper bound
     gemv_kernel<LAYOUT, QT, LPR, CPL, U><<<grid, kThreads, smem, st>>>(a, mode);
     count_launch();
     return cudaGetLastError();

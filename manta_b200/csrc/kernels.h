@@ -42,6 +42,7 @@ struct GemvArgs {
     SelectWs ws;       // kModeTopk
     float* out_scores; // kModeScores: [nq][rows]
     int32_t* out_acc;  // kModeAccum: [rows][3]
+    int no_startup_wait; // debugging: do not wait for the first threshold after two unfiltered tiles
 };
 // How a row of `chunks` 16-byte chunks is split over lanes: lpr lanes per row, cpl chunks per lane, u rows in
 // flight per lane group.  Smallest padded footprint first, then the wider group.
