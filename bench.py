@@ -1,15 +1,17 @@
 #!/usr/bin/env python
 """Benchmark of the fused score + top-k pass.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
-Workload (the configuration the headline metric is quoted on): q8 cosine, 10,000,000 candidates x 768
-(int8 codes + one f32 scale per row, 7.72 GB), one f16 query per step, k = 10.  A step is one pass of the
-hot path over all candidates.  With N GPUs the rows are sharded (strong scaling: the 10 M rows are split),
-each rank scans its shard and the per-shard lists are all-gathered (NCCL) and merged on every rank.
+Default workload `c3` is the configuration the headline metric is quoted on: q8 cosine, 10,000,000 candidates x
+768 (int8 codes + one f32 scale per row, 7.72 GB), one f16 query per step, k = 10.  A step is one pass of the
+hot path over all candidates for one query batch.  With N GPUs the rows are sharded (strong scaling: the rows
+are split), each rank scans its shard and the per-shard lists are all-gathered (NCCL) and merged on every rank.
+Other workloads (`--workload`) are the remaining configurations of the survey, used for profiles and parity at
+size; they print the same JSON line.
 
 Prints ONE JSON line.  `value` is measured with candidates and queries resident in HBM (CUDA events on the
-launching stream, max over ranks); `e2e` goes through the host-buffer C-ABI call (query copied H2D from pinned
+launching stream, max over ranks); `e2e` goes through the host-buffer C-ABI call (queries copied H2D from pinned
 memory and ids/scores copied D2H inside the timed region, candidates resident as bound parameters).
 `--impl reference` times the CPU restatement of the reference's Go host path (the oracle) on this box's cores.
 """
@@ -22,14 +24,54 @@ import subprocess
 import sys
 import threading
 import time
+from dataclasses import dataclass
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-ROWS, COLS, K, NQ = 10_000_000, 768, 10, 1
-METRIC = "q8 cosine score+topk queries/s at 10M x 768 candidates (k=10, 1 query per pass)"
-N_QUERY_SET = 64  # distinct resident queries cycled through the steps
+N_QUERY_SET = 64  # distinct resident query batches cycled through the steps (fewer for large batches)
+
+
+@dataclass
+class Workload:
+    name: str
+    layout: str
+    metric: str
+    rows: int
+    cols: int
+    nq: int
+    k: int
+    smallest: bool = False
+    normalise: bool = True
+    note: str = ""
+
+    def row_bytes(self) -> float:
+        """Algorithmic bytes per candidate row and pass: stored codes + the per-row values the metric reads."""
+        if self.layout == "q8":
+            return self.cols + 4 + (0 if self.metric == "cosine" else 4) - (4 if self.metric == "dot" else 0)
+        if self.layout == "q4":
+            return self.cols / 2 + self.cols / 16 + (0 if self.metric == "dot" else 4)
+        extra = 4 if self.metric == "cosine" else 0
+        return 2 * self.cols + extra
+
+    def describe(self) -> str:
+        order = "smallest" if self.smallest else "largest"
+        return (f"{self.layout} {self.metric} {self.rows / 1e6:g}M x {self.cols}, {self.nq} "
+                f"quer{'y' if self.nq == 1 else 'ies'} per pass, k={self.k} {order}")
+
+
+WORKLOADS = {
+    "c1": Workload("c1", "q8", "cosine", 10_000, 128, 1, 10, note="CPU-runnable select configuration"),
+    "c2": Workload("c2", "f16", "dot", 1_000_000, 384, 64, 100, note="batched f16 dot"),
+    "c3": Workload("c3", "q8", "cosine", 10_000_000, 768, 1, 10, note="headline: single-query q8 cosine at scale"),
+    "c3q256": Workload("c3q256", "q8", "cosine", 10_000_000, 768, 256, 10, note="q8 cosine at scale, query batch 256"),
+    "c4": Workload("c4", "q4", "l2_distance", 12_500_000, 256, 1, 1000, smallest=True, normalise=False,
+                   note="one GPU's share (1/8) of the 100M x 256 q4 set"),
+    "c4q32": Workload("c4q32", "q4", "l2_distance", 12_500_000, 256, 32, 1000, smallest=True, normalise=False,
+                      note="one GPU's share (1/8) of the 100M x 256 q4 set, query batch 32"),
+}
+METRIC_NAME = "q8 cosine score+topk queries/s at 10M x 768 candidates (k=10, 1 query per pass)"
 
 
 def _peaks():
@@ -52,33 +94,36 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.gpu)], stdout=subprocess.PIPE,
+                                          "-lms", "20", "-i", str(self.gpu)], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
+            time.sleep(0.3)  # let the first samples arrive before the timed region starts
         except Exception:
             self.proc = None
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.perf_counter(), line.strip()))
 
-    def stop(self) -> dict:
+    def stop(self, t_begin: float, t_end: float) -> dict:
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
+        time.sleep(0.1)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
-        sm, mx, reasons = [], [], set()
-        for ln in self.lines:
+        sm, mx, reasons, power = [], [], set(), []
+        inside = [ln for (t, ln) in self.lines if t_begin <= t <= t_end + 0.05] or [ln for (_, ln) in self.lines]
+        for ln in inside:
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 9:
                 continue
             try:
                 sm.append(float(f[1]))
                 mx.append(float(f[2]))
+                power.append(float(f[3]))
             except ValueError:
                 continue
             for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
@@ -86,85 +131,94 @@ class ClockSampler:
                     reasons.add(name)
         sm.sort()
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "power_w_max": max(power) if power else None}
 
 
-def _shard(rank: int, world: int):
-    return rank * ROWS // world, (rank + 1) * ROWS // world
+def _shard(rows: int, rank: int, world: int):
+    return rank * rows // world, (rank + 1) * rows // world
 
 
 # ------------------------------------------------------------------------------------------------------------
-def cpu_reference_pass(sample_rows: int, threads: int, steps: int, warmup: int):
-    """Times the oracle (C restatement of cosineRows + topKTensor) on the first `sample_rows` rows of the
-    seeded set held as f32 (the reference's layout), `steps` queries; returns (queries/s extrapolated to ROWS
-    rows, seconds per sample pass, ids of the last pass)."""
+_SAMPLE_CACHE = {}
+
+
+def _cpu_sample(wl: Workload, sample_rows: int, nsets: int):
+    """First `sample_rows` rows of the seeded set, de-quantised to f32 (the layout the reference holds), and the
+    query batches -- the same values the GPU arm scores (same seeds, same generator)."""
+    import numpy as np
+    import torch
+
+    import oracle
+    from manta_b200 import synth
+
+    key = (wl.name, sample_rows)
+    if key in _SAMPLE_CACHE:
+        return _SAMPLE_CACHE[key]
+    dev = "cuda" if torch.cuda.is_available() else "cpu"
+    x = synth.rows_f16(0, sample_rows, wl.cols, normalise=wl.normalise, device=dev).float().cpu().numpy()
+    q = synth.queries_f16(nsets * wl.nq, wl.cols, normalise=wl.normalise, device=dev).float().cpu().numpy().reshape(nsets, wl.nq, wl.cols)
+    if wl.layout == "q8":
+        docs = oracle.unpack_q8_rows(*oracle.pack_q8_rows(x))
+    elif wl.layout == "q4":
+        docs = oracle.unpack_q4_b32(*oracle.pack_q4_b32(x))
+    else:
+        docs = np.ascontiguousarray(x)
+    _SAMPLE_CACHE[key] = (docs, q)
+    return docs, q
+
+
+def cpu_reference_pass(wl: Workload, sample_rows: int, threads: int, steps: int, warmup: int, nsets: int):
+    """Times the oracle (C restatement of the score builtin + full-sort topKTensor) on the bounded sample;
+    returns (queries/s extrapolated to wl.rows rows, seconds per sample pass, ids of the last pass)."""
     import numpy as np
 
     import oracle
 
     oracle.set_threads(threads)
-    docs, queries = _cpu_sample(sample_rows)
-    last = None
-    times = []
+    docs, queries = _cpu_sample(wl, sample_rows, nsets)
+    last, times = None, []
     for i in range(warmup + steps):
-        q = queries[i % queries.shape[0]]
+        q = queries[i % nsets]
         t0 = time.perf_counter()
-        scores = oracle.cosine_rows(q, docs)
-        last = oracle.topk(scores, K)
+        scores = oracle.SCORE_FNS[wl.metric](q, docs)
+        last = oracle.topk(scores, min(wl.k, sample_rows), wl.smallest)
         t1 = time.perf_counter()
         if i >= warmup:
             times.append(t1 - t0)
     sec = sum(times) / len(times)
-    qps = 1.0 / (sec * (ROWS / sample_rows))
+    qps = wl.nq / (sec * (wl.rows / sample_rows))
     return qps, sec, np.asarray(last)
 
 
-_SAMPLE_CACHE = {}
+def _sample_rows_for(wl: Workload) -> int:
+    # about 1 GB of f32 rows, at most the whole set; the timed CPU work stays in the 10-30 s range
+    return int(min(wl.rows, max(10_000, 250_000_000 // wl.cols // max(1, wl.nq // 4))))
 
 
-def _cpu_sample(sample_rows: int):
-    """First `sample_rows` de-quantised rows (f32) and the query set, identical to what the GPU arm scores.
-    Generated with torch on the device when there is one, else on the CPU with the same seeds' API (values
-    differ between the two generators; each arm is self-consistent)."""
-    import numpy as np
-    import torch
-
-    import oracle
-
-    if sample_rows in _SAMPLE_CACHE:
-        return _SAMPLE_CACHE[sample_rows]
-    from manta_b200 import synth
-
-    dev = "cuda" if torch.cuda.is_available() else "cpu"
-    x = synth.rows_f16(0, sample_rows, COLS, device=dev).float().cpu().numpy()
-    q = synth.queries_f16(N_QUERY_SET, COLS, device=dev).float().cpu().numpy()
-    codes, scales = oracle.pack_q8_rows(x)
-    docs = oracle.unpack_q8_rows(codes, scales)
-    _SAMPLE_CACHE[sample_rows] = (docs, q)
-    return docs, q
-
-
-def run_reference(args):
+def run_reference(args, wl: Workload):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     import oracle
 
     threads = os.cpu_count() or 1
-    sample_rows = min(1_000_000, ROWS)
+    sample_rows = _sample_rows_for(wl)
+    nsets = max(1, min(N_QUERY_SET, 4096 // wl.nq))
     t0 = time.perf_counter()
-    qps, sec, _ = cpu_reference_pass(sample_rows, threads, args.steps, args.warmup)
+    steps = max(1, min(args.steps, 10))
+    qps, sec, _ = cpu_reference_pass(wl, sample_rows, threads, steps, min(args.warmup, 1), nsets)
     line = {
-        "impl": "reference", "metric": METRIC, "value": qps, "unit": "queries/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * (ROWS / sample_rows) * 1e3,
-        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f64 accumulate / f32 result",
+        "impl": "reference", "metric": METRIC_NAME if wl.name == "c3" else f"{wl.describe()} queries/s",
+        "value": qps, "unit": "queries/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": sec * (wl.rows / sample_rows) * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f64 accumulate / f32 result" if wl.metric != "dot" else "f32",
         "data": "synthetic",
-        "config": {"workload": "q8 cosine 10M x 768, 1 query, k=10 (reference fp32 layout, host cores)",
-                   "rows": ROWS, "cols": COLS, "k": K, "queries_per_step": NQ},
+        "config": {"workload": wl.describe() + " (reference f32 layout, host cores)", "rows": wl.rows, "cols": wl.cols,
+                   "k": wl.k, "queries_per_step": wl.nq},
         "cpu_baseline": {"value": qps, "unit": "queries/s", "cores": threads, "kind": "port",
-                         "sample": f"{sample_rows} of {ROWS} rows per step as f32 (3.07 GB), cosineRows + full-sort "
-                                   f"topKTensor restated in C, OpenMP over rows; queries/s extrapolated x{ROWS // sample_rows}; "
-                                   "Go toolchain unavailable so the reference itself cannot run"},
+                         "sample": f"{sample_rows} of {wl.rows} rows per step as f32, {steps} timed steps, score builtin + "
+                                   f"full-sort topKTensor restated in C with OpenMP over rows; queries/s extrapolated "
+                                   f"x{wl.rows / sample_rows:g}; the Go toolchain is unavailable so the reference itself cannot run"},
         "e2e": {"value": qps, "unit": "queries/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0, "oracle_threads": oracle.num_threads(), "wall_s": time.perf_counter() - t0,
     }
@@ -172,7 +226,7 @@ def run_reference(args):
 
 
 # ------------------------------------------------------------------------------------------------------------
-def run_ours(args):
+def run_ours(args, wl: Workload):
     import numpy as np
     import torch
 
@@ -193,30 +247,31 @@ def run_ours(args):
     native.load()
     rt = native.Runtime(local_rank)
     stream = torch.cuda.ExternalStream(rt.stream)
+    nq, k = wl.nq, wl.k
+    nsets = max(1, min(N_QUERY_SET, 4096 // nq))
 
-    r0, r1 = _shard(rank, world)
-    data, scales = synth.packed_candidates(rt, "q8", r0, r1, COLS)
-    cands = rt.bind("q8", data, scales, row_base=r0, rows=r1 - r0, cols=COLS)
+    r0, r1 = _shard(wl.rows, rank, world)
+    data, scales = synth.packed_candidates(rt, wl.layout, r0, r1, wl.cols, normalise=wl.normalise)
+    cands = rt.bind(wl.layout, data, scales, row_base=r0, rows=r1 - r0, cols=wl.cols)
     with torch.cuda.stream(stream):
-        d_queries = synth.queries_f16(N_QUERY_SET, COLS)
-        d_ids = torch.empty((NQ, K), dtype=torch.int32, device="cuda")
-        d_scores = torch.empty((NQ, K), dtype=torch.float32, device="cuda")
+        d_queries = synth.queries_f16(nsets * nq, wl.cols, normalise=wl.normalise).view(nsets, nq, wl.cols)
+        d_ids = torch.empty((nq, k), dtype=torch.int32, device="cuda")
+        d_scores = torch.empty((nq, k), dtype=torch.float32, device="cuda")
         if world > 1:
-            g_ids = torch.empty((world, NQ, K), dtype=torch.int32, device="cuda")
-            g_scores = torch.empty((world, NQ, K), dtype=torch.float32, device="cuda")
-            m_ids = torch.empty((NQ, K), dtype=torch.int32, device="cuda")
-            m_scores = torch.empty((NQ, K), dtype=torch.float32, device="cuda")
+            g_ids = torch.empty((world, nq, k), dtype=torch.int32, device="cuda")
+            g_scores = torch.empty((world, nq, k), dtype=torch.float32, device="cuda")
+            m_ids = torch.empty((nq, k), dtype=torch.int32, device="cuda")
+            m_scores = torch.empty((nq, k), dtype=torch.float32, device="cuda")
     stream.synchronize()
     h_queries = d_queries.cpu().numpy().view(np.uint16)
 
     def step_device(i):
-        q = d_queries[i % N_QUERY_SET]
-        rt.score_topk_device(cands, "cosine", q, NQ, K, d_ids, d_scores, sync=False)
+        rt.score_topk_device(cands, wl.metric, d_queries[i % nsets], nq, k, d_ids, d_scores, smallest=wl.smallest, sync=False)
         if world > 1:
             with torch.cuda.stream(stream):
                 dist.all_gather_into_tensor(g_ids, d_ids)
                 dist.all_gather_into_tensor(g_scores, d_scores)
-            rt.topk_merge_device(g_ids, g_scores, world, NQ, K, m_ids, m_scores, sync=False)
+            rt.topk_merge_device(g_ids, g_scores, world, nq, k, m_ids, m_scores, smallest=wl.smallest, sync=False)
 
     def barrier():
         if world > 1:
@@ -227,38 +282,43 @@ def run_ours(args):
     for i in range(args.warmup):
         step_device(i)
     barrier()
+    rt.synchronize()  # raises if a warm-up pass overflowed its pool
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
     rt.profile(True)
     launches0 = native.kernel_launch_count()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_begin = time.perf_counter()
     ev0.record(stream)
     for i in range(args.steps):
         step_device(args.warmup + i)
     ev1.record(stream)
     barrier()
+    t_end = time.perf_counter()
+    rt.synchronize()
     launches = native.kernel_launch_count() - launches0
     total_ms = ev0.elapsed_time(ev1)
     scan_ms, scan_passes = rt.scan_time()
     rt.profile(False)
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop(t_begin, t_end) if rank == 0 else None
     t = torch.tensor([total_ms, scan_ms / max(scan_passes, 1)], dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     total_ms, scan_ms_per_pass = float(t[0]), float(t[1])
     final_ids = (m_ids if world > 1 else d_ids).cpu().numpy().copy()
+    stats_device = rt.stats()
 
     # ---- end to end through the host-buffer ABI call ------------------------------------------------
     def step_host(i):
-        ids, sc = rt.score_topk(cands, "cosine", h_queries[i % N_QUERY_SET], K)
+        ids, sc = rt.score_topk(cands, wl.metric, h_queries[i % nsets], k, smallest=wl.smallest)
         if world > 1:
             with torch.cuda.stream(stream):
-                d_ids.copy_(torch.from_numpy(ids).view(NQ, K), non_blocking=False)
-                d_scores.copy_(torch.from_numpy(sc).view(NQ, K), non_blocking=False)
+                d_ids.copy_(torch.from_numpy(ids).view(nq, k), non_blocking=False)
+                d_scores.copy_(torch.from_numpy(sc).view(nq, k), non_blocking=False)
                 dist.all_gather_into_tensor(g_ids, d_ids)
                 dist.all_gather_into_tensor(g_scores, d_scores)
-            rt.topk_merge_device(g_ids, g_scores, world, NQ, K, m_ids, m_scores, sync=True)
+            rt.topk_merge_device(g_ids, g_scores, world, nq, k, m_ids, m_scores, smallest=wl.smallest, sync=True)
             return m_ids.cpu().numpy(), m_scores.cpu().numpy()
         return ids, sc
 
@@ -275,48 +335,53 @@ def run_ours(args):
         dist.all_reduce(te, op=dist.ReduceOp.MAX)
     e2e_s = float(te[0])
 
-    # ---- parity spot check on the bounded sample the CPU baseline uses (rank 0, N=1) ------------------
+    # ---- CPU baseline + parity spot check on the same bounded sample (rank 0, N=1) ----------------------
     cpu = None
     parity = None
     if rank == 0 and world == 1 and not args.no_cpu:
-        import oracle
-
-        sample_rows = min(1_000_000, ROWS)
+        sample_rows = _sample_rows_for(wl)
         threads = os.cpu_count() or 1
-        qps, sec, ref_ids = cpu_reference_pass(sample_rows, threads, 3, 1)
-        qps1, sec1, _ = cpu_reference_pass(sample_rows, 1, 1, 0)
+        qps, sec, ref_ids = cpu_reference_pass(wl, sample_rows, threads, 3, 1, nsets)
+        qps1, sec1, _ = cpu_reference_pass(wl, sample_rows, 1, 1, 0, nsets)
         cpu = {"value": qps, "unit": "queries/s", "cores": threads, "kind": "port",
-               "sample": f"first {sample_rows} of {ROWS} rows as f32 per pass, 3 timed passes after 1 warm-up, "
-                         f"C restatement of cosineRows + full-sort topKTensor with OpenMP over rows; queries/s "
-                         f"extrapolated x{ROWS // sample_rows}; single thread (the reference's own threading): "
+               "sample": f"first {sample_rows} of {wl.rows} rows as f32 per pass, 3 timed passes after 1 warm-up, "
+                         f"C restatement of the score builtin + full-sort topKTensor with OpenMP over rows; queries/s "
+                         f"extrapolated x{wl.rows / sample_rows:g}; single thread (the reference's own threading): "
                          f"{qps1:.4f} queries/s",
                "single_thread_value": qps1, "sample_seconds_per_pass": sec}
-        sub = rt.bind("q8", data[:sample_rows], scales[:sample_rows], row_base=0, rows=sample_rows, cols=COLS)
-        qi = (1 + 3 - 1) % N_QUERY_SET  # the query of the last CPU pass
-        ids, sc = rt.score_topk(sub, "cosine", h_queries[qi], K)
-        parity = {"sample_rows": sample_rows, "ids_equal_oracle": bool((ids == ref_ids).all())}
+        sub = rt.bind(wl.layout, data[:sample_rows], None if scales is None else scales[:sample_rows], row_base=0,
+                      rows=sample_rows, cols=wl.cols)
+        kk = min(k, sample_rows)
+        ids, sc = rt.score_topk(sub, wl.metric, h_queries[(1 + 3 - 1) % nsets], kk, smallest=wl.smallest)
+        same = (np.asarray(ids).reshape(nq, kk) == ref_ids.reshape(nq, kk))
+        parity = {"sample_rows": sample_rows, "ids_equal_oracle": bool(same.all()), "ids_equal_fraction": float(same.mean())}
         sub.unbind()
 
     if rank == 0:
         peak, peak_src = _peaks()
         shard_rows = r1 - r0
-        algo_bytes = shard_rows * (COLS + 4)  # codes + one 4-byte per-row statistic, read once per pass
+        algo_bytes = shard_rows * wl.row_bytes()
         achieved = algo_bytes / (scan_ms_per_pass * 1e-3) / 1e9
+        value = args.steps * nq / (total_ms * 1e-3)
         line = {
-            "metric": METRIC, "value": args.steps * NQ / (total_ms * 1e-3), "unit": "queries/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps,
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8 x int8 -> int32 (dp4a), f32 epilogue",
+            "metric": METRIC_NAME if wl.name == "c3" else f"{wl.describe()} queries/s",
+            "value": value, "unit": "queries/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": {"q8": "int8 x int8 -> int32 (two int8 query planes), f32 epilogue",
+                      "q4": "int4 x int8 -> int32 per block, f32 across blocks", "f16": "f16 x f16 -> f32"}[wl.layout],
             "data": "synthetic",
-            "config": {"workload": f"q8 cosine {ROWS / 1e6:g}M x 768, 1 query per pass, k=10", "rows": ROWS, "cols": COLS, "k": K,
-                       "queries_per_step": NQ, "layout": "q8 per-row f32 scale", "shards": world,
-                       "l2": "inputs larger than L2 (7.7 GB scanned per pass / shards)"},
-            "candidates_dim_per_s": args.steps * NQ * ROWS * COLS / (total_ms * 1e-3),
+            "config": {"workload": wl.describe(), "rows": wl.rows, "cols": wl.cols, "k": k, "queries_per_step": nq,
+                       "layout": wl.layout, "shards": world, "note": wl.note,
+                       "l2": f"inputs larger than L2: {algo_bytes / 1e9:.3f} GB scanned per pass and GPU" if algo_bytes > 2.5e8
+                             else "inputs smaller than L2 (latency-bound configuration, not a roofline point)"},
+            "candidates_dim_per_s": value * wl.rows * wl.cols,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "peak_source": peak_src, "kernel": "gemv_kernel<q8,QT=1,LPR=16,CPL=3>",
+                         "traffic": None, "peak_source": peak_src,
+                         "kernel": "tcgen05 scan (mma.cu)" if stats_device["mma_passes"] else "gemv_kernel (gemv.cuh)",
                          "kernel_ms": scan_ms_per_pass, "algorithmic_bytes_per_launch": algo_bytes,
                          "frac_of_nominal_8TBs": achieved / 8000.0},
-            "e2e": {"value": args.steps * NQ / e2e_s, "unit": "queries/s", "h2d_bytes_per_step": NQ * COLS * 2,
-                    "d2h_bytes_per_step": NQ * K * 8, "ms_per_step": e2e_s / args.steps * 1e3,
+            "e2e": {"value": args.steps * nq / e2e_s, "unit": "queries/s", "h2d_bytes_per_step": nq * wl.cols * 2,
+                    "d2h_bytes_per_step": nq * k * 8, "ms_per_step": e2e_s / args.steps * 1e3,
                     "note": "host-buffer C-ABI call per step; candidates stay bound (resident) as plan parameters"},
             "gpu_launches": int(launches), "clocks": clocks, "cpu_baseline": cpu, "parity_check": parity,
             "result_checksum": int(np.asarray(final_ids, dtype=np.int64).sum()),
@@ -335,17 +400,25 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline / parity spot check")
-    ap.add_argument("--rows", type=int, default=ROWS,
-                    help="candidate rows (default: the 10M of the headline workload; smaller values are for profiling)")
+    ap.add_argument("--rows", type=int, default=0, help="override the workload's row count (smaller cases for profiling)")
+    ap.add_argument("--nq", type=int, default=0, help="override the workload's query batch")
+    ap.add_argument("--k", type=int, default=0, help="override the workload's k")
     args = ap.parse_args()
-    globals()["ROWS"] = args.rows
     if args.warmup < 3:
         args.warmup = 3
+    wl = WORKLOADS[args.workload]
+    if args.rows:
+        wl.rows = args.rows
+    if args.nq:
+        wl.nq = args.nq
+    if args.k:
+        wl.k = args.k
     if args.impl == "reference":
-        run_reference(args)
+        run_reference(args, wl)
     else:
-        run_ours(args)
+        run_ours(args, wl)
 
 
 if __name__ == "__main__":

@@ -482,7 +482,10 @@ static uint32_t pool_cap_for(const MantaB200Runtime* rt, const CandView& cv, int
     const int64_t rows = cv.rows;
     int64_t cap;
     if (mma_supported(cv, nq)) {
-        cap = (int64_t)mma_first_burst_rows(rt->sm_count) * 2;
+        cap = mma_pool_cap(k);  // observed tiles are replayed, so nothing enters the pool unfiltered
+        if (cap > rows) cap = rows;
+        if (cap < k) cap = k;
+        return (uint32_t)cap;
     } else {
         // Every row streamed before the first threshold lands enters the pool.  That takes on the order of ten
         // microseconds whatever the row size, so the allowance is a byte budget (HBM rate x ~20 us), in rows.
@@ -559,9 +562,13 @@ static int scan_rows(MantaB200Runtime* rt, const CandView& cv, const QueryPrep& 
         const char* why = nullptr;
         cudaError_t e = launch_mma_topk(rt->stream, rt->sm_count, &rt->mma, m, &launches, &why);
         rt->stats.kernel_launches += launches;
-        if (e != cudaSuccess) return fail(err, "score_topk(%s): tensor-core pass: %s (%s)", metric_name(metric), why ? why : "launch failed", cudaGetErrorName(e));
-        rt->stats.mma_passes++;
-        return 0;
+        if (e == cudaSuccess) {
+            rt->stats.mma_passes++;
+            return 0;
+        }
+        if (e != cudaErrorNotSupported)
+            return fail(err, "score_topk(%s): tensor-core pass: %s (%s)", metric_name(metric), why ? why : "launch failed", cudaGetErrorName(e));
+        // shapes the tensor-core pass declines go to the streaming kernel below
     }
     for (int q0 = 0; q0 < nq;) {
         int left = nq - q0;

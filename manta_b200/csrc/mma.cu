@@ -1,20 +1,576 @@
-// tcgen05 tensor-core scoring pass.
+// tcgen05 tensor-core scoring pass: a batch of queries against packed q8 or f16 candidate rows as a dense
+// contraction.  One persistent CTA per SM; candidate tiles of 128 rows stream through a TMA-fed shared-memory
+// ring, tcgen05.mma accumulates [128 rows x N columns] in tensor memory (int32 for q8: columns are the two int8
+// planes of every query; f32 for f16), and four epilogue warps read the accumulators back (tcgen05.ld), finish
+// the scores with the same epilogue functions as the streaming kernel and filter them into the top-k pools.
+//
+// Warp roles (7 warps): 0 = TMA producer, 1 = MMA issuer (owns the tensor-memory allocation), 2..5 = epilogue
+// (one per 32-lane quadrant of tensor memory), 6 = threshold refresher.
+//
+// Every wait in this file is bounded: a wait that runs out sets the abort flag of the CTA and the time-out flag
+// of the pass, every role leaves its loop, tensor memory is released and the kernel returns; the host then
+// reports the failure (and the streaming kernel can redo the pass).
+#include <cuda.h>
+
 #include "mma.h"
 
 namespace mb200 {
 
-struct MmaState {
-    int unused;
+namespace {
+
+constexpr int kTileRows = 128;
+constexpr int kChunkBytes = 128;      // K extent of one pipeline stage, in bytes (one 128-byte swizzle span)
+constexpr int kMmaThreads = 224;
+constexpr int kMmaCols = 256;         // N of one MMA
+constexpr int kBucketSlots = 4;       // bucket slots per epilogue warp (tiles rotate through them)
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+// ---- PTX wrappers -------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false (and raises the abort flag) when it gives up or when another role aborted.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_s) {
+    for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spin & 255u) == 255u && *abort_s) return false;
+    }
+    *abort_s = 1u;
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+template <bool I8>
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    if constexpr (I8) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+            : "memory");
+    }
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major operand tile in shared memory, 128-byte swizzle: rows of 128 bytes, groups of 8 rows 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);        // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                          // leading byte offset (unused for swizzled K-major), 16 B
+    d |= (uint64_t)(1024 >> 4) << 32;                // stride byte offset: 8 rows * 128 B
+    d |= (uint64_t)1 << 46;                          // descriptor version of this architecture
+    d |= (uint64_t)2 << 61;                          // 128-byte swizzle
+    return d;
+}
+
+struct KernelArgs {
+    CandView cv;
+    const QueryHeader* headers;   // [nq] (global query index)
+    SelectWs ws;
+    uint32_t* ready;              // CTAs that have published their observed tiles
+    int q0;                       // first query of this group
+    int qn;                       // queries in this group
+    int ncols;                    // N of the MMA (multiple of 16)
+    int lo_off;                   // q8: column offset of the low planes
+    int kchunks;                  // 128-byte chunks per row
+    int stages;
+    int metric;
+    int order;
+    int k;
+    int filtered;                 // 0: everything enters the pool (small sets)
+    int observe_tiles;            // tiles per CTA scored before the first bound exists (replayed at the end)
+    int64_t row_begin;
+    int64_t row_end;
 };
 
-bool mma_supported(const CandView&, int) { return false; }
-int mma_bucket_count(int) { return 0; }
-int mma_first_burst_rows(int) { return 0; }
-cudaError_t launch_mma_topk(cudaStream_t, int, MmaState**, const MmaArgs&, int* launches, const char** why) {
-    *launches = 0;
-    *why = "tensor-core pass not built";
-    return cudaErrorNotSupported;
+template <bool I8>
+__global__ void __launch_bounds__(kMmaThreads, 1)
+mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const KernelArgs a) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int S = a.stages;
+    const uint32_t b_stage_bytes = (uint32_t)a.ncols * kChunkBytes;
+    unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char* sA = base;
+    unsigned char* sB = sA + (size_t)S * kTileRows * kChunkBytes;
+    unsigned char* p = sB + (size_t)S * b_stage_bytes;
+    uint64_t* full = (uint64_t*)p;
+    uint64_t* empty = full + 8;
+    uint64_t* tfull = empty + 8;
+    uint64_t* tempty = tfull + 2;
+    uint32_t* tmem_slot = (uint32_t*)(tempty + 2);
+    volatile uint32_t* abort_s = tmem_slot + 1;
+    volatile uint32_t* done_s = tmem_slot + 2;
+    QueryHeader* hdr_s = (QueryHeader*)(p + 256);
+    uint32_t* thr_s = (uint32_t*)(hdr_s + kMmaCols);
+    uint32_t* bmax_s = thr_s + kMmaCols;                 // [qn][4]: maxima of the current tile per epilogue warp
+    uint32_t* pub_s = bmax_s + kMmaCols * 4;             // [qn][4][kBucketSlots]: last published values
+
+    const int64_t nrows = a.row_end - a.row_begin;
+    const int n_tiles = (int)((nrows + kTileRows - 1) / kTileRows);
+    const int grid = gridDim.x, cta = blockIdx.x;
+    const int n_my = (cta < n_tiles) ? (n_tiles - cta + grid - 1) / grid : 0;
+    const int n_obs = a.filtered ? min(a.observe_tiles, n_my) : 0;
+    const int n_iters = n_my + n_obs;   // observed tiles are replayed at the end in append mode
+    const int active_ctas = min(grid, n_tiles);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&tfull[b], 1);
+            mbar_init(&tempty[b], 4);
+        }
+        *abort_s = 0;
+        *done_s = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    for (int j = threadIdx.x; j < a.qn; j += blockDim.x) {
+        hdr_s[j] = a.headers[a.q0 + j];
+        thr_s[j] = 0;
+        for (int w = 0; w < 4; ++w) {
+            bmax_s[j * 4 + w] = 0;
+            for (int s = 0; s < kBucketSlots; ++s) pub_s[(j * 4 + w) * kBucketSlots + s] = 0;
+        }
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    auto tile_of = [&](int it) { return cta + ((it < n_my) ? it : it - n_my) * grid; };
+
+    if (n_my > 0) {
+        if (warp == 0) {
+            // ---------------- TMA producer ----------------
+            if (lane == 0) {
+                uint32_t g = 0;
+                for (int it = 0; it < n_iters && !*abort_s; ++it) {
+                    const int row0 = (int)(a.row_begin + (int64_t)tile_of(it) * kTileRows);
+                    for (int kc = 0; kc < a.kchunks; ++kc, ++g) {
+                        const int s = g % S;
+                        const uint32_t ph = (g / S) & 1u;
+                        if (!mbar_wait(&empty[s], ph ^ 1u, abort_s)) break;
+                        mbar_expect_tx(&full[s], (uint32_t)(kTileRows * kChunkBytes) + b_stage_bytes);
+                        tma_load_2d(sA + (size_t)s * kTileRows * kChunkBytes, &map_a, kc * kChunkBytes, row0, &full[s]);
+                        tma_load_2d(sB + (size_t)s * b_stage_bytes, &map_b, kc * kChunkBytes, 0, &full[s]);
+                    }
+                }
+            }
+        } else if (warp == 1) {
+            // ---------------- MMA issuer ----------------
+            if (lane == 0) {
+                const uint32_t idesc = I8 ? ((2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(a.ncols >> 3) << 17) | ((uint32_t)(kTileRows >> 4) << 24))
+                                          : ((1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(a.ncols >> 3) << 17) | ((uint32_t)(kTileRows >> 4) << 24));
+                uint32_t g = 0;
+                for (int it = 0; it < n_iters && !*abort_s; ++it) {
+                    const int acc = it & 1;
+                    if (!mbar_wait(&tempty[acc], ((uint32_t)(it >> 1) & 1u) ^ 1u, abort_s)) break;
+                    tc_fence_after();
+                    const uint32_t d_tmem = tmem_base + (uint32_t)acc * kMmaCols;
+                    bool ok = true;
+                    for (int kc = 0; kc < a.kchunks; ++kc, ++g) {
+                        const int s = g % S;
+                        const uint32_t ph = (g / S) & 1u;
+                        if (!mbar_wait(&full[s], ph, abort_s)) { ok = false; break; }
+                        tc_fence_after();
+                        const uint32_t a_addr = smem_u32(sA + (size_t)s * kTileRows * kChunkBytes);
+                        const uint32_t b_addr = smem_u32(sB + (size_t)s * b_stage_bytes);
+#pragma unroll
+                        for (int ks = 0; ks < kChunkBytes / 32; ++ks) {
+                            tc_mma<I8>(d_tmem, smem_desc_sw128(a_addr + ks * 32), smem_desc_sw128(b_addr + ks * 32), idesc,
+                                       (kc > 0 || ks > 0) ? 1u : 0u);
+                        }
+                        tc_commit(&empty[s]);   // frees the stage when these MMAs have read it
+                    }
+                    if (!ok) break;
+                    tc_commit(&tfull[acc]);     // accumulator complete
+                }
+            }
+        } else if (warp < 6) {
+            // ---------------- epilogue ----------------
+            const int quad = warp & 3;              // tensor-memory lanes 32*quad .. 32*quad+31
+            const int ew = warp - 2;                // bucket owner index 0..3
+            const int et = threadIdx.x - 64;        // 0..127 among epilogue threads
+            const float sign = (a.order == MANTA_B200_ORDER_SMALLEST) ? -1.0f : 1.0f;
+            const bool want_scale = I8 && a.metric != MANTA_B200_METRIC_COSINE;
+            const bool want_stats = a.metric != MANTA_B200_METRIC_DOT;
+            for (int it = 0; it < n_iters; ++it) {
+                const bool observe = it < n_obs;            // score and record maxima only
+                const bool replay = it >= n_my;             // append only
+                if (a.filtered && it == n_obs && n_obs > 0) {
+                    // the first bounds must exist before anything is appended (bounded wait)
+                    for (int j = et; j < a.qn; j += 128) {
+                        uint32_t t = 0;
+                        for (uint32_t spin = 0; spin < 4000u && t == 0 && !*abort_s; ++spin) {
+                            t = ld_relaxed_u32(a.ws.thr + a.q0 + j);
+                            if (t == 0) __nanosleep(64);
+                        }
+                        thr_s[j] = t;
+                    }
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                }
+                const int acc = it & 1;
+                if (!mbar_wait(&tfull[acc], (uint32_t)(it >> 1) & 1u, abort_s)) break;
+                tc_fence_after();
+                const int64_t row = a.row_begin + (int64_t)tile_of(it) * kTileRows + quad * 32 + lane;
+                const bool rv = row < a.row_end;
+                float sd = 0.0f;
+                uint32_t stat = 0;
+                if (rv && want_scale) sd = ((const float*)a.cv.scales)[row];
+                if (rv && want_stats) stat = ((const uint32_t*)a.cv.stats)[row];
+                const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)acc * kMmaCols;
+                for (int c0 = 0; c0 < a.qn; c0 += 16) {
+                    uint32_t vh[16], vl[16];
+                    tmem_ld16(t_row + c0, vh);
+                    if constexpr (I8) tmem_ld16(t_row + a.lo_off + c0, vl);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int jj = 0; jj < 16; ++jj) {
+                        const int j = c0 + jj;
+                        if (j >= a.qn) break;   // uniform across the warp
+                        float score;
+                        if constexpr (I8)
+                            score = q8_finish(a.metric, (int)vh[jj], (int)vl[jj], (int)stat, sd, hdr_s[j]);
+                        else
+                            score = float_finish(a.metric, __uint_as_float(vh[jj]), __uint_as_float(stat), hdr_s[j], hdr_s[j].qn2d);
+                        const float g = score * sign + 0.0f;
+                        const uint32_t o = rv ? ord_from_float(g) : 0u;
+                        if (!replay) {
+                            const uint32_t wmax = __reduce_max_sync(0xffffffffu, o);
+                            if (lane == 0 && wmax > bmax_s[j * 4 + ew]) bmax_s[j * 4 + ew] = wmax;
+                        }
+                        const bool pass = rv && !observe && (!a.filtered || o >= thr_s[j]);
+                        const uint32_t ballot = __ballot_sync(0xffffffffu, pass);
+                        if (ballot != 0) {
+                            uint32_t pos0 = 0;
+                            if (lane == 0) pos0 = atomicAdd(a.ws.count + a.q0 + j, (uint32_t)__popc(ballot));
+                            pos0 = __shfl_sync(0xffffffffu, pos0, 0);
+                            if (pass) {
+                                const uint32_t pos = pos0 + __popc(ballot & ((1u << lane) - 1u));
+                                if (pos < a.ws.cap)
+                                    a.ws.pool[(size_t)(a.q0 + j) * a.ws.cap + pos] = make_key(g, (int32_t)(a.cv.row_base + row));
+                                else
+                                    a.ws.flags[kFlagOverflow] = 1u;
+                            }
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&tempty[acc]);
+                // ---- per-tile housekeeping: publish the tile's maxima, reload the bounds
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (a.filtered) {
+                    if (!replay) {
+                        const int slot = it % kBucketSlots;
+                        for (int i = et; i < a.qn * 4; i += 128) {
+                            const uint32_t v = bmax_s[i];
+                            bmax_s[i] = 0;
+                            if (v > pub_s[i * kBucketSlots + slot]) {
+                                pub_s[i * kBucketSlots + slot] = v;
+                                const int j = i >> 2, w = i & 3;
+                                st_relaxed_u32(a.ws.bucket + (size_t)(a.q0 + j) * a.ws.nb + ((size_t)(cta * 4 + w) * kBucketSlots + slot), v);
+                            }
+                        }
+                    }
+                    if (it + 1 == n_obs) {
+                        // this CTA's observed tiles are all published
+                        __threadfence();
+                        asm volatile("bar.sync 1, 128;" ::: "memory");
+                        if (et == 0) atomicAdd(a.ready, 1u);
+                    } else if (it + 1 > n_obs) {
+                        for (int j = et; j < a.qn; j += 128) thr_s[j] = ld_relaxed_u32(a.ws.thr + a.q0 + j);
+                    }
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                }
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (et == 0) *done_s = 1u;
+        } else if (a.filtered) {
+            // ---------------- threshold refresher ----------------
+            // Waits until every active CTA has published its observed tiles, then keeps recomputing, for the
+            // queries this CTA is responsible for in each round, the k-th largest bucket maximum (top 20 bits).
+            uint32_t seen = 0;
+            for (uint32_t spin = 0; spin < 100000u && seen < (uint32_t)active_ctas && !*abort_s && !*done_s; ++spin) {
+                seen = ld_relaxed_u32(a.ready);
+                if (seen < (uint32_t)active_ctas) __nanosleep(64);
+            }
+            const uint32_t nb = a.ws.nb;
+            for (uint32_t round = 0; !*done_s && !*abort_s; ++round) {
+                const int j = (int)(((uint64_t)cta + (uint64_t)round * grid) % (uint64_t)a.qn);
+                const uint32_t* b = a.ws.bucket + (size_t)(a.q0 + j) * nb;
+                uint32_t t = 0;
+                for (int bit = 31; bit >= 12; --bit) {
+                    const uint32_t cand = t | (1u << bit);
+                    uint32_t cnt = 0;
+                    for (uint32_t i = lane; i < nb; i += 32) cnt += (__ldcg(b + i) >= cand) ? 1u : 0u;
+                    cnt = __reduce_add_sync(0xffffffffu, cnt);
+                    if (cnt >= (uint32_t)a.k) t = cand;
+                }
+                if (lane == 0 && t != 0) atomicMax(a.ws.thr + a.q0 + j, t);
+                __syncwarp();
+                if (round > (uint32_t)(2 * a.qn) ) __nanosleep(2000);   // steady state: refresh at a relaxed pace
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+    if (threadIdx.x == 0 && *abort_s) a.ws.flags[kFlagTimeout] = 1u;
 }
-void mma_state_destroy(MmaState* s) { delete s; }
+
+// Operand B: [ncols][kpad] bytes, K-major.  q8: rows 0..qn-1 are the high planes, lo_off.. the low planes.
+// f16: row j is query j as half bits.  Everything else is zero.
+__global__ void build_b_kernel(unsigned char* __restrict__ out, int ncols, int kpad, int layout, QueryPrep qp, int q0,
+                               int qn, int lo_off, int cols) {
+    const size_t total = (size_t)ncols * kpad;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int n = (int)(i / kpad), kb = (int)(i % kpad);
+        unsigned char v = 0;
+        if (layout == MANTA_B200_LAYOUT_Q8_ROW_F32) {
+            if (kb < qp.plane_stride) {
+                if (n < qn)
+                    v = (unsigned char)qp.plane_hi[(size_t)(q0 + n) * qp.plane_stride + kb];
+                else if (n >= lo_off && n < lo_off + qn)
+                    v = (unsigned char)qp.plane_lo[(size_t)(q0 + n - lo_off) * qp.plane_stride + kb];
+            }
+        } else if (n < qn && (kb >> 1) < cols) {
+            const __half h = __float2half_rn(qp.qf32[(size_t)(q0 + n) * cols + (kb >> 1)]);
+            v = (unsigned char)((__half_as_ushort(h) >> ((kb & 1) * 8)) & 0xFF);
+        }
+        out[i] = v;
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+}  // namespace
+
+struct MmaState {
+    EncodeTiledFn encode = nullptr;
+    unsigned char* d_b = nullptr;     // operand B staging
+    size_t d_b_bytes = 0;
+    uint32_t* d_ready = nullptr;
+    bool attr_set[2] = {false, false};
+};
+
+static int mma_group_queries(const CandView& cv) { return cv.layout == MANTA_B200_LAYOUT_Q8_ROW_F32 ? kMmaCols / 2 : kMmaCols; }
+
+bool mma_supported(const CandView& cv, int nq) {
+    if (cv.layout != MANTA_B200_LAYOUT_Q8_ROW_F32 && cv.layout != MANTA_B200_LAYOUT_F16) return false;
+    if (nq < 8) return false;               // small batches stream faster on the GEMV kernel
+    if (cv.rows < kTileRows) return false;
+    if (((uintptr_t)cv.data & 15) || (cv.row_bytes & 15)) return false;
+    return true;
+}
+int mma_bucket_count(int sm_count) { return sm_count * 4 * kBucketSlots; }
+int mma_first_burst_rows(int) { return 0; }
+int mma_pool_cap(int k) {
+    int cap = 64 * k;
+    return cap < 16384 ? 16384 : cap;
+}
+
+void mma_state_destroy(MmaState* s) {
+    if (!s) return;
+    if (s->d_b) cudaFree(s->d_b);
+    if (s->d_ready) cudaFree(s->d_ready);
+    delete s;
+}
+
+static cudaError_t make_map(MmaState* st, CUtensorMap* map, const void* base, uint64_t inner_bytes, uint64_t rows,
+                            uint64_t stride_bytes, uint32_t box_rows, const char** why) {
+    cuuint64_t dims[2] = {inner_bytes, rows};
+    cuuint64_t strides[1] = {stride_bytes};
+    cuuint32_t box[2] = {(cuuint32_t)kChunkBytes, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = st->encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        *why = "cuTensorMapEncodeTiled failed";
+        return cudaErrorInvalidValue;
+    }
+    return cudaSuccess;
+}
+
+cudaError_t launch_mma_topk(cudaStream_t stream, int sm_count, MmaState** state, const MmaArgs& a, int* launches, const char** why) {
+    *launches = 0;
+    *why = nullptr;
+    if (!*state) {
+        MmaState* s = new MmaState();
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+        if (e != cudaSuccess || !fn || qres != cudaDriverEntryPointSuccess) {
+            delete s;
+            *why = "cuTensorMapEncodeTiled is not available";
+            return e != cudaSuccess ? e : cudaErrorNotSupported;
+        }
+        s->encode = (EncodeTiledFn)fn;
+        e = cudaMalloc(&s->d_ready, 256);
+        if (e != cudaSuccess) {
+            delete s;
+            *why = "cudaMalloc(ready)";
+            return e;
+        }
+        *state = s;
+    }
+    MmaState* st = *state;
+    const CandView& cv = a.cv;
+    const bool i8 = cv.layout == MANTA_B200_LAYOUT_Q8_ROW_F32;
+    const int group = mma_group_queries(cv);
+    const int kchunks = (cv.row_bytes + kChunkBytes - 1) / kChunkBytes;
+    const int kpad = kchunks * kChunkBytes;
+    const size_t b_bytes = (size_t)kMmaCols * kpad;
+    if (st->d_b_bytes < b_bytes) {
+        cudaError_t e = cudaStreamSynchronize(stream);
+        if (e != cudaSuccess) return e;
+        if (st->d_b) cudaFree(st->d_b);
+        st->d_b = nullptr;
+        st->d_b_bytes = 0;
+        e = cudaMalloc(&st->d_b, b_bytes);
+        if (e != cudaSuccess) {
+            *why = "cudaMalloc(operand B)";
+            return e;
+        }
+        st->d_b_bytes = b_bytes;
+    }
+    const int64_t nrows = a.row_end - a.row_begin;
+    const int n_tiles = (int)((nrows + kTileRows - 1) / kTileRows);
+    const int grid = sm_count < n_tiles ? sm_count : n_tiles;
+    const int filtered = (nrows > (int64_t)a.ws.cap) ? 1 : 0;
+    int observe = (a.k + grid * 4 - 1) / (grid * 4);
+    if (filtered && observe > kBucketSlots) {
+        *why = "k exceeds the bucket capacity of the tensor-core pass for this grid";
+        return cudaErrorNotSupported;
+    }
+
+    CUtensorMap map_a;
+    cudaError_t e = make_map(st, &map_a, cv.data, (uint64_t)cv.row_bytes, (uint64_t)cv.rows, (uint64_t)cv.row_bytes, kTileRows, why);
+    if (e != cudaSuccess) return e;
+
+    for (int q0 = 0; q0 < a.nq; q0 += group) {
+        const int qn = (a.nq - q0 < group) ? a.nq - q0 : group;
+        const int qpad = (qn + 15) / 16 * 16;
+        const int ncols = i8 ? 2 * qpad : qpad;
+        const int lo_off = qpad;
+        build_b_kernel<<<128, 256, 0, stream>>>(st->d_b, ncols, kpad, cv.layout, a.qp, q0, qn, lo_off, cv.cols);
+        count_launch();
+        ++*launches;
+        e = cudaGetLastError();
+        if (e != cudaSuccess) { *why = "operand B build launch"; return e; }
+        e = cudaMemsetAsync(st->d_ready, 0, 4, stream);
+        if (e != cudaSuccess) { *why = "cudaMemsetAsync(ready)"; return e; }
+        CUtensorMap map_b;
+        e = make_map(st, &map_b, st->d_b, (uint64_t)kpad, (uint64_t)ncols, (uint64_t)kpad, (uint32_t)ncols, why);
+        if (e != cudaSuccess) return e;
+
+        const size_t stage_bytes = (size_t)kTileRows * kChunkBytes + (size_t)ncols * kChunkBytes;
+        const size_t fixed = 1024 /*alignment slack*/ + 256 /*barriers*/ + sizeof(QueryHeader) * kMmaCols + 4 * kMmaCols +
+                             16 * kMmaCols + 16 * kMmaCols * kBucketSlots;
+        int stages = (int)((220 * 1024 - fixed) / stage_bytes);
+        if (stages > 8) stages = 8;
+        if (stages < 2) { *why = "not enough shared memory for two pipeline stages"; return cudaErrorInvalidValue; }
+        const size_t smem = fixed + (size_t)stages * stage_bytes;
+
+        KernelArgs ka;
+        ka.cv = cv;
+        ka.headers = a.qp.headers;
+        ka.ws = a.ws;
+        ka.ready = st->d_ready;
+        ka.q0 = q0;
+        ka.qn = qn;
+        ka.ncols = ncols;
+        ka.lo_off = lo_off;
+        ka.kchunks = kchunks;
+        ka.stages = stages;
+        ka.metric = a.metric;
+        ka.order = a.order;
+        ka.k = a.k;
+        ka.filtered = filtered;
+        ka.observe_tiles = observe;
+        ka.row_begin = a.row_begin;
+        ka.row_end = a.row_end;
+        if (i8) {
+            if (!st->attr_set[0]) {
+                e = cudaFuncSetAttribute(mma_scan_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024);
+                if (e != cudaSuccess) { *why = "cudaFuncSetAttribute"; return e; }
+                st->attr_set[0] = true;
+            }
+            mma_scan_kernel<true><<<grid, kMmaThreads, smem, stream>>>(map_a, map_b, ka);
+        } else {
+            if (!st->attr_set[1]) {
+                e = cudaFuncSetAttribute(mma_scan_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024);
+                if (e != cudaSuccess) { *why = "cudaFuncSetAttribute"; return e; }
+                st->attr_set[1] = true;
+            }
+            mma_scan_kernel<false><<<grid, kMmaThreads, smem, stream>>>(map_a, map_b, ka);
+        }
+        count_launch();
+        ++*launches;
+        e = cudaGetLastError();
+        if (e != cudaSuccess) { *why = "tensor-core scan launch"; return e; }
+    }
+    return cudaSuccess;
+}
 
 }  // namespace mb200

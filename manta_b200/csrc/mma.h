@@ -23,6 +23,8 @@ struct MmaArgs {
 bool mma_supported(const CandView& cv, int nq);
 int mma_bucket_count(int sm_count);
 int mma_first_burst_rows(int sm_count);
+// Pool capacity per query of a filtered tensor-core pass.
+int mma_pool_cap(int k);
 cudaError_t launch_mma_topk(cudaStream_t st, int sm_count, MmaState** state, const MmaArgs& a, int* launches,
                             const char** why);
 void mma_state_destroy(MmaState* s);
