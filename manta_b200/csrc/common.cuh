@@ -38,7 +38,7 @@ struct QueryHeader {
     float s_hi;   // scale of the high int8 plane (q8/q4 candidates)
     float s_lo;   // scale of the low int8 plane
     float qn;     // ||q|| (f32 of the f64 root)
-    float qn2;    // ||q||^2 (f32 of the f64 sum)
+    float qinv;   // 1/||q|| (f32 division), 0 for a zero query
     double qn2d;  // ||q||^2 in f64
     double qhat2; // ||s_hi*hi + s_lo*lo||^2 in f64: the squared norm of the query the int8 planes represent
 };
@@ -72,20 +72,30 @@ struct CandView {
 };
 
 // score epilogues -----------------------------------------------------------------------------------------
-// q8: t = s_hi*I_hi + s_lo*I_lo is q . codes (without the row scale).  Fixed operation order, every
-// operation correctly rounded, so a CPU model can reproduce the bits.
-__device__ __forceinline__ float q8_finish(int metric, int ih, int il, int nn, float sd, const QueryHeader& h) {
+// Cosine is finished as t * (qinv * rinv): qinv = 1/||q|| once per query, rinv = 1/||d|| once per row, so a score
+// costs multiplications only; either factor is 0 for a zero vector, which yields exactly 0 as the reference does.
+// Every operation below is a single correctly rounded IEEE operation in a fixed order, so a CPU model can
+// reproduce the bits.
+
+// q8 rows: 1/sqrt(sum code^2) (0 for an all-zero row); the row scale cancels out of the cosine.
+__device__ __forceinline__ float q8_row_inv_norm(int nn) {
+    return (nn > 0) ? __frcp_rn(__fsqrt_rn((float)nn)) : 0.0f;
+}
+// f16 / q4 rows: 1/sqrt(||d||^2) from the bind-time statistic.
+__device__ __forceinline__ float float_row_inv_norm(float dn2) {
+    return (dn2 > 0.0f) ? __frcp_rn(__fsqrt_rn(dn2)) : 0.0f;
+}
+
+// q8: t = s_hi*I_hi + s_lo*I_lo is q . codes (without the row scale).  rinv is used by cosine only, nn and sd by
+// l2 (sd also by dot).
+__device__ __forceinline__ float q8_finish(int metric, int ih, int il, int nn, float rinv, float sd, const QueryHeader& h) {
     float a = __fmul_rn((float)ih, h.s_hi);
     float t = __fmaf_rn((float)il, h.s_lo, a);
     float res;
     if (metric == MANTA_B200_METRIC_DOT) {
         res = __fmul_rn(t, sd);
     } else if (metric == MANTA_B200_METRIC_COSINE) {
-        if (nn == 0 || h.qn == 0.0f) {
-            res = 0.0f;
-        } else {
-            res = __fdiv_rn(t, __fmul_rn(h.qn, __fsqrt_rn((float)nn)));
-        }
+        res = __fmul_rn(t, __fmul_rn(h.qinv, rinv));
     } else {
         // ||qhat - d||^2 = ||qhat||^2 + ||d||^2 - 2 qhat.d, combined in f64 so that the cancellation near zero
         // distance costs nothing; qhat is the query the two planes represent (|qhat - q| <= s_lo/2 per element).
@@ -98,15 +108,15 @@ __device__ __forceinline__ float q8_finish(int metric, int ih, int il, int nn, f
     return res + 0.0f;  // -0 -> +0 so equal scores have equal bits
 }
 
-// float layouts (f16, q4): dotv = q . d, dn2 = ||d||^2 from the bind-time statistics, q2 = squared norm of the
-// query as the kernel sees it (f64).  The l2 combination runs in f64; dotv and dn2 carry f32 rounding.
-__device__ __forceinline__ float float_finish(int metric, float dotv, float dn2, const QueryHeader& h, double q2) {
+// float layouts (f16, q4): dotv = q . d, dn2 = ||d||^2 from the bind-time statistics (rinv its inverse root, used
+// by cosine only), q2 = squared norm of the query as the kernel sees it (f64).  The l2 combination runs in f64;
+// dotv and dn2 carry f32 rounding.
+__device__ __forceinline__ float float_finish(int metric, float dotv, float dn2, float rinv, const QueryHeader& h, double q2) {
     float res;
     if (metric == MANTA_B200_METRIC_DOT) {
         res = dotv;
     } else if (metric == MANTA_B200_METRIC_COSINE) {
-        float den = __fmul_rn(h.qn, __fsqrt_rn(dn2));
-        res = (den == 0.0f) ? 0.0f : __fdiv_rn(dotv, den);
+        res = __fmul_rn(dotv, __fmul_rn(h.qinv, rinv));
     } else {
         double x = __dadd_rn(__dadd_rn(q2, (double)dn2), -__dmul_rn(2.0, (double)dotv));
         res = __double2float_rn(__dsqrt_rn(fmax(x, 0.0)));

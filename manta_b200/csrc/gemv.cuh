@@ -348,6 +348,8 @@ __global__ void __launch_bounds__(kThreads, (QT == 1 && CPL <= 4) ? 2 : 1) gemv_
         const bool rv = leader && my_row < a.row_end;
         const int nn = (int)cur.stat;
         const float dn2 = __uint_as_float(cur.stat);
+        float rinv = 0.0f;
+        if (a.metric == MANTA_B200_METRIC_COSINE) rinv = kQ8 ? q8_row_inv_norm(nn) : float_row_inv_norm(dn2);
 #pragma unroll
         for (int q = 0; q < QT; ++q) {
             float score;
@@ -363,18 +365,18 @@ __global__ void __launch_bounds__(kThreads, (QT == 1 && CPL <= 4) ? 2 : 1) gemv_
                     }
                     continue;
                 }
-                score = q8_finish(a.metric, h, l, nn, cur.sd, hdr[q]);
+                score = q8_finish(a.metric, h, l, nn, rinv, cur.sd, hdr[q]);
             } else if constexpr (kQ4) {
                 const float th = reduce_scatter<LPR, U>(fa[q], gl);
                 const float tl = reduce_scatter<LPR, U>(fb[q], gl);
                 const float dotv = __fmaf_rn(tl, q4_sl[q], __fmul_rn(th, q4_sh[q]));
-                score = float_finish(a.metric, dotv, dn2, hdr[q], hdr[q].qhat2);
+                score = float_finish(a.metric, dotv, dn2, rinv, hdr[q], hdr[q].qhat2);
             } else {
                 const float dotv = reduce_scatter<LPR, U>(fa[q], gl);
                 if (a.metric == MANTA_B200_METRIC_L2_DISTANCE)
                     score = __fsqrt_rn(dotv) + 0.0f;  // dotv holds sum (q - d)^2 here
                 else
-                    score = float_finish(a.metric, dotv, dn2, hdr[q], hdr[q].qn2d);
+                    score = float_finish(a.metric, dotv, dn2, rinv, hdr[q], hdr[q].qn2d);
             }
             const bool mine = rv && q < a.qt;
             if (mode == kModeScores) {

@@ -179,7 +179,7 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     }
     for (int j = threadIdx.x; j < a.qn; j += blockDim.x) {
         hdr_s[j] = a.headers[a.q0 + j];
-        thr_s[j] = 0;
+        thr_s[j] = 1;
         for (int w = 0; w < 4; ++w) {
             bmax_s[j * 4 + w] = 0;
             for (int s = 0; s < kBucketSlots; ++s) pub_s[(j * 4 + w) * kBucketSlots + s] = 0;
@@ -259,53 +259,75 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                             t = ld_relaxed_u32(a.ws.thr + a.q0 + j);
                             if (t == 0) __nanosleep(64);
                         }
-                        thr_s[j] = t;
+                        thr_s[j] = max(t, 1u);
                     }
                     asm volatile("bar.sync 1, 128;" ::: "memory");
                 }
                 const int acc = it & 1;
-                if (!mbar_wait(&tfull[acc], (uint32_t)(it >> 1) & 1u, abort_s)) break;
-                tc_fence_after();
+                // row constants of this tile (issued before the wait so their latency hides behind it)
                 const int64_t row = a.row_begin + (int64_t)tile_of(it) * kTileRows + quad * 32 + lane;
                 const bool rv = row < a.row_end;
                 float sd = 0.0f;
                 uint32_t stat = 0;
                 if (rv && want_scale) sd = ((const float*)a.cv.scales)[row];
                 if (rv && want_stats) stat = ((const uint32_t*)a.cv.stats)[row];
+                float rinv = 0.0f;
+                if (a.metric == MANTA_B200_METRIC_COSINE) rinv = I8 ? q8_row_inv_norm((int)stat) : float_row_inv_norm(__uint_as_float(stat));
+                if (!mbar_wait(&tfull[acc], (uint32_t)(it >> 1) & 1u, abort_s)) break;
+                tc_fence_after();
                 const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)acc * kMmaCols;
+                const int32_t my_id = (int32_t)(a.cv.row_base + row);
                 for (int c0 = 0; c0 < a.qn; c0 += 16) {
                     uint32_t vh[16], vl[16];
                     tmem_ld16(t_row + c0, vh);
                     if constexpr (I8) tmem_ld16(t_row + a.lo_off + c0, vl);
                     tmem_ld_wait();
+                    // scores of 16 queries for this lane's row: independent arithmetic, no branches
+                    float g[16];
+                    uint32_t o[16];
 #pragma unroll
                     for (int jj = 0; jj < 16; ++jj) {
-                        const int j = c0 + jj;
-                        if (j >= a.qn) break;   // uniform across the warp
+                        const int j = min(c0 + jj, a.qn - 1);
                         float score;
                         if constexpr (I8)
-                            score = q8_finish(a.metric, (int)vh[jj], (int)vl[jj], (int)stat, sd, hdr_s[j]);
+                            score = q8_finish(a.metric, (int)vh[jj], (int)vl[jj], (int)stat, rinv, sd, hdr_s[j]);
                         else
-                            score = float_finish(a.metric, __uint_as_float(vh[jj]), __uint_as_float(stat), hdr_s[j], hdr_s[j].qn2d);
-                        const float g = score * sign + 0.0f;
-                        const uint32_t o = rv ? ord_from_float(g) : 0u;
+                            score = float_finish(a.metric, __uint_as_float(vh[jj]), __uint_as_float(stat), rinv, hdr_s[j], hdr_s[j].qn2d);
+                        g[jj] = score * sign + 0.0f;
+                        o[jj] = (rv && c0 + jj < a.qn) ? ord_from_float(g[jj]) : 0u;   // 0 never passes (bounds are >= 1)
+                    }
+                    // filter: one vote per query; everything behind a non-empty vote is the rare path
+                    uint32_t votes[16];
+                    uint32_t any = 0;
+#pragma unroll
+                    for (int jj = 0; jj < 16; ++jj) {
+                        const int j = min(c0 + jj, a.qn - 1);
+                        votes[jj] = __ballot_sync(0xffffffffu, o[jj] >= thr_s[j]);
+                        any |= votes[jj];
+                    }
+                    if (any == 0) continue;
+#pragma unroll
+                    for (int jj = 0; jj < 16; ++jj) {
+                        const uint32_t ballot = votes[jj];
+                        if (ballot == 0) continue;
+                        const int j = c0 + jj;
+                        const bool pass = (ballot >> lane) & 1u;
                         if (!replay) {
-                            const uint32_t wmax = __reduce_max_sync(0xffffffffu, o);
+                            // only scores at or above the current bound can raise it, so the bucket maxima are
+                            // maintained from the passing rows (all valid rows while no bound exists)
+                            const uint32_t wmax = __reduce_max_sync(0xffffffffu, pass ? o[jj] : 0u);
                             if (lane == 0 && wmax > bmax_s[j * 4 + ew]) bmax_s[j * 4 + ew] = wmax;
                         }
-                        const bool pass = rv && !observe && (!a.filtered || o >= thr_s[j]);
-                        const uint32_t ballot = __ballot_sync(0xffffffffu, pass);
-                        if (ballot != 0) {
-                            uint32_t pos0 = 0;
-                            if (lane == 0) pos0 = atomicAdd(a.ws.count + a.q0 + j, (uint32_t)__popc(ballot));
-                            pos0 = __shfl_sync(0xffffffffu, pos0, 0);
-                            if (pass) {
-                                const uint32_t pos = pos0 + __popc(ballot & ((1u << lane) - 1u));
-                                if (pos < a.ws.cap)
-                                    a.ws.pool[(size_t)(a.q0 + j) * a.ws.cap + pos] = make_key(g, (int32_t)(a.cv.row_base + row));
-                                else
-                                    a.ws.flags[kFlagOverflow] = 1u;
-                            }
+                        if (observe) continue;
+                        uint32_t pos0 = 0;
+                        if (lane == 0) pos0 = atomicAdd(a.ws.count + a.q0 + j, (uint32_t)__popc(ballot));
+                        pos0 = __shfl_sync(0xffffffffu, pos0, 0);
+                        if (pass) {
+                            const uint32_t pos = pos0 + __popc(ballot & ((1u << lane) - 1u));
+                            if (pos < a.ws.cap)
+                                a.ws.pool[(size_t)(a.q0 + j) * a.ws.cap + pos] = make_key(g[jj], my_id);
+                            else
+                                a.ws.flags[kFlagOverflow] = 1u;
                         }
                     }
                 }
@@ -333,7 +355,7 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         asm volatile("bar.sync 1, 128;" ::: "memory");
                         if (et == 0) atomicAdd(a.ready, 1u);
                     } else if (it + 1 > n_obs) {
-                        for (int j = et; j < a.qn; j += 128) thr_s[j] = ld_relaxed_u32(a.ws.thr + a.q0 + j);
+                        for (int j = et; j < a.qn; j += 128) thr_s[j] = max(ld_relaxed_u32(a.ws.thr + a.q0 + j), 1u);
                     }
                     asm volatile("bar.sync 1, 128;" ::: "memory");
                 }

@@ -45,8 +45,8 @@ __global__ void __launch_bounds__(256) query_prep_kernel(const __half* __restric
         for (int off = 16; off > 0; off >>= 1) part = __dadd_rn(part, __shfl_xor_sync(0xffffffffu, part, off));
         if (tid == 0) {
             QueryHeader h;
-            h.qn2 = __double2float_rn(part);
             h.qn = __double2float_rn(__dsqrt_rn(part));
+            h.qinv = (h.qn > 0.0f) ? __fdiv_rn(1.0f, h.qn) : 0.0f;
             h.qn2d = part;
             h.qhat2 = part;
             float sh = 0.0f, sl = 0.0f;

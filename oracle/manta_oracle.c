@@ -544,14 +544,12 @@ int mo_q8_model_scores(const float* query, const int8_t* codes, const float* sca
             volatile float p = t * sd;
             res = p;
         } else if (metric == 1) {
-            if (nn == 0 || qn == 0.0f) {
-                res = 0.0f;
-            } else {
-                volatile float rn = sqrtf((float)nn);
-                volatile float den = qn * rn;
-                volatile float qv = t / den;
-                res = qv;
-            }
+            volatile float qinv = (qn > 0.0f) ? 1.0f / qn : 0.0f;
+            volatile float root = sqrtf((float)nn);
+            volatile float rinv = (nn > 0) ? 1.0f / root : 0.0f;
+            volatile float w = qinv * rinv;
+            volatile float qv = t * w;
+            res = qv + 0.0f;
         } else {
             double td = (double)ih * (double)s_hi + (double)il * (double)s_lo;
             double dotd = td * (double)sd;
@@ -560,7 +558,7 @@ int mo_q8_model_scores(const float* query, const int8_t* codes, const float* sca
             if (!(x > 0.0)) x = 0.0;
             res = (float)sqrt(x);
         }
-        out[r] = res;
+        out[r] = res + 0.0f; /* -0 -> +0, as the device does */
     }
     free(hi);
     free(lo);
