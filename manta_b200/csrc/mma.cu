@@ -4,13 +4,16 @@
 // planes of every query; f32 for f16), and four epilogue warps read the accumulators back (tcgen05.ld), finish
 // the scores with the same epilogue functions as the streaming kernel and filter them into the top-k pools.
 //
-// Warp roles (7 warps): 0 = TMA producer, 1 = MMA issuer (owns the tensor-memory allocation), 2..5 = epilogue
-// (one per 32-lane quadrant of tensor memory), 6 = threshold refresher.
+// Warp roles (11 warps): 0 = TMA producer, 1 = MMA issuer (owns the tensor-memory allocation), 2..9 = epilogue
+// (two per 32-lane quadrant of tensor memory, taking alternate 16-query chunks), 10 = threshold refresher.
 //
 // Every wait in this file is bounded: a wait that runs out sets the abort flag of the CTA and the time-out flag
 // of the pass, every role leaves its loop, tensor memory is released and the kernel returns; the host then
 // reports the failure (and the streaming kernel can redo the pass).
 #include <cuda.h>
+
+#include <cstdio>
+#include <cstdlib>
 
 #include "mma.h"
 
@@ -20,10 +23,12 @@ namespace {
 
 constexpr int kTileRows = 128;
 constexpr int kChunkBytes = 128;      // K extent of one pipeline stage, in bytes (one 128-byte swizzle span)
-constexpr int kMmaThreads = 224;
+constexpr int kEpiWarps = 8;          // two per tensor-memory quadrant, taking alternate 16-query chunks
+constexpr int kMmaThreads = 32 * (2 + kEpiWarps + 1);
 constexpr int kMmaCols = 256;         // N of one MMA
 constexpr int kBucketSlots = 4;       // bucket slots per epilogue warp (tiles rotate through them)
 constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr int kRefStage = 2560;       // bucket maxima per query the refresher can hold (80 registers per lane)
 
 // ---- PTX wrappers -------------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -131,7 +136,27 @@ struct KernelArgs {
     int observe_tiles;            // tiles per CTA scored before the first bound exists (replayed at the end)
     int64_t row_begin;
     int64_t row_end;
+    unsigned long long* dbg;      // debugging: cycle counts of one epilogue warp (null in normal use)
 };
+
+// Scores of 16 consecutive queries for one candidate row (one lane).  METRIC is a compile-time constant so that
+// the sixteen evaluations are one basic block the compiler can interleave.
+template <bool I8, int METRIC>
+__device__ __forceinline__ void score16(const uint32_t (&vh)[16], const uint32_t (&vl)[16], uint32_t stat, float rinv, float sd,
+                                        const QueryHeader* hdr_s, int c0, int qn, bool rv, float sign, float (&g)[16],
+                                        uint32_t (&o)[16]) {
+#pragma unroll
+    for (int jj = 0; jj < 16; ++jj) {
+        const int j = min(c0 + jj, qn - 1);
+        float score;
+        if constexpr (I8)
+            score = q8_finish(METRIC, (int)vh[jj], (int)vl[jj], (int)stat, rinv, sd, hdr_s[j]);
+        else
+            score = float_finish(METRIC, __uint_as_float(vh[jj]), __uint_as_float(stat), rinv, hdr_s[j], hdr_s[j].qn2d);
+        g[jj] = score * sign + 0.0f;
+        o[jj] = (rv && c0 + jj < qn) ? ord_from_float(g[jj]) : 0u;   // 0 never passes (bounds are >= 1)
+    }
+}
 
 template <bool I8>
 __global__ void __launch_bounds__(kMmaThreads, 1)
@@ -150,7 +175,8 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     uint64_t* tempty = tfull + 2;
     uint32_t* tmem_slot = (uint32_t*)(tempty + 2);
     volatile uint32_t* abort_s = tmem_slot + 1;
-    volatile uint32_t* done_s = tmem_slot + 2;
+    volatile uint32_t* done_s = tmem_slot + 2;       // epilogue warps that have finished
+    volatile uint32_t* thr_ready_s = tmem_slot + 3;  // set by the refresher once every query has a bound
     QueryHeader* hdr_s = (QueryHeader*)(p + 256);
     uint32_t* thr_s = (uint32_t*)(hdr_s + kMmaCols);
     uint32_t* bmax_s = thr_s + kMmaCols;                 // [qn][4]: maxima of the current tile per epilogue warp
@@ -171,10 +197,11 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&tfull[b], 1);
-            mbar_init(&tempty[b], 4);
+            mbar_init(&tempty[b], kEpiWarps);
         }
         *abort_s = 0;
         *done_s = 0;
+        *thr_ready_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     for (int j = threadIdx.x; j < a.qn; j += blockDim.x) {
@@ -240,29 +267,28 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     tc_commit(&tfull[acc]);     // accumulator complete
                 }
             }
-        } else if (warp < 6) {
+        } else if (warp < 2 + kEpiWarps) {
             // ---------------- epilogue ----------------
+            // The epilogue warps never synchronise with each other: each reads one quadrant of tensor memory for
+            // its half of the query chunks, owns the bucket maxima of (quadrant, those queries), and arrives on the
+            // accumulator's "empty" barrier by itself.
             const int quad = warp & 3;              // tensor-memory lanes 32*quad .. 32*quad+31
-            const int ew = warp - 2;                // bucket owner index 0..3
-            const int et = threadIdx.x - 64;        // 0..127 among epilogue threads
+            const int ew = quad;                    // bucket owner index 0..3 (rows of a quadrant are one bucket)
+            const int half = (warp - 2) >> 2;       // which of the alternating 16-query chunks this warp takes
             const float sign = (a.order == MANTA_B200_ORDER_SMALLEST) ? -1.0f : 1.0f;
             const bool want_scale = I8 && a.metric != MANTA_B200_METRIC_COSINE;
             const bool want_stats = a.metric != MANTA_B200_METRIC_DOT;
+            unsigned long long c_wait = 0, c_ld = 0, c_math = 0, c_slow = 0, c_house = 0, n_slow = 0, c_thr = 0;
+            const bool timing = a.dbg != nullptr && cta == 0 && warp == 4;
             for (int it = 0; it < n_iters; ++it) {
+                long long t0 = timing ? clock64() : 0;
                 const bool observe = it < n_obs;            // score and record maxima only
                 const bool replay = it >= n_my;             // append only
                 if (a.filtered && it == n_obs && n_obs > 0) {
-                    // the first bounds must exist before anything is appended (bounded wait)
-                    for (int j = et; j < a.qn; j += 128) {
-                        uint32_t t = 0;
-                        for (uint32_t spin = 0; spin < 4000u && t == 0 && !*abort_s; ++spin) {
-                            t = ld_relaxed_u32(a.ws.thr + a.q0 + j);
-                            if (t == 0) __nanosleep(64);
-                        }
-                        thr_s[j] = max(t, 1u);
-                    }
-                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    // the first bounds must exist before anything is appended (bounded wait on the refresher)
+                    for (uint32_t spin = 0; spin < 40000u && !*thr_ready_s && !*abort_s; ++spin) __nanosleep(100);
                 }
+                if (timing) { long long t1 = clock64(); c_thr += t1 - t0; t0 = t1; }
                 const int acc = it & 1;
                 // row constants of this tile (issued before the wait so their latency hides behind it)
                 const int64_t row = a.row_begin + (int64_t)tile_of(it) * kTileRows + quad * 32 + lane;
@@ -275,26 +301,33 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 if (a.metric == MANTA_B200_METRIC_COSINE) rinv = I8 ? q8_row_inv_norm((int)stat) : float_row_inv_norm(__uint_as_float(stat));
                 if (!mbar_wait(&tfull[acc], (uint32_t)(it >> 1) & 1u, abort_s)) break;
                 tc_fence_after();
+                if (timing) { long long t1 = clock64(); c_wait += t1 - t0; t0 = t1; }
                 const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)acc * kMmaCols;
                 const int32_t my_id = (int32_t)(a.cv.row_base + row);
-                for (int c0 = 0; c0 < a.qn; c0 += 16) {
+                for (int c0 = half * 16; c0 < a.qn; c0 += 32) {
                     uint32_t vh[16], vl[16];
                     tmem_ld16(t_row + c0, vh);
-                    if constexpr (I8) tmem_ld16(t_row + a.lo_off + c0, vl);
+                    if constexpr (I8) {
+                        tmem_ld16(t_row + a.lo_off + c0, vl);
+                    } else {
+#pragma unroll
+                        for (int jj = 0; jj < 16; ++jj) vl[jj] = 0;
+                    }
                     tmem_ld_wait();
-                    // scores of 16 queries for this lane's row: independent arithmetic, no branches
+                    if (timing) { long long t1 = clock64(); c_ld += t1 - t0; t0 = t1; }
+                    // scores of 16 queries for this lane's row: straight-line, independent arithmetic
                     float g[16];
                     uint32_t o[16];
-#pragma unroll
-                    for (int jj = 0; jj < 16; ++jj) {
-                        const int j = min(c0 + jj, a.qn - 1);
-                        float score;
-                        if constexpr (I8)
-                            score = q8_finish(a.metric, (int)vh[jj], (int)vl[jj], (int)stat, rinv, sd, hdr_s[j]);
-                        else
-                            score = float_finish(a.metric, __uint_as_float(vh[jj]), __uint_as_float(stat), rinv, hdr_s[j], hdr_s[j].qn2d);
-                        g[jj] = score * sign + 0.0f;
-                        o[jj] = (rv && c0 + jj < a.qn) ? ord_from_float(g[jj]) : 0u;   // 0 never passes (bounds are >= 1)
+                    switch (a.metric) {
+                        case MANTA_B200_METRIC_DOT:
+                            score16<I8, MANTA_B200_METRIC_DOT>(vh, vl, stat, rinv, sd, hdr_s, c0, a.qn, rv, sign, g, o);
+                            break;
+                        case MANTA_B200_METRIC_COSINE:
+                            score16<I8, MANTA_B200_METRIC_COSINE>(vh, vl, stat, rinv, sd, hdr_s, c0, a.qn, rv, sign, g, o);
+                            break;
+                        default:
+                            score16<I8, MANTA_B200_METRIC_L2_DISTANCE>(vh, vl, stat, rinv, sd, hdr_s, c0, a.qn, rv, sign, g, o);
+                            break;
                     }
                     // filter: one vote per query; everything behind a non-empty vote is the rare path
                     uint32_t votes[16];
@@ -305,7 +338,9 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         votes[jj] = __ballot_sync(0xffffffffu, o[jj] >= thr_s[j]);
                         any |= votes[jj];
                     }
+                    if (timing) { long long t1 = clock64(); c_math += t1 - t0; t0 = t1; }
                     if (any == 0) continue;
+                    n_slow++;
 #pragma unroll
                     for (int jj = 0; jj < 16; ++jj) {
                         const uint32_t ballot = votes[jj];
@@ -330,62 +365,82 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                                 a.ws.flags[kFlagOverflow] = 1u;
                         }
                     }
+                    if (timing) { long long t1 = clock64(); c_slow += t1 - t0; t0 = t1; }
                 }
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&tempty[acc]);
-                // ---- per-tile housekeeping: publish the tile's maxima, reload the bounds
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (a.filtered) {
-                    if (!replay) {
-                        const int slot = it % kBucketSlots;
-                        for (int i = et; i < a.qn * 4; i += 128) {
-                            const uint32_t v = bmax_s[i];
-                            bmax_s[i] = 0;
-                            if (v > pub_s[i * kBucketSlots + slot]) {
-                                pub_s[i * kBucketSlots + slot] = v;
-                                const int j = i >> 2, w = i & 3;
-                                st_relaxed_u32(a.ws.bucket + (size_t)(a.q0 + j) * a.ws.nb + ((size_t)(cta * 4 + w) * kBucketSlots + slot), v);
-                            }
+                // ---- publish this warp's maxima of the tile (bucket slot it % kBucketSlots)
+                if (a.filtered && !replay) {
+                    const int slot = it % kBucketSlots;
+                    for (int j = lane; j < a.qn; j += 32) {
+                        if (((j >> 4) & 1) != half) continue;   // the other warp of the quadrant owns this query
+                        const int i = j * 4 + ew;
+                        const uint32_t v = bmax_s[i];
+                        bmax_s[i] = 0;
+                        if (v > pub_s[i * kBucketSlots + slot]) {
+                            pub_s[i * kBucketSlots + slot] = v;
+                            st_relaxed_u32(a.ws.bucket + (size_t)(a.q0 + j) * a.ws.nb + ((size_t)(cta * 4 + ew) * kBucketSlots + slot), v);
                         }
                     }
+                    __syncwarp();
                     if (it + 1 == n_obs) {
-                        // this CTA's observed tiles are all published
+                        // this warp's observed tiles are all published
                         __threadfence();
-                        asm volatile("bar.sync 1, 128;" ::: "memory");
-                        if (et == 0) atomicAdd(a.ready, 1u);
-                    } else if (it + 1 > n_obs) {
-                        for (int j = et; j < a.qn; j += 128) thr_s[j] = max(ld_relaxed_u32(a.ws.thr + a.q0 + j), 1u);
+                        __syncwarp();
+                        if (lane == 0) atomicAdd(a.ready, 1u);
                     }
-                    asm volatile("bar.sync 1, 128;" ::: "memory");
                 }
+                if (timing) { long long t1 = clock64(); c_house += t1 - t0; t0 = t1; }
             }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (et == 0) *done_s = 1u;
+            if (timing && lane == 0) {
+                a.dbg[0] = c_thr; a.dbg[1] = c_wait; a.dbg[2] = c_ld; a.dbg[3] = c_math; a.dbg[4] = c_slow; a.dbg[5] = c_house;
+                a.dbg[6] = n_slow; a.dbg[7] = (unsigned long long)n_iters;
+            }
+            __syncwarp();
+            if (lane == 0) atomicAdd((uint32_t*)done_s, 1u);
         } else if (a.filtered) {
             // ---------------- threshold refresher ----------------
-            // Waits until every active CTA has published its observed tiles, then keeps recomputing, for the
-            // queries this CTA is responsible for in each round, the k-th largest bucket maximum (top 20 bits).
+            // Waits until every epilogue warp of every active CTA has published its observed tiles, then keeps
+            // recomputing, for one query per round, the k-th largest bucket maximum (top 20 bits; rounding a bound
+            // down keeps it valid) and refreshing this CTA's copy of all bounds.
             uint32_t seen = 0;
-            for (uint32_t spin = 0; spin < 100000u && seen < (uint32_t)active_ctas && !*abort_s && !*done_s; ++spin) {
+            const uint32_t want = (uint32_t)active_ctas * (uint32_t)kEpiWarps;
+            for (uint32_t spin = 0; spin < 100000u && seen < want && !*abort_s && *done_s < (uint32_t)kEpiWarps; ++spin) {
                 seen = ld_relaxed_u32(a.ready);
-                if (seen < (uint32_t)active_ctas) __nanosleep(64);
+                if (seen < want) __nanosleep(64);
             }
-            const uint32_t nb = a.ws.nb;
-            for (uint32_t round = 0; !*done_s && !*abort_s; ++round) {
+            const uint32_t nb = min(a.ws.nb, (uint32_t)kRefStage);
+            for (uint32_t round = 0; *done_s < (uint32_t)kEpiWarps && !*abort_s; ++round) {
                 const int j = (int)(((uint64_t)cta + (uint64_t)round * grid) % (uint64_t)a.qn);
-                const uint32_t* b = a.ws.bucket + (size_t)(a.q0 + j) * nb;
+                const uint32_t* b = a.ws.bucket + (size_t)(a.q0 + j) * a.ws.nb;
+                // the bucket maxima of the query live in registers for the twenty counting passes
+                uint32_t v[kRefStage / 32];
+#pragma unroll
+                for (int i = 0; i < kRefStage / 32; ++i) {
+                    const uint32_t idx = (uint32_t)i * 32u + lane;
+                    v[i] = (idx < nb) ? __ldcg(b + idx) : 0u;
+                }
                 uint32_t t = 0;
                 for (int bit = 31; bit >= 12; --bit) {
                     const uint32_t cand = t | (1u << bit);
                     uint32_t cnt = 0;
-                    for (uint32_t i = lane; i < nb; i += 32) cnt += (__ldcg(b + i) >= cand) ? 1u : 0u;
+#pragma unroll
+                    for (int i = 0; i < kRefStage / 32; ++i) cnt += (v[i] >= cand) ? 1u : 0u;
                     cnt = __reduce_add_sync(0xffffffffu, cnt);
                     if (cnt >= (uint32_t)a.k) t = cand;
                 }
                 if (lane == 0 && t != 0) atomicMax(a.ws.thr + a.q0 + j, t);
                 __syncwarp();
-                if (round > (uint32_t)(2 * a.qn) ) __nanosleep(2000);   // steady state: refresh at a relaxed pace
+                bool allset = true;
+                for (int jj = lane; jj < a.qn; jj += 32) {
+                    const uint32_t v = ld_relaxed_u32(a.ws.thr + a.q0 + jj);
+                    thr_s[jj] = max(v, 1u);
+                    allset = allset && (v != 0u);
+                }
+                allset = __all_sync(0xffffffffu, allset);
+                if (allset && lane == 0) *thr_ready_s = 1u;
+                if (round > (uint32_t)(4 * a.qn)) __nanosleep(1000);   // steady state: refresh at a relaxed pace
             }
         }
     }
@@ -432,6 +487,7 @@ struct MmaState {
     unsigned char* d_b = nullptr;     // operand B staging
     size_t d_b_bytes = 0;
     uint32_t* d_ready = nullptr;
+    unsigned long long* d_dbg = nullptr;
     bool attr_set[2] = {false, false};
 };
 
@@ -455,6 +511,7 @@ void mma_state_destroy(MmaState* s) {
     if (!s) return;
     if (s->d_b) cudaFree(s->d_b);
     if (s->d_ready) cudaFree(s->d_ready);
+    if (s->d_dbg) cudaFree(s->d_dbg);
     delete s;
 }
 
@@ -572,6 +629,13 @@ cudaError_t launch_mma_topk(cudaStream_t stream, int sm_count, MmaState** state,
         ka.observe_tiles = observe;
         ka.row_begin = a.row_begin;
         ka.row_end = a.row_end;
+        ka.dbg = nullptr;
+        static const bool timing = getenv("MANTA_B200_MMA_TIMING") != nullptr;  // debugging switch
+        if (timing) {
+            if (!st->d_dbg) cudaMalloc(&st->d_dbg, 64);
+            cudaMemsetAsync(st->d_dbg, 0, 64, stream);
+            ka.dbg = st->d_dbg;
+        }
         if (i8) {
             if (!st->attr_set[0]) {
                 e = cudaFuncSetAttribute(mma_scan_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024);
@@ -591,6 +655,13 @@ cudaError_t launch_mma_topk(cudaStream_t stream, int sm_count, MmaState** state,
         ++*launches;
         e = cudaGetLastError();
         if (e != cudaSuccess) { *why = "tensor-core scan launch"; return e; }
+        if (timing) {
+            unsigned long long h[8];
+            cudaStreamSynchronize(stream);
+            cudaMemcpy(h, st->d_dbg, 64, cudaMemcpyDeviceToHost);
+            fprintf(stderr, "[mma timing, CTA 0 warp 4, cycles] thr_wait %llu tfull_wait %llu tmem_ld %llu math %llu slow %llu house %llu | slow chunks %llu iters %llu\n",
+                    h[0], h[1], h[2], h[3], h[4], h[5], h[6], h[7]);
+        }
     }
     return cudaSuccess;
 }
