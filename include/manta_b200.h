@@ -165,11 +165,14 @@ int manta_b200_score_topk_static(MantaB200Runtime* rt, const MantaB200Candidates
                                  const void* d_queries, int nq, int k, int32_t* d_out_ids, float* d_out_scores,
                                  int sync, char** err);
 
-/* Merges `lists` per-shard results (device, each [nq, k] ids + scores, concatenated list-major) into the
- * global best k per query with the same ordering rule.  Used after the shards' lists are gathered. */
+/* Merges `lists` per-shard results (device memory) into the global best k per query with the same ordering
+ * rule.  List l holds ids at d_ids + l*list_stride and scores at d_scores + l*list_stride, each [nq, k];
+ * list_stride is in 4-byte elements and 0 means nq*k (lists back to back).  A stride lets one all-gather carry
+ * both arrays: every shard fills [2, nq, k] (ids, then scores) and the gathered [lists, 2, nq, k] buffer is merged
+ * with d_scores = d_ids + nq*k and list_stride = 2*nq*k.  Used after the shards' lists are gathered. */
 int manta_b200_topk_merge_device(MantaB200Runtime* rt, int order, const int32_t* d_ids, const float* d_scores,
-                                 int lists, int nq, int k, int32_t* d_out_ids, float* d_out_scores, int sync,
-                                 char** err);
+                                 int lists, int64_t list_stride, int nq, int k, int32_t* d_out_ids,
+                                 float* d_out_scores, int sync, char** err);
 
 /* gatherTensor on a rank-2 table (tensor_ops.go:794-827) for the bound set: de-quantised rows
  * out[i, :] = value(ids[i] - row_base, :) as f32 (the reference keeps them as float32 labelled q4).

@@ -792,15 +792,17 @@ int manta_b200_q8_accumulators(MantaB200Runtime* rt, const MantaB200Candidates* 
 }
 
 int manta_b200_topk_merge_device(MantaB200Runtime* rt, int order, const int32_t* d_ids, const float* d_scores,
-                                 int lists, int nq, int k, int32_t* d_out_ids, float* d_out_scores, int sync,
-                                 char** err) {
+                                 int lists, int64_t list_stride, int nq, int k, int32_t* d_out_ids,
+                                 float* d_out_scores, int sync, char** err) {
     if (!rt || !d_ids || !d_scores || !d_out_ids || !d_out_scores) return fail(err, "topk_merge: NULL argument");
     if (lists <= 0 || nq <= 0 || k <= 0 || k > kMaxK) return fail(err, "topk_merge: bad shape (lists %d, nq %d, k %d)", lists, nq, k);
+    if (list_stride == 0) list_stride = (int64_t)nq * k;
+    if (list_stride < (int64_t)nq * k) return fail(err, "topk_merge: list stride %lld is smaller than one list", (long long)list_stride);
     std::lock_guard<std::mutex> lk(rt->mu);
     CU_TRY(cudaSetDevice(rt->device));
     SelectWs ws;
     if (ensure_select_ws(rt, nq, (uint32_t)(lists * k), 1, &ws, err)) return 1;
-    cudaError_t e = launch_lists_to_pool(rt->stream, d_ids, d_scores, lists, nq, k, order, ws);
+    cudaError_t e = launch_lists_to_pool(rt->stream, d_ids, d_scores, lists, list_stride, nq, k, order, ws);
     rt->stats.kernel_launches++;
     if (e != cudaSuccess) return fail_cuda(err, "launch lists_to_pool", e);
     SelectArgs sa{};

@@ -97,7 +97,7 @@ struct SelectArgs {
 cudaError_t launch_select(cudaStream_t st, const SelectArgs& a);
 
 // Builds keys from gathered per-shard lists: pool[q][l*k + i] = key(ids[l][q][i], scores[l][q][i]).
-cudaError_t launch_lists_to_pool(cudaStream_t st, const int32_t* d_ids, const float* d_scores, int lists, int nq,
-                                 int k, int order, const SelectWs& ws);
+cudaError_t launch_lists_to_pool(cudaStream_t st, const int32_t* d_ids, const float* d_scores, int lists,
+                                 int64_t list_stride, int nq, int k, int order, const SelectWs& ws);
 
 }  // namespace mb200

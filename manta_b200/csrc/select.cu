@@ -127,13 +127,13 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectArgs a)
 }
 
 __global__ void lists_to_pool_kernel(const int32_t* __restrict__ ids, const float* __restrict__ scores, int lists,
-                                     int nq, int k, int order, SelectWs ws) {
+                                     int64_t list_stride, int nq, int k, int order, SelectWs ws) {
     const int q = blockIdx.x;
     const float sign = (order == MANTA_B200_ORDER_SMALLEST) ? -1.0f : 1.0f;
     const int per = lists * k;
     for (int i = threadIdx.x; i < per; i += blockDim.x) {
         const int l = i / k, j = i % k;
-        const size_t src = ((size_t)l * nq + q) * k + j;
+        const size_t src = (size_t)l * list_stride + (size_t)q * k + j;
         const int32_t id = ids[src];
         // entries a shard could not fill (id < 0) rank below everything
         ws.pool[(size_t)q * ws.cap + i] = (id < 0) ? 0ull : make_key(scores[src] * sign + 0.0f, id);
@@ -153,9 +153,9 @@ cudaError_t launch_select(cudaStream_t st, const SelectArgs& a) {
     return cudaGetLastError();
 }
 
-cudaError_t launch_lists_to_pool(cudaStream_t st, const int32_t* d_ids, const float* d_scores, int lists, int nq,
-                                 int k, int order, const SelectWs& ws) {
-    lists_to_pool_kernel<<<nq, 256, 0, st>>>(d_ids, d_scores, lists, nq, k, order, ws);
+cudaError_t launch_lists_to_pool(cudaStream_t st, const int32_t* d_ids, const float* d_scores, int lists,
+                                 int64_t list_stride, int nq, int k, int order, const SelectWs& ws) {
+    lists_to_pool_kernel<<<nq, 256, 0, st>>>(d_ids, d_scores, lists, list_stride, nq, k, order, ws);
     count_launch();
     return cudaGetLastError();
 }

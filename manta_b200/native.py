@@ -87,7 +87,7 @@ def load() -> ctypes.CDLL:
                                          c_void_p, c_int, E],
         "manta_b200_score_topk_static": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p,
                                          c_void_p, c_int, E],
-        "manta_b200_topk_merge_device": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
+        "manta_b200_topk_merge_device": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_void_p,
                                          c_void_p, c_int, E],
         "manta_b200_gather_rows": [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, E],
         "manta_b200_q8_accumulators": [c_void_p, c_void_p, c_void_p, c_void_p, E],
@@ -295,9 +295,9 @@ class Runtime:
              _ptr(d_scores), c_int(1 if sync else 0))
 
     def topk_merge_device(self, d_ids, d_scores, lists: int, nq: int, k: int, d_out_ids, d_out_scores,
-                          smallest: bool = False, sync: bool = False):
+                          smallest: bool = False, sync: bool = False, list_stride: int = 0):
         call("manta_b200_topk_merge_device", self.handle, c_int(ORDER_SMALLEST if smallest else ORDER_LARGEST), _ptr(d_ids),
-             _ptr(d_scores), c_int(lists), c_int(nq), c_int(k), _ptr(d_out_ids), _ptr(d_out_scores),
+             _ptr(d_scores), c_int(lists), c_int64(list_stride), c_int(nq), c_int(k), _ptr(d_out_ids), _ptr(d_out_scores),
              c_int(1 if sync else 0))
 
     def gather_rows(self, cands: Candidates, ids) -> np.ndarray:

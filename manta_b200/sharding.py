@@ -1,0 +1,37 @@
+"""Row sharding of a candidate set over ranks (one process per GPU) and the exchange of per-shard top-k lists.
+
+Rank r owns the contiguous rows [r*N/G, (r+1)*N/G) and binds them with ``row_base`` = its first row, so the ids a
+shard returns are global.  After the local fused pass every rank holds ``pair`` = int32 [2, nq, k] (ids, then the
+f32 scores bit-cast); one all-gather produces [G, 2, nq, k] on every rank, which
+``manta_b200_topk_merge_device`` reduces with ``list_stride = 2*nq*k``.
+"""
+from __future__ import annotations
+
+import torch
+
+
+def shard_bounds(rows: int, rank: int, world: int):
+    """First and one-past-last global row of a rank's shard."""
+    return rank * rows // world, (rank + 1) * rows // world
+
+
+def new_pair(nq: int, k: int, device):
+    """Buffer a rank's fused pass writes into: (pair, ids view, scores view)."""
+    pair = torch.empty((2, nq, k), dtype=torch.int32, device=device)
+    return pair, pair[0], pair[1].view(torch.float32)
+
+
+def gather_pairs(pair: torch.Tensor, gathered: torch.Tensor, dist) -> torch.Tensor:
+    """All-gathers every rank's pair into ``gathered`` [G, 2, nq, k] (same on all ranks)."""
+    if dist.get_backend() == "nccl":
+        dist.all_gather_into_tensor(gathered, pair)
+    else:  # gloo (CPU tests) has no all_gather_into_tensor
+        parts = [torch.empty_like(pair) for _ in range(dist.get_world_size())]
+        dist.all_gather(parts, pair)
+        gathered.copy_(torch.stack(parts))
+    return gathered
+
+
+def merge_args(gathered: torch.Tensor, nq: int, k: int):
+    """(ids pointer tensor, scores pointer tensor, lists, list_stride) for manta_b200_topk_merge_device."""
+    return gathered[0, 0], gathered[0, 1], gathered.shape[0], 2 * nq * k
