@@ -68,6 +68,10 @@ WORKLOADS = {
     "c3q256": Workload("c3q256", "q8", "cosine", 10_000_000, 768, 256, 10, note="q8 cosine at scale, query batch 256"),
     "c4": Workload("c4", "q4", "l2_distance", 12_500_000, 256, 1, 1000, smallest=True, normalise=False,
                    note="one GPU's share (1/8) of the 100M x 256 q4 set"),
+    "c4x8": Workload("c4x8", "q4", "l2_distance", 100_000_000, 256, 1, 1000, smallest=True, normalise=False,
+                     note="the whole 100M x 256 q4 set (14.4 GB), meant to be sharded over 8 GPUs"),
+    "c4x8q32": Workload("c4x8q32", "q4", "l2_distance", 100_000_000, 256, 32, 1000, smallest=True, normalise=False,
+                        note="the whole 100M x 256 q4 set, query batch 32"),
     "c4q32": Workload("c4q32", "q4", "l2_distance", 12_500_000, 256, 32, 1000, smallest=True, normalise=False,
                       note="one GPU's share (1/8) of the 100M x 256 q4 set, query batch 32"),
 }

@@ -1,0 +1,68 @@
+/*
+ * manta_b200_host.h -- host side of the score/select path above the kernels' C ABI: a plan (Module) loader and
+ * step walker with the reference's Backend/Executor contract (reference paths are inside odvcencio/manta).
+ *
+ * In the reference this layer is Go: Runtime.Load / Program.Run (runtime/runtime.go:43-119), the plan
+ * interpreter ExecuteSymbolic + executeStep (runtime/backend/symbolic.go:14-163, tensor_ops.go:13-135) and the
+ * CUDA executor's dispatch (runtime/backends/cuda/cuda.go:222-429).  Go is not available to this build, so the
+ * same contract is implemented in C++ inside libmanta_b200.so and exported with a C ABI; tests drive it through
+ * ctypes (manta_b200/program.py).  What it keeps from the reference:
+ *   - the Module JSON schema (artifact/manta/module.go:109-207, version "manta/v0alpha1");
+ *   - tensors as (dtype label, shape, float32 / int32 / int64 data) (runtime/backend/tensor.go:11-19);
+ *   - request validation, symbol binding (N, D, Q) and their error texts (symbolic.go:265-277, tensor.go:388-517);
+ *   - Result.Outputs with Producer / Metadata, Result.Trace with one entry per ORIGINAL step, Result.Metadata
+ *     (backend.go:12-36, symbolic.go:76-161);
+ *   - error texts of topk / gather (tensor_ops.go:1532, 803).
+ * What it changes: launch_kernel{dot|cosine|l2_distance} -> topk -> gather(scores, ids) is recognised at run time
+ * and executed as ONE fused device pass; rank-2 q4/q8/f16 params feeding a score kernel are quantised into the
+ * packed layouts and bound resident at load; nothing falls back to the CPU.
+ */
+#ifndef MANTA_B200_HOST_H_
+#define MANTA_B200_HOST_H_
+
+#include "manta_b200.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct MantaB200Program MantaB200Program; /* backend.Executor + loaded Program, runtime/runtime.go:88-119 */
+typedef struct MantaB200Result MantaB200Result;   /* backend.Result, runtime/backend/backend.go:250-254 */
+
+/* backend.Tensor (runtime/backend/tensor.go:11-19): data is float32 for the labels f16, f32, q4, q8 (the
+ * reference stores every float-like tensor widened to float32), int32 for i32, int64 for i64. */
+typedef struct {
+    const char* name;
+    const char* dtype;
+    int rank;
+    const int64_t* shape;
+    const void* data;
+} MantaB200TensorArg;
+
+/* Runtime.Load for one backend (runtime/runtime.go:43-86 + cuda.Backend.load, cuda.go:67-109): parses and
+ * validates the Module JSON.  rt may be NULL: the program can then be inspected (manta_b200_program_plan) but
+ * not run. */
+int manta_b200_program_load(MantaB200Runtime* rt, const char* module_json, MantaB200Program** out, char** err);
+/* WithWeight (runtime/runtime.go load options; fixtures at runtime/runtime_test.go:1576-1593). */
+int manta_b200_program_bind_weight(MantaB200Program* prog, const MantaB200TensorArg* weight, char** err);
+/* The steps of an entry point as this backend will execute them (which steps are fused), as JSON.  The string is
+ * released with manta_b200_free_cstring. */
+int manta_b200_program_plan(MantaB200Program* prog, const char* entry, char** out_json, char** err);
+/* Program.Run (runtime/runtime.go:113-119 -> executor.Run, cuda.go:222-241 -> ExecuteSymbolic). */
+int manta_b200_program_run(MantaB200Program* prog, const char* entry, const MantaB200TensorArg* inputs, int n_inputs,
+                           MantaB200Result** out, char** err);
+int manta_b200_program_destroy(MantaB200Program* prog, char** err);
+
+/* Result as JSON: {"outputs": {name: {kind, dtype, shape, producer, inputs, metadata}}, "trace": [...],
+ * "metadata": {...}}.  Owned by the result. */
+const char* manta_b200_result_json(const MantaB200Result* res);
+/* Borrowed view of an output tensor; field is "" for tensors and "ids" / "scores" / "docs" for a candidate_pack
+ * (runtime/backend/tensor.go:26-31).  Valid until manta_b200_result_free. */
+int manta_b200_result_tensor(const MantaB200Result* res, const char* output, const char* field, MantaB200TensorArg* view,
+                             char** err);
+void manta_b200_result_free(MantaB200Result* res);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MANTA_B200_HOST_H_ */

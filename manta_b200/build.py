@@ -17,7 +17,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(CSRC, "_obj")
 LIB = os.path.join(HERE, "libmanta_b200.so")
-SOURCES = ["api.cu", "prep.cu", "select.cu", "gemv_f16.cu", "gemv_q8.cu", "gemv_q4.cu", "mma.cu", "noalloc.cu"]
+SOURCES = ["api.cu", "prep.cu", "select.cu", "gemv_f16.cu", "gemv_q8.cu", "gemv_q4.cu", "mma.cu", "noalloc.cu", "host/executor.cpp"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall", "--expt-relaxed-constexpr",
@@ -37,15 +37,19 @@ def _sources():
 
 def _newest_header() -> float:
     t = 0.0
-    for d in (CSRC, os.path.join(os.path.dirname(HERE), "include")):
+    for d in (CSRC, os.path.join(CSRC, "host"), os.path.join(os.path.dirname(HERE), "include")):
         for f in os.listdir(d):
             if f.endswith((".h", ".cuh")):
                 t = max(t, os.path.getmtime(os.path.join(d, f)))
     return t
 
 
+def _obj_path(src: str) -> str:
+    return os.path.join(OBJ, os.path.splitext(src)[0].replace("/", "_") + ".o")
+
+
 def _compile(src: str, verbose: bool) -> str:
-    obj = os.path.join(OBJ, src[:-3] + ".o")
+    obj = _obj_path(src)
     cmd = [_nvcc(), *NVCC_FLAGS, "-c", os.path.join(CSRC, src), "-o", obj]
     if verbose:
         cmd.insert(1, "-Xptxas")
@@ -63,7 +67,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     hdr = _newest_header()
     todo, objs = [], []
     for src in _sources():
-        obj = os.path.join(OBJ, src[:-3] + ".o")
+        obj = _obj_path(src)
         objs.append(obj)
         stamp = max(os.path.getmtime(os.path.join(CSRC, src)), hdr)
         if force or not os.path.exists(obj) or os.path.getmtime(obj) < stamp:

@@ -8,8 +8,8 @@ from manta_b200 import native
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _declared_symbols():
-    text = open(os.path.join(ROOT, "include", "manta_b200.h")).read()
+def _declared_symbols(header="manta_b200.h"):
+    text = open(os.path.join(ROOT, "include", header)).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     return sorted(set(re.findall(r"\b(manta_b200_[a-z0-9_]+)\s*\(", text)))
 
@@ -24,6 +24,10 @@ def test_library_exports_every_declared_symbol():
     for name in declared:
         assert hasattr(lib, name), f"{name} is declared in the header but not exported"
     assert sorted(native.EXPORTS) == sorted(declared)
+    host = _declared_symbols("manta_b200_host.h")
+    assert len(host) >= 8
+    for name in host:
+        assert hasattr(lib, name), f"{name} is declared in the host header but not exported"
 
 
 def test_header_cites_reference_for_each_entry_point():

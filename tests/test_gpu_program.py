@@ -1,0 +1,181 @@
+"""End-to-end runs of the host executor on the GPU, written after the reference's own runtime tests
+(runtime/runtime_test.go:483-678, 928-963, 1143-1184, 1356-1419 of odvcencio/manta): same tiny fixtures, same
+outputs, producers, trace and metadata keys."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+import oracle
+from helpers import assert_topk_matches, make_rows
+
+pytestmark = pytest.mark.gpu
+
+MODS = os.path.join(os.path.dirname(__file__), "golden", "modules")
+TOL = 5e-4  # the reference's tolerance for these fixtures
+
+
+def load(name):
+    return json.load(open(os.path.join(MODS, name + ".json")))
+
+
+@pytest.fixture(scope="module")
+def rt():
+    from manta_b200 import native
+
+    r = native.Runtime(0)
+    yield r
+    r.close()
+
+
+def T(*a):
+    from manta_b200.program import Tensor
+
+    return Tensor(*a)
+
+
+def tiny_rerank_weights(prog):
+    prog.bind_weight("docs", T("q4", [3, 2], [1, 0, 0, 1, 1, 1]))  # tinyRerankWeights, runtime_test.go:1585-1593
+
+
+def test_run_tiny_score_entry_point(rt):
+    from manta_b200.program import Program
+
+    prog = Program(rt, load("tiny_score"))
+    prog.bind_weight("docs", T("q4", [2, 2], [1, 0, 0, 1]))  # tinyScoreWeights
+    res = prog.run("score", {"query": T("f16", [2], [1, 0])})
+    out = res.outputs["scores"]
+    assert out.producer == "kernel:cosine"
+    assert out.kind == "tensor" and out.dtype == "f32"
+    np.testing.assert_allclose(out.data, [1, 0], atol=TOL)
+    assert out.metadata["variant_entry"] == "cosine_cuda"
+    assert out.metadata["device_execution"] is True
+    assert res.metadata["compiled_kernels"] == "1"
+    assert res.metadata["entrypoint"] == "score"
+
+
+def test_run_tiny_rerank_entry_point(rt):
+    from manta_b200.program import Program
+
+    prog = Program(rt, load("tiny_rerank"))
+    tiny_rerank_weights(prog)
+    res = prog.run("rerank", {"query": T("f16", [2], [1, 0])})
+    assert res.outputs["top_ids"].producer == "topk:topk"
+    np.testing.assert_array_equal(res.outputs["top_ids"].data, [0, 2])
+    assert res.outputs["top_ids"].data.dtype == np.int32
+    assert res.outputs["top_scores"].producer == "gather:gather"
+    np.testing.assert_allclose(res.outputs["top_scores"].data, [1, 0.70710677], atol=TOL)
+    assert res.metadata["entrypoint"] == "rerank"
+    assert len(res.trace) == 4
+    assert res.trace[1]["kind"] == "topk" and res.trace[2]["kind"] == "gather"
+    assert res.trace[0]["variant"] == "cosine_cuda"
+    assert res.metadata["fused_passes"] == "1"
+
+
+def test_run_tiny_select_and_retrieve(rt):
+    from manta_b200.program import Program
+
+    prog = Program(rt, load("tiny_select"))
+    tiny_rerank_weights(prog)
+    res = prog.run("select_scores", {"query": T("f16", [2], [1, 0])})
+    assert res.outputs["top_scores"].producer == "gather:gather"
+    np.testing.assert_allclose(res.outputs["top_scores"].data, [1, 0.70710677], atol=TOL)
+    assert len(res.trace) == 4 and res.trace[2]["kind"] == "gather"
+
+    prog = Program(rt, load("tiny_retrieve"))
+    tiny_rerank_weights(prog)
+    res = prog.run("retrieve", {"query": T("f16", [2], [1, 0])})
+    np.testing.assert_array_equal(res.outputs["top_ids"].data, [0, 2])
+    np.testing.assert_allclose(res.outputs["top_scores"].data, [1, 0.70710677], atol=TOL)
+    np.testing.assert_allclose(res.outputs["top_docs"].data, [[1, 0], [1, 1]], atol=TOL)
+    assert res.outputs["top_docs"].dtype == "q4"
+    assert len(res.trace) == 5 and res.trace[3]["kind"] == "gather"
+    # a second run reuses the resident candidate set
+    res2 = prog.run("retrieve", {"query": T("f16", [2], [0, 1])})
+    np.testing.assert_array_equal(res2.outputs["top_ids"].data, [1, 2])
+
+
+def test_run_tiny_candidates_and_packed(rt):
+    from manta_b200.program import Program
+
+    inputs = {"query": T("f16", [2], [1, 0]), "docs": T("q4", [3, 2], [1, 0, 0, 1, 1, 1]),
+              "candidate_ids": T("i64", [3], [1001, 2002, 3003])}
+    res = Program(rt, load("tiny_candidates")).run("rerank_candidates", inputs)
+    np.testing.assert_array_equal(res.outputs["top_candidate_ids"].data, [1001, 3003])
+    assert res.outputs["top_candidate_ids"].data.dtype == np.int64
+    np.testing.assert_allclose(res.outputs["top_scores"].data, [1, 0.70710677], atol=TOL)
+    np.testing.assert_allclose(res.outputs["top_docs"].data, [[1, 0], [1, 1]], atol=TOL)
+    assert res.outputs["top_docs"].dtype == "q4"
+
+    res = Program(rt, load("tiny_packed_candidates")).run("rerank_candidates_packed", inputs)
+    out = res.outputs["candidates"]
+    assert out.kind == "candidate_pack"
+    np.testing.assert_array_equal(out.data["ids"], [1001, 3003])
+    np.testing.assert_allclose(out.data["scores"], [1, 0.70710677], atol=TOL)
+    np.testing.assert_allclose(out.data["docs"], [[1, 0], [1, 1]], atol=TOL)
+    assert out.data["docs_dtype"] == "q4"
+
+
+@pytest.mark.parametrize("op,want", [("dot", [1, 0, 1]), ("cosine", [1, 0, 0.70710677]), ("l2_distance", [0, 1.4142135, 1])])
+def test_run_direct_quantized_builtin_score_ops(rt, op, want):
+    from manta_b200.program import Program
+
+    res = Program(rt, load("direct_" + op)).run("score", {"query": T("f16", [2], [1, 0]), "docs": T("q4", [3, 2], [1, 0, 0, 1, 1, 1])})
+    out = res.outputs["scores"]
+    assert out.producer == "kernel:" + op
+    np.testing.assert_allclose(out.data, want, atol=TOL)
+    assert out.metadata["device_execution"] is True
+
+
+def test_request_validation_errors(rt):
+    from manta_b200.program import MantaError, Program
+
+    prog = Program(rt, load("tiny_rerank"))
+    with pytest.raises(MantaError, match='missing weight binding for param "docs"'):
+        prog.run("rerank", {"query": T("f16", [2], [1, 0])})
+    tiny_rerank_weights(prog)
+    with pytest.raises(MantaError, match='unknown entrypoint "nope"'):
+        prog.run("nope", {})
+    with pytest.raises(MantaError, match='entrypoint "rerank" missing input "query"'):
+        prog.run("rerank", {})
+    with pytest.raises(MantaError, match='entrypoint "rerank" does not declare input "extra"'):
+        prog.run("rerank", {"query": T("f16", [2], [1, 0]), "extra": T("f16", [2], [1, 0])})
+    with pytest.raises(MantaError, match='symbol "D" mismatch: expected 2, got 3'):
+        prog.run("rerank", {"query": T("f16", [3], [1, 0, 0])})
+    with pytest.raises(MantaError, match="tensor rank 2 does not match expected rank 1"):
+        prog.run("rerank", {"query": T("f16", [1, 2], [1, 0])})
+    with pytest.raises(MantaError, match='tensor dtype "i32" does not match expected "f16"'):
+        prog.run("rerank", {"query": T("i32", [2], [1, 0])})
+    # f32-labelled data is accepted where f16 is expected (runtime/backend/tensor.go:392-395)
+    res = prog.run("rerank", {"query": T("f32", [2], [1, 0])})
+    np.testing.assert_array_equal(res.outputs["top_ids"].data, [0, 2])
+    # k larger than the candidate count is topKTensor's error, reported on the topk step
+    mod = load("tiny_rerank")
+    mod["steps"][1]["attributes"]["k"] = "5"
+    prog5 = Program(rt, mod)
+    tiny_rerank_weights(prog5)
+    with pytest.raises(MantaError, match='step "topk": topk limit 5 out of range for 3 scores'):
+        prog5.run("rerank", {"query": T("f16", [2], [1, 0])})
+
+
+def test_rerank_at_size_against_oracle(rt):
+    """The same plan on a real-sized q8 parameter and a query batch (shared-candidate extension)."""
+    from manta_b200.program import Program
+
+    rows, cols, nq, k = 30000, 128, 3, 10
+    rng = np.random.default_rng(8)
+    x = make_rows(rng, rows, cols)
+    q = make_rows(rng, nq, cols)
+    mod = load("tiny_rerank")
+    mod["params"][0]["type"]["tensor"]["dtype"] = "q8"
+    mod["kernels"][0]["inputs"][1]["type"]["tensor"]["dtype"] = "q8"
+    mod["entry_points"][0]["inputs"][0]["type"]["tensor"]["shape"] = ["Q", "D"]
+    mod["entry_points"][0]["outputs"][0]["type"]["tensor"]["shape"] = ["Q", str(k)]
+    mod["entry_points"][0]["outputs"][1]["type"]["tensor"]["shape"] = ["Q", str(k)]
+    mod["steps"][1]["attributes"]["k"] = str(k)
+    prog = Program(rt, mod)
+    prog.bind_weight("docs", T("q8", [rows, cols], x))
+    res = prog.run("rerank", {"query": T("f16", [nq, cols], q)})
+    deq = oracle.unpack_q8_rows(*oracle.pack_q8_rows(x))
+    assert_topk_matches("cosine", q, deq, res.outputs["top_ids"].data, res.outputs["top_scores"].data, k)
