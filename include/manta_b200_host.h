@@ -53,6 +53,18 @@ int manta_b200_program_run(MantaB200Program* prog, const char* entry, const Mant
                            MantaB200Result** out, char** err);
 int manta_b200_program_destroy(MantaB200Program* prog, char** err);
 
+/* NewMemoryPlan (runtime/memory_plan.go:59-138) over the bound weights: JSON document with version
+ * "manta/memory/v0alpha1" (same fields as MemoryPlan / WeightMemoryPlan, :34-56).  accounting 0 budgets the
+ * reference's logical bytes (tensorLogicalBytes, :381-406: codes only); accounting 1 budgets what one of `shards`
+ * row shards really holds in HBM in the packed layouts (padded codes + scales + row statistic).  The string is
+ * released with manta_b200_free_cstring. */
+int manta_b200_program_memory_plan(MantaB200Program* prog, int64_t device_budget_bytes, int shared_host_weights, int shards,
+                                   int accounting, char** out_json, char** err);
+/* WithMemoryPlan (runtime/runtime.go:172-197): params whose residency is not device_resident are bound only for
+ * the run that reads them and released afterwards (the reference honours lazy_staged the same way,
+ * runtime/backend/symbolic.go:139-152, 165-171). */
+int manta_b200_program_apply_memory_plan(MantaB200Program* prog, const char* plan_json, char** err);
+
 /* Result as JSON: {"outputs": {name: {kind, dtype, shape, producer, inputs, metadata}}, "trace": [...],
  * "metadata": {...}}.  Owned by the result. */
 const char* manta_b200_result_json(const MantaB200Result* res);

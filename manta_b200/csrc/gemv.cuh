@@ -222,15 +222,25 @@ __global__ void __launch_bounds__(kThreads, (QT == 1 && CPL <= 4) ? 2 : 1) gemv_
     Meta nxt;
     load_meta(gw, nxt);
     uint32_t iter = 0;
+    uint32_t overflow_seen = 0;
+    uint32_t thr[QT];
+#pragma unroll
+    for (int q = 0; q < QT; ++q) thr[q] = 0;
     int stage = 0;
     for (int64_t wt = gw; wt < n_wt; wt += nwarps) {
         ++iter;
-        uint32_t thr[QT];
         if (mode == kModeTopk) {
+            // the bounds move fast only at the start: reread them every tile early on, every eighth tile later
+            if (iter <= 16 || (iter & 7) == 0) {
 #pragma unroll
-            for (int q = 0; q < QT; ++q) thr[q] = ld_relaxed_u32(a.ws.thr + a.q0 + ((q < a.qt) ? q : 0));
-            // a pool that overflowed makes the host redo the pass in chunks: stop streaming
-            if ((iter & 15) == 0 && ld_relaxed_u32(a.ws.flags + kFlagOverflow) != 0) break;
+                for (int q = 0; q < QT; ++q) thr[q] = ld_relaxed_u32(a.ws.thr + a.q0 + ((q < a.qt) ? q : 0));
+            }
+            // a pool that overflowed makes the host redo the pass in chunks: stop streaming.  The flag is
+            // loaded in one check and tested in the next, so its latency never stalls the stream.
+            if ((iter & 63) == 0) {
+                if (overflow_seen != 0) break;
+                overflow_seen = ld_relaxed_u32(a.ws.flags + kFlagOverflow);
+            }
             // Two tiles per warp have entered the pool unfiltered.  Before streaming on, let the first bound
             // arrive (the warps on refresh duty at tile counts 2 and 3 are computing it), so that the number of
             // unfiltered rows does not depend on timing.  The wait is bounded; giving up only costs pool space.
@@ -424,16 +434,42 @@ __global__ void __launch_bounds__(kThreads, (QT == 1 && CPL <= 4) ? 2 : 1) gemv_
         if (warp_in_cta == 0 && duty_iter && ((blockIdx.x & 7) == ((iter == 3 || iter == 6) ? 7 - (iter / 3) : ((31 - __clz(iter)) & 7)))) {
             for (int q = 0; q < a.qt; ++q) {
                 const uint32_t* b = a.ws.bucket + (size_t)(a.q0 + q) * a.ws.nb;
-                const uint32_t nb = min(a.ws.nb, (uint32_t)kStageWords);
-                for (uint32_t i = lane; i < nb; i += 32) s_stage[i] = ld_relaxed_u32(b + i);
-                __syncwarp();
+                // A bound needs k buckets; for small k the first 256 warps' maxima are plenty (any subset of
+                // buckets gives a valid, slightly lower bound) and fit in eight registers per lane.
+                const uint32_t nb_all = min(min(a.ws.nb, (uint32_t)kStageWords), (uint32_t)nwarps);
                 uint32_t t = 0;
-                for (int bit = 31; bit >= 12; --bit) {
-                    const uint32_t cand = t | (1u << bit);
-                    uint32_t cnt = 0;
-                    for (uint32_t i = lane; i < nb; i += 32) cnt += (s_stage[i] >= cand) ? 1u : 0u;
-                    cnt = __reduce_add_sync(0xffffffffu, cnt);
-                    if (cnt >= (uint32_t)a.k) t = cand;
+                if (2u * (uint32_t)a.k <= 256u) {
+                    const uint32_t nb = min(nb_all, 256u);
+                    uint32_t v[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) v[u] = ((uint32_t)(u * 32 + lane) < nb) ? __ldcg(b + u * 32 + lane) : 0u;
+                    for (int bit = 31; bit >= 12; --bit) {
+                        const uint32_t cand = t | (1u << bit);
+                        uint32_t cnt = 0;
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) cnt += (v[u] >= cand) ? 1u : 0u;
+                        cnt = __reduce_add_sync(0xffffffffu, cnt);
+                        if (cnt >= (uint32_t)a.k) t = cand;
+                    }
+                } else {
+                    const uint32_t nb = nb_all;
+                    // eight independent loads at a time (a volatile load per element would serialise on its store)
+                    for (uint32_t i0 = lane; i0 < nb; i0 += 256) {
+                        uint32_t v[8];
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) v[u] = (i0 + u * 32 < nb) ? __ldcg(b + i0 + u * 32) : 0u;
+#pragma unroll
+                        for (int u = 0; u < 8; ++u)
+                            if (i0 + u * 32 < nb) s_stage[i0 + u * 32] = v[u];
+                    }
+                    __syncwarp();
+                    for (int bit = 31; bit >= 12; --bit) {
+                        const uint32_t cand = t | (1u << bit);
+                        uint32_t cnt = 0;
+                        for (uint32_t i = lane; i < nb; i += 32) cnt += (s_stage[i] >= cand) ? 1u : 0u;
+                        cnt = __reduce_add_sync(0xffffffffu, cnt);
+                        if (cnt >= (uint32_t)a.k) t = cand;
+                    }
                 }
                 if (lane == 0 && t != 0) atomicMax(a.ws.thr + a.q0 + q, t);
                 __syncwarp();

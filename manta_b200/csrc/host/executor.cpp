@@ -50,6 +50,7 @@ struct Binding {
 struct Param {
     std::string name, binding;
     ValueType type;
+    bool trainable = false;
 };
 struct EntryPoint {
     std::string name, kind;
@@ -144,7 +145,11 @@ bool parse_module(const std::string& text, Module* m, std::string* err) {
     m->version = root.get_string("version");
     m->name = root.get_string("name");
     if (const Value* ps = root.get("params"))
-        for (const auto& e : ps->items()) m->params.push_back(Param{e.get_string("name"), e.get_string("binding"), parse_type(e.get("type"))});
+        for (const auto& e : ps->items()) {
+            Param p{e.get_string("name"), e.get_string("binding"), parse_type(e.get("type"))};
+            if (const Value* tr = e.get("trainable")) p.trainable = tr->kind == Value::Bool && tr->b;
+            m->params.push_back(p);
+        }
     if (const Value* es = root.get("entry_points"))
         for (const auto& e : es->items())
             m->entries.push_back(EntryPoint{e.get_string("name"), e.get_string("kind"), parse_bindings(e.get("inputs")), parse_bindings(e.get("outputs"))});
@@ -241,6 +246,7 @@ struct MantaB200Program {
     Module mod;
     std::map<std::string, TensorP> weights;
     std::map<std::string, BoundSet> resident;  // params feeding score kernels, bound at first run
+    std::map<std::string, std::string> residency;  // param -> residency of an applied memory plan
     uint64_t runs = 0;
 };
 
@@ -447,7 +453,152 @@ Value fusion_json(const std::vector<const Step*>& steps, const std::vector<Fusio
 
 }  // namespace
 
+namespace {
+
+// tensorLogicalBytes (runtime/memory_plan.go:381-406): codes only, q4 = (n+1)/2, q8 = n.
+int64_t logical_bytes(const Tensor& t) {
+    int64_t n = 1;
+    for (int64_t d : t.shape) {
+        if (d <= 0) return 0;
+        n *= d;
+    }
+    if (t.dtype == "q4") return (n + 1) / 2;
+    if (t.dtype == "q8") return n;
+    if (t.dtype == "f16") return n * 2;
+    if (t.dtype == "i64") return n * 8;
+    return n * 4;
+}
+
+// Bytes one shard really holds in HBM when the tensor is bound as a candidate set: padded codes + scales + the
+// 4-byte row statistic.  Tensors that are not rank-2 float-like are counted as the reference counts them.
+int64_t device_bytes(const Tensor& t, int shards) {
+    if (t.shape.size() != 2 || !float_like(t.dtype) || t.shape[0] <= 0 || t.shape[1] <= 0) return logical_bytes(t);
+    const int64_t rows = (t.shape[0] + shards - 1) / shards, cols = t.shape[1];
+    if (t.dtype == "q8") return rows * ((cols + 15) / 16 * 16 + 4 + 4);
+    if (t.dtype == "q4") {
+        const int64_t pc = (cols + 31) / 32 * 32;
+        return rows * (pc / 2 + (pc / 32) * 2 + 4);
+    }
+    return rows * ((cols + 7) / 8 * 16 + 4);  // stored as f16
+}
+
+}  // namespace
+
 extern "C" {
+
+/* NewMemoryPlan (runtime/memory_plan.go:59-138): same ordering (trainable first, then access count descending,
+ * bytes ascending, name) and the same residency rule.  accounting 0 budgets the reference's logical bytes, 1 the
+ * bytes a shard really holds on the device (codes + scales + row statistic). */
+int manta_b200_program_memory_plan(MantaB200Program* prog, int64_t device_budget_bytes, int shared_host_weights, int shards,
+                                   int accounting, char** out_json, char** err) {
+    if (!prog || !out_json) return fail(err, "memory_plan: NULL argument");
+    if (shards <= 0) return fail(err, "memory_plan: shard count %d out of range", shards);
+    struct Item {
+        std::string name, dtype, residency;
+        std::vector<int64_t> shape;
+        bool trainable;
+        int64_t bytes, dev_bytes;
+        int access;
+    };
+    std::map<std::string, int> access;
+    for (const auto& s : prog->mod.steps)
+        for (const auto& in : s.inputs)
+            if (param_by_name(prog->mod, in)) access[in]++;
+    std::vector<Item> items;
+    int64_t total = 0;
+    for (const auto& kv : prog->weights) {
+        const Param* p = param_by_name(prog->mod, kv.first);
+        Item it{kv.first, kv.second->dtype, "device_resident", kv.second->shape, p ? p->trainable : false,
+                logical_bytes(*kv.second), device_bytes(*kv.second, shards), access[kv.first]};
+        total += accounting ? it.dev_bytes : it.bytes;
+        items.push_back(it);
+    }
+    auto cost = [&](const Item& it) { return accounting ? it.dev_bytes : it.bytes; };
+    std::sort(items.begin(), items.end(), [&](const Item& a, const Item& b) {
+        if (a.trainable != b.trainable) return a.trainable;
+        if (a.access != b.access) return a.access > b.access;
+        if (cost(a) != cost(b)) return cost(a) < cost(b);
+        return a.name < b.name;
+    });
+    int64_t used = 0, dev = 0, host = 0, lazy = 0;
+    const bool budgeted = device_budget_bytes > 0;
+    for (auto& it : items) {
+        const bool fits = !budgeted || used + cost(it) <= device_budget_bytes;
+        if (it.trainable || fits) {
+            it.residency = "device_resident";
+            used += cost(it);
+            dev += cost(it);
+        } else if (shared_host_weights) {
+            it.residency = "host_shared";
+            host += cost(it);
+        } else if (it.access <= 1) {
+            it.residency = "lazy_staged";
+            lazy += cost(it);
+        } else {
+            it.residency = "host_pinned";
+            host += cost(it);
+        }
+    }
+    std::sort(items.begin(), items.end(), [](const Item& a, const Item& b) { return a.name < b.name; });
+    Value root = Value::make_object();
+    root.set("version", Value::make_string("manta/memory/v0alpha1"));
+    root.set("module_name", Value::make_string(prog->mod.name));
+    root.set("backend", Value::make_string("cuda"));
+    root.set("device_budget_bytes", Value::make_number((double)device_budget_bytes));
+    root.set("accounting", Value::make_string(accounting ? "device_bytes_per_shard" : "logical_bytes"));
+    root.set("shards", Value::make_number(shards));
+    root.set("total_weight_bytes", Value::make_number((double)total));
+    root.set("device_resident_bytes", Value::make_number((double)dev));
+    root.set("host_resident_bytes", Value::make_number((double)host));
+    root.set("lazy_staged_bytes", Value::make_number((double)lazy));
+    Value ws = Value::make_array();
+    for (const auto& it : items) {
+        Value w = Value::make_object();
+        w.set("name", Value::make_string(it.name));
+        w.set("dtype", Value::make_string(it.dtype));
+        w.set("shape", shape_json(it.shape));
+        w.set("trainable", Value::make_bool(it.trainable));
+        w.set("bytes", Value::make_number((double)it.bytes));
+        w.set("device_bytes_per_shard", Value::make_number((double)it.dev_bytes));
+        w.set("access_count", Value::make_number(it.access));
+        w.set("residency", Value::make_string(it.residency));
+        ws.push(w);
+    }
+    root.set("weights", ws);
+    std::string text;
+    mjson::write(root, &text);
+    char* out = (char*)malloc(text.size() + 1);
+    if (!out) return fail(err, "out of memory");
+    memcpy(out, text.c_str(), text.size() + 1);
+    *out_json = out;
+    return 0;
+}
+
+/* WithMemoryPlan (applied at runtime.go:172-197): params whose residency is not device_resident are not kept on
+ * the device between runs; they are bound for the run that needs them and released afterwards. */
+int manta_b200_program_apply_memory_plan(MantaB200Program* prog, const char* plan_json, char** err) {
+    if (!prog || !plan_json) return fail(err, "apply_memory_plan: NULL argument");
+    Value root;
+    std::string perr;
+    const std::string plan_text(plan_json);
+    mjson::Parser p(plan_text);
+    if (!p.parse(&root, &perr)) return fail(err, "%s", perr.c_str());
+    if (root.get_string("version") != "manta/memory/v0alpha1") return fail(err, "unsupported memory plan version \"%s\"", root.get_string("version").c_str());
+    const Value* ws = root.get("weights");
+    if (!ws) return fail(err, "memory plan has no weights");
+    for (const auto& w : ws->items()) {
+        const std::string name = w.get_string("name"), res = w.get_string("residency");
+        if (res != "device_resident" && res != "host_pinned" && res != "host_shared" && res != "lazy_staged")
+            return fail(err, "memory plan weight \"%s\" has unknown residency \"%s\"", name.c_str(), res.c_str());
+        prog->residency[name] = res;
+        auto it = prog->resident.find(name);
+        if (res != "device_resident" && it != prog->resident.end()) {
+            if (prog->rt && it->second.set) manta_b200_candidates_unbind(prog->rt, it->second.set, nullptr);
+            prog->resident.erase(it);
+        }
+    }
+    return 0;
+}
 
 int manta_b200_program_load(MantaB200Runtime* rt, const char* module_json, MantaB200Program** out, char** err) {
     if (!module_json || !out) return fail(err, "program_load: NULL argument");
@@ -556,7 +707,10 @@ int manta_b200_program_run(MantaB200Program* prog, const char* entry_name, const
         v.tensor = w->second;
         v.producer = "param:" + p.name;
         v.metadata.set("materialized", Value::make_string("eager"));
-        v.metadata.set("weight_residency", Value::make_string("device_resident"));
+        {
+            auto rit = prog->residency.find(p.name);
+            v.metadata.set("weight_residency", Value::make_string(rit == prog->residency.end() ? "device_resident" : rit->second));
+        }
         env[p.name] = v;
     }
     for (const auto& in : entry->inputs) {
@@ -580,9 +734,14 @@ int manta_b200_program_run(MantaB200Program* prog, const char* entry_name, const
     auto res = std::make_unique<MantaB200Result>();
     Value trace = Value::make_array();
     std::vector<BoundSet> temp_sets;  // docs that arrived as request inputs
+    int temp_sets_released = 0;
     auto cleanup = [&]() {
         for (auto& b : temp_sets)
-            if (b.set) manta_b200_candidates_unbind(prog->rt, b.set, nullptr);
+            if (b.set) {
+                manta_b200_candidates_unbind(prog->rt, b.set, nullptr);
+                b.set = nullptr;
+                ++temp_sets_released;
+            }
     };
     std::map<std::string, BoundSet> set_of_value;  // env name -> candidate set it is bound as
     // results of fused passes, keyed by the scores value name
@@ -664,7 +823,9 @@ int manta_b200_program_run(MantaB200Program* prog, const char* entry_name, const
             if (!float_like(query.dtype) || !float_like(docs.dtype)) STEP_FAIL("score inputs must be float-like tensors");
             // candidate set: resident for params, bound for this call for request inputs
             BoundSet bs;
-            if (param_by_name(mod, f->docs_name)) {
+            auto rit = prog->residency.find(f->docs_name);
+            const bool keep_resident = rit == prog->residency.end() || rit->second.empty() || rit->second == "device_resident";
+            if (param_by_name(mod, f->docs_name) && keep_resident) {
                 auto it = prog->resident.find(f->docs_name);
                 if (it == prog->resident.end()) {
                     char* berr = nullptr;
@@ -896,6 +1057,7 @@ int manta_b200_program_run(MantaB200Program* prog, const char* entry_name, const
     md.set("params_total", Value::make_string(std::to_string(mod.params.size())));
     md.set("params_eager_materialized", Value::make_string(std::to_string(mod.params.size())));
     md.set("fused_passes", Value::make_string(std::to_string(fused.size())));
+    md.set("params_released", Value::make_string(std::to_string(temp_sets_released)));
     md.set("device_kernel_launches", Value::make_string(std::to_string(manta_b200_kernel_launch_count() - launches_before)));
     root.set("metadata", md);
     mjson::write(root, &res->json);

@@ -49,6 +49,10 @@ def _lib():
         lib.manta_b200_program_plan.argtypes = [c_void_p, c_char_p, POINTER(c_void_p), E]
         lib.manta_b200_program_run.argtypes = [c_void_p, c_char_p, POINTER(TensorArg), c_int, POINTER(c_void_p), E]
         lib.manta_b200_program_destroy.argtypes = [c_void_p, E]
+        lib.manta_b200_program_memory_plan.argtypes = [c_void_p, c_int64, c_int, c_int, c_int, POINTER(c_void_p), E]
+        lib.manta_b200_program_apply_memory_plan.argtypes = [c_void_p, c_char_p, E]
+        lib.manta_b200_program_memory_plan.restype = c_int
+        lib.manta_b200_program_apply_memory_plan.restype = c_int
         lib.manta_b200_result_json.argtypes = [c_void_p]
         lib.manta_b200_result_json.restype = c_char_p
         lib.manta_b200_result_tensor.argtypes = [c_void_p, c_char_p, c_char_p, POINTER(TensorArg), E]
@@ -102,6 +106,19 @@ class Program:
         text = ctypes.cast(out, c_char_p).value.decode()
         self._lib.manta_b200_free_cstring(out)
         return json.loads(text)
+
+    def memory_plan(self, device_budget_bytes: int = 0, shared_host_weights: bool = False, shards: int = 1,
+                    accounting: str = "device") -> dict:
+        """NewMemoryPlan over the bound weights; accounting "logical" reproduces the reference's byte counts."""
+        out = c_void_p()
+        native.call("manta_b200_program_memory_plan", self.handle, c_int64(device_budget_bytes), c_int(1 if shared_host_weights else 0),
+                    c_int(shards), c_int(0 if accounting == "logical" else 1), byref(out))
+        text = ctypes.cast(out, c_char_p).value.decode()
+        self._lib.manta_b200_free_cstring(out)
+        return json.loads(text)
+
+    def apply_memory_plan(self, plan: dict):
+        native.call("manta_b200_program_apply_memory_plan", self.handle, json.dumps(plan).encode())
 
     def run(self, entry: str, inputs: dict) -> Result:
         keep = []

@@ -179,3 +179,28 @@ def test_rerank_at_size_against_oracle(rt):
     res = prog.run("rerank", {"query": T("f16", [nq, cols], q)})
     deq = oracle.unpack_q8_rows(*oracle.pack_q8_rows(x))
     assert_topk_matches("cosine", q, deq, res.outputs["top_ids"].data, res.outputs["top_scores"].data, k)
+
+
+def test_memory_plan_residency_is_honoured(rt):
+    """A param the plan does not keep device_resident is bound for the run and released afterwards; results are
+    the same (the reference's lazy_staged behaviour, runtime/runtime_test.go:223-271)."""
+    from manta_b200.program import Program
+
+    prog = Program(rt, load("tiny_retrieve"))
+    tiny_rerank_weights(prog)
+    plan = prog.memory_plan(1)  # nothing fits; docs is read by two steps (score, gather) -> host_pinned
+    assert plan["weights"][0]["residency"] == "host_pinned" and plan["weights"][0]["access_count"] == 2
+    prog.apply_memory_plan(plan)
+    binds0 = rt.stats()["bind_calls"]
+    for _ in range(2):
+        res = prog.run("retrieve", {"query": T("f16", [2], [1, 0])})
+        np.testing.assert_array_equal(res.outputs["top_ids"].data, [0, 2])
+        np.testing.assert_allclose(res.outputs["top_docs"].data, [[1, 0], [1, 1]], atol=TOL)
+        assert res.metadata["params_released"] == "1"
+    assert rt.stats()["bind_calls"] == binds0 + 2
+    prog.apply_memory_plan(prog.memory_plan())  # unbudgeted: resident again
+    binds1 = rt.stats()["bind_calls"]
+    for _ in range(2):
+        res = prog.run("retrieve", {"query": T("f16", [2], [1, 0])})
+        assert res.metadata["params_released"] == "0"
+    assert rt.stats()["bind_calls"] == binds1 + 1

@@ -70,3 +70,43 @@ def test_run_without_runtime_fails_loudly():
     prog = Program(None, load("tiny_rerank"))
     with pytest.raises(MantaError, match="no host fallback"):
         prog.run("rerank", {"query": Tensor("f16", [2], [1, 0])})
+
+
+def test_memory_plan_budgeted_residency():
+    """NewMemoryPlan's ordering and residency rule on the reference's own fixture shapes
+    (runtime/memory_plan_test.go:60-86: q8 [32,16] embedding + q8 [16,16] projection, 300-byte budget)."""
+    from manta_b200.program import Tensor
+
+    mod = {"version": "manta/v0alpha1", "name": "tiny_embed_pooled",
+           "params": [{"name": "token_embedding", "binding": "weights/token_embedding", "type": {"kind": "tensor", "tensor": {"dtype": "q8", "shape": ["V", "D"]}}},
+                      {"name": "projection", "binding": "weights/projection", "type": {"kind": "tensor", "tensor": {"dtype": "q8", "shape": ["D", "E"]}}}],
+           "entry_points": [{"name": "embed_pooled", "kind": "pipeline", "inputs": [], "outputs": []}],
+           "requirements": {"supported_backends": ["cuda"]}, "kernels": [],
+           "steps": [{"entry": "embed_pooled", "kind": "gather", "name": "gather", "inputs": ["token_embedding", "tokens"], "outputs": ["hidden"]},
+                     {"entry": "embed_pooled", "kind": "matmul", "name": "matmul", "inputs": ["hidden", "projection"], "outputs": ["projected"]}]}
+    prog = Program(None, mod)
+    prog.bind_weight("token_embedding", Tensor("q8", [32, 16], [0.0] * 512))
+    prog.bind_weight("projection", Tensor("q8", [16, 16], [0.0] * 256))
+    plan = prog.memory_plan(300, shared_host_weights=True, accounting="logical")
+    assert plan["version"] == "manta/memory/v0alpha1" and len(plan["weights"]) == 2
+    res = {w["name"]: w for w in plan["weights"]}
+    assert res["projection"]["bytes"] == 256 and res["token_embedding"]["bytes"] == 512  # tensorLogicalBytes
+    assert res["projection"]["residency"] == "device_resident"
+    assert res["token_embedding"]["residency"] == "host_shared"
+    assert plan["device_resident_bytes"] == 256 and plan["host_resident_bytes"] == 512
+    # without shared host weights a once-read weight is lazily staged
+    plan = prog.memory_plan(300, accounting="logical")
+    assert {w["name"]: w["residency"] for w in plan["weights"]}["token_embedding"] == "lazy_staged"
+    # device accounting counts scales and the row statistic: 16*(16+4+4) = 384, 32*(16+4+4) = 768
+    plan = prog.memory_plan(400, shared_host_weights=True)
+    res = {w["name"]: w for w in plan["weights"]}
+    assert res["projection"]["device_bytes_per_shard"] == 384 and res["token_embedding"]["device_bytes_per_shard"] == 768
+    assert res["projection"]["residency"] == "device_resident" and res["token_embedding"]["residency"] == "host_shared"
+    # sharding the rows over 8 GPUs divides what each device holds
+    plan = prog.memory_plan(400, shared_host_weights=True, shards=8)
+    assert {w["name"]: w["device_bytes_per_shard"] for w in plan["weights"]} == {"projection": 48, "token_embedding": 96}
+    assert all(w["residency"] == "device_resident" for w in plan["weights"])
+    # unbudgeted: everything resident
+    assert all(w["residency"] == "device_resident" for w in prog.memory_plan()["weights"])
+    with pytest.raises(MantaError, match="unknown residency"):
+        prog.apply_memory_plan({"version": "manta/memory/v0alpha1", "weights": [{"name": "projection", "residency": "moon"}]})
