@@ -245,33 +245,50 @@ def run_ours(args, wl: Workload):
         dist = dist_mod
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     native.load()
-    rt = native.Runtime(local_rank)
-    stream = torch.cuda.ExternalStream(rt.stream)
+    # One "lane" = a runtime (stream + scratch) with its own result buffers.  With more than one GPU two lanes
+    # alternate steps, so that the selection, the all-gather and the merge of one step overlap the scan of the
+    # next (independent queries; throughput, not latency).  A single GPU runs one lane.
+    n_lanes = args.lanes if args.lanes > 0 else (2 if world > 1 else 1)
     nq, k = wl.nq, wl.k
     nsets = max(1, min(N_QUERY_SET, 4096 // nq))
+
+    class Lane:
+        def __init__(self):
+            self.rt = native.Runtime(local_rank)
+            self.stream = torch.cuda.ExternalStream(self.rt.stream)
+            with torch.cuda.stream(self.stream):
+                # ids and scores of a rank share one buffer so that a single all-gather carries both
+                self.d_pair, self.d_ids, self.d_scores = sharding.new_pair(nq, k, "cuda")
+                if world > 1:
+                    self.g_pair = torch.empty((world, 2, nq, k), dtype=torch.int32, device="cuda")
+                    self.g_ids, self.g_scores, _, self.g_stride = sharding.merge_args(self.g_pair, nq, k)
+                    self.m_ids = torch.empty((nq, k), dtype=torch.int32, device="cuda")
+                    self.m_scores = torch.empty((nq, k), dtype=torch.float32, device="cuda")
+            self.stream.synchronize()
+
+    lanes = [Lane() for _ in range(n_lanes)]
+    rt, stream = lanes[0].rt, lanes[0].stream
 
     r0, r1 = sharding.shard_bounds(wl.rows, rank, world)
     data, scales = synth.packed_candidates(rt, wl.layout, r0, r1, wl.cols, normalise=wl.normalise)
     cands = rt.bind(wl.layout, data, scales, row_base=r0, rows=r1 - r0, cols=wl.cols)
     with torch.cuda.stream(stream):
         d_queries = synth.queries_f16(nsets * nq, wl.cols, normalise=wl.normalise).view(nsets, nq, wl.cols)
-        # ids and scores of a rank share one buffer so that a single all-gather carries both
-        d_pair, d_ids, d_scores = sharding.new_pair(nq, k, "cuda")
-        if world > 1:
-            g_pair = torch.empty((world, 2, nq, k), dtype=torch.int32, device="cuda")
-            g_ids, g_scores, _, g_stride = sharding.merge_args(g_pair, nq, k)
-            m_ids = torch.empty((nq, k), dtype=torch.int32, device="cuda")
-            m_scores = torch.empty((nq, k), dtype=torch.float32, device="cuda")
     stream.synchronize()
     h_queries = d_queries.cpu().numpy().view(np.uint16)
+    d_ids, d_scores, d_pair = lanes[0].d_ids, lanes[0].d_scores, lanes[0].d_pair
+    if world > 1:
+        g_pair, g_ids, g_scores, g_stride = lanes[0].g_pair, lanes[0].g_ids, lanes[0].g_scores, lanes[0].g_stride
+        m_ids, m_scores = lanes[0].m_ids, lanes[0].m_scores
 
     def step_device(i):
-        rt.score_topk_device(cands, wl.metric, d_queries[i % nsets], nq, k, d_ids, d_scores, smallest=wl.smallest, sync=False)
+        ln = lanes[i % n_lanes]
+        ln.rt.score_topk_device(cands, wl.metric, d_queries[i % nsets], nq, k, ln.d_ids, ln.d_scores, smallest=wl.smallest, sync=False)
         if world > 1:
-            with torch.cuda.stream(stream):
-                sharding.gather_pairs(d_pair, g_pair, dist)
-            rt.topk_merge_device(g_ids, g_scores, world, nq, k, m_ids, m_scores, smallest=wl.smallest, sync=False,
-                                 list_stride=g_stride)
+            with torch.cuda.stream(ln.stream):
+                sharding.gather_pairs(ln.d_pair, ln.g_pair, dist)
+            ln.rt.topk_merge_device(ln.g_ids, ln.g_scores, world, nq, k, ln.m_ids, ln.m_scores, smallest=wl.smallest, sync=False,
+                                    list_stride=ln.g_stride)
 
     def barrier():
         if world > 1:
@@ -279,9 +296,10 @@ def run_ours(args, wl: Workload):
         torch.cuda.synchronize()
 
     # ---- device-resident timing ------------------------------------------------------------------
-    for i in range(args.warmup):
+    for i in range(max(args.warmup, n_lanes)):
         step_device(i)
-    rt.synchronize()  # raises if a warm-up pass overflowed its pool
+    for ln in lanes:
+        ln.rt.synchronize()  # raises if a warm-up pass overflowed its pool
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -292,11 +310,16 @@ def run_ours(args, wl: Workload):
     t_begin = time.perf_counter()
     ev0.record(stream)
     for i in range(args.steps):
-        step_device(args.warmup + i)
+        step_device(i)
+    for ln in lanes[1:]:  # the closing event waits for every lane
+        done = torch.cuda.Event()
+        done.record(ln.stream)
+        stream.wait_event(done)
     ev1.record(stream)
     barrier()
     t_end = time.perf_counter()
-    rt.synchronize()
+    for ln in lanes:
+        ln.rt.synchronize()
     launches = native.kernel_launch_count() - launches0
     total_ms = ev0.elapsed_time(ev1)
     scan_ms, scan_passes = rt.scan_time()
@@ -306,7 +329,8 @@ def run_ours(args, wl: Workload):
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     total_ms, scan_ms_per_pass = float(t[0]), float(t[1])
-    final_ids = (m_ids if world > 1 else d_ids).cpu().numpy().copy()
+    last = lanes[(args.steps - 1) % n_lanes]
+    final_ids = (last.m_ids if world > 1 else last.d_ids).cpu().numpy().copy()
     stats_device = rt.stats()
 
     # ---- end to end through the host-buffer ABI call ------------------------------------------------
@@ -371,7 +395,7 @@ def run_ours(args, wl: Workload):
                       "q4": "int4 x int8 -> int32 per block, f32 across blocks", "f16": "f16 x f16 -> f32"}[wl.layout],
             "data": "synthetic",
             "config": {"workload": wl.describe(), "rows": wl.rows, "cols": wl.cols, "k": k, "queries_per_step": nq,
-                       "layout": wl.layout, "shards": world, "note": wl.note,
+                       "layout": wl.layout, "shards": world, "note": wl.note, "lanes": n_lanes,
                        "l2": f"inputs larger than L2: {algo_bytes / 1e9:.3f} GB scanned per pass and GPU" if algo_bytes > 2.5e8
                              else "inputs smaller than L2 (latency-bound configuration, not a roofline point)"},
             "candidates_dim_per_s": value * wl.rows * wl.cols,
@@ -389,7 +413,8 @@ def run_ours(args, wl: Workload):
         }
         print(json.dumps(line), flush=True)
     cands.unbind()
-    rt.close()
+    for ln in lanes:
+        ln.rt.close()
     if world > 1:
         dist.destroy_process_group()
 
@@ -405,6 +430,8 @@ def main():
     ap.add_argument("--rows", type=int, default=0, help="override the workload's row count (smaller cases for profiling)")
     ap.add_argument("--nq", type=int, default=0, help="override the workload's query batch")
     ap.add_argument("--k", type=int, default=0, help="override the workload's k")
+    ap.add_argument("--lanes", type=int, default=0,
+                    help="runtimes alternating steps (0: one on a single GPU, two when sharded so that merge and scan overlap)")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

@@ -224,8 +224,43 @@ __global__ void __launch_bounds__(kThreads, (QT == 1 && CPL <= 4) ? 2 : 1) gemv_
     uint32_t iter = 0;
     uint32_t overflow_seen = 0;
     uint32_t thr[QT];
+    // Rows of the first two tiles are scored before any bound exists.  They are held back (one key per lane and
+    // tile) and enter the pool, filtered, once the first bound has arrived, so the pool never sees a burst.
+    uint64_t early_key[QT][2];
+    bool early_ok[QT][2];
 #pragma unroll
-    for (int q = 0; q < QT; ++q) thr[q] = 0;
+    for (int q = 0; q < QT; ++q) {
+        thr[q] = 0;
+        early_ok[q][0] = early_ok[q][1] = false;
+        early_key[q][0] = early_key[q][1] = 0;
+    }
+    // one reservation per call for all lanes that pass
+    auto append = [&](int q, bool pass, uint64_t key) {
+        const uint32_t ballot = __ballot_sync(0xffffffffu, pass);
+        if (ballot == 0) return;
+        uint32_t base = 0;
+        if (lane == 0) base = atomicAdd(a.ws.count + a.q0 + q, (uint32_t)__popc(ballot));
+        base = __shfl_sync(0xffffffffu, base, 0);
+        if (pass) {
+            const uint32_t pos = base + __popc(ballot & ((1u << lane) - 1u));
+            if (pos < a.ws.cap)
+                a.ws.pool[(size_t)(a.q0 + q) * a.ws.cap + pos] = key;
+            else
+                a.ws.flags[kFlagOverflow] = 1u;
+        }
+    };
+    auto flush_early = [&]() {
+#pragma unroll
+        for (int q = 0; q < QT; ++q) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                if (__any_sync(0xffffffffu, early_ok[q][e])) {
+                    append(q, early_ok[q][e] && (uint32_t)(early_key[q][e] >> 32) >= thr[q], early_key[q][e]);
+                    early_ok[q][e] = false;
+                }
+            }
+        }
+    };
     int stage = 0;
     for (int64_t wt = gw; wt < n_wt; wt += nwarps) {
         ++iter;
@@ -241,17 +276,20 @@ __global__ void __launch_bounds__(kThreads, (QT == 1 && CPL <= 4) ? 2 : 1) gemv_
                 if (overflow_seen != 0) break;
                 overflow_seen = ld_relaxed_u32(a.ws.flags + kFlagOverflow);
             }
-            // Two tiles per warp have entered the pool unfiltered.  Before streaming on, let the first bound
-            // arrive (the warps on refresh duty at tile counts 2 and 3 are computing it), so that the number of
-            // unfiltered rows does not depend on timing.  The wait is bounded; giving up only costs pool space.
-            if (iter == 3 && !a.no_startup_wait && !(warp_in_cta == 0 && (blockIdx.x & 7) == 6)) {
+            // Two tiles per warp have been scored without a bound and are held back.  Before streaming on, let
+            // the first bound arrive (the warps on refresh duty at tile counts 2 and 3 are computing it), then
+            // release the held rows through the filter.  The wait is bounded; giving up only costs pool space.
+            if (iter == 3) {
+                if (!a.no_startup_wait && !(warp_in_cta == 0 && (blockIdx.x & 7) == 6)) {
 #pragma unroll
-                for (int q = 0; q < QT; ++q) {
-                    for (int spin = 0; thr[q] == 0 && spin < 2000; ++spin) {
-                        __nanosleep(32);
-                        thr[q] = ld_relaxed_u32(a.ws.thr + a.q0 + ((q < a.qt) ? q : 0));
+                    for (int q = 0; q < QT; ++q) {
+                        for (int spin = 0; thr[q] == 0 && spin < 2000; ++spin) {
+                            __nanosleep(32);
+                            thr[q] = ld_relaxed_u32(a.ws.thr + a.q0 + ((q < a.qt) ? q : 0));
+                        }
                     }
                 }
+                flush_early();
             }
         }
         cp_async_wait<kStages - 2>();  // the copies of this tile have landed
@@ -394,24 +432,16 @@ __global__ void __launch_bounds__(kThreads, (QT == 1 && CPL <= 4) ? 2 : 1) gemv_
             } else if (mode == kModeTopk) {
                 const float g = score * sign + 0.0f;
                 const uint32_t o = ord_from_float(g);
-                bool pass = false;
-                if (mine) {
-                    bmax[q] = max(bmax[q], o);
-                    pass = o >= thr[q];
-                }
-                // one reservation per warp-tile and query for all rows that passed
-                const uint32_t ballot = __ballot_sync(0xffffffffu, pass);
-                if (ballot != 0) {
-                    uint32_t base = 0;
-                    if (lane == 0) base = atomicAdd(a.ws.count + a.q0 + q, (uint32_t)__popc(ballot));
-                    base = __shfl_sync(0xffffffffu, base, 0);
-                    if (pass) {
-                        const uint32_t pos = base + __popc(ballot & ((1u << lane) - 1u));
-                        if (pos < a.ws.cap)
-                            a.ws.pool[(size_t)(a.q0 + q) * a.ws.cap + pos] = make_key(g, (int32_t)(cv.row_base + my_row));
-                        else
-                            a.ws.flags[kFlagOverflow] = 1u;
-                    }
+                if (mine) bmax[q] = max(bmax[q], o);
+                const uint64_t key = make_key(g, (int32_t)(cv.row_base + my_row));
+                if (iter == 1) {
+                    early_key[q][0] = key;
+                    early_ok[q][0] = mine;
+                } else if (iter == 2) {
+                    early_key[q][1] = key;
+                    early_ok[q][1] = mine;
+                } else {
+                    append(q, mine && o >= thr[q], key);
                 }
             }
         }
@@ -475,6 +505,13 @@ __global__ void __launch_bounds__(kThreads, (QT == 1 && CPL <= 4) ? 2 : 1) gemv_
                 __syncwarp();
             }
         }
+    }
+    if (mode == kModeTopk) {
+        // warps that ran out of tiles before the release point: whatever they still hold goes through the
+        // filter with the freshest bounds
+#pragma unroll
+        for (int q = 0; q < QT; ++q) thr[q] = ld_relaxed_u32(a.ws.thr + a.q0 + ((q < a.qt) ? q : 0));
+        flush_early();
     }
     cp_async_wait<0>();
 }

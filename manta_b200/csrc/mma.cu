@@ -181,6 +181,7 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     uint32_t* thr_s = (uint32_t*)(hdr_s + kMmaCols);
     uint32_t* bmax_s = thr_s + kMmaCols;                 // [qn][4]: maxima of the current tile per epilogue warp
     uint32_t* pub_s = bmax_s + kMmaCols * 4;             // [qn][4][kBucketSlots]: last published values
+    float4* filt_s = (float4*)(pub_s + kMmaCols * 4 * kBucketSlots);  // [qn]: s_hi, s_lo, cheap pre-filter bound
 
     const int64_t nrows = a.row_end - a.row_begin;
     const int n_tiles = (int)((nrows + kTileRows - 1) / kTileRows);
@@ -206,6 +207,7 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     }
     for (int j = threadIdx.x; j < a.qn; j += blockDim.x) {
         hdr_s[j] = a.headers[a.q0 + j];
+        filt_s[j] = make_float4(hdr_s[j].s_hi, hdr_s[j].s_lo, -INFINITY, 0.0f);
         thr_s[j] = 1;
         for (int w = 0; w < 4; ++w) {
             bmax_s[j * 4 + w] = 0;
@@ -278,6 +280,7 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const float sign = (a.order == MANTA_B200_ORDER_SMALLEST) ? -1.0f : 1.0f;
             const bool want_scale = I8 && a.metric != MANTA_B200_METRIC_COSINE;
             const bool want_stats = a.metric != MANTA_B200_METRIC_DOT;
+            const bool cheap = a.order == MANTA_B200_ORDER_LARGEST && a.metric != MANTA_B200_METRIC_L2_DISTANCE;
             unsigned long long c_wait = 0, c_ld = 0, c_math = 0, c_slow = 0, c_house = 0, n_slow = 0, c_thr = 0;
             const bool timing = a.dbg != nullptr && cta == 0 && warp == 4;
             for (int it = 0; it < n_iters; ++it) {
@@ -304,6 +307,9 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 if (timing) { long long t1 = clock64(); c_wait += t1 - t0; t0 = t1; }
                 const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)acc * kMmaCols;
                 const int32_t my_id = (int32_t)(a.cv.row_base + row);
+                // row factor of the pre-filter; NaN for rows past the end makes every comparison false
+                float rowc = __int_as_float(0x7fc00000);
+                if (rv) rowc = (a.metric == MANTA_B200_METRIC_COSINE) ? rinv : (I8 ? sd : 1.0f);
                 for (int c0 = half * 16; c0 < a.qn; c0 += 32) {
                     uint32_t vh[16], vl[16];
                     tmem_ld16(t_row + c0, vh);
@@ -315,6 +321,26 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     }
                     tmem_ld_wait();
                     if (timing) { long long t1 = clock64(); c_ld += t1 - t0; t0 = t1; }
+                    if (cheap) {
+                        // Pre-filter without finishing the scores: score >= bound  <=>  t * rowc >= bound / qinv, the
+                        // right-hand side (slackened by a few ulps) kept per query by the refresher.  Almost every
+                        // chunk ends here; the exact evaluation below decides the rest.
+                        bool hit = false;
+#pragma unroll
+                        for (int jj = 0; jj < 16; ++jj) {
+                            const float4 f = filt_s[min(c0 + jj, a.qn - 1)];
+                            float t;
+                            if constexpr (I8)
+                                t = __fmaf_rn((float)(int)vl[jj], f.y, __fmul_rn((float)(int)vh[jj], f.x));
+                            else
+                                t = __uint_as_float(vh[jj]);
+                            hit = hit || (t * rowc >= f.z);
+                        }
+                        if (!__any_sync(0xffffffffu, hit)) {
+                            if (timing) { long long t1 = clock64(); c_math += t1 - t0; t0 = t1; }
+                            continue;
+                        }
+                    }
                     // scores of 16 queries for this lane's row: straight-line, independent arithmetic
                     float g[16];
                     uint32_t o[16];
@@ -437,6 +463,15 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     const uint32_t v = ld_relaxed_u32(a.ws.thr + a.q0 + jj);
                     thr_s[jj] = max(v, 1u);
                     allset = allset && (v != 0u);
+                    // pre-filter bound: bound / qinv for cosine, the bound itself for dot, lowered by a few ulps
+                    float c = -INFINITY;
+                    if (v > 1u) {
+                        const float tf = float_from_ord(v);
+                        const float qi = hdr_s[jj].qinv;
+                        c = (a.metric == MANTA_B200_METRIC_COSINE) ? ((qi > 0.0f) ? tf / qi : -INFINITY) : tf;
+                        c = c - fabsf(c) * 2e-6f - 1e-30f;
+                    }
+                    filt_s[jj].z = c;
                 }
                 allset = __all_sync(0xffffffffu, allset);
                 if (allset && lane == 0) *thr_ready_s = 1u;
@@ -605,7 +640,7 @@ cudaError_t launch_mma_topk(cudaStream_t stream, int sm_count, MmaState** state,
 
         const size_t stage_bytes = (size_t)kTileRows * kChunkBytes + (size_t)ncols * kChunkBytes;
         const size_t fixed = 1024 /*alignment slack*/ + 256 /*barriers*/ + sizeof(QueryHeader) * kMmaCols + 4 * kMmaCols +
-                             16 * kMmaCols + 16 * kMmaCols * kBucketSlots;
+                             16 * kMmaCols + 16 * kMmaCols * kBucketSlots + 16 * kMmaCols;
         int stages = (int)((220 * 1024 - fixed) / stage_bytes);
         if (stages > 8) stages = 8;
         if (stages < 2) { *why = "not enough shared memory for two pipeline stages"; return cudaErrorInvalidValue; }
