@@ -386,6 +386,12 @@ def run_ours(args, wl: Workload):
         shard_rows = r1 - r0
         algo_bytes = shard_rows * wl.row_bytes()
         achieved = algo_bytes / (scan_ms_per_pass * 1e-3) / 1e9
+        # DRAM traffic per launch from the committed ncu capture of the same kernel on a 2 M-row case
+        # (profiles/gemv_q8_cosine_2Mx768.md: dram__bytes_read+write = 1.5477e9 B for 2e6 rows), scaled by rows;
+        # traffic grows in proportion because every row is read exactly once.
+        traffic = None
+        if wl.layout == "q8" and wl.metric == "cosine" and wl.cols == 768 and nq <= 4:
+            traffic = shard_rows * (1.544046e9 + 3.98e6) / 2e6
         value = args.steps * nq / (total_ms * 1e-3)
         line = {
             "metric": METRIC_NAME if wl.name == "c3" else f"{wl.describe()} queries/s",
@@ -400,7 +406,7 @@ def run_ours(args, wl: Workload):
                              else "inputs smaller than L2 (latency-bound configuration, not a roofline point)"},
             "candidates_dim_per_s": value * wl.rows * wl.cols,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "peak_source": peak_src,
+                         "traffic": traffic, "peak_source": peak_src,
                          "kernel": "tcgen05 scan (mma.cu)" if stats_device["mma_passes"] else "gemv_kernel (gemv.cuh)",
                          "kernel_ms": scan_ms_per_pass, "algorithmic_bytes_per_launch": algo_bytes,
                          "frac_of_nominal_8TBs": achieved / 8000.0},
