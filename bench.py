@@ -45,6 +45,7 @@ class Workload:
     smallest: bool = False
     normalise: bool = True
     note: str = ""
+    embed: tuple = ()  # (vocab, dim, seq): queries come from the embedding front end instead of a query set
 
     def row_bytes(self) -> float:
         """Algorithmic bytes per candidate row and pass: stored codes + the per-row values the metric reads."""
@@ -57,7 +58,9 @@ class Workload:
 
     def describe(self) -> str:
         order = "smallest" if self.smallest else "largest"
-        return (f"{self.layout} {self.metric} {self.rows / 1e6:g}M x {self.cols}, {self.nq} "
+        front = (f"embed(tokens i32[{self.nq},{self.embed[2]}], table f16[{self.embed[0]},{self.embed[1]}], projection "
+                 f"f16[{self.embed[1]},{self.cols}], masked mean_pool, normalize) -> ") if self.embed else ""
+        return (f"{front}{self.layout} {self.metric} {self.rows / 1e6:g}M x {self.cols}, {self.nq} "
                 f"quer{'y' if self.nq == 1 else 'ies'} per pass, k={self.k} {order}")
 
 
@@ -74,6 +77,8 @@ WORKLOADS = {
                         note="the whole 100M x 256 q4 set, query batch 32"),
     "c4q32": Workload("c4q32", "q4", "l2_distance", 12_500_000, 256, 32, 1000, smallest=True, normalise=False,
                       note="one GPU's share (1/8) of the 100M x 256 q4 set, query batch 32"),
+    "c5": Workload("c5", "q8", "dot", 5_000_000, 384, 128, 50, embed=(32000, 384, 128),
+                   note="end to end: token batch -> embedding front end -> q8 dot score + top-k, queries never leave the device"),
 }
 METRIC_NAME = "q8 cosine score+topk queries/s at 10M x 768 candidates (k=10, 1 query per pass)"
 
@@ -156,7 +161,14 @@ def _cpu_sample(wl: Workload, sample_rows: int, nsets: int):
         return _SAMPLE_CACHE[key]
     dev = "cuda" if torch.cuda.is_available() else "cpu"
     x = synth.rows_f16(0, sample_rows, wl.cols, normalise=wl.normalise, device=dev).float().cpu().numpy()
-    q = synth.queries_f16(nsets * wl.nq, wl.cols, normalise=wl.normalise, device=dev).float().cpu().numpy().reshape(nsets, wl.nq, wl.cols)
+    if wl.embed:
+        # the token batches themselves; cpu_reference_pass embeds them inside its timed region
+        nsets = min(nsets, 2)
+        table, proj = synth.embed_weights_f16(wl.embed[0], wl.embed[1], wl.cols, device=dev)
+        tokens, mask = synth.token_batches(nsets, wl.nq, wl.embed[2], wl.embed[0], device=dev)
+        q = (table.float().cpu().numpy(), proj.float().cpu().numpy(), tokens.cpu().numpy(), mask.cpu().numpy())
+    else:
+        q = synth.queries_f16(nsets * wl.nq, wl.cols, normalise=wl.normalise, device=dev).float().cpu().numpy().reshape(nsets, wl.nq, wl.cols)
     if wl.layout == "q8":
         docs = oracle.unpack_q8_rows(*oracle.pack_q8_rows(x))
     elif wl.layout == "q4":
@@ -176,17 +188,26 @@ def cpu_reference_pass(wl: Workload, sample_rows: int, threads: int, steps: int,
 
     oracle.set_threads(threads)
     docs, queries = _cpu_sample(wl, sample_rows, nsets)
-    last, times = None, []
+    last, times, front = None, [], []
     for i in range(warmup + steps):
-        q = queries[i % nsets]
         t0 = time.perf_counter()
+        if wl.embed:
+            table, proj, tokens, mask = queries
+            j = i % tokens.shape[0]
+            q = oracle.half_to_float(oracle.float_to_half(oracle.embed_pooled(table, proj, tokens[j], mask[j], 0)))
+        else:
+            q = queries[i % nsets]
+        tq = time.perf_counter()
         scores = oracle.SCORE_FNS[wl.metric](q, docs)
         last = oracle.topk(scores, min(wl.k, sample_rows), wl.smallest)
         t1 = time.perf_counter()
         if i >= warmup:
-            times.append(t1 - t0)
+            times.append(t1 - tq)
+            front.append(tq - t0)
     sec = sum(times) / len(times)
-    qps = wl.nq / (sec * (wl.rows / sample_rows))
+    front_sec = sum(front) / len(front)  # the embedding front end does not grow with the candidate rows
+    qps = wl.nq / (front_sec + sec * (wl.rows / sample_rows))
+    sec += front_sec
     return qps, sec, np.asarray(last)
 
 
@@ -210,7 +231,7 @@ def run_reference(args, wl: Workload):
     line = {
         "impl": "reference", "metric": METRIC_NAME if wl.name == "c3" else f"{wl.describe()} queries/s",
         "value": qps, "unit": "queries/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": sec * (wl.rows / sample_rows) * 1e3, "higher_is_better": True, "scaling": "strong",
+        "ms_per_step": wl.nq / qps * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f64 accumulate / f32 result" if wl.metric != "dot" else "f32",
         "data": "synthetic",
         "config": {"workload": wl.describe() + " (reference f32 layout, host cores)", "rows": wl.rows, "cols": wl.cols,
@@ -251,6 +272,8 @@ def run_ours(args, wl: Workload):
     n_lanes = args.lanes if args.lanes > 0 else (2 if world > 1 else 1)
     nq, k = wl.nq, wl.k
     nsets = max(1, min(N_QUERY_SET, 4096 // nq))
+    if wl.embed:
+        nsets = 8
 
     class Lane:
         def __init__(self):
@@ -259,6 +282,7 @@ def run_ours(args, wl: Workload):
             with torch.cuda.stream(self.stream):
                 # ids and scores of a rank share one buffer so that a single all-gather carries both
                 self.d_pair, self.d_ids, self.d_scores = sharding.new_pair(nq, k, "cuda")
+                self.d_q = torch.empty((nq, wl.cols), dtype=torch.float16, device="cuda") if wl.embed else None
                 if world > 1:
                     self.g_pair = torch.empty((world, 2, nq, k), dtype=torch.int32, device="cuda")
                     self.g_ids, self.g_scores, _, self.g_stride = sharding.merge_args(self.g_pair, nq, k)
@@ -272,10 +296,21 @@ def run_ours(args, wl: Workload):
     r0, r1 = sharding.shard_bounds(wl.rows, rank, world)
     data, scales = synth.packed_candidates(rt, wl.layout, r0, r1, wl.cols, normalise=wl.normalise)
     cands = rt.bind(wl.layout, data, scales, row_base=r0, rows=r1 - r0, cols=wl.cols)
+    emb = None
     with torch.cuda.stream(stream):
-        d_queries = synth.queries_f16(nsets * nq, wl.cols, normalise=wl.normalise).view(nsets, nq, wl.cols)
+        if wl.embed:
+            vocab, dim, seq = wl.embed
+            table, proj = synth.embed_weights_f16(vocab, dim, wl.cols)
+            d_tokens, d_mask = synth.token_batches(nsets, nq, seq, vocab)
+        else:
+            d_queries = synth.queries_f16(nsets * nq, wl.cols, normalise=wl.normalise).view(nsets, nq, wl.cols)
     stream.synchronize()
-    h_queries = d_queries.cpu().numpy().view(np.uint16)
+    if wl.embed:
+        emb = rt.bind_embedder(table.cpu().numpy().view(np.uint16), proj.cpu().numpy().view(np.uint16))
+        h_tokens = d_tokens.cpu().pin_memory().numpy()
+        h_mask = d_mask.cpu().pin_memory().numpy()
+    else:
+        h_queries = d_queries.cpu().numpy().view(np.uint16)
     d_ids, d_scores, d_pair = lanes[0].d_ids, lanes[0].d_scores, lanes[0].d_pair
     if world > 1:
         g_pair, g_ids, g_scores, g_stride = lanes[0].g_pair, lanes[0].g_ids, lanes[0].g_scores, lanes[0].g_stride
@@ -283,7 +318,12 @@ def run_ours(args, wl: Workload):
 
     def step_device(i):
         ln = lanes[i % n_lanes]
-        ln.rt.score_topk_device(cands, wl.metric, d_queries[i % nsets], nq, k, ln.d_ids, ln.d_scores, smallest=wl.smallest, sync=False)
+        if wl.embed:
+            ln.rt.embed_device(emb, d_tokens[i % nsets], d_mask[i % nsets], nq, wl.embed[2], ln.d_q, sync=False)
+            dq = ln.d_q
+        else:
+            dq = d_queries[i % nsets]
+        ln.rt.score_topk_device(cands, wl.metric, dq, nq, k, ln.d_ids, ln.d_scores, smallest=wl.smallest, sync=False)
         if world > 1:
             with torch.cuda.stream(ln.stream):
                 sharding.gather_pairs(ln.d_pair, ln.g_pair, dist)
@@ -335,7 +375,10 @@ def run_ours(args, wl: Workload):
 
     # ---- end to end through the host-buffer ABI call ------------------------------------------------
     def step_host(i):
-        ids, sc = rt.score_topk(cands, wl.metric, h_queries[i % nsets], k, smallest=wl.smallest)
+        if wl.embed:
+            ids, sc = rt.embed_score_topk(emb, cands, h_tokens[i % nsets], h_mask[i % nsets], wl.metric, k, smallest=wl.smallest)
+        else:
+            ids, sc = rt.score_topk(cands, wl.metric, h_queries[i % nsets], k, smallest=wl.smallest)
         if world > 1:
             with torch.cuda.stream(stream):
                 d_ids.copy_(torch.from_numpy(ids).view(nq, k), non_blocking=False)
@@ -376,7 +419,10 @@ def run_ours(args, wl: Workload):
         sub = rt.bind(wl.layout, data[:sample_rows], None if scales is None else scales[:sample_rows], row_base=0,
                       rows=sample_rows, cols=wl.cols)
         kk = min(k, sample_rows)
-        ids, sc = rt.score_topk(sub, wl.metric, h_queries[(1 + 3 - 1) % nsets], kk, smallest=wl.smallest)
+        if wl.embed:  # the CPU pass cycles through two token batches; its last pass used batch 3 % 2
+            ids, sc = rt.embed_score_topk(emb, sub, h_tokens[1], h_mask[1], wl.metric, kk, smallest=wl.smallest)
+        else:
+            ids, sc = rt.score_topk(sub, wl.metric, h_queries[(1 + 3 - 1) % nsets], kk, smallest=wl.smallest)
         same = (np.asarray(ids).reshape(nq, kk) == ref_ids.reshape(nq, kk))
         parity = {"sample_rows": sample_rows, "ids_equal_oracle": bool(same.all()), "ids_equal_fraction": float(same.mean())}
         sub.unbind()
@@ -410,7 +456,7 @@ def run_ours(args, wl: Workload):
                          "kernel": "tcgen05 scan (mma.cu)" if stats_device["mma_passes"] else "gemv_kernel (gemv.cuh)",
                          "kernel_ms": scan_ms_per_pass, "algorithmic_bytes_per_launch": algo_bytes,
                          "frac_of_nominal_8TBs": achieved / 8000.0},
-            "e2e": {"value": args.steps * nq / e2e_s, "unit": "queries/s", "h2d_bytes_per_step": nq * wl.cols * 2,
+            "e2e": {"value": args.steps * nq / e2e_s, "unit": "queries/s", "h2d_bytes_per_step": (2 * nq * wl.embed[2] * 4) if wl.embed else nq * wl.cols * 2,
                     "d2h_bytes_per_step": nq * k * 8, "ms_per_step": e2e_s / args.steps * 1e3,
                     "note": "host-buffer C-ABI call per step; candidates stay bound (resident) as plan parameters"},
             "gpu_launches": int(launches), "clocks": clocks, "cpu_baseline": cpu, "parity_check": parity,
@@ -419,6 +465,8 @@ def run_ours(args, wl: Workload):
         }
         print(json.dumps(line), flush=True)
     cands.unbind()
+    if emb is not None:
+        rt.unbind_embedder(emb)
     for ln in lanes:
         ln.rt.close()
     if world > 1:

@@ -180,6 +180,39 @@ int manta_b200_topk_merge_device(MantaB200Runtime* rt, int order, const int32_t*
 int manta_b200_gather_rows(MantaB200Runtime* rt, const MantaB200Candidates* set, const int32_t* ids, int64_t n,
                            float* out, char** err);
 
+/* ---- embedding front end: the caller of the score path in the reference's embed pipelines ----------------
+ * gather(token_embedding, tokens) -> @matmul(projection) -> masked mean_pool / normalize
+ * (examples/embed_masked_pooled.manta; steps runtime/backend/tensor_ops.go:31-47, 83-118, 646-658; host math
+ * :751-827 gather, :981-1011 matmul, :1210-1275 masked mean pool, :1114-1138 normalize).  In the reference every
+ * one of these steps uploads and downloads its operands (native_linux.go:3608-3670, 1583-1622) and mean_pool has
+ * no device kernel at all (:1734-1750); here the weights stay resident and the pooled query batch is handed to the
+ * scoring kernels on the device. */
+typedef struct MantaB200Embedder MantaB200Embedder;
+enum {
+    MANTA_B200_POOL_THEN_NORMALIZE = 0, /* normalize(mean_pool(x, mask)) */
+    MANTA_B200_NORMALIZE_THEN_POOL = 1  /* mean_pool(normalize(x), mask), the order of embed_masked_pooled.manta */
+};
+/* table: [vocab, dim] half bits, projection: [dim, out_dim] half bits (row-major, as the reference's @matmul reads
+ * its right operand); mem as for manta_b200_candidates_bind (HOST or DEVICE_COPY). */
+int manta_b200_embedder_bind(MantaB200Runtime* rt, int vocab, int dim, int out_dim, const uint16_t* table,
+                             const uint16_t* projection, int mem, MantaB200Embedder** out, char** err);
+int manta_b200_embedder_unbind(MantaB200Runtime* rt, MantaB200Embedder* emb, char** err);
+/* tokens, mask: host int32 [batch, seq] (mask != 0 keeps a position); out: host f32 [batch, out_dim].
+ * A token outside the table fails with "gather index %d out of range" (tensor_ops.go:803). */
+int manta_b200_embed_pooled(MantaB200Runtime* rt, const MantaB200Embedder* emb, const int32_t* tokens,
+                            const int32_t* mask, int batch, int seq, int pool_order, float* out, char** err);
+/* Device-resident form: tokens / mask are device int32 [batch, seq]; writes the pooled rows rounded to f16 into
+ * d_out_queries [batch, out_dim], ready for manta_b200_score_topk_device on the runtime's stream.  With sync == 0 a
+ * token outside the table is reported by the next manta_b200_runtime_synchronize. */
+int manta_b200_embed_device(MantaB200Runtime* rt, const MantaB200Embedder* emb, const int32_t* d_tokens,
+                            const int32_t* d_mask, int batch, int seq, int pool_order, void* d_out_queries, int sync,
+                            char** err);
+/* Embed, then fused score + top-k against a bound candidate set whose cols == out_dim; the pooled queries are
+ * rounded to f16 on the device and never visit the host.  out_ids / out_scores: host [batch, k]. */
+int manta_b200_embed_score_topk(MantaB200Runtime* rt, const MantaB200Embedder* emb, const MantaB200Candidates* set,
+                                const int32_t* tokens, const int32_t* mask, int batch, int seq, int pool_order,
+                                int metric, int order, int k, int32_t* out_ids, float* out_scores, char** err);
+
 /* Integer accumulators of the packed q8 path for one query: out_acc int32 [rows, 3] =
  * (sum hi*code, sum lo*code, sum code*code) where hi/lo are the two int8 planes the query is split into.
  * Exists so that parity tests can demand bit equality of the integer work. */

@@ -81,7 +81,7 @@ struct MantaB200Runtime {
     std::mutex mu;
     MantaB200Stats stats{};
     // grow-only device buffers
-    DevBuf queries, headers, qf32, plane_hi, plane_lo, pool, count, thr, bucket, flags, out_ids, out_scores, misc;
+    DevBuf queries, headers, qf32, plane_hi, plane_lo, pool, count, thr, bucket, flags, out_ids, out_scores, misc, embed_flag;
     // pinned host staging
     void* h_stage = nullptr;
     size_t h_stage_bytes = 0;
@@ -93,6 +93,7 @@ struct MantaB200Runtime {
     cudaEvent_t prof_ev[2 * kMaxProf];
     int prof_created = 0;
     int prof_used = 0;
+    bool async_embed_pending = false;  // a sync == 0 embed pass copied its bad-token word to h_flags[10..11]
     bool async_flags_pending = false;  // a sync == 0 pass copied its flags to h_flags; checked at synchronize
 };
 
@@ -106,6 +107,13 @@ static void prof_mark(MantaB200Runtime* rt, int which) {
     cudaEventRecord(rt->prof_ev[idx], rt->stream);
     if (which == 1) rt->prof_used++;
 }
+
+struct MantaB200Embedder {
+    int device = 0;
+    int vocab = 0, dim = 0, out_dim = 0;
+    void* d_table = nullptr;
+    void* d_proj = nullptr;
+};
 
 struct MantaB200Candidates {
     CandView cv{};
@@ -208,7 +216,7 @@ int manta_b200_runtime_destroy(MantaB200Runtime* rt, char** err) {
     cudaSetDevice(rt->device);
     cudaError_t e = cudaStreamSynchronize(rt->stream);
     DevBuf* bufs[] = {&rt->queries, &rt->headers, &rt->qf32, &rt->plane_hi, &rt->plane_lo, &rt->pool, &rt->count,
-                      &rt->thr, &rt->bucket, &rt->flags, &rt->out_ids, &rt->out_scores, &rt->misc};
+                      &rt->thr, &rt->bucket, &rt->flags, &rt->out_ids, &rt->out_scores, &rt->misc, &rt->embed_flag};
     for (DevBuf* b : bufs) free_buf(*b);
     mma_state_destroy(rt->mma);
     for (int i = 0; i < rt->prof_created; ++i) cudaEventDestroy(rt->prof_ev[i]);
@@ -231,6 +239,10 @@ int manta_b200_runtime_synchronize(MantaB200Runtime* rt, char** err) {
     std::lock_guard<std::mutex> lk(rt->mu);
     CU_TRY(cudaSetDevice(rt->device));
     CU_TRY(cudaStreamSynchronize(rt->stream));
+    if (rt->async_embed_pending) {
+        rt->async_embed_pending = false;
+        if (rt->h_flags[10]) return fail(err, "gather index %d out of range", (int32_t)rt->h_flags[11]);
+    }
     if (rt->async_flags_pending) {
         rt->async_flags_pending = false;
         if (rt->h_flags[kFlagTimeout]) return fail(err, "runtime_synchronize: a bounded device wait gave up in an asynchronous pass");
@@ -754,6 +766,151 @@ int manta_b200_score(MantaB200Runtime* rt, const MantaB200Candidates* set, int m
     CU_TRY(cudaStreamSynchronize(rt->stream));
     rt->stats.h2d_bytes += qbytes;
     rt->stats.d2h_bytes += obytes;
+    return 0;
+}
+
+// ---- embedding front end ------------------------------------------------------------------------------------
+int manta_b200_embedder_bind(MantaB200Runtime* rt, int vocab, int dim, int out_dim, const uint16_t* table,
+                             const uint16_t* projection, int mem, MantaB200Embedder** out, char** err) {
+    if (!rt || !table || !projection || !out) return fail(err, "embedder_bind: NULL argument");
+    *out = nullptr;
+    if (vocab <= 0 || dim <= 0 || out_dim <= 0 || out_dim > 1024 || dim > 4096)
+        return fail(err, "embedder_bind: shape [%d,%d] x [%d,%d] out of range", vocab, dim, dim, out_dim);
+    if (mem != MANTA_B200_MEM_HOST && mem != MANTA_B200_MEM_DEVICE_COPY) return fail(err, "embedder_bind: mem must be HOST or DEVICE_COPY");
+    std::lock_guard<std::mutex> lk(rt->mu);
+    CU_TRY(cudaSetDevice(rt->device));
+    MantaB200Embedder* e = new (std::nothrow) MantaB200Embedder();
+    if (!e) return fail(err, "embedder_bind: out of host memory");
+    e->device = rt->device;
+    e->vocab = vocab;
+    e->dim = dim;
+    e->out_dim = out_dim;
+    const cudaMemcpyKind kind = (mem == MANTA_B200_MEM_HOST) ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToDevice;
+    const size_t tb = (size_t)vocab * dim * 2, pb = (size_t)dim * out_dim * 2;
+    cudaError_t ce = cudaMalloc(&e->d_table, tb);
+    if (ce == cudaSuccess) ce = cudaMalloc(&e->d_proj, pb);
+    if (ce == cudaSuccess) ce = cudaMemcpyAsync(e->d_table, table, tb, kind, rt->stream);
+    if (ce == cudaSuccess) ce = cudaMemcpyAsync(e->d_proj, projection, pb, kind, rt->stream);
+    if (ce == cudaSuccess) ce = cudaStreamSynchronize(rt->stream);
+    if (ce != cudaSuccess) {
+        if (e->d_table) cudaFree(e->d_table);
+        if (e->d_proj) cudaFree(e->d_proj);
+        delete e;
+        return fail_cuda(err, "embedder_bind", ce);
+    }
+    rt->stats.bind_calls++;
+    rt->stats.bound_bytes += tb + pb;
+    if (mem == MANTA_B200_MEM_HOST) rt->stats.h2d_bytes += tb + pb;
+    *out = e;
+    return 0;
+}
+
+int manta_b200_embedder_unbind(MantaB200Runtime* rt, MantaB200Embedder* emb, char** err) {
+    if (!emb) return 0;
+    if (!rt) return fail(err, "embedder_unbind: NULL runtime");
+    std::lock_guard<std::mutex> lk(rt->mu);
+    CU_TRY(cudaSetDevice(rt->device));
+    CU_TRY(cudaStreamSynchronize(rt->stream));
+    cudaFree(emb->d_table);
+    cudaFree(emb->d_proj);
+    delete emb;
+    return 0;
+}
+
+// Runs the embed kernel on device tokens / mask into d_out_f32 and / or d_out_f16.  Caller holds the lock.  With
+// sync the bad-token word is read back and reported here, otherwise at the next runtime_synchronize.
+static int embed_device_locked(MantaB200Runtime* rt, const MantaB200Embedder* emb, const int32_t* d_tok, const int32_t* d_mask,
+                               int batch, int seq, int pool_order, float* d_out_f32, void* d_out_f16, int sync, char** err) {
+    if (ensure(rt, rt->embed_flag, 16, err)) return 1;
+    uint32_t* d_flag = (uint32_t*)rt->embed_flag.p;
+    int32_t* d_bad = (int32_t*)rt->embed_flag.p + 1;
+    CU_TRY(cudaMemsetAsync(d_flag, 0, 8, rt->stream));
+    cudaError_t e = launch_embed_pooled(rt->stream, emb->d_table, emb->vocab, emb->dim, emb->d_proj, emb->out_dim, d_tok, d_mask, batch,
+                                        seq, pool_order, d_out_f32, d_out_f16, d_bad, d_flag);
+    rt->stats.kernel_launches++;
+    if (e != cudaSuccess) return fail_cuda(err, "launch embed kernel", e);
+    CU_TRY(cudaMemcpyAsync(&rt->h_flags[10], d_flag, 8, cudaMemcpyDeviceToHost, rt->stream));
+    if (!sync) {
+        rt->async_embed_pending = true;
+        return 0;
+    }
+    CU_TRY(cudaStreamSynchronize(rt->stream));
+    rt->async_embed_pending = false;
+    if (rt->h_flags[10]) return fail(err, "gather index %d out of range", (int32_t)rt->h_flags[11]);  // tensor_ops.go:803
+    return 0;
+}
+
+// Uploads host tokens + mask (staged in rt->out_ids), then embeds into rt->queries (f16) and optionally rt->misc (f32).
+static int embed_locked(MantaB200Runtime* rt, const MantaB200Embedder* emb, const int32_t* tokens, const int32_t* mask, int batch,
+                        int seq, int pool_order, bool want_f32, char** err) {
+    const size_t tb = (size_t)batch * seq * 4;
+    if (ensure(rt, rt->out_ids, 2 * tb, err)) return 1;
+    if (ensure(rt, rt->queries, (size_t)batch * emb->out_dim * 2, err)) return 1;
+    if (want_f32 && ensure(rt, rt->misc, (size_t)batch * emb->out_dim * 4, err)) return 1;
+    int32_t* d_tok = (int32_t*)rt->out_ids.p;
+    int32_t* d_mask = d_tok + (size_t)batch * seq;
+    CU_TRY(cudaMemcpyAsync(d_tok, tokens, tb, cudaMemcpyHostToDevice, rt->stream));
+    CU_TRY(cudaMemcpyAsync(d_mask, mask, tb, cudaMemcpyHostToDevice, rt->stream));
+    rt->stats.h2d_bytes += 2 * tb;
+    return embed_device_locked(rt, emb, d_tok, d_mask, batch, seq, pool_order, want_f32 ? (float*)rt->misc.p : nullptr, rt->queries.p,
+                               1, err);
+}
+
+static int check_embed_args(const MantaB200Runtime* rt, const MantaB200Embedder* emb, const int32_t* tokens, const int32_t* mask,
+                            int batch, int seq, int pool_order, char** err) {
+    if (!rt || !emb || !tokens || !mask) return fail(err, "embed: NULL argument");
+    if (emb->device != rt->device) return fail(err, "embed: embedder lives on device %d, runtime on %d", emb->device, rt->device);
+    if (batch <= 0 || seq <= 0 || seq > 8192) return fail(err, "embed: tokens shape [%d,%d] out of range", batch, seq);
+    if (pool_order != MANTA_B200_POOL_THEN_NORMALIZE && pool_order != MANTA_B200_NORMALIZE_THEN_POOL) return fail(err, "embed: unknown pool order %d", pool_order);
+    return 0;
+}
+
+int manta_b200_embed_pooled(MantaB200Runtime* rt, const MantaB200Embedder* emb, const int32_t* tokens, const int32_t* mask,
+                            int batch, int seq, int pool_order, float* out, char** err) {
+    if (check_embed_args(rt, emb, tokens, mask, batch, seq, pool_order, err)) return 1;
+    if (!out) return fail(err, "embed: NULL output");
+    std::lock_guard<std::mutex> lk(rt->mu);
+    CU_TRY(cudaSetDevice(rt->device));
+    if (embed_locked(rt, emb, tokens, mask, batch, seq, pool_order, true, err)) return 1;
+    const size_t ob = (size_t)batch * emb->out_dim * 4;
+    CU_TRY(cudaMemcpyAsync(out, rt->misc.p, ob, cudaMemcpyDeviceToHost, rt->stream));
+    CU_TRY(cudaStreamSynchronize(rt->stream));
+    rt->stats.d2h_bytes += ob;
+    return 0;
+}
+
+int manta_b200_embed_device(MantaB200Runtime* rt, const MantaB200Embedder* emb, const int32_t* d_tokens, const int32_t* d_mask,
+                            int batch, int seq, int pool_order, void* d_out_queries_f16, int sync, char** err) {
+    if (check_embed_args(rt, emb, d_tokens, d_mask, batch, seq, pool_order, err)) return 1;
+    if (!d_out_queries_f16) return fail(err, "embed: NULL output");
+    std::lock_guard<std::mutex> lk(rt->mu);
+    CU_TRY(cudaSetDevice(rt->device));
+    return embed_device_locked(rt, emb, d_tokens, d_mask, batch, seq, pool_order, nullptr, d_out_queries_f16, sync, err);
+}
+
+int manta_b200_embed_score_topk(MantaB200Runtime* rt, const MantaB200Embedder* emb, const MantaB200Candidates* set,
+                                const int32_t* tokens, const int32_t* mask, int batch, int seq, int pool_order, int metric,
+                                int order, int k, int32_t* out_ids, float* out_scores, char** err) {
+    if (check_embed_args(rt, emb, tokens, mask, batch, seq, pool_order, err)) return 1;
+    if (check_score_args(rt, set, metric, batch, err)) return 1;
+    if (check_topk_args(set, order, k, err)) return 1;
+    if (!out_ids || !out_scores) return fail(err, "embed_score_topk: NULL output");
+    if (set->cv.cols != emb->out_dim) return fail(err, "score mismatch [%d %d] x [%lld %d]", batch, emb->out_dim, (long long)set->cv.rows, set->cv.cols);
+    std::lock_guard<std::mutex> lk(rt->mu);
+    CU_TRY(cudaSetDevice(rt->device));
+    rt->stats.score_topk_calls++;
+    const size_t obytes = (size_t)batch * k * 4;
+    // result buffers live in misc (out_ids holds the tokens until the embed kernel has run)
+    if (ensure(rt, rt->misc, 2 * obytes + 256, err)) return 1;
+    if (embed_locked(rt, emb, tokens, mask, batch, seq, pool_order, false, err)) return 1;
+    int32_t* d_ids = (int32_t*)rt->misc.p;
+    float* d_sc = (float*)((char*)rt->misc.p + (obytes + 255) / 256 * 256);
+    int rc = score_topk_locked(rt, set, metric, order, rt->queries.p, batch, k, d_ids, d_sc, 1, err);
+    if (rc) return rc;
+    CU_TRY(cudaMemcpyAsync(out_ids, d_ids, obytes, cudaMemcpyDeviceToHost, rt->stream));
+    CU_TRY(cudaMemcpyAsync(out_scores, d_sc, obytes, cudaMemcpyDeviceToHost, rt->stream));
+    CU_TRY(cudaStreamSynchronize(rt->stream));
+    rt->stats.d2h_bytes += 2 * obytes;
     return 0;
 }
 

@@ -27,6 +27,12 @@ void launch_pack_q4(cudaStream_t st, const void* d_src, bool src_f16, int64_t ro
 void launch_gather_rows(cudaStream_t st, const CandView& cv, const int32_t* d_ids, int64_t n, float* d_out,
                         int32_t* d_bad_id, uint32_t* d_bad_flag);
 
+// Embedding front end: gather -> matmul -> masked mean_pool / normalize (order 0: normalize(mean_pool(x)),
+// 1: mean_pool(normalize(x))); writes the pooled rows as f32 and / or f16.
+cudaError_t launch_embed_pooled(cudaStream_t st, const void* table_f16, int vocab, int dim, const void* proj_f16, int out_dim,
+                                const int32_t* d_tokens, const int32_t* d_mask, int batch, int seq, int order, float* d_out_f32,
+                                void* d_out_f16, int32_t* d_bad_token, uint32_t* d_bad_flag);
+
 // Streaming (GEMV) scoring kernel.  mode: what the epilogue does with a score.
 enum { kModeScores = 0, kModeTopk = 1, kModeAccum = 2 };
 struct GemvArgs {

@@ -33,6 +33,8 @@ EXPORTS = [
     "manta_b200_pack_q8_rows_device", "manta_b200_pack_q4_b32_device", "manta_b200_score",
     "manta_b200_score_topk", "manta_b200_score_topk_device", "manta_b200_topk_merge_device",
     "manta_b200_gather_rows", "manta_b200_q8_accumulators", "manta_b200_score_topk_static",
+    "manta_b200_embedder_bind", "manta_b200_embedder_unbind", "manta_b200_embed_pooled", "manta_b200_embed_score_topk",
+    "manta_b200_embed_device",
 ]
 
 
@@ -90,6 +92,12 @@ def load() -> ctypes.CDLL:
         "manta_b200_topk_merge_device": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_void_p,
                                          c_void_p, c_int, E],
         "manta_b200_gather_rows": [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, E],
+        "manta_b200_embedder_bind": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, POINTER(c_void_p), E],
+        "manta_b200_embedder_unbind": [c_void_p, c_void_p, E],
+        "manta_b200_embed_pooled": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, E],
+        "manta_b200_embed_device": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, E],
+        "manta_b200_embed_score_topk": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                        c_int, c_void_p, c_void_p, E],
         "manta_b200_q8_accumulators": [c_void_p, c_void_p, c_void_p, c_void_p, E],
     }
     for name, args in sigs.items():
@@ -299,6 +307,43 @@ class Runtime:
         call("manta_b200_topk_merge_device", self.handle, c_int(ORDER_SMALLEST if smallest else ORDER_LARGEST), _ptr(d_ids),
              _ptr(d_scores), c_int(lists), c_int64(list_stride), c_int(nq), c_int(k), _ptr(d_out_ids), _ptr(d_out_scores),
              c_int(1 if sync else 0))
+
+    # ---- embedding front end -----------------------------------------------------------------------------
+    def bind_embedder(self, table, projection):
+        """table [V,D], projection [D,E] (float arrays are rounded to f16); returns an opaque handle."""
+        t, p = f16_bits(table), f16_bits(projection)
+        h = c_void_p()
+        call("manta_b200_embedder_bind", self.handle, c_int(t.shape[0]), c_int(t.shape[1]), c_int(p.shape[1]), _ptr(t), _ptr(p),
+             c_int(MEM_HOST), byref(h))
+        return h
+
+    def unbind_embedder(self, emb):
+        call("manta_b200_embedder_unbind", self.handle, emb)
+
+    def embed_pooled(self, emb, out_dim: int, tokens, mask, normalize_then_pool: bool = False) -> np.ndarray:
+        tokens = np.ascontiguousarray(tokens, dtype=np.int32)
+        mask = np.ascontiguousarray(mask, dtype=np.int32)
+        out = np.empty((tokens.shape[0], out_dim), np.float32)
+        call("manta_b200_embed_pooled", self.handle, emb, _ptr(tokens), _ptr(mask), c_int(tokens.shape[0]), c_int(tokens.shape[1]),
+             c_int(1 if normalize_then_pool else 0), _ptr(out))
+        return out
+
+    def embed_device(self, emb, d_tokens, d_mask, batch: int, seq: int, d_out_queries, normalize_then_pool: bool = False,
+                     sync: bool = False):
+        call("manta_b200_embed_device", self.handle, emb, _ptr(d_tokens), _ptr(d_mask), c_int(batch), c_int(seq),
+             c_int(1 if normalize_then_pool else 0), _ptr(d_out_queries), c_int(1 if sync else 0))
+
+    def embed_score_topk(self, emb, cands: Candidates, tokens, mask, metric: str, k: int, smallest: bool = False,
+                         normalize_then_pool: bool = False):
+        tokens = np.ascontiguousarray(tokens, dtype=np.int32)
+        mask = np.ascontiguousarray(mask, dtype=np.int32)
+        b = tokens.shape[0]
+        ids = np.empty((b, max(k, 0)), np.int32)
+        scores = np.empty((b, max(k, 0)), np.float32)
+        call("manta_b200_embed_score_topk", self.handle, emb, cands.handle, _ptr(tokens), _ptr(mask), c_int(b), c_int(tokens.shape[1]),
+             c_int(1 if normalize_then_pool else 0), c_int(METRICS[metric]), c_int(ORDER_SMALLEST if smallest else ORDER_LARGEST),
+             c_int(int(k)), _ptr(ids), _ptr(scores))
+        return ids, scores
 
     def gather_rows(self, cands: Candidates, ids) -> np.ndarray:
         ids = np.ascontiguousarray(ids, dtype=np.int32)

@@ -12,6 +12,8 @@ import torch
 CHUNK = 1 << 18  # rows per generator seed
 SEED_DOCS = 0x4D414E54
 SEED_QUERIES = SEED_DOCS + 1
+SEED_TOKENS = SEED_DOCS + 2
+SEED_WEIGHTS = SEED_DOCS + 3
 
 
 def _chunk_f16(seed: int, chunk: int, cols: int, normalise: bool, device) -> torch.Tensor:
@@ -75,3 +77,22 @@ def packed_candidates(rt, layout: str, row_begin: int, row_end: int, cols: int, 
                 rt.pack_q4_b32_device(src, True, n, cols, data[o:o + n], scales[o:o + n])
             stream.synchronize()  # src is released after the pack kernel has consumed it
     return data, scales
+
+
+def embed_weights_f16(vocab: int, dim: int, out_dim: int, seed: int = SEED_WEIGHTS, device="cuda"):
+    """token_embedding f16[vocab, dim] ~ N(0, 0.02) and projection f16[dim, out_dim] ~ N(0, 0.05)."""
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    table = (torch.randn((vocab, dim), generator=g, device=device, dtype=torch.float32) * 0.02).to(torch.float16)
+    proj = (torch.randn((dim, out_dim), generator=g, device=device, dtype=torch.float32) * 0.05).to(torch.float16)
+    return table, proj
+
+
+def token_batches(nsets: int, batch: int, seq: int, vocab: int, min_len: int = 16, seed: int = SEED_TOKENS, device="cuda"):
+    """tokens i32[nsets, batch, seq] uniform in [0, vocab) and the mask of lengths uniform in min_len..seq."""
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    tokens = torch.randint(0, vocab, (nsets, batch, seq), generator=g, device=device, dtype=torch.int32)
+    lengths = torch.randint(min(min_len, seq), seq + 1, (nsets, batch, 1), generator=g, device=device, dtype=torch.int32)
+    mask = (torch.arange(seq, device=device, dtype=torch.int32).view(1, 1, seq) < lengths).to(torch.int32)
+    return tokens, mask

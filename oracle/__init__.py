@@ -241,3 +241,19 @@ def score_topk(metric: str, queries, docs_f32, k: int, smallest: bool = False):
     ids = topk(scores, k, smallest)
     top = np.take_along_axis(scores, ids.astype(np.int64), axis=1)
     return (ids[0], top[0]) if one else (ids, top)
+
+
+def embed_pooled(table, proj, tokens, mask, order: int = 0) -> np.ndarray:
+    """gather -> matmul -> masked mean_pool / normalize in the given order (0: normalize(mean_pool(x)),
+    1: mean_pool(normalize(x))); table [V,D], proj [D,E], tokens/mask i32 [B,T] -> f32 [B,E]."""
+    table, proj = _f32(table), _f32(proj)
+    tokens = np.ascontiguousarray(tokens, dtype=np.int32)
+    mask = np.ascontiguousarray(mask, dtype=np.int32)
+    b, t = tokens.shape
+    out = np.empty((b, proj.shape[1]), dtype=np.float32)
+    rc = lib().mo_embed_pooled(_p(table), ctypes.c_int64(table.shape[0]), ctypes.c_int64(table.shape[1]), _p(proj),
+                               ctypes.c_int64(proj.shape[1]), _p(tokens), _p(mask), ctypes.c_int64(b), ctypes.c_int64(t),
+                               ctypes.c_int(order), _p(out))
+    if rc != 0:
+        raise OracleError("gather index out of range")
+    return out

@@ -564,3 +564,74 @@ int mo_q8_model_scores(const float* query, const int8_t* codes, const float* sca
     free(lo);
     return MO_OK;
 }
+
+/* ---- embedding front end (the callers' side of the score path) ------------------------------------ */
+
+/* gatherTensor on a rank-2 table (runtime/backend/tensor_ops.go:794-827) -> matmulTensor rank-3 x rank-2
+ * (:981-1011 and its batched form: f32 sequential accumulate, products and sums rounded separately) ->
+ * meanPoolMaskedTensor (:1210-1275: rows with mask != 0 summed in order in f32, times 1/count) and
+ * normalizeRows (:1114-1138: f64 sum of squares, f32 norm, f32 divide; zero rows untouched), in either order:
+ *   order 0: normalize(mean_pool(x, mask))   (the end-to-end embed+score configuration)
+ *   order 1: mean_pool(normalize(x), mask)   (examples/embed_masked_pooled.manta)
+ * table [vocab, dim] and proj [dim, out] are f32 (f16-representable values); tokens / mask are [batch, seq].
+ * Returns MO_ERR_RANGE for a token outside the table. */
+int mo_embed_pooled(const float* table, int64_t vocab, int64_t dim, const float* proj, int64_t out_dim,
+                    const int32_t* tokens, const int32_t* mask, int64_t batch, int64_t seq, int order, float* out) {
+    for (int64_t i = 0; i < batch * seq; i++)
+        if (tokens[i] < 0 || tokens[i] >= vocab) return MO_ERR_RANGE;
+    int rc = MO_OK;
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int64_t b = 0; b < batch; b++) {
+        float* projected = (float*)malloc((size_t)out_dim * sizeof(float));
+        float* pooled = out + b * out_dim;
+        if (!projected) {
+            rc = MO_ERR_RANGE;
+            continue;
+        }
+        for (int64_t c = 0; c < out_dim; c++) pooled[c] = 0.0f;
+        int count = 0;
+        for (int64_t t = 0; t < seq; t++) {
+            if (mask[b * seq + t] == 0) continue; /* unmasked rows never reach the output */
+            const float* h = table + (int64_t)tokens[b * seq + t] * dim;
+            for (int64_t c = 0; c < out_dim; c++) {
+                float sum = 0.0f;
+                for (int64_t k = 0; k < dim; k++) {
+                    volatile float p = h[k] * proj[k * out_dim + c];
+                    sum += p;
+                }
+                projected[c] = sum;
+            }
+            if (order == 1) { /* normalizeRows on this row */
+                double ss = 0.0;
+                for (int64_t c = 0; c < out_dim; c++) ss += (double)projected[c] * (double)projected[c];
+                float norm = (float)sqrt(ss);
+                if (norm != 0.0f)
+                    for (int64_t c = 0; c < out_dim; c++) {
+                        volatile float v = projected[c] / norm;
+                        projected[c] = v;
+                    }
+            }
+            count++;
+            for (int64_t c = 0; c < out_dim; c++) pooled[c] += projected[c];
+        }
+        if (count > 0) {
+            volatile float inv = 1.0f / (float)count;
+            for (int64_t c = 0; c < out_dim; c++) {
+                volatile float v = pooled[c] * inv;
+                pooled[c] = v;
+            }
+        }
+        if (order == 0) {
+            double ss = 0.0;
+            for (int64_t c = 0; c < out_dim; c++) ss += (double)pooled[c] * (double)pooled[c];
+            float norm = (float)sqrt(ss);
+            if (norm != 0.0f)
+                for (int64_t c = 0; c < out_dim; c++) {
+                    volatile float v = pooled[c] / norm;
+                    pooled[c] = v;
+                }
+        }
+        free(projected);
+    }
+    return rc;
+}

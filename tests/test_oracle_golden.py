@@ -182,3 +182,34 @@ def test_q8_model_close_to_reference_float_path():
         err = np.abs(got - ref) / np.maximum(np.maximum(np.abs(got), np.abs(ref)), floor)
         assert err.max() < 1e-3, (metric, err.max())
         np.testing.assert_array_equal(acc[:, 2], (codes.astype(np.int32) ** 2).sum(axis=1))
+
+
+@pytest.mark.parametrize("case", GOLD["embed"], ids=lambda c: c["source"].split()[1])
+def test_embed_pooled_kat(case):
+    out = oracle.embed_pooled(np.array(case["table"], np.float32), np.array(case["projection"], np.float32),
+                              np.array(case["tokens"], np.int32), np.array(case["mask"], np.int32), case["order"])
+    np.testing.assert_allclose(out, np.array(case["want"], np.float32), atol=TOL, rtol=0)
+
+
+def test_embed_pooled_against_numpy():
+    rng = np.random.default_rng(5)
+    table = oracle.half_to_float(oracle.float_to_half(rng.normal(0, 0.02, (500, 48)).astype(np.float32)))
+    proj = oracle.half_to_float(oracle.float_to_half(rng.normal(0, 0.05, (48, 40)).astype(np.float32)))
+    tokens = rng.integers(0, 500, (6, 17)).astype(np.int32)
+    lengths = np.array([17, 1, 9, 0, 16, 3])
+    mask = (np.arange(17)[None, :] < lengths[:, None]).astype(np.int32)
+    x = table[tokens].astype(np.float64) @ proj.astype(np.float64)
+    m = mask[:, :, None].astype(np.float64)
+    cnt = np.maximum(lengths, 1)[:, None]
+    pooled = (x * m).sum(1) / cnt
+    n = np.linalg.norm(pooled, axis=1, keepdims=True)
+    want0 = np.where(n > 0, pooled / np.where(n > 0, n, 1), pooled)
+    xn = x / np.linalg.norm(x, axis=2, keepdims=True)
+    want1 = (xn * m).sum(1) / cnt
+    np.testing.assert_allclose(oracle.embed_pooled(table, proj, tokens, mask, 0), want0, atol=2e-6)
+    np.testing.assert_allclose(oracle.embed_pooled(table, proj, tokens, mask, 1), want1, atol=2e-6)
+    assert not oracle.embed_pooled(table, proj, tokens, mask, 0)[3].any()  # an all-masked row pools to zeros
+    bad = tokens.copy()
+    bad[0, 0] = 500
+    with pytest.raises(oracle.OracleError, match="out of range"):
+        oracle.embed_pooled(table, proj, bad, mask, 0)
