@@ -60,8 +60,12 @@ def test_embed_matches_oracle(rt, vocab, dim, out_dim, batch, seq, order):
     finally:
         rt.unbind_embedder(emb)
     want = oracle.embed_pooled(table, proj, tokens, mask, order)
-    # same f32 operation order for the products and the pooling; the sum of squares is a parallel f64 reduction
-    np.testing.assert_allclose(got, want, atol=3e-7, rtol=1e-6)
+    if order == 1:
+        # same f32 operation order for the products and the pooling; the sums of squares are parallel f64 reductions
+        np.testing.assert_allclose(got, want, atol=3e-7, rtol=1e-6)
+    else:
+        # the pool is taken before the projection (it is linear): f32 sums associate differently from the oracle's
+        np.testing.assert_allclose(got, want, atol=2e-6, rtol=2e-5)
     assert not got[-1].any()
 
 
