@@ -129,6 +129,7 @@ struct KernelArgs {
     int lo_off;                   // q8: column offset of the low planes
     int kchunks;                  // 128-byte chunks per row
     int stages;
+    int b_resident;               // operand B (all K chunks) is loaded once and stays in shared memory
     int metric;
     int order;
     int k;
@@ -158,7 +159,7 @@ __device__ __forceinline__ void score16(const uint32_t (&vh)[16], const uint32_t
     }
 }
 
-template <bool I8>
+template <bool I8, int METRIC>
 __global__ void __launch_bounds__(kMmaThreads, 1)
 mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const KernelArgs a) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -168,12 +169,13 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* sA = base;
     unsigned char* sB = sA + (size_t)S * kTileRows * kChunkBytes;
-    unsigned char* p = sB + (size_t)S * b_stage_bytes;
+    unsigned char* p = sB + (size_t)(a.b_resident ? a.kchunks : S) * b_stage_bytes;
     uint64_t* full = (uint64_t*)p;
     uint64_t* empty = full + 8;
     uint64_t* tfull = empty + 8;
     uint64_t* tempty = tfull + 2;
-    uint32_t* tmem_slot = (uint32_t*)(tempty + 2);
+    uint64_t* bfull = tempty + 2;
+    uint32_t* tmem_slot = (uint32_t*)(bfull + 1);
     volatile uint32_t* abort_s = tmem_slot + 1;
     volatile uint32_t* done_s = tmem_slot + 2;       // epilogue warps that have finished
     volatile uint32_t* thr_ready_s = tmem_slot + 3;  // set by the refresher once every query has a bound
@@ -200,6 +202,7 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             mbar_init(&tfull[b], 1);
             mbar_init(&tempty[b], kEpiWarps);
         }
+        mbar_init(bfull, 1);
         *abort_s = 0;
         *done_s = 0;
         *thr_ready_s = 0;
@@ -227,15 +230,22 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             // ---------------- TMA producer ----------------
             if (lane == 0) {
                 uint32_t g = 0;
+                if (a.b_resident) {
+                    // the query operand fits beside the candidate ring: one load, then only candidates stream
+                    mbar_expect_tx(bfull, (uint32_t)a.kchunks * b_stage_bytes);
+                    for (int kc = 0; kc < a.kchunks; ++kc)
+                        tma_load_2d(sB + (size_t)kc * b_stage_bytes, &map_b, kc * kChunkBytes, 0, bfull);
+                }
+                const uint32_t stage_tx = (uint32_t)(kTileRows * kChunkBytes) + (a.b_resident ? 0u : b_stage_bytes);
                 for (int it = 0; it < n_iters && !*abort_s; ++it) {
                     const int row0 = (int)(a.row_begin + (int64_t)tile_of(it) * kTileRows);
                     for (int kc = 0; kc < a.kchunks; ++kc, ++g) {
                         const int s = g % S;
                         const uint32_t ph = (g / S) & 1u;
                         if (!mbar_wait(&empty[s], ph ^ 1u, abort_s)) break;
-                        mbar_expect_tx(&full[s], (uint32_t)(kTileRows * kChunkBytes) + b_stage_bytes);
+                        mbar_expect_tx(&full[s], stage_tx);
                         tma_load_2d(sA + (size_t)s * kTileRows * kChunkBytes, &map_a, kc * kChunkBytes, row0, &full[s]);
-                        tma_load_2d(sB + (size_t)s * b_stage_bytes, &map_b, kc * kChunkBytes, 0, &full[s]);
+                        if (!a.b_resident) tma_load_2d(sB + (size_t)s * b_stage_bytes, &map_b, kc * kChunkBytes, 0, &full[s]);
                     }
                 }
             }
@@ -245,7 +255,12 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 const uint32_t idesc = I8 ? ((2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(a.ncols >> 3) << 17) | ((uint32_t)(kTileRows >> 4) << 24))
                                           : ((1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(a.ncols >> 3) << 17) | ((uint32_t)(kTileRows >> 4) << 24));
                 uint32_t g = 0;
-                for (int it = 0; it < n_iters && !*abort_s; ++it) {
+                bool b_ok = true;
+                if (a.b_resident) {
+                    b_ok = mbar_wait(bfull, 0u, abort_s);
+                    tc_fence_after();
+                }
+                for (int it = 0; b_ok && it < n_iters && !*abort_s; ++it) {
                     const int acc = it & 1;
                     if (!mbar_wait(&tempty[acc], ((uint32_t)(it >> 1) & 1u) ^ 1u, abort_s)) break;
                     tc_fence_after();
@@ -257,7 +272,7 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         if (!mbar_wait(&full[s], ph, abort_s)) { ok = false; break; }
                         tc_fence_after();
                         const uint32_t a_addr = smem_u32(sA + (size_t)s * kTileRows * kChunkBytes);
-                        const uint32_t b_addr = smem_u32(sB + (size_t)s * b_stage_bytes);
+                        const uint32_t b_addr = smem_u32(sB + (size_t)(a.b_resident ? kc : s) * b_stage_bytes);
 #pragma unroll
                         for (int ks = 0; ks < kChunkBytes / 32; ++ks) {
                             tc_mma<I8>(d_tmem, smem_desc_sw128(a_addr + ks * 32), smem_desc_sw128(b_addr + ks * 32), idesc,
@@ -278,9 +293,9 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const int ew = quad;                    // bucket owner index 0..3 (rows of a quadrant are one bucket)
             const int half = (warp - 2) >> 2;       // which of the alternating 16-query chunks this warp takes
             const float sign = (a.order == MANTA_B200_ORDER_SMALLEST) ? -1.0f : 1.0f;
-            const bool want_scale = I8 && a.metric != MANTA_B200_METRIC_COSINE;
-            const bool want_stats = a.metric != MANTA_B200_METRIC_DOT;
-            const bool cheap = a.order == MANTA_B200_ORDER_LARGEST && a.metric != MANTA_B200_METRIC_L2_DISTANCE;
+            const bool want_scale = I8 && METRIC != MANTA_B200_METRIC_COSINE;
+            const bool want_stats = METRIC != MANTA_B200_METRIC_DOT;
+            const bool cheap = a.order == MANTA_B200_ORDER_LARGEST && METRIC != MANTA_B200_METRIC_L2_DISTANCE;
             unsigned long long c_wait = 0, c_ld = 0, c_math = 0, c_slow = 0, c_house = 0, n_slow = 0, c_thr = 0;
             const bool timing = a.dbg != nullptr && cta == 0 && warp == 4;
             for (int it = 0; it < n_iters; ++it) {
@@ -301,7 +316,7 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 if (rv && want_scale) sd = ((const float*)a.cv.scales)[row];
                 if (rv && want_stats) stat = ((const uint32_t*)a.cv.stats)[row];
                 float rinv = 0.0f;
-                if (a.metric == MANTA_B200_METRIC_COSINE) rinv = I8 ? q8_row_inv_norm((int)stat) : float_row_inv_norm(__uint_as_float(stat));
+                if (METRIC == MANTA_B200_METRIC_COSINE) rinv = I8 ? q8_row_inv_norm((int)stat) : float_row_inv_norm(__uint_as_float(stat));
                 if (!mbar_wait(&tfull[acc], (uint32_t)(it >> 1) & 1u, abort_s)) break;
                 tc_fence_after();
                 if (timing) { long long t1 = clock64(); c_wait += t1 - t0; t0 = t1; }
@@ -309,7 +324,8 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 const int32_t my_id = (int32_t)(a.cv.row_base + row);
                 // row factor of the pre-filter; NaN for rows past the end makes every comparison false
                 float rowc = __int_as_float(0x7fc00000);
-                if (rv) rowc = (a.metric == MANTA_B200_METRIC_COSINE) ? rinv : (I8 ? sd : 1.0f);
+                if (rv) rowc = (METRIC == MANTA_B200_METRIC_COSINE) ? rinv : (I8 ? sd : 1.0f);
+                // chunks of 16 queries for this lane's row
                 for (int c0 = half * 16; c0 < a.qn; c0 += 32) {
                     uint32_t vh[16], vl[16];
                     tmem_ld16(t_row + c0, vh);
@@ -320,12 +336,10 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         for (int jj = 0; jj < 16; ++jj) vl[jj] = 0;
                     }
                     tmem_ld_wait();
-                    if (timing) { long long t1 = clock64(); c_ld += t1 - t0; t0 = t1; }
                     if (cheap) {
                         // Pre-filter without finishing the scores: score >= bound  <=>  t * rowc >= bound / qinv, the
-                        // right-hand side (slackened by a few ulps) kept per query by the refresher.  Almost every
-                        // chunk ends here; the exact evaluation below decides the rest.
-                        bool hit = false;
+                        // right-hand side (slackened by a few ulps) kept per query by the refresher.
+                        uint32_t hit = 0;
 #pragma unroll
                         for (int jj = 0; jj < 16; ++jj) {
                             const float4 f = filt_s[min(c0 + jj, a.qn - 1)];
@@ -334,27 +348,14 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                                 t = __fmaf_rn((float)(int)vl[jj], f.y, __fmul_rn((float)(int)vh[jj], f.x));
                             else
                                 t = __uint_as_float(vh[jj]);
-                            hit = hit || (t * rowc >= f.z);
+                            hit |= (t * rowc >= f.z) ? 1u : 0u;
                         }
-                        if (!__any_sync(0xffffffffu, hit)) {
-                            if (timing) { long long t1 = clock64(); c_math += t1 - t0; t0 = t1; }
-                            continue;
-                        }
+                        if (!__any_sync(0xffffffffu, hit != 0u)) continue;
                     }
                     // scores of 16 queries for this lane's row: straight-line, independent arithmetic
                     float g[16];
                     uint32_t o[16];
-                    switch (a.metric) {
-                        case MANTA_B200_METRIC_DOT:
-                            score16<I8, MANTA_B200_METRIC_DOT>(vh, vl, stat, rinv, sd, hdr_s, c0, a.qn, rv, sign, g, o);
-                            break;
-                        case MANTA_B200_METRIC_COSINE:
-                            score16<I8, MANTA_B200_METRIC_COSINE>(vh, vl, stat, rinv, sd, hdr_s, c0, a.qn, rv, sign, g, o);
-                            break;
-                        default:
-                            score16<I8, MANTA_B200_METRIC_L2_DISTANCE>(vh, vl, stat, rinv, sd, hdr_s, c0, a.qn, rv, sign, g, o);
-                            break;
-                    }
+                    score16<I8, METRIC>(vh, vl, stat, rinv, sd, hdr_s, c0, a.qn, rv, sign, g, o);
                     // filter: one vote per query; everything behind a non-empty vote is the rare path
                     uint32_t votes[16];
                     uint32_t any = 0;
@@ -364,7 +365,6 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         votes[jj] = __ballot_sync(0xffffffffu, o[jj] >= thr_s[j]);
                         any |= votes[jj];
                     }
-                    if (timing) { long long t1 = clock64(); c_math += t1 - t0; t0 = t1; }
                     if (any == 0) continue;
                     n_slow++;
 #pragma unroll
@@ -391,14 +391,16 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                                 a.ws.flags[kFlagOverflow] = 1u;
                         }
                     }
-                    if (timing) { long long t1 = clock64(); c_slow += t1 - t0; t0 = t1; }
                 }
+                if (timing) { long long t1 = clock64(); c_math += t1 - t0; t0 = t1; }
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&tempty[acc]);
                 // ---- publish this warp's maxima of the tile (bucket slot it % kBucketSlots)
-                if (a.filtered && !replay) {
-                    const int slot = it % kBucketSlots;
+                // (every tile at first, while the bounds are still forming; every fourth tile afterwards -- the maxima
+                // of the tiles in between stay accumulated in bmax_s and go out with the next publication)
+                if (a.filtered && !replay && (it < 16 || (it & 3) == 3 || it + 1 == n_my)) {
+                    const int slot = (it < 16 ? it : (it >> 2)) % kBucketSlots;
                     for (int j = lane; j < a.qn; j += 32) {
                         if (((j >> 4) & 1) != half) continue;   // the other warp of the quadrant owns this query
                         const int i = j * 4 + ew;
@@ -468,7 +470,7 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     if (v > 1u) {
                         const float tf = float_from_ord(v);
                         const float qi = hdr_s[jj].qinv;
-                        c = (a.metric == MANTA_B200_METRIC_COSINE) ? ((qi > 0.0f) ? tf / qi : -INFINITY) : tf;
+                        c = (METRIC == MANTA_B200_METRIC_COSINE) ? ((qi > 0.0f) ? tf / qi : -INFINITY) : tf;
                         c = c - fabsf(c) * 2e-6f - 1e-30f;
                     }
                     filt_s[jj].z = c;
@@ -523,7 +525,7 @@ struct MmaState {
     size_t d_b_bytes = 0;
     uint32_t* d_ready = nullptr;
     unsigned long long* d_dbg = nullptr;
-    bool attr_set[2] = {false, false};
+    bool attr_set[6] = {false, false, false, false, false, false};
 };
 
 static int mma_group_queries(const CandView& cv) { return cv.layout == MANTA_B200_LAYOUT_Q8_ROW_F32 ? kMmaCols / 2 : kMmaCols; }
@@ -564,6 +566,32 @@ static cudaError_t make_map(MmaState* st, CUtensorMap* map, const void* base, ui
         return cudaErrorInvalidValue;
     }
     return cudaSuccess;
+}
+
+template <bool I8, int METRIC>
+static cudaError_t launch_scan_one(MmaState* st, int slot, int grid, size_t smem, cudaStream_t stream, const CUtensorMap& map_a,
+                                   const CUtensorMap& map_b, const KernelArgs& ka, const char** why) {
+    if (!st->attr_set[slot]) {
+        cudaError_t e = cudaFuncSetAttribute(mma_scan_kernel<I8, METRIC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024);
+        if (e != cudaSuccess) { *why = "cudaFuncSetAttribute"; return e; }
+        st->attr_set[slot] = true;
+    }
+    mma_scan_kernel<I8, METRIC><<<grid, kMmaThreads, smem, stream>>>(map_a, map_b, ka);
+    return cudaSuccess;
+}
+
+// One instantiation per (layout, metric): the epilogue of each is straight-line code for its own metric.
+static cudaError_t launch_scan_variant(MmaState* st, bool i8, int metric, int grid, size_t smem, cudaStream_t stream,
+                                       const CUtensorMap& map_a, const CUtensorMap& map_b, const KernelArgs& ka, const char** why) {
+    const int slot = (i8 ? 0 : 3) + metric;
+    switch (slot) {
+        case 0: return launch_scan_one<true, MANTA_B200_METRIC_DOT>(st, slot, grid, smem, stream, map_a, map_b, ka, why);
+        case 1: return launch_scan_one<true, MANTA_B200_METRIC_COSINE>(st, slot, grid, smem, stream, map_a, map_b, ka, why);
+        case 2: return launch_scan_one<true, MANTA_B200_METRIC_L2_DISTANCE>(st, slot, grid, smem, stream, map_a, map_b, ka, why);
+        case 3: return launch_scan_one<false, MANTA_B200_METRIC_DOT>(st, slot, grid, smem, stream, map_a, map_b, ka, why);
+        case 4: return launch_scan_one<false, MANTA_B200_METRIC_COSINE>(st, slot, grid, smem, stream, map_a, map_b, ka, why);
+        default: return launch_scan_one<false, MANTA_B200_METRIC_L2_DISTANCE>(st, slot, grid, smem, stream, map_a, map_b, ka, why);
+    }
 }
 
 cudaError_t launch_mma_topk(cudaStream_t stream, int sm_count, MmaState** state, const MmaArgs& a, int* launches, const char** why) {
@@ -638,13 +666,18 @@ cudaError_t launch_mma_topk(cudaStream_t stream, int sm_count, MmaState** state,
         e = make_map(st, &map_b, st->d_b, (uint64_t)kpad, (uint64_t)ncols, (uint64_t)kpad, (uint32_t)ncols, why);
         if (e != cudaSuccess) return e;
 
-        const size_t stage_bytes = (size_t)kTileRows * kChunkBytes + (size_t)ncols * kChunkBytes;
+        const size_t a_stage = (size_t)kTileRows * kChunkBytes, b_stage = (size_t)ncols * kChunkBytes;
         const size_t fixed = 1024 /*alignment slack*/ + 256 /*barriers*/ + sizeof(QueryHeader) * kMmaCols + 4 * kMmaCols +
                              16 * kMmaCols + 16 * kMmaCols * kBucketSlots + 16 * kMmaCols;
-        int stages = (int)((220 * 1024 - fixed) / stage_bytes);
+        const size_t budget = 220 * 1024 - fixed;
+        // Operand B stays resident when it leaves room for at least four candidate stages: the ring then carries
+        // only candidate bytes instead of re-reading the queries from L2 for every tile.
+        static const bool no_resident = getenv("MANTA_B200_MMA_NO_RESIDENT_B") != nullptr;  // debugging switch
+        const int b_resident = (!no_resident && b_stage * kchunks + 4 * a_stage <= budget) ? 1 : 0;
+        int stages = b_resident ? (int)((budget - b_stage * kchunks) / a_stage) : (int)(budget / (a_stage + b_stage));
         if (stages > 8) stages = 8;
         if (stages < 2) { *why = "not enough shared memory for two pipeline stages"; return cudaErrorInvalidValue; }
-        const size_t smem = fixed + (size_t)stages * stage_bytes;
+        const size_t smem = fixed + (b_resident ? b_stage * kchunks + stages * a_stage : stages * (a_stage + b_stage));
 
         KernelArgs ka;
         ka.cv = cv;
@@ -657,6 +690,7 @@ cudaError_t launch_mma_topk(cudaStream_t stream, int sm_count, MmaState** state,
         ka.lo_off = lo_off;
         ka.kchunks = kchunks;
         ka.stages = stages;
+        ka.b_resident = b_resident;
         ka.metric = a.metric;
         ka.order = a.order;
         ka.k = a.k;
@@ -671,21 +705,8 @@ cudaError_t launch_mma_topk(cudaStream_t stream, int sm_count, MmaState** state,
             cudaMemsetAsync(st->d_dbg, 0, 64, stream);
             ka.dbg = st->d_dbg;
         }
-        if (i8) {
-            if (!st->attr_set[0]) {
-                e = cudaFuncSetAttribute(mma_scan_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024);
-                if (e != cudaSuccess) { *why = "cudaFuncSetAttribute"; return e; }
-                st->attr_set[0] = true;
-            }
-            mma_scan_kernel<true><<<grid, kMmaThreads, smem, stream>>>(map_a, map_b, ka);
-        } else {
-            if (!st->attr_set[1]) {
-                e = cudaFuncSetAttribute(mma_scan_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024);
-                if (e != cudaSuccess) { *why = "cudaFuncSetAttribute"; return e; }
-                st->attr_set[1] = true;
-            }
-            mma_scan_kernel<false><<<grid, kMmaThreads, smem, stream>>>(map_a, map_b, ka);
-        }
+        e = launch_scan_variant(st, i8, a.metric, grid, smem, stream, map_a, map_b, ka, why);
+        if (e != cudaSuccess) return e;
         count_launch();
         ++*launches;
         e = cudaGetLastError();
