@@ -180,6 +180,20 @@ int manta_b200_topk_merge_device(MantaB200Runtime* rt, int order, const int32_t*
 int manta_b200_gather_rows(MantaB200Runtime* rt, const MantaB200Candidates* set, const int32_t* ids, int64_t n,
                            float* out, char** err);
 
+/* ---- per-query candidate sets: queries [Q,D] x docs [Q,N,D] ----------------------------------------------
+ * The second legal shape of the score builtins (scoreLayout, runtime/backend/tensor_ops.go:1492-1521), used by
+ * ScoreModel.ScoreBatch / RetrievalModel.RetrieveBatch (runtime/score_model.go:238-324, retrieval_model.go:246-332).
+ * The reference's CUDA backend computes it on the host (runtime/backends/cuda/cuda.go:961-976).  queries / docs are
+ * float32 (the reference's tensor storage), host pointers for MANTA_B200_MEM_HOST, device pointers for
+ * MANTA_B200_MEM_DEVICE_COPY (read in place); outputs live where the inputs live.  out: [Q,N] float32. */
+int manta_b200_score_batched(MantaB200Runtime* rt, int metric, const float* queries, const float* docs, int nq,
+                             int64_t rows, int cols, int mem, float* out, char** err);
+/* Fused with topKTensor per query row (tensor_ops.go:1548-1590; error "topk limit %d out of range for row width
+ * %d") and gather(scores, ids): out_ids int32 [Q,k] (row index within the query's own set), out_scores [Q,k]. */
+int manta_b200_score_topk_batched(MantaB200Runtime* rt, int metric, int order, const float* queries, const float* docs,
+                                  int nq, int64_t rows, int cols, int mem, int k, int32_t* out_ids, float* out_scores,
+                                  char** err);
+
 /* ---- embedding front end: the caller of the score path in the reference's embed pipelines ----------------
  * gather(token_embedding, tokens) -> @matmul(projection) -> masked mean_pool / normalize
  * (examples/embed_masked_pooled.manta; steps runtime/backend/tensor_ops.go:31-47, 83-118, 646-658; host math

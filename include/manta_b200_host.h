@@ -74,6 +74,21 @@ int manta_b200_result_tensor(const MantaB200Result* res, const char* output, con
                              char** err);
 void manta_b200_result_free(MantaB200Result* res);
 
+/* computeRetrievalQuality of the eval-retrieval command (runtime/retrieval_eval.go:541-584, gate cmd/manta/main.go:
+ * 2446-2452) with topRetrievalScores (:586-616) replaced by fused score + top-k passes: the document vectors
+ * ([n_docs, dim] float32, rounded to f16) are bound once in document-ID order, so that the device's tie rule (lower
+ * row first) is the reference's (smaller ID string first, :618-626); queries with a relevant document in the corpus
+ * are scored 256 per pass with k = min(max(top_k, 100), n_docs).  qrels arrive as n_qrels (query id, doc id,
+ * relevance) triples.  out_json (released with manta_b200_free_cstring):
+ *   {"quality": {"ndcg_at_10", "mrr_at_10", "recall_at_10", "recall_at_100"}, "evaluated_queries",
+ *    "relevant_pairs", "skipped_relevant_docs", "skipped_no_relevant", "scored_pairs", "top_k"}
+ * -- the fields RetrievalEvalQualityMetrics / RetrievalEvalInputMetrics / RetrievalEvalSkippedCounts take from it
+ * (:38-98). */
+int manta_b200_retrieval_quality(MantaB200Runtime* rt, const float* query_vectors, const char* const* query_ids,
+                                 int n_queries, const float* doc_vectors, const char* const* doc_ids, int64_t n_docs,
+                                 int dim, const char* const* qrel_query_ids, const char* const* qrel_doc_ids,
+                                 const double* qrel_values, int64_t n_qrels, int top_k, char** out_json, char** err);
+
 #ifdef __cplusplus
 }
 #endif

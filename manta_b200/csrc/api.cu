@@ -81,7 +81,7 @@ struct MantaB200Runtime {
     std::mutex mu;
     MantaB200Stats stats{};
     // grow-only device buffers
-    DevBuf queries, headers, qf32, plane_hi, plane_lo, pool, count, thr, bucket, flags, out_ids, out_scores, misc, embed_flag;
+    DevBuf queries, headers, qf32, plane_hi, plane_lo, pool, count, thr, bucket, flags, out_ids, out_scores, misc, embed_flag, batch_in;
     // pinned host staging
     void* h_stage = nullptr;
     size_t h_stage_bytes = 0;
@@ -216,7 +216,7 @@ int manta_b200_runtime_destroy(MantaB200Runtime* rt, char** err) {
     cudaSetDevice(rt->device);
     cudaError_t e = cudaStreamSynchronize(rt->stream);
     DevBuf* bufs[] = {&rt->queries, &rt->headers, &rt->qf32, &rt->plane_hi, &rt->plane_lo, &rt->pool, &rt->count,
-                      &rt->thr, &rt->bucket, &rt->flags, &rt->out_ids, &rt->out_scores, &rt->misc, &rt->embed_flag};
+                      &rt->thr, &rt->bucket, &rt->flags, &rt->out_ids, &rt->out_scores, &rt->misc, &rt->embed_flag, &rt->batch_in};
     for (DevBuf* b : bufs) free_buf(*b);
     mma_state_destroy(rt->mma);
     for (int i = 0; i < rt->prof_created; ++i) cudaEventDestroy(rt->prof_ev[i]);
@@ -767,6 +767,97 @@ int manta_b200_score(MantaB200Runtime* rt, const MantaB200Candidates* set, int m
     rt->stats.h2d_bytes += qbytes;
     rt->stats.d2h_bytes += obytes;
     return 0;
+}
+
+// ---- per-query candidate sets -----------------------------------------------------------------------------------
+static int batched_common(MantaB200Runtime* rt, int metric, int order, const float* queries, const float* docs, int nq, int64_t rows,
+                          int cols, int mem, int k, float* out_full, int32_t* out_ids, float* out_scores, char** err) {
+    if (!rt || !queries || !docs) return fail(err, "score: NULL argument");
+    if (metric < 0 || metric > 2) return fail(err, "score: unknown metric %d", metric);
+    if (nq <= 0 || rows <= 0 || cols <= 0) return fail(err, "score mismatch [%d %d] x [%d %lld %d]", nq, cols, nq, (long long)rows, cols);
+    if (mem != MANTA_B200_MEM_HOST && mem != MANTA_B200_MEM_DEVICE_COPY) return fail(err, "score: mem must be HOST or DEVICE_COPY");
+    const bool topk = out_ids != nullptr;
+    if (topk) {
+        if (order != MANTA_B200_ORDER_LARGEST && order != MANTA_B200_ORDER_SMALLEST) return fail(err, "score_topk: unknown order %d", order);
+        // message of topKTensor for rank-2 scores, runtime/backend/tensor_ops.go:1561
+        if (k <= 0 || k > rows) return fail(err, "topk limit %d out of range for row width %lld", k, (long long)rows);
+        if (k > kMaxK) return fail(err, "topk limit %d exceeds the fused pass maximum %d", k, kMaxK);
+        if (rows > (int64_t)1 << 26) return fail(err, "score_topk: %lld rows per query exceed the per-query form's limit", (long long)rows);
+    }
+    std::lock_guard<std::mutex> lk(rt->mu);
+    CU_TRY(cudaSetDevice(rt->device));
+    const bool host = mem == MANTA_B200_MEM_HOST;
+    const size_t qbytes = (size_t)nq * cols * 4, dbytes = (size_t)nq * rows * cols * 4, sbytes = (size_t)nq * rows * 4;
+    const float* d_q = queries;
+    const float* d_d = docs;
+    if (host) {
+        if (ensure(rt, rt->batch_in, qbytes + 256 + dbytes, err)) return 1;
+        float* bq = (float*)rt->batch_in.p;
+        float* bd = (float*)((char*)rt->batch_in.p + (qbytes + 255) / 256 * 256);
+        CU_TRY(cudaMemcpyAsync(bq, queries, qbytes, cudaMemcpyHostToDevice, rt->stream));
+        CU_TRY(cudaMemcpyAsync(bd, docs, dbytes, cudaMemcpyHostToDevice, rt->stream));
+        rt->stats.h2d_bytes += qbytes + dbytes;
+        d_q = bq;
+        d_d = bd;
+    }
+    float* d_full = nullptr;
+    if (out_full) {
+        d_full = out_full;
+        if (host) {
+            if (ensure(rt, rt->misc, sbytes, err)) return 1;
+            d_full = (float*)rt->misc.p;
+        }
+    }
+    SelectWs ws{};
+    if (topk && ensure_select_ws(rt, nq, (uint32_t)rows, 1, &ws, err)) return 1;
+    cudaError_t e = launch_score_batched(rt->stream, rt->sm_count, metric, d_q, d_d, nq, rows, cols, order, d_full, ws, topk ? 1 : 0);
+    rt->stats.kernel_launches++;
+    rt->stats.score_calls++;
+    if (e != cudaSuccess) return fail_cuda(err, "launch batched score kernel", e);
+    if (out_full && host) {
+        CU_TRY(cudaMemcpyAsync(out_full, d_full, sbytes, cudaMemcpyDeviceToHost, rt->stream));
+        rt->stats.d2h_bytes += sbytes;
+    }
+    if (topk) {
+        const size_t obytes = (size_t)nq * k * 4;
+        int32_t* d_ids = out_ids;
+        float* d_sc = out_scores;
+        if (host) {
+            if (ensure(rt, rt->out_ids, obytes, err)) return 1;
+            if (ensure(rt, rt->out_scores, obytes, err)) return 1;
+            d_ids = (int32_t*)rt->out_ids.p;
+            d_sc = (float*)rt->out_scores.p;
+        }
+        SelectArgs sa{};
+        sa.ws = ws;
+        sa.nq = nq;
+        sa.k = k;
+        sa.order = order;
+        sa.out_ids = d_ids;
+        sa.out_scores = d_sc;
+        e = launch_select(rt->stream, sa);
+        rt->stats.kernel_launches++;
+        if (e != cudaSuccess) return fail_cuda(err, "launch select kernel", e);
+        if (host) {
+            CU_TRY(cudaMemcpyAsync(out_ids, d_ids, obytes, cudaMemcpyDeviceToHost, rt->stream));
+            CU_TRY(cudaMemcpyAsync(out_scores, d_sc, obytes, cudaMemcpyDeviceToHost, rt->stream));
+            rt->stats.d2h_bytes += 2 * obytes;
+        }
+    }
+    CU_TRY(cudaStreamSynchronize(rt->stream));
+    return 0;
+}
+
+int manta_b200_score_batched(MantaB200Runtime* rt, int metric, const float* queries, const float* docs, int nq, int64_t rows,
+                             int cols, int mem, float* out, char** err) {
+    if (!out) return fail(err, "score: NULL output");
+    return batched_common(rt, metric, MANTA_B200_ORDER_LARGEST, queries, docs, nq, rows, cols, mem, 0, out, nullptr, nullptr, err);
+}
+
+int manta_b200_score_topk_batched(MantaB200Runtime* rt, int metric, int order, const float* queries, const float* docs, int nq,
+                                  int64_t rows, int cols, int mem, int k, int32_t* out_ids, float* out_scores, char** err) {
+    if (!out_ids || !out_scores) return fail(err, "score_topk: NULL output");
+    return batched_common(rt, metric, order, queries, docs, nq, rows, cols, mem, k, nullptr, out_ids, out_scores, err);
 }
 
 // ---- embedding front end ------------------------------------------------------------------------------------

@@ -14,11 +14,13 @@
 #include <vector>
 
 #include "../../../include/manta_b200_host.h"
+#include "half.h"
 #include "json.h"
 
 namespace {
 
 using mjson::Value;
+using mb200_host::half_bits;
 
 const char* kVersion = "manta/v0alpha1";  // artifact/manta/module.go:9
 
@@ -261,23 +263,6 @@ int layout_of_label(const std::string& dtype) {
     if (dtype == "q8") return MANTA_B200_LAYOUT_Q8_ROW_F32;
     if (dtype == "q4") return MANTA_B200_LAYOUT_Q4_B32_F16;
     return MANTA_B200_LAYOUT_F16;  // f16 / f32 labels
-}
-
-// f32 -> f16 bits, round to nearest even (the kernels take IEEE half bits).
-uint16_t half_bits(float f) {
-    uint32_t x;
-    memcpy(&x, &f, 4);
-    uint32_t sign = (x >> 16) & 0x8000u, absx = x & 0x7fffffffu;
-    if (absx >= 0x7f800000u) return (uint16_t)(sign | 0x7c00u | ((absx > 0x7f800000u) ? 0x0200u : 0));
-    if (absx >= 0x477ff000u) return (uint16_t)(sign | 0x7c00u);
-    if (absx < 0x33000001u) return (uint16_t)sign;
-    int32_t e = (int32_t)(absx >> 23) - 127;
-    uint32_t m = (absx & 0x007fffffu) | 0x00800000u, shift, base;
-    if (e < -14) { shift = (uint32_t)(13 + (-14 - e)); base = 0; }
-    else { shift = 13; base = ((uint32_t)(e + 15) << 10) - 0x0400u; }
-    uint32_t q = m >> shift, rem = m & ((1u << shift) - 1), halfway = 1u << (shift - 1);
-    if (rem > halfway || (rem == halfway && (q & 1u))) q++;
-    return (uint16_t)(sign | (base + q));
 }
 
 // Quantises a [rows, cols] float32 tensor into the packed layout its dtype label names and binds it.
@@ -811,11 +796,62 @@ int manta_b200_program_run(MantaB200Program* prog, const char* entry_name, const
             // scoreLayout (tensor_ops.go:1492-1521) + the shared-candidate batch [Q,D] x [N,D]
             const bool rank1 = query.shape.size() == 1 && docs.shape.size() == 2;
             const bool shared = query.shape.size() == 2 && docs.shape.size() == 2;
-            if (!rank1 && !shared) {
-                if (query.shape.size() == 2 && docs.shape.size() == 3)
-                    STEP_FAIL("per-query candidate sets [Q,D] x [Q,N,D] are not on the device path of this backend (the reference runs them on the host, cuda.go:961-976); bind one shared [N,D] set instead");
-                STEP_FAIL("score expects query/docs as [D] x [N,D] or [Q,D] x [Q,N,D]");
-            }
+            const bool per_query = query.shape.size() == 2 && docs.shape.size() == 3;
+            if (!rank1 && !shared && !per_query) STEP_FAIL("score expects query/docs as [D] x [N,D] or [Q,D] x [Q,N,D]");
+            if (per_query) {
+                // [Q,D] x [Q,N,D]: every query against its own rows, streamed through the device for this call
+                const int64_t bq = docs.shape[0], bn = docs.shape[1], bd = docs.shape[2];
+                if (query.shape[0] != bq || query.shape[1] != bd) STEP_FAIL("score mismatch %s x %s", shape_text(query.shape).c_str(), shape_text(docs.shape).c_str());
+                if (!float_like(query.dtype) || !float_like(docs.dtype)) STEP_FAIL("score inputs must be float-like tensors");
+                const int metric = metric_of(k->op);
+                RValue sv;
+                auto t = std::make_shared<Tensor>();
+                t->dtype = "f32";
+                t->shape = {bq, bn};
+                sv.tensor = t;
+                if (f->need_full_scores) {
+                    t->f32.resize((size_t)bq * bn);
+                    char* serr = nullptr;
+                    if (manta_b200_score_batched(prog->rt, metric, query.f32.data(), docs.f32.data(), (int)bq, bn, (int)bd, MANTA_B200_MEM_HOST,
+                                                 t->f32.data(), &serr)) {
+                        std::string m = serr ? serr : "score failed";
+                        free(serr);
+                        STEP_FAIL("%s", m.c_str());
+                    }
+                } else {
+                    sv.metadata.set("materialized", Value::make_string("device_only"));
+                }
+                if (f->topk_step >= 0) {
+                    const Step& ts = *steps[f->topk_step];
+                    if (f->k <= 0) {
+                        cleanup();
+                        return fail(err, "entrypoint \"%s\" step \"%s\": topk step \"%s\" is missing limit attribute", entry->name.c_str(), ts.name.c_str(), ts.name.c_str());
+                    }
+                    Fused fu;
+                    fu.f = f;
+                    fu.ids = std::make_shared<Tensor>();
+                    fu.top_scores = std::make_shared<Tensor>();
+                    fu.ids->dtype = "i32";
+                    fu.top_scores->dtype = "f32";
+                    fu.ids->shape = fu.top_scores->shape = {bq, (int64_t)f->k};
+                    fu.ids->i32.resize((size_t)bq * f->k);
+                    fu.top_scores->f32.resize((size_t)bq * f->k);
+                    char* serr = nullptr;
+                    if (manta_b200_score_topk_batched(prog->rt, metric, MANTA_B200_ORDER_LARGEST, query.f32.data(), docs.f32.data(), (int)bq, bn,
+                                                      (int)bd, MANTA_B200_MEM_HOST, f->k, fu.ids->i32.data(), fu.top_scores->f32.data(), &serr)) {
+                        std::string m = serr ? serr : "score_topk failed";
+                        free(serr);
+                        cleanup();
+                        return fail(err, "entrypoint \"%s\" step \"%s\": %s", entry->name.c_str(), ts.name.c_str(), m.c_str());
+                    }
+                    fused[f->scores_name] = fu;
+                }
+                sv.type = out_type(0, *sv.tensor);
+                base_meta(&sv);
+                device_meta(&sv, f->topk_step >= 0 ? "launch_kernel+topk+gather" : "launch_kernel");
+                sv.metadata.set("candidate_sets", Value::make_string("per_query"));
+                produced.push_back(sv);
+            } else {
             const int64_t d = docs.shape[1], n = docs.shape[0];
             const int64_t qd = rank1 ? query.shape[0] : query.shape[1];
             const int nq = rank1 ? 1 : (int)query.shape[0];
@@ -904,6 +940,7 @@ int manta_b200_program_run(MantaB200Program* prog, const char* entry_name, const
             base_meta(&sv);
             device_meta(&sv, f->topk_step >= 0 ? "launch_kernel+topk+gather" : "launch_kernel");
             produced.push_back(sv);
+            }  // shared / rank-1 candidate set
         } else if (step.kind == "topk") {
             if (step.inputs.size() != 1 || step.outputs.size() != 1) STEP_FAIL("topk step \"%s\" expects 1 input and 1 output", step.name.c_str());
             auto it = fused.find(step.inputs[0]);
@@ -957,15 +994,50 @@ int manta_b200_program_run(MantaB200Program* prog, const char* entry_name, const
                 // gatherTensor on a host table (candidate_ids and the like), tensor_ops.go:761-827
                 const Tensor& tb = *table.tensor;
                 const Tensor& ix = *index.tensor;
-                if (tb.shape.size() != 1 || ix.shape.size() != 1) STEP_FAIL("gather of a rank-%d table with rank-%d indices is not on this path", (int)tb.shape.size(), (int)ix.shape.size());
                 auto t = std::make_shared<Tensor>();
                 t->dtype = tb.dtype;
-                t->shape = {ix.shape[0]};
-                for (int32_t id : ix.i32) {
-                    if (id < 0 || id >= tb.shape[0]) STEP_FAIL("gather index %d out of range", id);
-                    if (tb.dtype == "i32") t->i32.push_back(tb.i32[id]);
-                    else if (tb.dtype == "i64") t->i64.push_back(tb.i64[id]);
-                    else t->f32.push_back(tb.f32[id]);
+                auto copy_elems = [&](size_t src, size_t count) {
+                    if (tb.dtype == "i32") t->i32.insert(t->i32.end(), tb.i32.begin() + src, tb.i32.begin() + src + count);
+                    else if (tb.dtype == "i64") t->i64.insert(t->i64.end(), tb.i64.begin() + src, tb.i64.begin() + src + count);
+                    else t->f32.insert(t->f32.end(), tb.f32.begin() + src, tb.f32.begin() + src + count);
+                };
+                if (tb.shape.size() == 1 && ix.shape.size() == 1) {
+                    t->shape = {ix.shape[0]};
+                    for (int32_t id : ix.i32) {
+                        if (id < 0 || id >= tb.shape[0]) STEP_FAIL("gather index %d out of range", id);
+                        copy_elems((size_t)id, 1);
+                    }
+                } else if (tb.shape.size() == 2 && ix.shape.size() == 1) {
+                    const int64_t cols = tb.shape[1];
+                    t->shape = {ix.shape[0], cols};
+                    for (int32_t id : ix.i32) {
+                        if (id < 0 || id >= tb.shape[0]) STEP_FAIL("gather index %d out of range", id);
+                        copy_elems((size_t)id * cols, (size_t)cols);
+                    }
+                } else if (tb.shape.size() == 2 && ix.shape.size() == 2) {
+                    // batched element gather [Q,N] x [Q,k] -> [Q,k] (tensor_ops.go:875-925)
+                    if (tb.shape[0] != ix.shape[0]) STEP_FAIL("gather batch mismatch %s x %s", shape_text(tb.shape).c_str(), shape_text(ix.shape).c_str());
+                    const int64_t rows = tb.shape[1], kk = ix.shape[1];
+                    t->shape = {ix.shape[0], kk};
+                    for (int64_t b = 0; b < ix.shape[0]; ++b)
+                        for (int64_t i = 0; i < kk; ++i) {
+                            const int32_t id = ix.i32[(size_t)(b * kk + i)];
+                            if (id < 0 || id >= rows) STEP_FAIL("gather index %d out of range", id);
+                            copy_elems((size_t)(b * rows + id), 1);
+                        }
+                } else if (tb.shape.size() == 3 && ix.shape.size() == 2) {
+                    // batched row gather [Q,N,D] x [Q,k] -> [Q,k,D] (tensor_ops.go:926-975)
+                    if (tb.shape[0] != ix.shape[0]) STEP_FAIL("gather batch mismatch %s x %s", shape_text(tb.shape).c_str(), shape_text(ix.shape).c_str());
+                    const int64_t rows = tb.shape[1], cols = tb.shape[2], kk = ix.shape[1];
+                    t->shape = {ix.shape[0], kk, cols};
+                    for (int64_t b = 0; b < ix.shape[0]; ++b)
+                        for (int64_t i = 0; i < kk; ++i) {
+                            const int32_t id = ix.i32[(size_t)(b * kk + i)];
+                            if (id < 0 || id >= rows) STEP_FAIL("gather index %d out of range", id);
+                            copy_elems((size_t)((b * rows + id) * cols), (size_t)cols);
+                        }
+                } else {
+                    STEP_FAIL("gather expects table rank 1, 2, or 3 with compatible indices");
                 }
                 v.tensor = t;
                 base_meta(&v);
@@ -987,6 +1059,12 @@ int manta_b200_program_run(MantaB200Program* prog, const char* entry_name, const
             if (v.pack->docs->dtype != "q4") STEP_FAIL("candidate pack docs dtype \"%s\" does not match expected \"q4\"", v.pack->docs->dtype.c_str());
             if (v.pack->docs->shape.size() == 2 && (v.pack->ids->shape.size() != 1 || v.pack->ids->shape[0] != v.pack->docs->shape[0] || v.pack->scores->shape[0] != v.pack->docs->shape[0]))
                 STEP_FAIL("candidate pack leading dimension mismatch");
+            if (v.pack->docs->shape.size() == 3) {
+                if (v.pack->ids->shape.size() != 2 || v.pack->scores->shape.size() != 2) STEP_FAIL("candidate pack rank-3 docs require rank-2 ids and scores");
+                if (v.pack->ids->shape[0] != v.pack->docs->shape[0] || v.pack->scores->shape[0] != v.pack->docs->shape[0] ||
+                    v.pack->ids->shape[1] != v.pack->docs->shape[1] || v.pack->scores->shape[1] != v.pack->docs->shape[1])
+                    STEP_FAIL("candidate pack leading dimensions mismatch");
+            }
             v.type.kind = "candidate_pack";
             for (int64_t dd : v.pack->docs->shape) v.type.shape.push_back(std::to_string(dd));
             base_meta(&v);

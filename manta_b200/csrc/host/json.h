@@ -199,7 +199,7 @@ inline void write(const Value& v, std::string* out) {
         case Value::Number: {
             char buf[40];
             if (v.num == std::floor(v.num) && std::fabs(v.num) < 1e15) snprintf(buf, sizeof buf, "%lld", (long long)v.num);
-            else snprintf(buf, sizeof buf, "%.9g", v.num);
+            else snprintf(buf, sizeof buf, "%.17g", v.num);
             *out += buf;
             break;
         }

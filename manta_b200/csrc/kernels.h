@@ -27,6 +27,11 @@ void launch_pack_q4(cudaStream_t st, const void* d_src, bool src_f16, int64_t ro
 void launch_gather_rows(cudaStream_t st, const CandView& cv, const int32_t* d_ids, int64_t n, float* d_out,
                         int32_t* d_bad_id, uint32_t* d_bad_flag);
 
+// Per-query candidate sets ([Q,D] x [Q,N,D], float32 docs): scores [Q,N] and / or the keys of every row in the
+// selection pools (ws.cap >= rows).
+cudaError_t launch_score_batched(cudaStream_t st, int sm_count, int metric, const float* d_queries, const float* d_docs, int nq,
+                                 int64_t rows, int cols, int order, float* d_out_scores, const SelectWs& ws, int fill_pool);
+
 // Embedding front end: gather -> matmul -> masked mean_pool / normalize (order 0: normalize(mean_pool(x)),
 // 1: mean_pool(normalize(x))); writes the pooled rows as f32 and / or f16.
 cudaError_t launch_embed_pooled(cudaStream_t st, const void* table_f16, int vocab, int dim, const void* proj_f16, int out_dim,

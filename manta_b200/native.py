@@ -34,7 +34,7 @@ EXPORTS = [
     "manta_b200_score_topk", "manta_b200_score_topk_device", "manta_b200_topk_merge_device",
     "manta_b200_gather_rows", "manta_b200_q8_accumulators", "manta_b200_score_topk_static",
     "manta_b200_embedder_bind", "manta_b200_embedder_unbind", "manta_b200_embed_pooled", "manta_b200_embed_score_topk",
-    "manta_b200_embed_device",
+    "manta_b200_embed_device", "manta_b200_score_batched", "manta_b200_score_topk_batched",
 ]
 
 
@@ -92,6 +92,9 @@ def load() -> ctypes.CDLL:
         "manta_b200_topk_merge_device": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_void_p,
                                          c_void_p, c_int, E],
         "manta_b200_gather_rows": [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, E],
+        "manta_b200_score_batched": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_void_p, E],
+        "manta_b200_score_topk_batched": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_int, c_void_p,
+                                          c_void_p, E],
         "manta_b200_embedder_bind": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, POINTER(c_void_p), E],
         "manta_b200_embedder_unbind": [c_void_p, c_void_p, E],
         "manta_b200_embed_pooled": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, E],
@@ -307,6 +310,34 @@ class Runtime:
         call("manta_b200_topk_merge_device", self.handle, c_int(ORDER_SMALLEST if smallest else ORDER_LARGEST), _ptr(d_ids),
              _ptr(d_scores), c_int(lists), c_int64(list_stride), c_int(nq), c_int(k), _ptr(d_out_ids), _ptr(d_out_scores),
              c_int(1 if sync else 0))
+
+    # ---- per-query candidate sets [Q,D] x [Q,N,D] -----------------------------------------------------------
+    @staticmethod
+    def _batched_args(queries, docs):
+        q = np.ascontiguousarray(queries, dtype=np.float32)
+        d = np.ascontiguousarray(docs, dtype=np.float32)
+        if q.ndim != 2 or d.ndim != 3:
+            raise MantaError("score expects query/docs as [D] x [N,D] or [Q,D] x [Q,N,D]")  # tensor_ops.go:1520
+        if q.shape[0] != d.shape[0] or q.shape[1] != d.shape[2]:
+            raise MantaError(f"score mismatch {list(q.shape)} x {list(d.shape)}")
+        return q, d
+
+    def score_batched(self, metric: str, queries, docs) -> np.ndarray:
+        q, d = self._batched_args(queries, docs)
+        out = np.empty((d.shape[0], d.shape[1]), np.float32)
+        call("manta_b200_score_batched", self.handle, c_int(METRICS[metric]), _ptr(q), _ptr(d), c_int(d.shape[0]), c_int64(d.shape[1]),
+             c_int(d.shape[2]), c_int(MEM_HOST), _ptr(out))
+        return out
+
+    def score_topk_batched(self, metric: str, queries, docs, k: int, smallest: bool = False):
+        q, d = self._batched_args(queries, docs)
+        kk = max(int(k), 0)
+        ids = np.empty((d.shape[0], kk), np.int32)
+        scores = np.empty((d.shape[0], kk), np.float32)
+        call("manta_b200_score_topk_batched", self.handle, c_int(METRICS[metric]), c_int(ORDER_SMALLEST if smallest else ORDER_LARGEST),
+             _ptr(q), _ptr(d), c_int(d.shape[0]), c_int64(d.shape[1]), c_int(d.shape[2]), c_int(MEM_HOST), c_int(int(k)), _ptr(ids),
+             _ptr(scores))
+        return ids, scores
 
     # ---- embedding front end -----------------------------------------------------------------------------
     def bind_embedder(self, table, projection):

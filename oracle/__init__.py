@@ -257,3 +257,46 @@ def embed_pooled(table, proj, tokens, mask, order: int = 0) -> np.ndarray:
     if rc != 0:
         raise OracleError("gather index out of range")
     return out
+
+
+def retrieval_quality(query_vectors, query_ids, doc_vectors, doc_ids, qrels, top_k: int = 100) -> dict:
+    """computeRetrievalQuality + topRetrievalScores + ndcgAt / mrrAt / recallAt of the reference's eval-retrieval
+    command (runtime/retrieval_eval.go:541-726), restated in Python for small cases: f32 sequential dot per
+    document (:649-659), ranking by score descending then document ID string ascending (:618-626), top_k raised to
+    at least 100 (:546-548) and clamped to the corpus (:587-589)."""
+    import math
+
+    q = _f32(query_vectors)
+    d = _f32(doc_vectors)
+    doc_set = set(doc_ids)
+    top_k = max(int(top_k), 100)
+    k = min(top_k, len(doc_ids)) if top_k <= len(doc_ids) else len(doc_ids)
+    totals = {"ndcg_at_10": 0.0, "mrr_at_10": 0.0, "recall_at_10": 0.0, "recall_at_100": 0.0}
+    evaluated = relevant_pairs = skipped_docs = skipped_queries = 0
+    for qi, qid in enumerate(query_ids):
+        rels = {}
+        for doc_id, rel in qrels.get(qid, {}).items():
+            if doc_id in doc_set:
+                rels[doc_id] = float(rel)
+            else:
+                skipped_docs += 1
+        if not rels:
+            skipped_queries += 1
+            continue
+        scores = dot_rows(q[qi], d)  # dotRetrievalVectors: f32 sequential
+        ranked = sorted(range(len(doc_ids)), key=lambda i: (-float(scores[i]), doc_ids[i]))[:k]
+        ids = [doc_ids[i] for i in ranked]
+        evaluated += 1
+        relevant_pairs += len(rels)
+        dcg = sum(rels.get(ids[i], 0.0) / math.log2(i + 2) for i in range(min(10, len(ids))) if rels.get(ids[i], 0.0) > 0)
+        ideal = sorted((r for r in rels.values() if r > 0), reverse=True)[:10]
+        idcg = sum(r / math.log2(i + 2) for i, r in enumerate(ideal))
+        totals["ndcg_at_10"] += dcg / idcg if idcg else 0.0
+        totals["mrr_at_10"] += next((1.0 / (i + 1) for i in range(min(10, len(ids))) if rels.get(ids[i], 0.0) > 0), 0.0)
+        totals["recall_at_10"] += sum(1 for i in ids[:10] if rels.get(i, 0.0) > 0) / len(rels)
+        totals["recall_at_100"] += sum(1 for i in ids[:100] if rels.get(i, 0.0) > 0) / len(rels)
+    if evaluated:
+        totals = {name: v / evaluated for name, v in totals.items()}
+    return {"quality": totals, "evaluated_queries": evaluated, "relevant_pairs": relevant_pairs,
+            "skipped_relevant_docs": skipped_docs, "skipped_no_relevant": skipped_queries,
+            "scored_pairs": evaluated * len(doc_ids), "top_k": k}

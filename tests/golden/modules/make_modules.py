@@ -102,6 +102,30 @@ def build():
         cand_steps("rerank_candidates_packed") +
         [step("rerank_candidates_packed", "pack_candidates", "pack_candidates", ["top_candidate_ids", "top_scores", "top_docs"], ["candidates"]),
          step("rerank_candidates_packed", "return", "return", None, ["candidates"])])
+    # the per-query-docs entries of the reference's score / retrieval bundles (runtime/score_model_test.go:86-131,
+    # runtime/retrieval_model_test.go:94-150)
+    qb_in = [{"name": "queries", "type": ttype("f16", ["Q", "D"])}, {"name": "docs", "type": ttype("q4", ["Q", "N", "D"])}]
+    cos_batch = dict(kernel("cosine", ["Q", "D"], ["Q", "N", "D"], ["Q", "N"]), name="cosine_batch")
+    mods["score_bundle"] = module("score_bundle", [],
+        [{"name": "score", "kind": "pipeline", "inputs": q_in + [{"name": "docs", "type": ttype("q4", ["N", "D"])}],
+          "outputs": [{"name": "scores", "type": ttype("f32", ["N"])}]},
+         {"name": "score_batch", "kind": "pipeline", "inputs": qb_in, "outputs": [{"name": "scores", "type": ttype("f32", ["Q", "N"])}]}],
+        cos + [cos_batch],
+        [step("score", "launch_kernel", "cosine", ["query", "docs"], ["scores"], "cosine"), step("score", "return", "return", None, ["scores"]),
+         step("score_batch", "launch_kernel", "cosine_batch", ["queries", "docs"], ["scores"], "cosine_batch"),
+         step("score_batch", "return", "return", None, ["scores"])])
+    eb = "rerank_candidates_packed_batch"
+    mods["retrieval_bundle"] = module("retrieval_bundle", [],
+        [{"name": eb, "kind": "pipeline", "inputs": qb_in + [{"name": "candidate_ids", "type": ttype("i64", ["Q", "N"])}],
+          "outputs": [{"name": "candidates", "type": {"kind": "candidate_pack", "candidate_pack": {"shape": ["Q", "2", "D"]}}}]}],
+        [cos_batch],
+        [step(eb, "launch_kernel", "cosine_batch", ["queries", "docs"], ["scores"], "cosine_batch"),
+         step(eb, "topk", "topk", ["scores"], ["top_indices"], None, {"k": "2"}),
+         step(eb, "gather", "gather", ["candidate_ids", "top_indices"], ["top_candidate_ids"]),
+         step(eb, "gather", "gather", ["scores", "top_indices"], ["top_scores"]),
+         step(eb, "gather", "gather", ["docs", "top_indices"], ["top_docs"]),
+         step(eb, "pack_candidates", "pack_candidates", ["top_candidate_ids", "top_scores", "top_docs"], ["candidates"]),
+         step(eb, "return", "return", None, ["candidates"])])
     for op in ("dot", "cosine", "l2_distance"):
         mods["direct_" + op] = module(op, [],
             [{"name": "score", "kind": "pipeline",

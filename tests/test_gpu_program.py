@@ -204,3 +204,78 @@ def test_memory_plan_residency_is_honoured(rt):
         res = prog.run("retrieve", {"query": T("f16", [2], [1, 0])})
         assert res.metadata["params_released"] == "0"
     assert rt.stats()["bind_calls"] == binds1 + 1
+
+
+# ---- per-query candidate sets [Q,D] x [Q,N,D] -----------------------------------------------------------------
+BATCH_Q = [1, 0, 0, 1]
+BATCH_DOCS = [1, 0, 0, 1, 1, 1, 0, 1, 1, 0, 1, 1]
+
+
+def test_score_bundle_score_batch(rt):
+    # TestScoreModelScoreBatch, runtime/score_model_test.go:86-131
+    from manta_b200.program import Program
+
+    prog = Program(rt, load("score_bundle"))
+    res = prog.run("score_batch", {"queries": T("f16", [2, 2], BATCH_Q), "docs": T("q4", [2, 3, 2], BATCH_DOCS)})
+    out = res.outputs["scores"]
+    assert out.producer == "kernel:cosine_batch" and out.dtype == "f32"
+    assert list(out.data.shape) == [2, 3]
+    np.testing.assert_allclose(out.data, [[1, 0, 0.70710677], [1, 0, 0.70710677]], atol=TOL)
+    assert out.metadata["device_execution"] is True and out.metadata["candidate_sets"] == "per_query"
+    # the rank-1 entry of the same bundle still runs
+    res = prog.run("score", {"query": T("f16", [2], [1, 0]), "docs": T("q4", [2, 2], [1, 0, 0, 1])})
+    np.testing.assert_allclose(res.outputs["scores"].data, [1, 0], atol=TOL)
+
+
+def test_retrieval_bundle_packed_batch(rt):
+    # TestRetrievalModelRetrieveBatch, runtime/retrieval_model_test.go:94-150
+    from manta_b200.program import Program
+
+    prog = Program(rt, load("retrieval_bundle"))
+    res = prog.run("rerank_candidates_packed_batch", {
+        "queries": T("f16", [2, 2], BATCH_Q), "docs": T("q4", [2, 3, 2], BATCH_DOCS),
+        "candidate_ids": T("i64", [2, 3], [1001, 2002, 3003, 4004, 5005, 6006])})
+    out = res.outputs["candidates"]
+    assert out.kind == "candidate_pack"
+    np.testing.assert_array_equal(out.data["ids"], [[1001, 3003], [4004, 6006]])
+    np.testing.assert_allclose(out.data["scores"], [[1, 0.70710677], [1, 0.70710677]], atol=TOL)
+    np.testing.assert_allclose(out.data["docs"], [[[1, 0], [1, 1]], [[0, 1], [1, 1]]], atol=TOL)
+    assert res.metadata["fused_passes"] == "1"
+    with pytest.raises(Exception, match="score mismatch"):
+        prog.run("rerank_candidates_packed_batch", {
+            "queries": T("f16", [3, 2], [1, 0, 0, 1, 1, 1]), "docs": T("q4", [2, 3, 2], BATCH_DOCS),
+            "candidate_ids": T("i64", [2, 3], [1, 2, 3, 4, 5, 6])})
+
+
+@pytest.mark.parametrize("metric", ["dot", "cosine", "l2_distance"])
+@pytest.mark.parametrize("shape", [(1, 1, 1), (3, 50, 7), (5, 300, 64), (16, 1000, 384), (2, 20000, 128)])
+def test_batched_abi_matches_oracle(rt, metric, shape):
+    nq, rows, cols = shape
+    rng = np.random.default_rng(nq * 1000 + rows + cols)
+    q = make_rows(rng, nq, cols)
+    docs = make_rows(rng, nq * rows, cols, normalised=False).reshape(nq, rows, cols)
+    docs[0, 0] = 0  # a zero row: cosine is exactly 0
+    got = rt.score_batched(metric, q, docs)
+    want = oracle.SCORE_FNS[metric](q, docs)
+    np.testing.assert_allclose(got, want, rtol=2e-6, atol=2e-6 * np.abs(want).max())
+    if metric == "cosine":
+        assert got[0, 0] == 0.0
+    k = min(10, rows)
+    for smallest in (False, True):
+        ids, sc = rt.score_topk_batched(metric, q, docs, k, smallest=smallest)
+        for i in range(nq):
+            ref_ids = oracle.topk(got[i], k, smallest)  # selection rule on the device's own scores: bit-exact
+            np.testing.assert_array_equal(ids[i], ref_ids)
+            np.testing.assert_array_equal(sc[i], got[i][ref_ids])
+
+
+def test_batched_abi_errors(rt):
+    from manta_b200 import native
+
+    q = np.zeros((2, 4), np.float32)
+    with pytest.raises(native.MantaError, match="score expects query/docs"):
+        rt.score_batched("dot", q, np.zeros((3, 4), np.float32))
+    with pytest.raises(native.MantaError, match="score mismatch"):
+        rt.score_batched("dot", q, np.zeros((2, 3, 5), np.float32))
+    with pytest.raises(native.MantaError, match="topk limit 4 out of range for row width 3"):
+        rt.score_topk_batched("dot", q, np.zeros((2, 3, 4), np.float32), 4)

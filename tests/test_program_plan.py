@@ -34,6 +34,16 @@ def test_retrieve_and_packed_plans():
     assert plan[0]["execution"] == "fused_pass" and plan[3]["execution"] == "fused_with_score"
 
 
+def test_per_query_bundle_plans():
+    # the [Q,D] x [Q,N,D] entries of the reference's score / retrieval bundles
+    prog = Program(None, load("score_bundle"))
+    assert [s["execution"] for s in prog.plan("score_batch")] == ["score_pass", "host"]
+    assert [s["execution"] for s in prog.plan("score")] == ["score_pass", "host"]
+    plan = Program(None, load("retrieval_bundle")).plan("rerank_candidates_packed_batch")
+    assert [s["kind"] for s in plan] == ["launch_kernel", "topk", "gather", "gather", "gather", "pack_candidates", "return"]
+    assert plan[0]["execution"] == "fused_pass" and plan[1]["execution"] == "fused_with_score"
+
+
 def test_scores_returned_next_to_topk_forces_full_scores():
     mod = load("tiny_rerank")
     mod["steps"][-1]["outputs"].append("scores")
