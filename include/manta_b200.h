@@ -180,6 +180,18 @@ int manta_b200_topk_merge_device(MantaB200Runtime* rt, int order, const int32_t*
 int manta_b200_gather_rows(MantaB200Runtime* rt, const MantaB200Candidates* set, const int32_t* ids, int64_t n,
                            float* out, char** err);
 
+/* ---- packed candidate files ------------------------------------------------------------------------------
+ * The stored form of a bound set (codes + scales of its layout) on disk.  The reference exports q4 / q8 tensors
+ * widened to float32 inside its MLL container (runtime/mll_export.go:833-866, read back by decodeTensorEntry,
+ * runtime/weight_file.go:304-367; the container library github.com/odvcencio/mll is a separate module); this file
+ * keeps the packed bytes, so a set is quantised once and a row shard [row_begin, row_end) of it can be bound per GPU
+ * (row_end < 0: to the end; ids continue from the file's row_base).  verify != 0 checks the payload checksum. */
+int manta_b200_candidates_save(MantaB200Runtime* rt, const MantaB200Candidates* set, const char* path, char** err);
+int manta_b200_candidates_load(MantaB200Runtime* rt, const char* path, int64_t row_begin, int64_t row_end, int verify,
+                               MantaB200Candidates** out, char** err);
+int manta_b200_packed_file_info(const char* path, int* layout, int64_t* rows, int* cols, int64_t* row_base,
+                                int64_t* stored_bytes, char** err);
+
 /* ---- per-query candidate sets: queries [Q,D] x docs [Q,N,D] ----------------------------------------------
  * The second legal shape of the score builtins (scoreLayout, runtime/backend/tensor_ops.go:1492-1521), used by
  * ScoreModel.ScoreBatch / RetrievalModel.RetrieveBatch (runtime/score_model.go:238-324, retrieval_model.go:246-332).

@@ -35,6 +35,7 @@ EXPORTS = [
     "manta_b200_gather_rows", "manta_b200_q8_accumulators", "manta_b200_score_topk_static",
     "manta_b200_embedder_bind", "manta_b200_embedder_unbind", "manta_b200_embed_pooled", "manta_b200_embed_score_topk",
     "manta_b200_embed_device", "manta_b200_score_batched", "manta_b200_score_topk_batched",
+    "manta_b200_candidates_save", "manta_b200_candidates_load", "manta_b200_packed_file_info",
 ]
 
 
@@ -92,6 +93,9 @@ def load() -> ctypes.CDLL:
         "manta_b200_topk_merge_device": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_void_p,
                                          c_void_p, c_int, E],
         "manta_b200_gather_rows": [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, E],
+        "manta_b200_candidates_save": [c_void_p, c_void_p, c_char_p, E],
+        "manta_b200_candidates_load": [c_void_p, c_char_p, c_int64, c_int64, c_int, POINTER(c_void_p), E],
+        "manta_b200_packed_file_info": [c_char_p, POINTER(c_int), POINTER(c_int64), POINTER(c_int), POINTER(c_int64), POINTER(c_int64), E],
         "manta_b200_score_batched": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_void_p, E],
         "manta_b200_score_topk_batched": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_int, c_void_p,
                                           c_void_p, E],
@@ -142,6 +146,12 @@ def f16_bits(x) -> np.ndarray:
     if a.dtype == np.float16:
         return np.ascontiguousarray(a).view(np.uint16)
     return np.ascontiguousarray(a.astype(np.float16)).view(np.uint16)
+
+
+def packed_file_info(path: str) -> dict:
+    layout, rows, cols, base, stored = c_int(), c_int64(), c_int(), c_int64(), c_int64()
+    call("manta_b200_packed_file_info", os.fsencode(path), byref(layout), byref(rows), byref(cols), byref(base), byref(stored))
+    return {"layout": layout.value, "rows": rows.value, "cols": cols.value, "row_base": base.value, "stored_bytes": stored.value}
 
 
 class Candidates:
@@ -212,6 +222,19 @@ class Runtime:
         s = Stats()
         call("manta_b200_runtime_stats", self.handle, byref(s))
         return s.as_dict()
+
+    # ---- packed candidate files ---------------------------------------------------------------------
+    def save_candidates(self, cands: "Candidates", path: str) -> None:
+        call("manta_b200_candidates_save", self.handle, cands.handle, os.fsencode(path))
+
+    def load_candidates(self, path: str, row_begin: int = 0, row_end: int = -1, verify: bool = False) -> "Candidates":
+        """Binds rows [row_begin, row_end) of a packed candidate file (row_end < 0: to the end)."""
+        info = packed_file_info(path)
+        end = info["rows"] if row_end < 0 else row_end
+        h = c_void_p()
+        call("manta_b200_candidates_load", self.handle, os.fsencode(path), c_int64(row_begin), c_int64(row_end), c_int(1 if verify else 0),
+             byref(h))
+        return Candidates(self, h, info["layout"], int(end - row_begin), info["cols"], info["row_base"] + int(row_begin))
 
     # ---- candidates -------------------------------------------------------------------------------
     def bind(self, layout, data, scales=None, row_base: int = 0, rows=None, cols=None, mem=None) -> Candidates:
