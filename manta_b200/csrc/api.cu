@@ -614,7 +614,8 @@ static int score_topk_locked(MantaB200Runtime* rt, const MantaB200Candidates* se
                              const void* d_queries, int nq, int k, int32_t* d_out_ids, float* d_out_scores, int sync,
                              char** err) {
     const CandView& cv = set->cv;
-    const uint32_t nb = (uint32_t)std::max(gemv_bucket_count(rt->sm_count), mma_bucket_count(rt->sm_count));
+    // a multiple of four, so that every query's bucket row starts on a 16-byte boundary
+    const uint32_t nb = ((uint32_t)std::max(gemv_bucket_count(rt->sm_count), mma_bucket_count(rt->sm_count)) + 3u) & ~3u;
     uint32_t cap = pool_cap_for(rt, cv, nq, k);
     SelectWs ws;
     if (ensure_select_ws(rt, nq, cap, nb, &ws, err)) return 1;

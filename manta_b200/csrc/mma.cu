@@ -4,8 +4,11 @@
 // planes of every query; f32 for f16), and four epilogue warps read the accumulators back (tcgen05.ld), finish
 // the scores with the same epilogue functions as the streaming kernel and filter them into the top-k pools.
 //
-// Warp roles (11 warps): 0 = TMA producer, 1 = MMA issuer (owns the tensor-memory allocation), 2..9 = epilogue
-// (two per 32-lane quadrant of tensor memory, taking alternate 16-query chunks), 10 = threshold refresher.
+// Warp roles (19 warps): 0 = TMA producer, 1 = MMA issuer (owns the tensor-memory allocation), 2..17 = epilogue
+// (four per 32-lane quadrant of tensor memory, each taking every fourth 16-query chunk), 18 = threshold refresher.
+// The epilogue is latency-bound (tensor-memory reads, dependent arithmetic), so it is spread over as many warps as
+// the register file allows: 608 threads x 104 registers.  To fit, the exact scoring of a chunk that passes the
+// cheap filter re-reads its accumulators four queries at a time instead of keeping sixteen finished scores live.
 //
 // Every wait in this file is bounded: a wait that runs out sets the abort flag of the CTA and the time-out flag
 // of the pass, every role leaves its loop, tensor memory is released and the kernel returns; the host then
@@ -23,12 +26,13 @@ namespace {
 
 constexpr int kTileRows = 128;
 constexpr int kChunkBytes = 128;      // K extent of one pipeline stage, in bytes (one 128-byte swizzle span)
-constexpr int kEpiWarps = 8;          // two per tensor-memory quadrant, taking alternate 16-query chunks
-constexpr int kMmaThreads = 32 * (2 + kEpiWarps + 1);
+// SUBS (template parameter of the kernel) = epilogue warps per tensor-memory quadrant; warp s of a quadrant takes the
+// 16-query chunks s, s + SUBS, ...
+constexpr int mma_threads(int subs) { return 32 * (2 + 4 * subs + 1); }
 constexpr int kMmaCols = 256;         // N of one MMA
 constexpr int kBucketSlots = 4;       // bucket slots per epilogue warp (tiles rotate through them)
 constexpr uint32_t kSpinLimit = 1u << 22;
-constexpr int kRefStage = 2560;       // bucket maxima per query the refresher can hold (80 registers per lane)
+constexpr int kRefStage = 2560;       // bucket maxima per query the refresher stages in shared memory
 
 // ---- PTX wrappers -------------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -105,6 +109,11 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
           "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
         : "r"(taddr));
 }
+__device__ __forceinline__ void tmem_ld4(uint32_t taddr, uint32_t (&v)[4]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3])
+                 : "r"(taddr));
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // K-major operand tile in shared memory, 128-byte swizzle: rows of 128 bytes, groups of 8 rows 1024 bytes apart.
@@ -129,6 +138,7 @@ struct KernelArgs {
     int lo_off;                   // q8: column offset of the low planes
     int kchunks;                  // 128-byte chunks per row
     int stages;
+    int epi_subs;                 // epilogue warps per tensor-memory quadrant (2 or 4): which instantiation runs
     int b_resident;               // operand B (all K chunks) is loaded once and stays in shared memory
     int metric;
     int order;
@@ -140,14 +150,13 @@ struct KernelArgs {
     unsigned long long* dbg;      // debugging: cycle counts of one epilogue warp (null in normal use)
 };
 
-// Scores of 16 consecutive queries for one candidate row (one lane).  METRIC is a compile-time constant so that
-// the sixteen evaluations are one basic block the compiler can interleave.
-template <bool I8, int METRIC>
-__device__ __forceinline__ void score16(const uint32_t (&vh)[16], const uint32_t (&vl)[16], uint32_t stat, float rinv, float sd,
-                                        const QueryHeader* hdr_s, int c0, int qn, bool rv, float sign, float (&g)[16],
-                                        uint32_t (&o)[16]) {
+// Scores of N consecutive queries for one candidate row (one lane).  METRIC is a compile-time constant so that
+// the evaluations are one basic block the compiler can interleave.
+template <bool I8, int METRIC, int N>
+__device__ __forceinline__ void score_n(const uint32_t (&vh)[N], const uint32_t (&vl)[N], uint32_t stat, float rinv, float sd,
+                                        const QueryHeader* hdr_s, int c0, int qn, bool rv, float sign, float (&g)[N], uint32_t (&o)[N]) {
 #pragma unroll
-    for (int jj = 0; jj < 16; ++jj) {
+    for (int jj = 0; jj < N; ++jj) {
         const int j = min(c0 + jj, qn - 1);
         float score;
         if constexpr (I8)
@@ -159,12 +168,14 @@ __device__ __forceinline__ void score16(const uint32_t (&vh)[16], const uint32_t
     }
 }
 
-template <bool I8, int METRIC>
-__global__ void __launch_bounds__(kMmaThreads, 1)
+template <bool I8, int METRIC, int SUBS>
+__global__ void __launch_bounds__(mma_threads(SUBS), 1)
 mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const KernelArgs a) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int S = a.stages;
+    constexpr int kEpiSubs = SUBS;
+    constexpr int kEpiWarps = 4 * SUBS;
     const uint32_t b_stage_bytes = (uint32_t)a.ncols * kChunkBytes;
     unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* sA = base;
@@ -184,6 +195,7 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     uint32_t* bmax_s = thr_s + kMmaCols;                 // [qn][4]: maxima of the current tile per epilogue warp
     uint32_t* pub_s = bmax_s + kMmaCols * 4;             // [qn][4][kBucketSlots]: last published values
     float4* filt_s = (float4*)(pub_s + kMmaCols * 4 * kBucketSlots);  // [qn]: s_hi, s_lo, cheap pre-filter bound
+    uint32_t* ref_s = (uint32_t*)(filt_s + kMmaCols);                 // [kRefStage]: the refresher's copy of one query's buckets (16-byte aligned)
 
     const int64_t nrows = a.row_end - a.row_begin;
     const int n_tiles = (int)((nrows + kTileRows - 1) / kTileRows);
@@ -223,6 +235,7 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
+    const long long t_start = (a.dbg != nullptr) ? clock64() : 0;
     auto tile_of = [&](int it) { return cta + ((it < n_my) ? it : it - n_my) * grid; };
 
     if (n_my > 0) {
@@ -287,17 +300,18 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         } else if (warp < 2 + kEpiWarps) {
             // ---------------- epilogue ----------------
             // The epilogue warps never synchronise with each other: each reads one quadrant of tensor memory for
-            // its half of the query chunks, owns the bucket maxima of (quadrant, those queries), and arrives on the
+            // its share of the query chunks, owns the bucket maxima of (quadrant, those queries), and arrives on the
             // accumulator's "empty" barrier by itself.
             const int quad = warp & 3;              // tensor-memory lanes 32*quad .. 32*quad+31
             const int ew = quad;                    // bucket owner index 0..3 (rows of a quadrant are one bucket)
-            const int half = (warp - 2) >> 2;       // which of the alternating 16-query chunks this warp takes
+            const int sub = (warp - 2) >> 2;        // this warp takes the 16-query chunks sub, sub + kEpiSubs, ...
             const float sign = (a.order == MANTA_B200_ORDER_SMALLEST) ? -1.0f : 1.0f;
             const bool want_scale = I8 && METRIC != MANTA_B200_METRIC_COSINE;
             const bool want_stats = METRIC != MANTA_B200_METRIC_DOT;
             const bool cheap = a.order == MANTA_B200_ORDER_LARGEST && METRIC != MANTA_B200_METRIC_L2_DISTANCE;
             unsigned long long c_wait = 0, c_ld = 0, c_math = 0, c_slow = 0, c_house = 0, n_slow = 0, c_thr = 0;
             const bool timing = a.dbg != nullptr && cta == 0 && warp == 4;
+            (void)c_ld; (void)c_slow;
             for (int it = 0; it < n_iters; ++it) {
                 long long t0 = timing ? clock64() : 0;
                 const bool observe = it < n_obs;            // score and record maxima only
@@ -319,26 +333,55 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 if (METRIC == MANTA_B200_METRIC_COSINE) rinv = I8 ? q8_row_inv_norm((int)stat) : float_row_inv_norm(__uint_as_float(stat));
                 if (!mbar_wait(&tfull[acc], (uint32_t)(it >> 1) & 1u, abort_s)) break;
                 tc_fence_after();
+                if (timing && it == 0 && lane == 0) a.dbg[11] = (unsigned long long)(clock64() - t_start);   // first accumulator ready
                 if (timing) { long long t1 = clock64(); c_wait += t1 - t0; t0 = t1; }
                 const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)acc * kMmaCols;
                 const int32_t my_id = (int32_t)(a.cv.row_base + row);
                 // row factor of the pre-filter; NaN for rows past the end makes every comparison false
                 float rowc = __int_as_float(0x7fc00000);
                 if (rv) rowc = (METRIC == MANTA_B200_METRIC_COSINE) ? rinv : (I8 ? sd : 1.0f);
-                // chunks of 16 queries for this lane's row
-                for (int c0 = half * 16; c0 < a.qn; c0 += 32) {
-                    uint32_t vh[16], vl[16];
-                    tmem_ld16(t_row + c0, vh);
-                    if constexpr (I8) {
-                        tmem_ld16(t_row + a.lo_off + c0, vl);
-                    } else {
-#pragma unroll
-                        for (int jj = 0; jj < 16; ++jj) vl[jj] = 0;
+                // One finished score of this lane's row for query j: vote against the bound, keep the bucket maximum,
+                // append the passing rows with one reservation per warp.
+                auto offer = [&](int j, float g, uint32_t o) {
+                    const uint32_t ballot = __ballot_sync(0xffffffffu, o >= thr_s[min(j, a.qn - 1)]);
+                    if (ballot == 0) return;
+                    const bool pass = (ballot >> lane) & 1u;
+                    if (!replay) {
+                        // only scores at or above the current bound can raise it, so the bucket maxima are
+                        // maintained from the passing rows (all valid rows while no bound exists)
+                        const uint32_t wmax = __reduce_max_sync(0xffffffffu, pass ? o : 0u);
+                        if (lane == 0 && wmax > bmax_s[j * 4 + ew]) bmax_s[j * 4 + ew] = wmax;
                     }
-                    tmem_ld_wait();
+                    if (observe) return;
+                    uint32_t pos0 = 0;
+                    if (lane == 0) pos0 = atomicAdd(a.ws.count + a.q0 + j, (uint32_t)__popc(ballot));
+                    pos0 = __shfl_sync(0xffffffffu, pos0, 0);
+                    if (pass) {
+                        const uint32_t pos = pos0 + __popc(ballot & ((1u << lane) - 1u));
+                        if (pos < a.ws.cap)
+                            a.ws.pool[(size_t)(a.q0 + j) * a.ws.cap + pos] = make_key(g, my_id);
+                        else
+                            a.ws.flags[kFlagOverflow] = 1u;
+                    }
+                };
+                // chunks of 16 queries for this lane's row
+                for (int c0 = sub * 16; c0 < a.qn; c0 += 16 * kEpiSubs) {
+                    uint32_t groups = 0xFu;   // four-query groups of the chunk that need the exact evaluation
+                    uint32_t vh[16], vl[16];
+                    if (cheap) {
+                        tmem_ld16(t_row + c0, vh);
+                        if constexpr (I8) {
+                            tmem_ld16(t_row + a.lo_off + c0, vl);
+                        } else {
+#pragma unroll
+                            for (int jj = 0; jj < 16; ++jj) vl[jj] = 0;
+                        }
+                        tmem_ld_wait();
+                    }
                     if (cheap) {
                         // Pre-filter without finishing the scores: score >= bound  <=>  t * rowc >= bound / qinv, the
-                        // right-hand side (slackened by a few ulps) kept per query by the refresher.
+                        // right-hand side (slackened by a few ulps) kept per query by the refresher.  Almost every
+                        // chunk ends here.
                         uint32_t hit = 0;
 #pragma unroll
                         for (int jj = 0; jj < 16; ++jj) {
@@ -348,47 +391,38 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                                 t = __fmaf_rn((float)(int)vl[jj], f.y, __fmul_rn((float)(int)vh[jj], f.x));
                             else
                                 t = __uint_as_float(vh[jj]);
-                            hit |= (t * rowc >= f.z) ? 1u : 0u;
+                            hit |= (t * rowc >= f.z) ? (1u << jj) : 0u;
                         }
-                        if (!__any_sync(0xffffffffu, hit != 0u)) continue;
+                        hit = __reduce_or_sync(0xffffffffu, hit);
+                        if (hit == 0u) continue;
+                        groups = ((hit & 0x000Fu) ? 1u : 0u) | ((hit & 0x00F0u) ? 2u : 0u) | ((hit & 0x0F00u) ? 4u : 0u) |
+                                 ((hit & 0xF000u) ? 8u : 0u);
                     }
-                    // scores of 16 queries for this lane's row: straight-line, independent arithmetic
-                    float g[16];
-                    uint32_t o[16];
-                    score16<I8, METRIC>(vh, vl, stat, rinv, sd, hdr_s, c0, a.qn, rv, sign, g, o);
-                    // filter: one vote per query; everything behind a non-empty vote is the rare path
-                    uint32_t votes[16];
-                    uint32_t any = 0;
-#pragma unroll
-                    for (int jj = 0; jj < 16; ++jj) {
-                        const int j = min(c0 + jj, a.qn - 1);
-                        votes[jj] = __ballot_sync(0xffffffffu, o[jj] >= thr_s[j]);
-                        any |= votes[jj];
-                    }
-                    if (any == 0) continue;
                     n_slow++;
+                    {
+                        // The accumulators of a group that passed are re-read four queries at a time instead of keeping
+                        // sixteen finished scores live: the epilogue stays under 104 registers, which is what lets four
+                        // warps per quadrant fit, and it is also the faster form when passing chunks are frequent.
+#pragma unroll 1
+                        for (int gq = 0; gq < 4; ++gq) {
+                            const int cg = c0 + 4 * gq;
+                            if (cg >= a.qn) break;
+                            if (!((groups >> gq) & 1u)) continue;
+                            uint32_t h4[4], l4[4];
+                            tmem_ld4(t_row + cg, h4);
+                            if constexpr (I8) {
+                                tmem_ld4(t_row + a.lo_off + cg, l4);
+                            } else {
 #pragma unroll
-                    for (int jj = 0; jj < 16; ++jj) {
-                        const uint32_t ballot = votes[jj];
-                        if (ballot == 0) continue;
-                        const int j = c0 + jj;
-                        const bool pass = (ballot >> lane) & 1u;
-                        if (!replay) {
-                            // only scores at or above the current bound can raise it, so the bucket maxima are
-                            // maintained from the passing rows (all valid rows while no bound exists)
-                            const uint32_t wmax = __reduce_max_sync(0xffffffffu, pass ? o[jj] : 0u);
-                            if (lane == 0 && wmax > bmax_s[j * 4 + ew]) bmax_s[j * 4 + ew] = wmax;
-                        }
-                        if (observe) continue;
-                        uint32_t pos0 = 0;
-                        if (lane == 0) pos0 = atomicAdd(a.ws.count + a.q0 + j, (uint32_t)__popc(ballot));
-                        pos0 = __shfl_sync(0xffffffffu, pos0, 0);
-                        if (pass) {
-                            const uint32_t pos = pos0 + __popc(ballot & ((1u << lane) - 1u));
-                            if (pos < a.ws.cap)
-                                a.ws.pool[(size_t)(a.q0 + j) * a.ws.cap + pos] = make_key(g[jj], my_id);
-                            else
-                                a.ws.flags[kFlagOverflow] = 1u;
+                                for (int jj = 0; jj < 4; ++jj) l4[jj] = 0;
+                            }
+                            tmem_ld_wait();
+                            float g[4];
+                            uint32_t o[4];
+                            score_n<I8, METRIC, 4>(h4, l4, stat, rinv, sd, hdr_s, cg, a.qn, rv, sign, g, o);
+#pragma unroll
+                            for (int jj = 0; jj < 4; ++jj)
+                                if (cg + jj < a.qn) offer(cg + jj, g[jj], o[jj]);
                         }
                     }
                 }
@@ -402,7 +436,7 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 if (a.filtered && !replay && (it < 16 || (it & 3) == 3 || it + 1 == n_my)) {
                     const int slot = (it < 16 ? it : (it >> 2)) % kBucketSlots;
                     for (int j = lane; j < a.qn; j += 32) {
-                        if (((j >> 4) & 1) != half) continue;   // the other warp of the quadrant owns this query
+                        if (((j >> 4) % kEpiSubs) != sub) continue;   // another warp of the quadrant owns this query
                         const int i = j * 4 + ew;
                         const uint32_t v = bmax_s[i];
                         bmax_s[i] = 0;
@@ -438,31 +472,76 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 seen = ld_relaxed_u32(a.ready);
                 if (seen < want) __nanosleep(64);
             }
+            if (a.dbg != nullptr && cta == 0 && lane == 0) a.dbg[8] = (unsigned long long)(clock64() - t_start);   // all CTAs published
             const uint32_t nb = min(a.ws.nb, (uint32_t)kRefStage);
             for (uint32_t round = 0; *done_s < (uint32_t)kEpiWarps && !*abort_s; ++round) {
                 const int j = (int)(((uint64_t)cta + (uint64_t)round * grid) % (uint64_t)a.qn);
                 const uint32_t* b = a.ws.bucket + (size_t)(a.q0 + j) * a.ws.nb;
-                // the bucket maxima of the query live in registers for the twenty counting passes
-                uint32_t v[kRefStage / 32];
-#pragma unroll
-                for (int i = 0; i < kRefStage / 32; ++i) {
-                    const uint32_t idx = (uint32_t)i * 32u + lane;
-                    v[i] = (idx < nb) ? __ldcg(b + idx) : 0u;
-                }
+                // k-th largest bucket maximum of the query, top 20 bits.  The four slots of one (CTA, quadrant) are
+                // adjacent, so one 16-byte load brings them; while 4k <= buckets their maximum is taken as ONE bucket
+                // (a union of disjoint row sets is still disjoint from the others), which leaves 20 values per lane in
+                // registers for the twenty counting passes.  Larger k stages all buckets in shared memory.
+                const uint32_t nb4 = nb >> 2;   // the bucket count is a multiple of four (sixteen per SM)
+                const uint4* b4 = reinterpret_cast<const uint4*>(b);
                 uint32_t t = 0;
-                for (int bit = 31; bit >= 12; --bit) {
-                    const uint32_t cand = t | (1u << bit);
-                    uint32_t cnt = 0;
+                if ((uint32_t)a.k <= nb4) {
+                    uint32_t m[kRefStage / 128];
 #pragma unroll
-                    for (int i = 0; i < kRefStage / 32; ++i) cnt += (v[i] >= cand) ? 1u : 0u;
-                    cnt = __reduce_add_sync(0xffffffffu, cnt);
-                    if (cnt >= (uint32_t)a.k) t = cand;
+                    for (int u0 = 0; u0 < kRefStage / 128; u0 += 5) {   // five independent loads in flight per lane
+                        uint4 tmp[5];
+#pragma unroll
+                        for (int u = 0; u < 5; ++u) {
+                            const uint32_t i = (uint32_t)(u0 + u) * 32u + lane;
+                            tmp[u] = (i < nb4) ? __ldcg(b4 + i) : make_uint4(0u, 0u, 0u, 0u);
+                        }
+#pragma unroll
+                        for (int u = 0; u < 5; ++u) m[u0 + u] = max(max(tmp[u].x, tmp[u].y), max(tmp[u].z, tmp[u].w));
+                    }
+                    if (a.dbg != nullptr && cta == 0 && lane == 0 && round == 0) a.dbg[12] = (unsigned long long)(clock64() - t_start);
+                    for (int bit = 31; bit >= 12; --bit) {
+                        const uint32_t cand = t | (1u << bit);
+                        uint32_t c0 = 0, c1 = 0, c2 = 0, c3 = 0;
+#pragma unroll
+                        for (int u = 0; u < kRefStage / 128; u += 4) {
+                            c0 += (m[u] >= cand) ? 1u : 0u;
+                            c1 += (m[u + 1] >= cand) ? 1u : 0u;
+                            c2 += (m[u + 2] >= cand) ? 1u : 0u;
+                            c3 += (m[u + 3] >= cand) ? 1u : 0u;
+                        }
+                        const uint32_t cnt = __reduce_add_sync(0xffffffffu, (c0 + c1) + (c2 + c3));
+                        if (cnt >= (uint32_t)a.k) t = cand;
+                    }
+                } else {
+                    uint4* ref4 = reinterpret_cast<uint4*>(ref_s);
+                    for (uint32_t i = lane; i < nb4; i += 32) ref4[i] = __ldcg(b4 + i);
+                    __syncwarp();
+                    for (int bit = 31; bit >= 12; --bit) {
+                        const uint32_t cand = t | (1u << bit);
+                        uint32_t cnt = 0;
+                        for (uint32_t i = lane; i < nb4; i += 32) {
+                            const uint4 v = ref4[i];
+                            cnt += (v.x >= cand ? 1u : 0u) + (v.y >= cand ? 1u : 0u) + (v.z >= cand ? 1u : 0u) + (v.w >= cand ? 1u : 0u);
+                        }
+                        cnt = __reduce_add_sync(0xffffffffu, cnt);
+                        if (cnt >= (uint32_t)a.k) t = cand;
+                    }
+                    __syncwarp();
                 }
+                if (a.dbg != nullptr && cta == 0 && lane == 0 && round == 0) a.dbg[13] = (unsigned long long)(clock64() - t_start);
                 if (lane == 0 && t != 0) atomicMax(a.ws.thr + a.q0 + j, t);
                 __syncwarp();
                 bool allset = true;
-                for (int jj = lane; jj < a.qn; jj += 32) {
-                    const uint32_t v = ld_relaxed_u32(a.ws.thr + a.q0 + jj);
+                uint32_t tv[kMmaCols / 32];
+#pragma unroll
+                for (int u = 0; u < kMmaCols / 32; ++u) {   // all bounds of the group, loads in flight together
+                    const int jj = u * 32 + lane;
+                    tv[u] = (jj < a.qn) ? ld_relaxed_u32(a.ws.thr + a.q0 + jj) : 1u;
+                }
+#pragma unroll
+                for (int u = 0; u < kMmaCols / 32; ++u) {
+                    const int jj = u * 32 + lane;
+                    if (jj >= a.qn) continue;
+                    const uint32_t v = tv[u];
                     thr_s[jj] = max(v, 1u);
                     allset = allset && (v != 0u);
                     // pre-filter bound: bound / qinv for cosine, the bound itself for dot, lowered by a few ulps
@@ -476,7 +555,14 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     filt_s[jj].z = c;
                 }
                 allset = __all_sync(0xffffffffu, allset);
-                if (allset && lane == 0) *thr_ready_s = 1u;
+                if (a.dbg != nullptr && cta == 0 && lane == 0 && round == 0) a.dbg[14] = (unsigned long long)(clock64() - t_start);
+                if (allset && lane == 0) {
+                    if (a.dbg != nullptr && cta == 0 && !*thr_ready_s) {
+                        a.dbg[9] = (unsigned long long)(clock64() - t_start);   // first complete set of bounds
+                        a.dbg[10] = round;
+                    }
+                    *thr_ready_s = 1u;
+                }
                 if (round > (uint32_t)(4 * a.qn)) __nanosleep(1000);   // steady state: refresh at a relaxed pace
             }
         }
@@ -525,7 +611,7 @@ struct MmaState {
     size_t d_b_bytes = 0;
     uint32_t* d_ready = nullptr;
     unsigned long long* d_dbg = nullptr;
-    bool attr_set[6] = {false, false, false, false, false, false};
+    bool attr_set[12] = {};
 };
 
 static int mma_group_queries(const CandView& cv) { return cv.layout == MANTA_B200_LAYOUT_Q8_ROW_F32 ? kMmaCols / 2 : kMmaCols; }
@@ -568,16 +654,24 @@ static cudaError_t make_map(MmaState* st, CUtensorMap* map, const void* base, ui
     return cudaSuccess;
 }
 
+template <bool I8, int METRIC, int SUBS>
+static cudaError_t launch_scan_subs(MmaState* st, int slot, int grid, size_t smem, cudaStream_t stream, const CUtensorMap& map_a,
+                                    const CUtensorMap& map_b, const KernelArgs& ka, const char** why) {
+    const int idx = slot * 2 + (SUBS == 4 ? 1 : 0);
+    if (!st->attr_set[idx]) {
+        cudaError_t e = cudaFuncSetAttribute(mma_scan_kernel<I8, METRIC, SUBS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024);
+        if (e != cudaSuccess) { *why = "cudaFuncSetAttribute"; return e; }
+        st->attr_set[idx] = true;
+    }
+    mma_scan_kernel<I8, METRIC, SUBS><<<grid, mma_threads(SUBS), smem, stream>>>(map_a, map_b, ka);
+    return cudaSuccess;
+}
+
 template <bool I8, int METRIC>
 static cudaError_t launch_scan_one(MmaState* st, int slot, int grid, size_t smem, cudaStream_t stream, const CUtensorMap& map_a,
                                    const CUtensorMap& map_b, const KernelArgs& ka, const char** why) {
-    if (!st->attr_set[slot]) {
-        cudaError_t e = cudaFuncSetAttribute(mma_scan_kernel<I8, METRIC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024);
-        if (e != cudaSuccess) { *why = "cudaFuncSetAttribute"; return e; }
-        st->attr_set[slot] = true;
-    }
-    mma_scan_kernel<I8, METRIC><<<grid, kMmaThreads, smem, stream>>>(map_a, map_b, ka);
-    return cudaSuccess;
+    if (ka.epi_subs == 4) return launch_scan_subs<I8, METRIC, 4>(st, slot, grid, smem, stream, map_a, map_b, ka, why);
+    return launch_scan_subs<I8, METRIC, 2>(st, slot, grid, smem, stream, map_a, map_b, ka, why);
 }
 
 // One instantiation per (layout, metric): the epilogue of each is straight-line code for its own metric.
@@ -668,7 +762,7 @@ cudaError_t launch_mma_topk(cudaStream_t stream, int sm_count, MmaState** state,
 
         const size_t a_stage = (size_t)kTileRows * kChunkBytes, b_stage = (size_t)ncols * kChunkBytes;
         const size_t fixed = 1024 /*alignment slack*/ + 256 /*barriers*/ + sizeof(QueryHeader) * kMmaCols + 4 * kMmaCols +
-                             16 * kMmaCols + 16 * kMmaCols * kBucketSlots + 16 * kMmaCols;
+                             16 * kMmaCols + 16 * kMmaCols * kBucketSlots + 16 * kMmaCols + 4 * kRefStage;
         const size_t budget = 220 * 1024 - fixed;
         // Operand B stays resident when it leaves room for at least four candidate stages: the ring then carries
         // only candidate bytes instead of re-reading the queries from L2 for every tile.
@@ -691,6 +785,9 @@ cudaError_t launch_mma_topk(cudaStream_t stream, int sm_count, MmaState** state,
         ka.kchunks = kchunks;
         ka.stages = stages;
         ka.b_resident = b_resident;
+        // Four epilogue warps per quadrant pay off when a tile carries many 16-query chunks and few K chunks.
+        static const char* subs_env = getenv("MANTA_B200_MMA_SUBS");  // debugging switch
+        ka.epi_subs = subs_env ? (atoi(subs_env) == 4 ? 4 : 2) : ((qn >= 96 && kchunks <= 4) ? 4 : 2);
         ka.metric = a.metric;
         ka.order = a.order;
         ka.k = a.k;
@@ -701,8 +798,8 @@ cudaError_t launch_mma_topk(cudaStream_t stream, int sm_count, MmaState** state,
         ka.dbg = nullptr;
         static const bool timing = getenv("MANTA_B200_MMA_TIMING") != nullptr;  // debugging switch
         if (timing) {
-            if (!st->d_dbg) cudaMalloc(&st->d_dbg, 64);
-            cudaMemsetAsync(st->d_dbg, 0, 64, stream);
+            if (!st->d_dbg) cudaMalloc(&st->d_dbg, 128);
+            cudaMemsetAsync(st->d_dbg, 0, 128, stream);
             ka.dbg = st->d_dbg;
         }
         e = launch_scan_variant(st, i8, a.metric, grid, smem, stream, map_a, map_b, ka, why);
@@ -712,9 +809,11 @@ cudaError_t launch_mma_topk(cudaStream_t stream, int sm_count, MmaState** state,
         e = cudaGetLastError();
         if (e != cudaSuccess) { *why = "tensor-core scan launch"; return e; }
         if (timing) {
-            unsigned long long h[8];
+            unsigned long long h[16];
             cudaStreamSynchronize(stream);
-            cudaMemcpy(h, st->d_dbg, 64, cudaMemcpyDeviceToHost);
+            cudaMemcpy(h, st->d_dbg, 128, cudaMemcpyDeviceToHost);
+            fprintf(stderr, "[mma timing, CTA 0, cycles since kernel start] first accumulator %llu, all CTAs published %llu, first bounds %llu (refresher round %llu); round 0: staged %llu, counted %llu, bounds re-read %llu\n",
+                    h[11], h[8], h[9], h[10], h[12], h[13], h[14]);
             fprintf(stderr, "[mma timing, CTA 0 warp 4, cycles] thr_wait %llu tfull_wait %llu tmem_ld %llu math %llu slow %llu house %llu | slow chunks %llu iters %llu\n",
                     h[0], h[1], h[2], h[3], h[4], h[5], h[6], h[7]);
         }
