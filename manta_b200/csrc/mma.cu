@@ -194,8 +194,8 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     uint32_t* thr_s = (uint32_t*)(hdr_s + kMmaCols);
     uint32_t* bmax_s = thr_s + kMmaCols;                 // [qn][4]: maxima of the current tile per epilogue warp
     uint32_t* pub_s = bmax_s + kMmaCols * 4;             // [qn][4][kBucketSlots]: last published values
-    float4* filt_s = (float4*)(pub_s + kMmaCols * 4 * kBucketSlots);  // [qn]: s_hi, s_lo, cheap pre-filter bound
-    uint32_t* ref_s = (uint32_t*)(filt_s + kMmaCols);                 // [kRefStage]: the refresher's copy of one query's buckets (16-byte aligned)
+    float* zq_s = (float*)(pub_s + kMmaCols * 4 * kBucketSlots);      // [kMmaCols]: pre-filter bound per query (+inf past qn)
+    uint32_t* ref_s = (uint32_t*)(zq_s + 4 * kMmaCols);                 // [kRefStage]: the refresher's copy of one query's buckets (16-byte aligned)
 
     const int64_t nrows = a.row_end - a.row_begin;
     const int n_tiles = (int)((nrows + kTileRows - 1) / kTileRows);
@@ -222,13 +222,14 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     }
     for (int j = threadIdx.x; j < a.qn; j += blockDim.x) {
         hdr_s[j] = a.headers[a.q0 + j];
-        filt_s[j] = make_float4(hdr_s[j].s_hi, hdr_s[j].s_lo, -INFINITY, 0.0f);
+        zq_s[j] = -INFINITY;   // no bound yet: every chunk takes the exact path
         thr_s[j] = 1;
         for (int w = 0; w < 4; ++w) {
             bmax_s[j * 4 + w] = 0;
             for (int s = 0; s < kBucketSlots; ++s) pub_s[(j * 4 + w) * kBucketSlots + s] = 0;
         }
     }
+    for (int j = a.qn + threadIdx.x; j < kMmaCols; j += blockDim.x) zq_s[j] = INFINITY;   // padding columns never pass
     if (warp == 1) tmem_alloc(tmem_slot, 512);
     tc_fence_before();
     __syncthreads();
@@ -340,6 +341,8 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 // row factor of the pre-filter; NaN for rows past the end makes every comparison false
                 float rowc = __int_as_float(0x7fc00000);
                 if (rv) rowc = (METRIC == MANTA_B200_METRIC_COSINE) ? rinv : (I8 ? sd : 1.0f);
+                // |T_f32 - T| and the 254 * s_lo != s_hi mismatch are below 4e-7 * 254 * |I_hi|, |I_hi| <= 127^2 * cols
+                const float srow = I8 ? rowc * (4e-7f * 254.0f * 16129.0f * (float)a.cv.cols) : 0.0f;
                 // One finished score of this lane's row for query j: vote against the bound, keep the bucket maximum,
                 // append the passing rows with one reservation per warp.
                 auto offer = [&](int j, float g, uint32_t o) {
@@ -379,19 +382,20 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         tmem_ld_wait();
                     }
                     if (cheap) {
-                        // Pre-filter without finishing the scores: score >= bound  <=>  t * rowc >= bound / qinv, the
-                        // right-hand side (slackened by a few ulps) kept per query by the refresher.  Almost every
-                        // chunk ends here.
+                        // Pre-filter without finishing the scores.  With s_hi = 254 * s_lo the unscaled dot product is
+                        // s_lo * T, T = 254 * I_hi + I_lo, so score >= bound  <=>  T * rowc >= bound / (qinv * s_lo) =: z
+                        // (kept per query by the refresher).  T is formed in f32; srow covers its rounding and the
+                        // rounding of s_lo itself, z is lowered by a few ulps, so the test can only pass too often.
+                        // Five arithmetic instructions per score; almost every chunk ends here.
                         uint32_t hit = 0;
 #pragma unroll
                         for (int jj = 0; jj < 16; ++jj) {
-                            const float4 f = filt_s[min(c0 + jj, a.qn - 1)];
                             float t;
                             if constexpr (I8)
-                                t = __fmaf_rn((float)(int)vl[jj], f.y, __fmul_rn((float)(int)vh[jj], f.x));
+                                t = __fmaf_rn((float)(int)vh[jj], 254.0f, (float)(int)vl[jj]);
                             else
                                 t = __uint_as_float(vh[jj]);
-                            hit |= (t * rowc >= f.z) ? (1u << jj) : 0u;
+                            hit |= (__fmaf_rn(t, rowc, srow) >= zq_s[c0 + jj]) ? (1u << jj) : 0u;
                         }
                         hit = __reduce_or_sync(0xffffffffu, hit);
                         if (hit == 0u) continue;
@@ -544,15 +548,21 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     const uint32_t v = tv[u];
                     thr_s[jj] = max(v, 1u);
                     allset = allset && (v != 0u);
-                    // pre-filter bound: bound / qinv for cosine, the bound itself for dot, lowered by a few ulps
+                    // pre-filter bound: bound / qinv for cosine, the bound itself for dot, lowered by a few ulps; for
+                    // q8 divided by s_lo (the filter compares the integer combination T, see the epilogue)
                     float c = -INFINITY;
                     if (v > 1u) {
                         const float tf = float_from_ord(v);
                         const float qi = hdr_s[jj].qinv;
                         c = (METRIC == MANTA_B200_METRIC_COSINE) ? ((qi > 0.0f) ? tf / qi : -INFINITY) : tf;
                         c = c - fabsf(c) * 2e-6f - 1e-30f;
+                        if constexpr (I8) {
+                            const float sl = hdr_s[jj].s_lo;
+                            c = (sl > 0.0f) ? c / sl : -INFINITY;
+                            c = c - fabsf(c) * 1e-6f;
+                        }
                     }
-                    filt_s[jj].z = c;
+                    zq_s[jj] = c;
                 }
                 allset = __all_sync(0xffffffffu, allset);
                 if (a.dbg != nullptr && cta == 0 && lane == 0 && round == 0) a.dbg[14] = (unsigned long long)(clock64() - t_start);
