@@ -32,7 +32,8 @@ constexpr int mma_threads(int subs) { return 32 * (2 + 4 * subs + 1); }
 constexpr int kMmaCols = 256;         // N of one MMA
 constexpr int kBucketSlots = 4;       // bucket slots per epilogue warp (tiles rotate through them)
 constexpr uint32_t kSpinLimit = 1u << 22;
-constexpr int kRefStage = 2560;       // bucket maxima per query the refresher stages in shared memory
+constexpr int kRefStage = 2560;       // bucket maxima per query the refresher looks at (20 merged values per lane)
+constexpr size_t kSmemLimit = 232448; // dynamic shared memory one CTA may ask for (227 KB)
 
 // ---- PTX wrappers -------------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -195,7 +196,6 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     uint32_t* bmax_s = thr_s + kMmaCols;                 // [qn][4]: maxima of the current tile per epilogue warp
     uint32_t* pub_s = bmax_s + kMmaCols * 4;             // [qn][4][kBucketSlots]: last published values
     float* zq_s = (float*)(pub_s + kMmaCols * 4 * kBucketSlots);      // [kMmaCols]: pre-filter bound per query (+inf past qn)
-    uint32_t* ref_s = (uint32_t*)(zq_s + 4 * kMmaCols);                 // [kRefStage]: the refresher's copy of one query's buckets (16-byte aligned)
 
     const int64_t nrows = a.row_end - a.row_begin;
     const int n_tiles = (int)((nrows + kTileRows - 1) / kTileRows);
@@ -484,7 +484,7 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 // k-th largest bucket maximum of the query, top 20 bits.  The four slots of one (CTA, quadrant) are
                 // adjacent, so one 16-byte load brings them; while 4k <= buckets their maximum is taken as ONE bucket
                 // (a union of disjoint row sets is still disjoint from the others), which leaves 20 values per lane in
-                // registers for the twenty counting passes.  Larger k stages all buckets in shared memory.
+                // registers for the twenty counting passes.
                 const uint32_t nb4 = nb >> 2;   // the bucket count is a multiple of four (sixteen per SM)
                 const uint4* b4 = reinterpret_cast<const uint4*>(b);
                 uint32_t t = 0;
@@ -516,20 +516,18 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         if (cnt >= (uint32_t)a.k) t = cand;
                     }
                 } else {
-                    uint4* ref4 = reinterpret_cast<uint4*>(ref_s);
-                    for (uint32_t i = lane; i < nb4; i += 32) ref4[i] = __ldcg(b4 + i);
-                    __syncwarp();
+                    // k larger than a quarter of the buckets (rare: several hundred results per query): every bucket
+                    // counts by itself, re-read from L2 in each pass
                     for (int bit = 31; bit >= 12; --bit) {
                         const uint32_t cand = t | (1u << bit);
                         uint32_t cnt = 0;
                         for (uint32_t i = lane; i < nb4; i += 32) {
-                            const uint4 v = ref4[i];
+                            const uint4 v = __ldcg(b4 + i);
                             cnt += (v.x >= cand ? 1u : 0u) + (v.y >= cand ? 1u : 0u) + (v.z >= cand ? 1u : 0u) + (v.w >= cand ? 1u : 0u);
                         }
                         cnt = __reduce_add_sync(0xffffffffu, cnt);
                         if (cnt >= (uint32_t)a.k) t = cand;
                     }
-                    __syncwarp();
                 }
                 if (a.dbg != nullptr && cta == 0 && lane == 0 && round == 0) a.dbg[13] = (unsigned long long)(clock64() - t_start);
                 if (lane == 0 && t != 0) atomicMax(a.ws.thr + a.q0 + j, t);
@@ -669,7 +667,7 @@ static cudaError_t launch_scan_subs(MmaState* st, int slot, int grid, size_t sme
                                     const CUtensorMap& map_b, const KernelArgs& ka, const char** why) {
     const int idx = slot * 2 + (SUBS == 4 ? 1 : 0);
     if (!st->attr_set[idx]) {
-        cudaError_t e = cudaFuncSetAttribute(mma_scan_kernel<I8, METRIC, SUBS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(mma_scan_kernel<I8, METRIC, SUBS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit);
         if (e != cudaSuccess) { *why = "cudaFuncSetAttribute"; return e; }
         st->attr_set[idx] = true;
     }
@@ -772,8 +770,8 @@ cudaError_t launch_mma_topk(cudaStream_t stream, int sm_count, MmaState** state,
 
         const size_t a_stage = (size_t)kTileRows * kChunkBytes, b_stage = (size_t)ncols * kChunkBytes;
         const size_t fixed = 1024 /*alignment slack*/ + 256 /*barriers*/ + sizeof(QueryHeader) * kMmaCols + 4 * kMmaCols +
-                             16 * kMmaCols + 16 * kMmaCols * kBucketSlots + 16 * kMmaCols + 4 * kRefStage;
-        const size_t budget = 220 * 1024 - fixed;
+                             16 * kMmaCols + 16 * kMmaCols * kBucketSlots + 4 * kMmaCols;
+        const size_t budget = kSmemLimit - fixed;
         // Operand B stays resident when it leaves room for at least four candidate stages: the ring then carries
         // only candidate bytes instead of re-reading the queries from L2 for every tile.
         static const bool no_resident = getenv("MANTA_B200_MMA_NO_RESIDENT_B") != nullptr;  // debugging switch
