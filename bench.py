@@ -374,20 +374,44 @@ def run_ours(args, wl: Workload):
     stats_device = rt.stats()
 
     # ---- end to end through the host-buffer ABI call ------------------------------------------------
-    def step_host(i):
+    hb = {}  # pinned host / staging buffers of the sharded end-to-end step (released before the streams they used)
+    if world > 1:
         if wl.embed:
-            ids, sc = rt.embed_score_topk(emb, cands, h_tokens[i % nsets], h_mask[i % nsets], wl.metric, k, smallest=wl.smallest)
+            hb["tokens"] = torch.from_numpy(h_tokens)
+            hb["mask"] = torch.from_numpy(h_mask)
+            hb["s_tokens"] = torch.empty((nq, wl.embed[2]), dtype=torch.int32, device="cuda")
+            hb["s_mask"] = torch.empty((nq, wl.embed[2]), dtype=torch.int32, device="cuda")
+            hb["s_q"] = torch.empty((nq, wl.cols), dtype=torch.float16, device="cuda")
         else:
-            ids, sc = rt.score_topk(cands, wl.metric, h_queries[i % nsets], k, smallest=wl.smallest)
-        if world > 1:
-            with torch.cuda.stream(stream):
-                d_ids.copy_(torch.from_numpy(ids).view(nq, k), non_blocking=False)
-                d_scores.copy_(torch.from_numpy(sc).view(nq, k), non_blocking=False)
-                sharding.gather_pairs(d_pair, g_pair, dist)
-            rt.topk_merge_device(g_ids, g_scores, world, nq, k, m_ids, m_scores, smallest=wl.smallest, sync=True,
-                                 list_stride=g_stride)
-            return m_ids.cpu().numpy(), m_scores.cpu().numpy()
-        return ids, sc
+            hb["queries"] = torch.from_numpy(h_queries.view(np.int16)).pin_memory()
+            hb["s_q"] = torch.empty((nq, wl.cols), dtype=torch.int16, device="cuda")
+        hb["ids"] = torch.empty((nq, k), dtype=torch.int32).pin_memory()
+        hb["scores"] = torch.empty((nq, k), dtype=torch.float32).pin_memory()
+
+    def step_host(i):
+        if world == 1:
+            if wl.embed:
+                return rt.embed_score_topk(emb, cands, h_tokens[i % nsets], h_mask[i % nsets], wl.metric, k, smallest=wl.smallest)
+            return rt.score_topk(cands, wl.metric, h_queries[i % nsets], k, smallest=wl.smallest)
+        # sharded: inputs from pinned host memory, one stream-ordered chain (upload, shard pass, all-gather, merge,
+        # download), one synchronisation at the end
+        with torch.cuda.stream(stream):
+            if wl.embed:
+                hb["s_tokens"].copy_(hb["tokens"][i % nsets], non_blocking=True)
+                hb["s_mask"].copy_(hb["mask"][i % nsets], non_blocking=True)
+            else:
+                hb["s_q"].copy_(hb["queries"][i % nsets], non_blocking=True)
+        if wl.embed:
+            rt.embed_device(emb, hb["s_tokens"], hb["s_mask"], nq, wl.embed[2], hb["s_q"], sync=False)
+        rt.score_topk_device(cands, wl.metric, hb["s_q"], nq, k, d_ids, d_scores, smallest=wl.smallest, sync=False)
+        with torch.cuda.stream(stream):
+            sharding.gather_pairs(d_pair, g_pair, dist)
+        rt.topk_merge_device(g_ids, g_scores, world, nq, k, m_ids, m_scores, smallest=wl.smallest, sync=False, list_stride=g_stride)
+        with torch.cuda.stream(stream):
+            hb["ids"].copy_(m_ids, non_blocking=True)
+            hb["scores"].copy_(m_scores, non_blocking=True)
+        rt.synchronize()  # also raises if the pass overflowed its pool
+        return hb["ids"].numpy(), hb["scores"].numpy()
 
     for i in range(args.warmup):
         step_host(i)
@@ -433,7 +457,7 @@ def run_ours(args, wl: Workload):
         algo_bytes = shard_rows * wl.row_bytes()
         achieved = algo_bytes / (scan_ms_per_pass * 1e-3) / 1e9
         # DRAM traffic per launch from the committed ncu capture of the same kernel on a 2 M-row case
-        # (profiles/gemv_q8_cosine_2Mx768.md: dram__bytes_read+write = 1.5477e9 B for 2e6 rows), scaled by rows;
+        # (the summary under profiles/ for q8 cosine 2M x 768: dram__bytes_read+write = 1.5477e9 B for 2e6 rows), scaled by rows;
         # traffic grows in proportion because every row is read exactly once.
         traffic = None
         if wl.layout == "q8" and wl.metric == "cosine" and wl.cols == 768 and nq <= 4:
@@ -458,12 +482,21 @@ def run_ours(args, wl: Workload):
                          "frac_of_nominal_8TBs": achieved / 8000.0},
             "e2e": {"value": args.steps * nq / e2e_s, "unit": "queries/s", "h2d_bytes_per_step": (2 * nq * wl.embed[2] * 4) if wl.embed else nq * wl.cols * 2,
                     "d2h_bytes_per_step": nq * k * 8, "ms_per_step": e2e_s / args.steps * 1e3,
-                    "note": "host-buffer C-ABI call per step; candidates stay bound (resident) as plan parameters"},
+                    "note": "host-buffer C-ABI call per step; candidates stay bound (resident) as plan parameters"
+                            if world == 1 else "inputs from pinned host memory, results to pinned host memory, one synchronisation per "
+                            "step (upload, shard pass, NCCL all-gather, merge, download on one stream)"},
             "gpu_launches": int(launches), "clocks": clocks, "cpu_baseline": cpu, "parity_check": parity,
             "result_checksum": int(np.asarray(final_ids, dtype=np.int64).sum()),
             "stats": rt.stats(),
         }
         print(json.dumps(line), flush=True)
+    torch.cuda.synchronize()
+    hb.clear()
+    if wl.embed:
+        h_tokens = h_mask = None  # pinned: released while the streams that read them still exist
+    import gc
+
+    gc.collect()
     cands.unbind()
     if emb is not None:
         rt.unbind_embedder(emb)

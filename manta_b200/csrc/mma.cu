@@ -820,7 +820,7 @@ cudaError_t launch_mma_topk(cudaStream_t stream, int sm_count, MmaState** state,
             unsigned long long h[16];
             cudaStreamSynchronize(stream);
             cudaMemcpy(h, st->d_dbg, 128, cudaMemcpyDeviceToHost);
-            fprintf(stderr, "[mma timing, CTA 0, cycles since kernel start] first accumulator %llu, all CTAs published %llu, first bounds %llu (refresher round %llu); round 0: staged %llu, counted %llu, bounds re-read %llu\n",
+            fprintf(stderr, "[mma timing, CTA 0, cycles since kernel start] first accumulator %llu, all CTAs published %llu, first bounds %llu (refresher pass %llu); pass 0: staged %llu, counted %llu, bounds re-read %llu\n",
                     h[11], h[8], h[9], h[10], h[12], h[13], h[14]);
             fprintf(stderr, "[mma timing, CTA 0 warp 4, cycles] thr_wait %llu tfull_wait %llu tmem_ld %llu math %llu slow %llu house %llu | slow chunks %llu iters %llu\n",
                     h[0], h[1], h[2], h[3], h[4], h[5], h[6], h[7]);
