@@ -289,6 +289,16 @@ def run_ours(args, wl: Workload):
                     self.m_ids = torch.empty((nq, k), dtype=torch.int32, device="cuda")
                     self.m_scores = torch.empty((nq, k), dtype=torch.float32, device="cuda")
             self.stream.synchronize()
+            self.px = sharding.PeerExchange(self.rt, dist, nq, k) if (world > 1 and args.exchange == "peer") else None
+
+        def merge(self, sync):
+            if self.px is not None:
+                self.px.merge(self.d_ids, self.d_scores, nq, k, self.m_ids, self.m_scores, smallest=wl.smallest, sync=sync)
+                return
+            with torch.cuda.stream(self.stream):
+                sharding.gather_pairs(self.d_pair, self.g_pair, dist)
+            self.rt.topk_merge_device(self.g_ids, self.g_scores, world, nq, k, self.m_ids, self.m_scores, smallest=wl.smallest,
+                                      sync=sync, list_stride=self.g_stride)
 
     lanes = [Lane() for _ in range(n_lanes)]
     rt, stream = lanes[0].rt, lanes[0].stream
@@ -325,10 +335,7 @@ def run_ours(args, wl: Workload):
             dq = d_queries[i % nsets]
         ln.rt.score_topk_device(cands, wl.metric, dq, nq, k, ln.d_ids, ln.d_scores, smallest=wl.smallest, sync=False)
         if world > 1:
-            with torch.cuda.stream(ln.stream):
-                sharding.gather_pairs(ln.d_pair, ln.g_pair, dist)
-            ln.rt.topk_merge_device(ln.g_ids, ln.g_scores, world, nq, k, ln.m_ids, ln.m_scores, smallest=wl.smallest, sync=False,
-                                    list_stride=ln.g_stride)
+            ln.merge(False)
 
     def barrier():
         if world > 1:
@@ -404,9 +411,7 @@ def run_ours(args, wl: Workload):
         if wl.embed:
             rt.embed_device(emb, hb["s_tokens"], hb["s_mask"], nq, wl.embed[2], hb["s_q"], sync=False)
         rt.score_topk_device(cands, wl.metric, hb["s_q"], nq, k, d_ids, d_scores, smallest=wl.smallest, sync=False)
-        with torch.cuda.stream(stream):
-            sharding.gather_pairs(d_pair, g_pair, dist)
-        rt.topk_merge_device(g_ids, g_scores, world, nq, k, m_ids, m_scores, smallest=wl.smallest, sync=False, list_stride=g_stride)
+        lanes[0].merge(False)
         with torch.cuda.stream(stream):
             hb["ids"].copy_(m_ids, non_blocking=True)
             hb["scores"].copy_(m_scores, non_blocking=True)
@@ -472,6 +477,7 @@ def run_ours(args, wl: Workload):
             "data": "synthetic",
             "config": {"workload": wl.describe(), "rows": wl.rows, "cols": wl.cols, "k": k, "queries_per_step": nq,
                        "layout": wl.layout, "shards": world, "note": wl.note, "lanes": n_lanes,
+                       "exchange": (args.exchange if world > 1 else None),
                        "l2": f"inputs larger than L2: {algo_bytes / 1e9:.3f} GB scanned per pass and GPU" if algo_bytes > 2.5e8
                              else "inputs smaller than L2 (latency-bound configuration, not a roofline point)"},
             "candidates_dim_per_s": value * wl.rows * wl.cols,
@@ -491,6 +497,9 @@ def run_ours(args, wl: Workload):
         }
         print(json.dumps(line), flush=True)
     torch.cuda.synchronize()
+    for ln in lanes:
+        if ln.px is not None:
+            ln.px.close()
     hb.clear()
     if wl.embed:
         h_tokens = h_mask = None  # pinned: released while the streams that read them still exist
@@ -517,6 +526,9 @@ def main():
     ap.add_argument("--rows", type=int, default=0, help="override the workload's row count (smaller cases for profiling)")
     ap.add_argument("--nq", type=int, default=0, help="override the workload's query batch")
     ap.add_argument("--k", type=int, default=0, help="override the workload's k")
+    ap.add_argument("--exchange", default="nccl", choices=["nccl", "peer"],
+                    help="sharded runs: how the per-shard lists meet (NCCL all-gather + merge, or peer stores over NVLink fused "
+                         "with the merge)")
     ap.add_argument("--lanes", type=int, default=0,
                     help="runtimes alternating steps (0: one on a single GPU, two when sharded so that merge and scan overlap)")
     args = ap.parse_args()

@@ -180,6 +180,24 @@ int manta_b200_topk_merge_device(MantaB200Runtime* rt, int order, const int32_t*
 int manta_b200_gather_rows(MantaB200Runtime* rt, const MantaB200Candidates* set, const int32_t* ids, int64_t n,
                            float* out, char** err);
 
+/* ---- exchange of per-shard lists over peer memory (no counterpart in the reference, which runs on one device) ------
+ * One process per GPU.  Every rank creates an exchange (an inbox on its own GPU), the 64-byte handles are passed to all
+ * ranks by the host (any transport), and manta_b200_exchange_connect maps the peers' inboxes.
+ * manta_b200_topk_exchange_merge_device then replaces "all-gather the [nq,k] lists + manta_b200_topk_merge_device":
+ * on the runtime's stream it stores this rank's list into every rank's inbox with peer stores over NVLink, waits
+ * (bounded, about two seconds) for the lists of all ranks and selects the global top k.  Ranks must issue the same
+ * sequence of merges.  A list that does not arrive fails the call (sync != 0) or the next
+ * manta_b200_runtime_synchronize (sync == 0); the context stays usable. */
+typedef struct MantaB200Exchange MantaB200Exchange;
+int manta_b200_exchange_create(MantaB200Runtime* rt, int world, int rank, int nq_max, int k_max, MantaB200Exchange** out,
+                               unsigned char* handle_out /* 64 bytes */, char** err);
+int manta_b200_exchange_connect(MantaB200Runtime* rt, MantaB200Exchange* ex, const unsigned char* handles /* world x 64 */,
+                                char** err);
+int manta_b200_exchange_destroy(MantaB200Runtime* rt, MantaB200Exchange* ex, char** err);
+int manta_b200_topk_exchange_merge_device(MantaB200Runtime* rt, MantaB200Exchange* ex, int order, const int32_t* d_ids,
+                                          const float* d_scores, int nq, int k, int32_t* d_out_ids, float* d_out_scores,
+                                          int sync, char** err);
+
 /* ---- packed candidate files ------------------------------------------------------------------------------
  * The stored form of a bound set (codes + scales of its layout) on disk.  The reference exports q4 / q8 tensors
  * widened to float32 inside its MLL container (runtime/mll_export.go:833-866, read back by decodeTensorEntry,

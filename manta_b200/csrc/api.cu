@@ -93,6 +93,7 @@ struct MantaB200Runtime {
     cudaEvent_t prof_ev[2 * kMaxProf];
     int prof_created = 0;
     int prof_used = 0;
+    bool async_exchange_pending = false;  // a sync == 0 exchange merge copied its flags to h_flags[4..7]
     bool async_embed_pending = false;  // a sync == 0 embed pass copied its bad-token word to h_flags[10..11]
     bool async_flags_pending = false;  // a sync == 0 pass copied its flags to h_flags; checked at synchronize
 };
@@ -239,6 +240,12 @@ int manta_b200_runtime_synchronize(MantaB200Runtime* rt, char** err) {
     std::lock_guard<std::mutex> lk(rt->mu);
     CU_TRY(cudaSetDevice(rt->device));
     CU_TRY(cudaStreamSynchronize(rt->stream));
+    if (rt->async_exchange_pending) {
+        rt->async_exchange_pending = false;
+        if (rt->h_flags[4 + kFlagTimeout])
+            return fail(err, "runtime_synchronize: a peer's top-k list did not arrive within the wait limit of the exchange");
+        if (rt->h_flags[4 + kFlagInternal]) return fail(err, "runtime_synchronize: the exchange merge found fewer than k candidates");
+    }
     if (rt->async_embed_pending) {
         rt->async_embed_pending = false;
         if (rt->h_flags[10]) return fail(err, "gather index %d out of range", (int32_t)rt->h_flags[11]);
@@ -547,6 +554,34 @@ static int ensure_select_ws(MantaB200Runtime* rt, int nq, uint32_t cap, uint32_t
     ws->nb = nb;
     return 0;
 }
+
+extern "C++" {
+namespace mb200 {
+// Selection workspace for the exchange merge (exchange.cu); takes the runtime's lock itself.
+int exchange_select_ws(MantaB200Runtime* rt, int nq, uint32_t cap, SelectWs* ws, char** err) {
+    std::lock_guard<std::mutex> lk(rt->mu);
+    CU_TRY(cudaSetDevice(rt->device));
+    rt->stats.kernel_launches += 4;
+    return ensure_select_ws(rt, nq, cap, 1, ws, err);
+}
+// Reads the merge's flags into host words 4..7 (the fused pass keeps 0..3); the caller holds the lock.
+void exchange_note_async_flags(MantaB200Runtime* rt, const SelectWs& ws, int sync, char** err, int* rc) {
+    *rc = 0;
+    cudaError_t e = cudaMemcpyAsync(rt->h_flags + 4, ws.flags, kNumFlags * 4, cudaMemcpyDeviceToHost, rt->stream);
+    if (e == cudaSuccess && sync) e = cudaStreamSynchronize(rt->stream);
+    if (e != cudaSuccess) {
+        *rc = fail_cuda(err, "topk_exchange_merge", e);
+        return;
+    }
+    if (!sync) {
+        rt->async_exchange_pending = true;
+        return;
+    }
+    if (rt->h_flags[4 + kFlagTimeout]) *rc = fail(err, "topk_exchange_merge: a peer's top-k list did not arrive within the wait limit");
+    else if (rt->h_flags[4 + kFlagInternal]) *rc = fail(err, "topk_exchange_merge: selection found fewer than k candidates");
+}
+}  // namespace mb200
+}  // extern "C++"
 
 static int check_score_args(const MantaB200Runtime* rt, const MantaB200Candidates* set, int metric, int nq, char** err) {
     if (!rt || !set) return fail(err, "score: NULL runtime or candidate set");

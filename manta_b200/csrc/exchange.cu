@@ -1,0 +1,246 @@
+// Exchange of per-shard top-k lists over peer memory (NVLink / NVSwitch), fused with the merge.
+// Every rank owns an inbox on its GPU: two parities x world slots of (ids, scores) plus one epoch word per slot.  After
+// its fused score + top-k pass a rank stores its list into slot [parity][rank] of EVERY rank's inbox with plain peer
+// stores, fences, and writes the step's epoch into the slot's word; the merge kernel of a rank waits (bounded) until
+// all of its own slots carry the epoch, then feeds them to the selection.  No collective library call and no host
+// round trip sit between the shard pass and the merged result.  Two parities are enough: a rank can push step s+2
+// only after it merged step s+1, which needs every peer's push of s+1, which a peer issues after its merge of step s.
+// Every wait has an iteration limit; when it runs out the time-out flag is raised and the kernel returns.
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+
+#include "../../include/manta_b200.h"
+#include "common.cuh"
+#include "internal.h"
+#include "kernels.h"
+
+constexpr int kMaxWorld = 16;
+
+struct MantaB200Exchange {
+    int device = 0, world = 0, rank = 0, nq_max = 0, k_max = 0;
+    size_t slot_words = 0;      // int32 words per slot: 2 * nq_max * k_max
+    size_t inbox_bytes = 0;
+    unsigned char* inbox = nullptr;           // [2][world] slots, then [2][world] epoch words (64-byte spaced)
+    unsigned char* peer[kMaxWorld] = {};      // every rank's inbox as mapped into this process (peer[rank] == inbox)
+    bool opened[kMaxWorld] = {};
+    uint32_t epoch = 0;
+    bool connected = false;
+};
+
+namespace {
+
+int fail(char** err, const char* fmt, ...) {
+    if (err) {
+        char buf[512];
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(buf, sizeof buf, fmt, ap);
+        va_end(ap);
+        size_t n = strlen(buf) + 1;
+        char* out = (char*)malloc(n);
+        if (out) memcpy(out, buf, n);
+        *err = out;
+    }
+    return 1;
+}
+
+struct PeerTable {
+    unsigned char* inbox[kMaxWorld];
+};
+
+__device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__host__ __device__ inline size_t slot_offset(size_t slot_words, int world, int parity, int r) {
+    return ((size_t)parity * world + r) * slot_words * 4;
+}
+__host__ __device__ inline size_t flag_offset(size_t slot_words, int world, int parity, int r) {
+    return (size_t)2 * world * slot_words * 4 + ((size_t)parity * world + r) * 64;
+}
+
+// Block p stores this rank's list into peer p's inbox slot [parity][rank], then publishes the epoch.
+__global__ void exchange_push_kernel(PeerTable peers, const int32_t* __restrict__ ids, const float* __restrict__ scores, int n,
+                                     size_t slot_words, int world, int rank, int parity, uint32_t epoch) {
+    unsigned char* box = peers.inbox[blockIdx.x];
+    int32_t* dst = reinterpret_cast<int32_t*>(box + slot_offset(slot_words, world, parity, rank));
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        dst[i] = ids[i];
+        dst[n + i] = __float_as_int(scores[i]);
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) st_release_sys_u32(reinterpret_cast<uint32_t*>(box + flag_offset(slot_words, world, parity, rank)), epoch);
+}
+
+// One block per query: waits until every rank's slot of this parity carries the epoch, then writes the keys of all
+// lists into the query's selection pool (entries a shard could not fill, id < 0, rank below everything).
+__global__ void exchange_collect_kernel(const unsigned char* __restrict__ inbox, size_t slot_words, int world, int parity,
+                                        uint32_t epoch, int nq, int k, int order, mb200::SelectWs ws, uint32_t spin_limit) {
+    __shared__ int ok_s;
+    const int q = blockIdx.x;
+    if (threadIdx.x == 0) ok_s = 1;
+    __syncthreads();
+    if (threadIdx.x < world) {
+        const uint32_t* flag = reinterpret_cast<const uint32_t*>(inbox + flag_offset(slot_words, world, parity, threadIdx.x));
+        uint32_t spin = 0;
+        while (ld_acquire_sys_u32(flag) != epoch) {
+            if (++spin > spin_limit) {
+                ok_s = 0;
+                break;
+            }
+            __nanosleep(200);
+        }
+    }
+    __syncthreads();
+    const float sign = (order == MANTA_B200_ORDER_SMALLEST) ? -1.0f : 1.0f;
+    const int n = nq * k;
+    const int per = world * k;
+    if (ok_s) {
+        for (int i = threadIdx.x; i < per; i += blockDim.x) {
+            const int r = i / k, j = i % k;
+            const int32_t* slot = reinterpret_cast<const int32_t*>(inbox + slot_offset(slot_words, world, parity, r));
+            const int32_t id = __ldcv(slot + (size_t)q * k + j);
+            const float sc = __int_as_float(__ldcv(slot + n + (size_t)q * k + j));
+            ws.pool[(size_t)q * ws.cap + i] = (id < 0) ? 0ull : mb200::make_key(sc * sign + 0.0f, id);
+        }
+    }
+    if (threadIdx.x == 0) {
+        ws.count[q] = ok_s ? (uint32_t)per : 0u;
+        ws.thr[q] = 0;
+        if (!ok_s) ws.flags[mb200::kFlagTimeout] = 1u;
+    }
+}
+
+__global__ void exchange_reset_flags_kernel(mb200::SelectWs ws) {
+    if (threadIdx.x < mb200::kNumFlags) ws.flags[threadIdx.x] = 0;
+}
+
+}  // namespace
+
+namespace mb200 {
+int exchange_select_ws(MantaB200Runtime* rt, int nq, uint32_t cap, SelectWs* ws, char** err);  // api.cu
+void exchange_note_async_flags(MantaB200Runtime* rt, const SelectWs& ws, int sync, char** err, int* rc);  // api.cu
+}
+
+extern "C" {
+
+int manta_b200_exchange_create(MantaB200Runtime* rt, int world, int rank, int nq_max, int k_max, MantaB200Exchange** out,
+                               unsigned char* handle_out, char** err) {
+    if (!rt || !out || !handle_out) return fail(err, "exchange_create: NULL argument");
+    *out = nullptr;
+    if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world) return fail(err, "exchange_create: rank %d of %d out of range (max %d ranks)", rank, world, kMaxWorld);
+    if (nq_max <= 0 || k_max <= 0 || k_max > 1024) return fail(err, "exchange_create: bad list shape [%d,%d]", nq_max, k_max);
+    mb200::RuntimeInfo ri = mb200::runtime_info(rt);
+    std::lock_guard<std::mutex> lk(*ri.mu);
+    cudaError_t e = cudaSetDevice(ri.device);
+    if (e != cudaSuccess) return fail(err, "exchange_create: %s", cudaGetErrorString(e));
+    MantaB200Exchange* ex = new (std::nothrow) MantaB200Exchange();
+    if (!ex) return fail(err, "exchange_create: out of host memory");
+    ex->device = ri.device;
+    ex->world = world;
+    ex->rank = rank;
+    ex->nq_max = nq_max;
+    ex->k_max = k_max;
+    ex->slot_words = ((size_t)2 * nq_max * k_max + 63) / 64 * 64;
+    ex->inbox_bytes = (size_t)2 * world * ex->slot_words * 4 + (size_t)2 * world * 64;
+    e = cudaMalloc((void**)&ex->inbox, ex->inbox_bytes);
+    if (e == cudaSuccess) e = cudaMemset(ex->inbox, 0, ex->inbox_bytes);
+    cudaIpcMemHandle_t h;
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, ex->inbox);
+    if (e != cudaSuccess) {
+        if (ex->inbox) cudaFree(ex->inbox);
+        delete ex;
+        return fail(err, "exchange_create: %s", cudaGetErrorString(e));
+    }
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle is 64 bytes");
+    memcpy(handle_out, &h, 64);
+    ex->peer[rank] = ex->inbox;
+    *out = ex;
+    return 0;
+}
+
+int manta_b200_exchange_connect(MantaB200Runtime* rt, MantaB200Exchange* ex, const unsigned char* handles, char** err) {
+    if (!rt || !ex || !handles) return fail(err, "exchange_connect: NULL argument");
+    mb200::RuntimeInfo ri = mb200::runtime_info(rt);
+    std::lock_guard<std::mutex> lk(*ri.mu);
+    cudaError_t e = cudaSetDevice(ri.device);
+    if (e != cudaSuccess) return fail(err, "exchange_connect: %s", cudaGetErrorString(e));
+    for (int r = 0; r < ex->world; ++r) {
+        if (r == ex->rank || ex->opened[r]) continue;
+        cudaIpcMemHandle_t h;
+        memcpy(&h, handles + (size_t)r * 64, 64);
+        void* p = nullptr;
+        e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) return fail(err, "exchange_connect: cannot map rank %d's inbox: %s", r, cudaGetErrorString(e));
+        ex->peer[r] = (unsigned char*)p;
+        ex->opened[r] = true;
+    }
+    ex->connected = true;
+    return 0;
+}
+
+int manta_b200_exchange_destroy(MantaB200Runtime* rt, MantaB200Exchange* ex, char** err) {
+    if (!ex) return 0;
+    if (!rt) return fail(err, "exchange_destroy: NULL runtime");
+    mb200::RuntimeInfo ri = mb200::runtime_info(rt);
+    std::lock_guard<std::mutex> lk(*ri.mu);
+    cudaSetDevice(ri.device);
+    cudaStreamSynchronize(ri.stream);
+    for (int r = 0; r < ex->world; ++r)
+        if (ex->opened[r]) cudaIpcCloseMemHandle(ex->peer[r]);
+    if (ex->inbox) cudaFree(ex->inbox);
+    delete ex;
+    return 0;
+}
+
+int manta_b200_topk_exchange_merge_device(MantaB200Runtime* rt, MantaB200Exchange* ex, int order, const int32_t* d_ids,
+                                          const float* d_scores, int nq, int k, int32_t* d_out_ids, float* d_out_scores,
+                                          int sync, char** err) {
+    if (!rt || !ex || !d_ids || !d_scores || !d_out_ids || !d_out_scores) return fail(err, "topk_exchange_merge: NULL argument");
+    if (!ex->connected && ex->world > 1) return fail(err, "topk_exchange_merge: the exchange is not connected to its peers");
+    if (nq <= 0 || k <= 0 || nq > ex->nq_max || k > ex->k_max || (size_t)2 * nq * k > ex->slot_words)
+        return fail(err, "topk_exchange_merge: list shape [%d,%d] exceeds the exchange's [%d,%d]", nq, k, ex->nq_max, ex->k_max);
+    if (order != MANTA_B200_ORDER_LARGEST && order != MANTA_B200_ORDER_SMALLEST) return fail(err, "topk_exchange_merge: unknown order %d", order);
+    mb200::RuntimeInfo ri = mb200::runtime_info(rt);
+    if (ri.device != ex->device) return fail(err, "topk_exchange_merge: the exchange lives on device %d, the runtime on %d", ex->device, ri.device);
+    mb200::SelectWs ws;
+    if (mb200::exchange_select_ws(rt, nq, (uint32_t)(ex->world * k), &ws, err)) return 1;
+    std::lock_guard<std::mutex> lk(*ri.mu);
+    cudaError_t e = cudaSetDevice(ri.device);
+    if (e != cudaSuccess) return fail(err, "topk_exchange_merge: %s", cudaGetErrorString(e));
+    const uint32_t epoch = ++ex->epoch;
+    const int parity = (int)(epoch & 1u);
+    PeerTable pt;
+    for (int r = 0; r < kMaxWorld; ++r) pt.inbox[r] = ex->peer[r];
+    exchange_reset_flags_kernel<<<1, 32, 0, ri.stream>>>(ws);
+    exchange_push_kernel<<<ex->world, 256, 0, ri.stream>>>(pt, d_ids, d_scores, nq * k, ex->slot_words, ex->world, ex->rank, parity, epoch);
+    // about two seconds of 200 ns naps before a missing peer is reported
+    exchange_collect_kernel<<<nq, 256, 0, ri.stream>>>(ex->inbox, ex->slot_words, ex->world, parity, epoch, nq, k, order, ws, 10000000u);
+    mb200::count_launch();
+    mb200::count_launch();
+    mb200::count_launch();
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(err, "topk_exchange_merge: launch failed: %s", cudaGetErrorString(e));
+    mb200::SelectArgs sa{};
+    sa.ws = ws;
+    sa.nq = nq;
+    sa.k = k;
+    sa.order = order;
+    sa.out_ids = d_out_ids;
+    sa.out_scores = d_out_scores;
+    e = mb200::launch_select(ri.stream, sa);
+    if (e != cudaSuccess) return fail(err, "topk_exchange_merge: select launch failed: %s", cudaGetErrorString(e));
+    int rc = 0;
+    mb200::exchange_note_async_flags(rt, ws, sync, err, &rc);
+    return rc;
+}
+
+}  // extern "C"

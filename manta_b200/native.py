@@ -36,6 +36,8 @@ EXPORTS = [
     "manta_b200_embedder_bind", "manta_b200_embedder_unbind", "manta_b200_embed_pooled", "manta_b200_embed_score_topk",
     "manta_b200_embed_device", "manta_b200_score_batched", "manta_b200_score_topk_batched",
     "manta_b200_candidates_save", "manta_b200_candidates_load", "manta_b200_packed_file_info",
+    "manta_b200_exchange_create", "manta_b200_exchange_connect", "manta_b200_exchange_destroy",
+    "manta_b200_topk_exchange_merge_device",
 ]
 
 
@@ -93,6 +95,10 @@ def load() -> ctypes.CDLL:
         "manta_b200_topk_merge_device": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_void_p,
                                          c_void_p, c_int, E],
         "manta_b200_gather_rows": [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, E],
+        "manta_b200_exchange_create": [c_void_p, c_int, c_int, c_int, c_int, POINTER(c_void_p), c_void_p, E],
+        "manta_b200_exchange_connect": [c_void_p, c_void_p, c_void_p, E],
+        "manta_b200_exchange_destroy": [c_void_p, c_void_p, E],
+        "manta_b200_topk_exchange_merge_device": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, E],
         "manta_b200_candidates_save": [c_void_p, c_void_p, c_char_p, E],
         "manta_b200_candidates_load": [c_void_p, c_char_p, c_int64, c_int64, c_int, POINTER(c_void_p), E],
         "manta_b200_packed_file_info": [c_char_p, POINTER(c_int), POINTER(c_int64), POINTER(c_int), POINTER(c_int64), POINTER(c_int64), E],
@@ -222,6 +228,27 @@ class Runtime:
         s = Stats()
         call("manta_b200_runtime_stats", self.handle, byref(s))
         return s.as_dict()
+
+    # ---- exchange of per-shard lists over peer memory ---------------------------------------------
+    def exchange_create(self, world: int, rank: int, nq_max: int, k_max: int):
+        """Returns (exchange handle, 64-byte IPC handle to pass to the other ranks)."""
+        h = c_void_p()
+        ipc = (ctypes.c_ubyte * 64)()
+        call("manta_b200_exchange_create", self.handle, c_int(world), c_int(rank), c_int(nq_max), c_int(k_max), byref(h), ipc)
+        return h, bytes(ipc)
+
+    def exchange_connect(self, ex, handles) -> None:
+        blob = b"".join(handles)
+        buf = (ctypes.c_ubyte * len(blob)).from_buffer_copy(blob)
+        call("manta_b200_exchange_connect", self.handle, ex, buf)
+
+    def exchange_destroy(self, ex) -> None:
+        call("manta_b200_exchange_destroy", self.handle, ex)
+
+    def topk_exchange_merge_device(self, ex, d_ids, d_scores, nq: int, k: int, d_out_ids, d_out_scores, smallest: bool = False,
+                                   sync: bool = False):
+        call("manta_b200_topk_exchange_merge_device", self.handle, ex, c_int(ORDER_SMALLEST if smallest else ORDER_LARGEST),
+             _ptr(d_ids), _ptr(d_scores), c_int(nq), c_int(k), _ptr(d_out_ids), _ptr(d_out_scores), c_int(1 if sync else 0))
 
     # ---- packed candidate files ---------------------------------------------------------------------
     def save_candidates(self, cands: "Candidates", path: str) -> None:

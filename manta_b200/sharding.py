@@ -35,3 +35,31 @@ def gather_pairs(pair: torch.Tensor, gathered: torch.Tensor, dist) -> torch.Tens
 def merge_args(gathered: torch.Tensor, nq: int, k: int):
     """(ids pointer tensor, scores pointer tensor, lists, list_stride) for manta_b200_topk_merge_device."""
     return gathered[0, 0], gathered[0, 1], gathered.shape[0], 2 * nq * k
+
+
+class PeerExchange:
+    """Per-shard lists exchanged with peer stores over NVLink and merged in the same stream-ordered chain
+    (``manta_b200_topk_exchange_merge_device``) instead of an NCCL all-gather followed by a merge.  The inbox
+    handles travel once, at set-up, through ``dist.all_gather_object``."""
+
+    def __init__(self, rt, dist, nq_max: int, k_max: int):
+        self.rt, self.dist = rt, dist
+        self.world = dist.get_world_size() if dist is not None else 1
+        self.rank = dist.get_rank() if dist is not None else 0
+        self.ex, handle = rt.exchange_create(self.world, self.rank, nq_max, k_max)
+        if self.world > 1:
+            handles = [None] * self.world
+            dist.all_gather_object(handles, handle)
+            rt.exchange_connect(self.ex, handles)
+            dist.barrier()  # every inbox is mapped everywhere before the first push
+
+    def merge(self, d_ids, d_scores, nq: int, k: int, d_out_ids, d_out_scores, smallest: bool = False, sync: bool = False):
+        self.rt.topk_exchange_merge_device(self.ex, d_ids, d_scores, nq, k, d_out_ids, d_out_scores, smallest=smallest, sync=sync)
+
+    def close(self):
+        if self.ex is not None:
+            self.rt.synchronize()
+            if self.world > 1:
+                self.dist.barrier()  # no rank unmaps an inbox a peer may still store into
+            self.rt.exchange_destroy(self.ex)
+            self.ex = None

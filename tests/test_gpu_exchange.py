@@ -1,0 +1,102 @@
+"""Exchange of per-shard top-k lists over peer memory + merge (manta_b200_topk_exchange_merge_device).
+
+On one GPU the exchange runs with world = 1 (the rank stores into its own inbox); with two or more GPUs a
+two-process run shards a candidate set and compares the merged result of both ranks with the unsharded pass."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+from helpers import make_rows, pack
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_single_rank_exchange_equals_direct_pass():
+    import torch
+
+    from manta_b200 import native, sharding
+
+    rt = native.Runtime(0)
+    rng = np.random.default_rng(21)
+    data, scales, _ = pack("q8", make_rows(rng, 30000, 128))
+    cands = rt.bind("q8", data, scales)
+    q = make_rows(rng, 5, 128)
+    k = 20
+    want_ids, want_sc = rt.score_topk(cands, "cosine", q, k)
+    stream = torch.cuda.ExternalStream(rt.stream)
+    with torch.cuda.stream(stream):
+        dq = torch.from_numpy(q.astype(np.float16)).cuda()
+        _, d_ids, d_sc = sharding.new_pair(5, k, "cuda")
+        o_ids = torch.empty((5, k), dtype=torch.int32, device="cuda")
+        o_sc = torch.empty((5, k), dtype=torch.float32, device="cuda")
+    stream.synchronize()
+    ex = sharding.PeerExchange(rt, None, 8, 32)
+    for _ in range(3):  # both parities and a reused slot
+        rt.score_topk_device(cands, "cosine", dq, 5, k, d_ids, d_sc, sync=False)
+        ex.merge(d_ids, d_sc, 5, k, o_ids, o_sc, sync=True)
+        np.testing.assert_array_equal(o_ids.cpu().numpy(), want_ids)
+        np.testing.assert_array_equal(o_sc.cpu().numpy(), want_sc)
+    with pytest.raises(native.MantaError, match="exceeds the exchange"):
+        ex.merge(d_ids, d_sc, 9, k, o_ids, o_sc, sync=True)
+    ex.close()
+    cands.unbind()
+    rt.close()
+
+
+_CHILD = r"""
+import os, sys
+import numpy as np
+import torch
+import torch.distributed as dist
+sys.path.insert(0, os.environ["MB200_ROOT"]); sys.path.insert(0, os.path.join(os.environ["MB200_ROOT"], "tests"))
+from helpers import make_rows, pack
+from manta_b200 import native, sharding
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+rt = native.Runtime(rank)
+rng = np.random.default_rng(5)
+rows, cols, nq, k = 40000, 96, 6, 25
+x = make_rows(rng, rows, cols)
+q = make_rows(rng, nq, cols)
+data, scales, _ = pack("q8", x)
+r0, r1 = sharding.shard_bounds(rows, rank, world)
+shard = rt.bind("q8", data[r0:r1], scales[r0:r1], row_base=r0)
+stream = torch.cuda.ExternalStream(rt.stream)
+with torch.cuda.stream(stream):
+    dq = torch.from_numpy(q.astype(np.float16)).cuda()
+    _, d_ids, d_sc = sharding.new_pair(nq, k, "cuda")
+    o_ids = torch.empty((nq, k), dtype=torch.int32, device="cuda")
+    o_sc = torch.empty((nq, k), dtype=torch.float32, device="cuda")
+stream.synchronize()
+ex = sharding.PeerExchange(rt, dist, nq, k)
+whole = rt.bind("q8", data, scales)
+want_ids, want_sc = rt.score_topk(whole, "cosine", q, k)
+for step in range(4):
+    rt.score_topk_device(shard, "cosine", dq, nq, k, d_ids, d_sc, sync=False)
+    ex.merge(d_ids, d_sc, nq, k, o_ids, o_sc, sync=True)
+    assert np.array_equal(o_ids.cpu().numpy(), want_ids), (rank, step)
+    assert np.array_equal(o_sc.cpu().numpy(), want_sc), (rank, step)
+ex.close()
+shard.unbind(); whole.unbind(); rt.close()
+dist.destroy_process_group()
+print("rank", rank, "ok")
+"""
+
+
+def test_two_rank_exchange_matches_unsharded_pass(tmp_path):
+    import torch
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    script = tmp_path / "child.py"
+    script.write_text(_CHILD)
+    env = dict(os.environ, MB200_ROOT=ROOT, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+                        "--master-port", "29577", str(script)], env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "rank 0 ok" in r.stdout and "rank 1 ok" in r.stdout
