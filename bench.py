@@ -289,7 +289,11 @@ def run_ours(args, wl: Workload):
                     self.m_ids = torch.empty((nq, k), dtype=torch.int32, device="cuda")
                     self.m_scores = torch.empty((nq, k), dtype=torch.float32, device="cuda")
             self.stream.synchronize()
-            self.px = sharding.PeerExchange(self.rt, dist, nq, k) if (world > 1 and args.exchange == "peer") else None
+            self.px = None
+            if world > 1 and args.exchange == "peer":
+                self.px = sharding.PeerExchange.try_create(self.rt, dist, nq, k)  # None on every rank if any rank cannot map its peers
+                if self.px is None:
+                    args.exchange = "nccl (peer mapping unavailable)"
 
         def merge(self, sync):
             if self.px is not None:
@@ -526,7 +530,7 @@ def main():
     ap.add_argument("--rows", type=int, default=0, help="override the workload's row count (smaller cases for profiling)")
     ap.add_argument("--nq", type=int, default=0, help="override the workload's query batch")
     ap.add_argument("--k", type=int, default=0, help="override the workload's k")
-    ap.add_argument("--exchange", default="nccl", choices=["nccl", "peer"],
+    ap.add_argument("--exchange", default="peer", choices=["nccl", "peer"],
                     help="sharded runs: how the per-shard lists meet (NCCL all-gather + merge, or peer stores over NVLink fused "
                          "with the merge)")
     ap.add_argument("--lanes", type=int, default=0,

@@ -561,7 +561,7 @@ namespace mb200 {
 int exchange_select_ws(MantaB200Runtime* rt, int nq, uint32_t cap, SelectWs* ws, char** err) {
     std::lock_guard<std::mutex> lk(rt->mu);
     CU_TRY(cudaSetDevice(rt->device));
-    rt->stats.kernel_launches += 4;
+    rt->stats.kernel_launches += 2;
     return ensure_select_ws(rt, nq, cap, 1, ws, err);
 }
 // Reads the merge's flags into host words 4..7 (the fused pass keeps 0..3); the caller holds the lock.

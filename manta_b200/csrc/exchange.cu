@@ -13,6 +13,7 @@
 
 #include "../../include/manta_b200.h"
 #include "common.cuh"
+#include "exchange.cuh"
 #include "internal.h"
 #include "kernels.h"
 
@@ -50,77 +51,21 @@ struct PeerTable {
     unsigned char* inbox[kMaxWorld];
 };
 
-__device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-
-__host__ __device__ inline size_t slot_offset(size_t slot_words, int world, int parity, int r) {
-    return ((size_t)parity * world + r) * slot_words * 4;
-}
-__host__ __device__ inline size_t flag_offset(size_t slot_words, int world, int parity, int r) {
-    return (size_t)2 * world * slot_words * 4 + ((size_t)parity * world + r) * 64;
-}
-
-// Block p stores this rank's list into peer p's inbox slot [parity][rank], then publishes the epoch.
+// Block p stores this rank's list into peer p's inbox slot [parity][rank], then publishes the epoch.  Block 0 also
+// clears the flags of the merge that follows on this stream.
 __global__ void exchange_push_kernel(PeerTable peers, const int32_t* __restrict__ ids, const float* __restrict__ scores, int n,
-                                     size_t slot_words, int world, int rank, int parity, uint32_t epoch) {
+                                     size_t slot_words, int world, int rank, int parity, uint32_t epoch, uint32_t* ws_flags) {
+    if (blockIdx.x == 0 && threadIdx.x < mb200::kNumFlags) ws_flags[threadIdx.x] = 0;
     unsigned char* box = peers.inbox[blockIdx.x];
-    int32_t* dst = reinterpret_cast<int32_t*>(box + slot_offset(slot_words, world, parity, rank));
+    int32_t* dst = reinterpret_cast<int32_t*>(box + mb200::exchange_slot_offset(slot_words, world, parity, rank));
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
         dst[i] = ids[i];
         dst[n + i] = __float_as_int(scores[i]);
     }
     __threadfence_system();
     __syncthreads();
-    if (threadIdx.x == 0) st_release_sys_u32(reinterpret_cast<uint32_t*>(box + flag_offset(slot_words, world, parity, rank)), epoch);
-}
-
-// One block per query: waits until every rank's slot of this parity carries the epoch, then writes the keys of all
-// lists into the query's selection pool (entries a shard could not fill, id < 0, rank below everything).
-__global__ void exchange_collect_kernel(const unsigned char* __restrict__ inbox, size_t slot_words, int world, int parity,
-                                        uint32_t epoch, int nq, int k, int order, mb200::SelectWs ws, uint32_t spin_limit) {
-    __shared__ int ok_s;
-    const int q = blockIdx.x;
-    if (threadIdx.x == 0) ok_s = 1;
-    __syncthreads();
-    if (threadIdx.x < world) {
-        const uint32_t* flag = reinterpret_cast<const uint32_t*>(inbox + flag_offset(slot_words, world, parity, threadIdx.x));
-        uint32_t spin = 0;
-        while (ld_acquire_sys_u32(flag) != epoch) {
-            if (++spin > spin_limit) {
-                ok_s = 0;
-                break;
-            }
-            __nanosleep(200);
-        }
-    }
-    __syncthreads();
-    const float sign = (order == MANTA_B200_ORDER_SMALLEST) ? -1.0f : 1.0f;
-    const int n = nq * k;
-    const int per = world * k;
-    if (ok_s) {
-        for (int i = threadIdx.x; i < per; i += blockDim.x) {
-            const int r = i / k, j = i % k;
-            const int32_t* slot = reinterpret_cast<const int32_t*>(inbox + slot_offset(slot_words, world, parity, r));
-            const int32_t id = __ldcv(slot + (size_t)q * k + j);
-            const float sc = __int_as_float(__ldcv(slot + n + (size_t)q * k + j));
-            ws.pool[(size_t)q * ws.cap + i] = (id < 0) ? 0ull : mb200::make_key(sc * sign + 0.0f, id);
-        }
-    }
-    if (threadIdx.x == 0) {
-        ws.count[q] = ok_s ? (uint32_t)per : 0u;
-        ws.thr[q] = 0;
-        if (!ok_s) ws.flags[mb200::kFlagTimeout] = 1u;
-    }
-}
-
-__global__ void exchange_reset_flags_kernel(mb200::SelectWs ws) {
-    if (threadIdx.x < mb200::kNumFlags) ws.flags[threadIdx.x] = 0;
+    if (threadIdx.x == 0)
+        mb200::st_release_sys_u32(reinterpret_cast<uint32_t*>(box + mb200::exchange_flag_offset(slot_words, world, parity, rank)), epoch);
 }
 
 }  // namespace
@@ -220,12 +165,8 @@ int manta_b200_topk_exchange_merge_device(MantaB200Runtime* rt, MantaB200Exchang
     const int parity = (int)(epoch & 1u);
     PeerTable pt;
     for (int r = 0; r < kMaxWorld; ++r) pt.inbox[r] = ex->peer[r];
-    exchange_reset_flags_kernel<<<1, 32, 0, ri.stream>>>(ws);
-    exchange_push_kernel<<<ex->world, 256, 0, ri.stream>>>(pt, d_ids, d_scores, nq * k, ex->slot_words, ex->world, ex->rank, parity, epoch);
-    // about two seconds of 200 ns naps before a missing peer is reported
-    exchange_collect_kernel<<<nq, 256, 0, ri.stream>>>(ex->inbox, ex->slot_words, ex->world, parity, epoch, nq, k, order, ws, 10000000u);
-    mb200::count_launch();
-    mb200::count_launch();
+    exchange_push_kernel<<<ex->world, 256, 0, ri.stream>>>(pt, d_ids, d_scores, nq * k, ex->slot_words, ex->world, ex->rank, parity, epoch,
+                                                          ws.flags);
     mb200::count_launch();
     e = cudaGetLastError();
     if (e != cudaSuccess) return fail(err, "topk_exchange_merge: launch failed: %s", cudaGetErrorString(e));
@@ -236,6 +177,12 @@ int manta_b200_topk_exchange_merge_device(MantaB200Runtime* rt, MantaB200Exchang
     sa.order = order;
     sa.out_ids = d_out_ids;
     sa.out_scores = d_out_scores;
+    sa.src.inbox = ex->inbox;   // the selection kernel waits for the lists of all ranks, then selects
+    sa.src.slot_words = ex->slot_words;
+    sa.src.world = ex->world;
+    sa.src.parity = parity;
+    sa.src.epoch = epoch;
+    sa.src.spin_limit = 10000000u;   // about two seconds of 200 ns naps before a missing list is reported
     e = mb200::launch_select(ri.stream, sa);
     if (e != cudaSuccess) return fail(err, "topk_exchange_merge: select launch failed: %s", cudaGetErrorString(e));
     int rc = 0;

@@ -96,6 +96,16 @@ cudaError_t launch_gemv(cudaStream_t st, int sm_count, const GemvArgs& a, int mo
 // Final selection: best k keys of each query's pool, sorted best first.  With write_back the k keys are
 // also written to the front of the pool, count becomes k and the threshold becomes the k-th goodness
 // (used between row chunks).  pool_override/count_override select a different key source (merge of lists).
+// Per-shard lists waiting in this rank's exchange inbox (exchange.cu); inbox == nullptr: the pool is already filled.
+struct ExchangeSource {
+    const unsigned char* inbox = nullptr;
+    size_t slot_words = 0;   // int32 words per (parity, rank) slot
+    int world = 0;
+    int parity = 0;
+    uint32_t epoch = 0;      // value every slot's word must carry before the lists are read
+    uint32_t spin_limit = 0; // 200 ns naps before a missing list is reported
+};
+
 struct SelectArgs {
     SelectWs ws;
     int nq;
@@ -104,6 +114,7 @@ struct SelectArgs {
     int write_back;
     int32_t* out_ids;    // [nq][k] or null
     float* out_scores;   // [nq][k] or null
+    ExchangeSource src;  // optional: fill the pool from the exchange inbox first
 };
 cudaError_t launch_select(cudaStream_t st, const SelectArgs& a);
 

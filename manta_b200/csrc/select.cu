@@ -1,6 +1,7 @@
 // Final selection: exact best-k of each query's candidate pool, sorted best first (goodness descending,
 // row id ascending -- the comparator of topKTensor, runtime/backend/tensor_ops.go:1539-1552).
 #include "kernels.h"
+#include "exchange.cuh"
 
 namespace mb200 {
 
@@ -41,6 +42,7 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectArgs a)
 
     const int q = blockIdx.x;
     const int tid = threadIdx.x;
+    if (a.src.inbox != nullptr) exchange_collect(a.src, q, a.nq, a.k, a.order, a.ws);   // sharded: lists arrive over peer memory
     const uint32_t total = min(a.ws.count[q], a.ws.cap);
     const uint64_t* pool = a.ws.pool + (size_t)q * a.ws.cap;
     const uint64_t floor_key = (uint64_t)a.ws.thr[q] << 32;

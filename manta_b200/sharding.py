@@ -53,6 +53,36 @@ class PeerExchange:
             rt.exchange_connect(self.ex, handles)
             dist.barrier()  # every inbox is mapped everywhere before the first push
 
+    @classmethod
+    def try_create(cls, rt, dist, nq_max: int, k_max: int):
+        """A connected exchange, or None on EVERY rank when any rank could not create or map the inboxes (no
+        peer access between the GPUs, IPC handles not permitted): the ranks agree through one all-reduce."""
+        import torch
+
+        self = cls.__new__(cls)
+        self.rt, self.dist, self.ex = rt, dist, None
+        self.world, self.rank = dist.get_world_size(), dist.get_rank()
+        ok, handle = 1, b"\0" * 64
+        try:
+            self.ex, handle = rt.exchange_create(self.world, self.rank, nq_max, k_max)
+        except Exception:
+            ok = 0
+        handles = [None] * self.world
+        dist.all_gather_object(handles, handle)
+        if ok:
+            try:
+                rt.exchange_connect(self.ex, handles)
+            except Exception:
+                ok = 0
+        flag = torch.tensor([ok], dtype=torch.int32, device="cuda" if dist.get_backend() == "nccl" else "cpu")
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 0:
+            if self.ex is not None:
+                rt.exchange_destroy(self.ex)
+            return None
+        dist.barrier()
+        return self
+
     def merge(self, d_ids, d_scores, nq: int, k: int, d_out_ids, d_out_scores, smallest: bool = False, sync: bool = False):
         self.rt.topk_exchange_merge_device(self.ex, d_ids, d_scores, nq, k, d_out_ids, d_out_scores, smallest=smallest, sync=sync)
 
