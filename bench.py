@@ -530,6 +530,8 @@ def main():
     ap.add_argument("--rows", type=int, default=0, help="override the workload's row count (smaller cases for profiling)")
     ap.add_argument("--nq", type=int, default=0, help="override the workload's query batch")
     ap.add_argument("--k", type=int, default=0, help="override the workload's k")
+    ap.add_argument("--metric", default="", choices=["", "dot", "cosine", "l2_distance"], help="override the workload's metric")
+    ap.add_argument("--smallest", action="store_true", help="select the k smallest scores instead of the k largest")
     ap.add_argument("--exchange", default="peer", choices=["nccl", "peer"],
                     help="sharded runs: how the per-shard lists meet (NCCL all-gather + merge, or peer stores over NVLink fused "
                          "with the merge)")
@@ -545,6 +547,10 @@ def main():
         wl.nq = args.nq
     if args.k:
         wl.k = args.k
+    if args.metric:
+        wl.metric = args.metric
+    if args.smallest:
+        wl.smallest = True
     if args.impl == "reference":
         run_reference(args, wl)
     else:

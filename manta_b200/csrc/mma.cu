@@ -196,6 +196,7 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     uint32_t* bmax_s = thr_s + kMmaCols;                 // [qn][4]: maxima of the current tile per epilogue warp
     uint32_t* pub_s = bmax_s + kMmaCols * 4;             // [qn][4][kBucketSlots]: last published values
     float* zq_s = (float*)(pub_s + kMmaCols * 4 * kBucketSlots);      // [kMmaCols]: pre-filter bound per query (+inf past qn)
+    float* wq_s = zq_s + kMmaCols;                                    // [kMmaCols]: l2 only, weight of ||row||^2 in the bound
 
     const int64_t nrows = a.row_end - a.row_begin;
     const int n_tiles = (int)((nrows + kTileRows - 1) / kTileRows);
@@ -223,13 +224,21 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     for (int j = threadIdx.x; j < a.qn; j += blockDim.x) {
         hdr_s[j] = a.headers[a.q0 + j];
         zq_s[j] = -INFINITY;   // no bound yet: every chunk takes the exact path
+        {
+            // l2: 1 / (2 s_lo) for q8 (the filter works on T = dot / (row scale * s_lo)), 1/2 for f16, a shade low
+            const float s2 = I8 ? 2.0f * hdr_s[j].s_lo : 2.0f;
+            wq_s[j] = (s2 > 0.0f) ? (1.0f / s2) * (1.0f - 1e-6f) : 0.0f;
+        }
         thr_s[j] = 1;
         for (int w = 0; w < 4; ++w) {
             bmax_s[j * 4 + w] = 0;
             for (int s = 0; s < kBucketSlots; ++s) pub_s[(j * 4 + w) * kBucketSlots + s] = 0;
         }
     }
-    for (int j = a.qn + threadIdx.x; j < kMmaCols; j += blockDim.x) zq_s[j] = INFINITY;   // padding columns never pass
+    for (int j = a.qn + threadIdx.x; j < kMmaCols; j += blockDim.x) {   // padding columns never pass
+        zq_s[j] = INFINITY;
+        wq_s[j] = 0.0f;
+    }
     if (warp == 1) tmem_alloc(tmem_slot, 512);
     tc_fence_before();
     __syncthreads();
@@ -309,7 +318,9 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const float sign = (a.order == MANTA_B200_ORDER_SMALLEST) ? -1.0f : 1.0f;
             const bool want_scale = I8 && METRIC != MANTA_B200_METRIC_COSINE;
             const bool want_stats = METRIC != MANTA_B200_METRIC_DOT;
-            const bool cheap = a.order == MANTA_B200_ORDER_LARGEST && METRIC != MANTA_B200_METRIC_L2_DISTANCE;
+            // every (metric, order) has a pre-filter except "largest l2 distance", which takes the exact path throughout
+            constexpr bool kL2 = METRIC == MANTA_B200_METRIC_L2_DISTANCE;
+            const bool cheap = !(kL2 && a.order == MANTA_B200_ORDER_LARGEST);
             unsigned long long c_wait = 0, c_ld = 0, c_math = 0, c_slow = 0, c_house = 0, n_slow = 0, c_thr = 0;
             const bool timing = a.dbg != nullptr && cta == 0 && warp == 4;
             (void)c_ld; (void)c_slow;
@@ -343,6 +354,11 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 if (rv) rowc = (METRIC == MANTA_B200_METRIC_COSINE) ? rinv : (I8 ? sd : 1.0f);
                 // |T_f32 - T| and the 254 * s_lo != s_hi mismatch are below 4e-7 * 254 * |I_hi|, |I_hi| <= 127^2 * cols
                 const float srow = I8 ? rowc * (4e-7f * 254.0f * 16129.0f * (float)a.cv.cols) : 0.0f;
+                // "smallest" orders compare -score; the smallest l2 distance asks for a LARGE dot product, see below
+                const float rowcs = kL2 ? rowc : sign * rowc;
+                // l2: ||row||^2 as the filter adds it to the per-query constant
+                float dn2row = 0.0f;
+                if constexpr (kL2) dn2row = I8 ? __fmul_rn(__fmul_rn(sd, sd), (float)(int)stat) : __uint_as_float(stat);
                 // One finished score of this lane's row for query j: vote against the bound, keep the bucket maximum,
                 // append the passing rows with one reservation per warp.
                 auto offer = [&](int j, float g, uint32_t o) {
@@ -395,7 +411,10 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                                 t = __fmaf_rn((float)(int)vh[jj], 254.0f, (float)(int)vl[jj]);
                             else
                                 t = __uint_as_float(vh[jj]);
-                            hit |= (__fmaf_rn(t, rowc, srow) >= zq_s[c0 + jj]) ? (1u << jj) : 0u;
+                            // l2 (smallest): dist <= B  <=>  dot >= (||q||^2 - B^2 + ||row||^2) / 2, in the units of T
+                            float rhs = zq_s[c0 + jj];
+                            if constexpr (kL2) rhs = __fmaf_rn(dn2row, wq_s[c0 + jj], rhs);
+                            hit |= (__fmaf_rn(t, rowcs, srow) >= rhs) ? (1u << jj) : 0u;
                         }
                         hit = __reduce_or_sync(0xffffffffu, hit);
                         if (hit == 0u) continue;
@@ -550,14 +569,25 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     // q8 divided by s_lo (the filter compares the integer combination T, see the epilogue)
                     float c = -INFINITY;
                     if (v > 1u) {
-                        const float tf = float_from_ord(v);
-                        const float qi = hdr_s[jj].qinv;
-                        c = (METRIC == MANTA_B200_METRIC_COSINE) ? ((qi > 0.0f) ? tf / qi : -INFINITY) : tf;
-                        c = c - fabsf(c) * 2e-6f - 1e-30f;
-                        if constexpr (I8) {
-                            const float sl = hdr_s[jj].s_lo;
-                            c = (sl > 0.0f) ? c / sl : -INFINITY;
-                            c = c - fabsf(c) * 1e-6f;
+                        const float tf = float_from_ord(v);   // bound on the goodness (score, or -score for "smallest")
+                        if constexpr (METRIC == MANTA_B200_METRIC_L2_DISTANCE) {
+                            // smallest distance: dist <= B = -tf.  z = (||q||^2 - B^2) / (2 s_lo) (q8) or / 2 (f16), with
+                            // B^2 raised and z lowered by a few ulps; the row's ||d||^2 is added in the epilogue.
+                            const float bnd = fmaxf(-tf, 0.0f);
+                            const double b2 = (double)bnd * (double)bnd * (1.0 + 4e-6) + 1e-30;
+                            const double q2 = I8 ? hdr_s[jj].qhat2 : hdr_s[jj].qn2d;
+                            const float s2 = I8 ? 2.0f * hdr_s[jj].s_lo : 2.0f;
+                            c = (s2 > 0.0f) ? (float)((q2 - b2) / (double)s2) : -INFINITY;
+                            c = c - fabsf(c) * 1e-6f - 1e-30f;
+                        } else {
+                            const float qi = hdr_s[jj].qinv;
+                            c = (METRIC == MANTA_B200_METRIC_COSINE) ? ((qi > 0.0f) ? tf / qi : -INFINITY) : tf;
+                            c = c - fabsf(c) * 2e-6f - 1e-30f;
+                            if constexpr (I8) {
+                                const float sl = hdr_s[jj].s_lo;
+                                c = (sl > 0.0f) ? c / sl : -INFINITY;
+                                c = c - fabsf(c) * 1e-6f;
+                            }
                         }
                     }
                     zq_s[jj] = c;
@@ -770,7 +800,7 @@ cudaError_t launch_mma_topk(cudaStream_t stream, int sm_count, MmaState** state,
 
         const size_t a_stage = (size_t)kTileRows * kChunkBytes, b_stage = (size_t)ncols * kChunkBytes;
         const size_t fixed = 1024 /*alignment slack*/ + 256 /*barriers*/ + sizeof(QueryHeader) * kMmaCols + 4 * kMmaCols +
-                             16 * kMmaCols + 16 * kMmaCols * kBucketSlots + 4 * kMmaCols;
+                             16 * kMmaCols + 16 * kMmaCols * kBucketSlots + 8 * kMmaCols;
         const size_t budget = kSmemLimit - fixed;
         // Operand B stays resident when it leaves room for at least four candidate stages: the ring then carries
         // only candidate bytes instead of re-reading the queries from L2 for every tile.

@@ -33,6 +33,10 @@ CASES = [  # (layout, metric, rows, cols, nq, k, smallest)
     ("f16", "cosine", 80000, 128, 200, 10, False),
     ("f16", "l2_distance", 40000, 64, 16, 20, True),
     ("f16", "dot", 30000, 100, 9, 7, False),          # ragged width
+    ("q8", "cosine", 90000, 128, 40, 10, True),       # "smallest" orders go through the pre-filter with the sign flipped
+    ("f16", "dot", 90000, 96, 12, 10, True),
+    ("q8", "l2_distance", 150000, 768, 130, 10, True),  # nearest neighbours, two query groups
+    ("f16", "l2_distance", 120000, 384, 64, 10, False),  # farthest rows: no pre-filter, exact path throughout
 ]
 
 
