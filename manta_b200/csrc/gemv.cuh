@@ -224,6 +224,29 @@ __global__ void __launch_bounds__(kThreads, (QT == 1 && CPL <= 4) ? 2 : 1) gemv_
     uint32_t iter = 0;
     uint32_t overflow_seen = 0;
     uint32_t thr[QT];
+    // Nearest-neighbour l2 on packed rows finishes a score in f64 (square root included).  In top-k mode a row is
+    // first tested in f32: dist <= B  <=>  dot >= (||q||^2 - B^2 + ||row||^2) / 2, with B the current bound and a few
+    // ulps of slack; a warp-tile in which no row passes skips the exact evaluation.  Rows that do not pass are below
+    // the bound, so leaving them out of the bucket maxima keeps those maxima valid lower bounds.
+    const bool l2_pref = (kQ8 || kQ4) && mode == kModeTopk && a.metric == MANTA_B200_METRIC_L2_DISTANCE &&
+                         a.order == MANTA_B200_ORDER_SMALLEST;
+    float l2_ch[QT];   // (||q||^2 - B^2) / 2 per query, lowered; -inf while no bound exists
+#pragma unroll
+    for (int q = 0; q < QT; ++q) l2_ch[q] = -INFINITY;
+    auto update_l2_bounds = [&]() {
+        if (!l2_pref) return;
+#pragma unroll
+        for (int q = 0; q < QT; ++q) {
+            float ch = -INFINITY;
+            if (thr[q] > 1u) {
+                const float bnd = fmaxf(-float_from_ord(thr[q]), 0.0f);
+                const double b2 = (double)bnd * (double)bnd * (1.0 + 4e-6) + 1e-30;
+                ch = (float)((hdr[q].qhat2 - b2) * 0.5);
+                ch = ch - fabsf(ch) * 1e-6f - 1e-30f;
+            }
+            l2_ch[q] = ch;
+        }
+    };
     // Rows of the first two tiles are scored before any bound exists.  They are held back (one key per lane and
     // tile) and enter the pool, filtered, once the first bound has arrived, so the pool never sees a burst.
     uint64_t early_key[QT][2];
@@ -269,6 +292,7 @@ __global__ void __launch_bounds__(kThreads, (QT == 1 && CPL <= 4) ? 2 : 1) gemv_
             if (iter <= 16 || (iter & 7) == 0) {
 #pragma unroll
                 for (int q = 0; q < QT; ++q) thr[q] = ld_relaxed_u32(a.ws.thr + a.q0 + ((q < a.qt) ? q : 0));
+                update_l2_bounds();
             }
             // a pool that overflowed makes the host redo the pass in chunks: stop streaming.  The flag is
             // loaded in one check and tested in the next, so its latency never stalls the stream.
@@ -288,6 +312,7 @@ __global__ void __launch_bounds__(kThreads, (QT == 1 && CPL <= 4) ? 2 : 1) gemv_
                             thr[q] = ld_relaxed_u32(a.ws.thr + a.q0 + ((q < a.qt) ? q : 0));
                         }
                     }
+                    update_l2_bounds();
                 }
                 flush_early();
             }
@@ -413,11 +438,23 @@ __global__ void __launch_bounds__(kThreads, (QT == 1 && CPL <= 4) ? 2 : 1) gemv_
                     }
                     continue;
                 }
+                if (l2_pref && iter > 2) {
+                    const float t = __fmaf_rn((float)l, hdr[q].s_lo, __fmul_rn((float)h, hdr[q].s_hi));
+                    float dc = __fmul_rn(t, cur.sd);
+                    dc = dc + 4e-7f * fabsf(dc);   // the exact path forms this product in f64
+                    const float dn2c = __fmul_rn(__fmul_rn(cur.sd, cur.sd), (float)nn);
+                    const bool pass = rv && dc >= __fmaf_rn(dn2c, 0.4999995f, l2_ch[q]);
+                    if (!__any_sync(0xffffffffu, pass)) continue;
+                }
                 score = q8_finish(a.metric, h, l, nn, rinv, cur.sd, hdr[q]);
             } else if constexpr (kQ4) {
                 const float th = reduce_scatter<LPR, U>(fa[q], gl);
                 const float tl = reduce_scatter<LPR, U>(fb[q], gl);
                 const float dotv = __fmaf_rn(tl, q4_sl[q], __fmul_rn(th, q4_sh[q]));
+                if (l2_pref && iter > 2) {
+                    const bool pass = rv && dotv >= __fmaf_rn(dn2, 0.4999995f, l2_ch[q]);
+                    if (!__any_sync(0xffffffffu, pass)) continue;
+                }
                 score = float_finish(a.metric, dotv, dn2, rinv, hdr[q], hdr[q].qhat2);
             } else {
                 const float dotv = reduce_scatter<LPR, U>(fa[q], gl);
