@@ -103,7 +103,9 @@ __device__ __forceinline__ T reduce_scatter(T (&v)[V], int gl) {
     return v[0];
 }
 
-template <int LAYOUT, int QT, int LPR, int CPL, int U>
+// L2P: instantiation for nearest-neighbour l2 on packed rows in top-k mode (an f32 pre-filter in front of the f64
+// finish); kept out of the other instantiations so that their code is untouched by it.
+template <int LAYOUT, int QT, int LPR, int CPL, int U, bool L2P>
 __global__ void __launch_bounds__(kThreads, (QT == 1 && CPL <= 4) ? 2 : 1) gemv_kernel(const GemvArgs a, const int mode) {
     constexpr bool kQ8 = LAYOUT == MANTA_B200_LAYOUT_Q8_ROW_F32;
     constexpr bool kQ4 = LAYOUT == MANTA_B200_LAYOUT_Q4_B32_F16;
@@ -228,13 +230,12 @@ __global__ void __launch_bounds__(kThreads, (QT == 1 && CPL <= 4) ? 2 : 1) gemv_
     // first tested in f32: dist <= B  <=>  dot >= (||q||^2 - B^2 + ||row||^2) / 2, with B the current bound and a few
     // ulps of slack; a warp-tile in which no row passes skips the exact evaluation.  Rows that do not pass are below
     // the bound, so leaving them out of the bucket maxima keeps those maxima valid lower bounds.
-    const bool l2_pref = (kQ8 || kQ4) && mode == kModeTopk && a.metric == MANTA_B200_METRIC_L2_DISTANCE &&
-                         a.order == MANTA_B200_ORDER_SMALLEST;
+    constexpr bool l2_pref = L2P && (kQ8 || kQ4);   // the launcher picks this instantiation for (top-k, l2, smallest) only
     float l2_ch[QT];   // (||q||^2 - B^2) / 2 per query, lowered; -inf while no bound exists
 #pragma unroll
     for (int q = 0; q < QT; ++q) l2_ch[q] = -INFINITY;
     auto update_l2_bounds = [&]() {
-        if (!l2_pref) return;
+        if constexpr (l2_pref) {
 #pragma unroll
         for (int q = 0; q < QT; ++q) {
             float ch = -INFINITY;
@@ -245,6 +246,7 @@ __global__ void __launch_bounds__(kThreads, (QT == 1 && CPL <= 4) ? 2 : 1) gemv_
                 ch = ch - fabsf(ch) * 1e-6f - 1e-30f;
             }
             l2_ch[q] = ch;
+        }
         }
     };
     // Rows of the first two tiles are scored before any bound exists.  They are held back (one key per lane and
@@ -438,7 +440,7 @@ __global__ void __launch_bounds__(kThreads, (QT == 1 && CPL <= 4) ? 2 : 1) gemv_
                     }
                     continue;
                 }
-                if (l2_pref && iter > 2) {
+                if constexpr (l2_pref) if (iter > 2) {
                     const float t = __fmaf_rn((float)l, hdr[q].s_lo, __fmul_rn((float)h, hdr[q].s_hi));
                     float dc = __fmul_rn(t, cur.sd);
                     dc = dc + 4e-7f * fabsf(dc);   // the exact path forms this product in f64
@@ -451,7 +453,7 @@ __global__ void __launch_bounds__(kThreads, (QT == 1 && CPL <= 4) ? 2 : 1) gemv_
                 const float th = reduce_scatter<LPR, U>(fa[q], gl);
                 const float tl = reduce_scatter<LPR, U>(fb[q], gl);
                 const float dotv = __fmaf_rn(tl, q4_sl[q], __fmul_rn(th, q4_sh[q]));
-                if (l2_pref && iter > 2) {
+                if constexpr (l2_pref) if (iter > 2) {
                     const bool pass = rv && dotv >= __fmaf_rn(dn2, 0.4999995f, l2_ch[q]);
                     if (!__any_sync(0xffffffffu, pass)) continue;
                 }
@@ -553,7 +555,7 @@ __global__ void __launch_bounds__(kThreads, (QT == 1 && CPL <= 4) ? 2 : 1) gemv_
     cp_async_wait<0>();
 }
 
-template <int LAYOUT, int QT, int LPR, int CPL>
+template <int LAYOUT, int QT, int LPR, int CPL, bool L2P>
 cudaError_t launch_gemv_shape(cudaStream_t st, int grid, const GemvArgs& a, int mode) {
     constexpr int U = (CPL == 1) ? 8 : (CPL == 2) ? 4 : (CPL <= 4) ? 2 : 1;
     constexpr size_t smem = (size_t)kStages * U * CPL * kThreads * 16 + (size_t)kStageWords * 4;
@@ -564,25 +566,25 @@ cudaError_t launch_gemv_shape(cudaStream_t st, int grid, const GemvArgs& a, int 
     cudaGetDevice(&dev);
     int occ = (dev >= 0 && dev < 64) ? resident[dev] : 0;
     if (occ == 0) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_kernel<LAYOUT, QT, LPR, CPL, U>,
+        cudaError_t e = cudaFuncSetAttribute(gemv_kernel<LAYOUT, QT, LPR, CPL, U, L2P>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
-        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, gemv_kernel<LAYOUT, QT, LPR, CPL, U>, kThreads, smem);
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, gemv_kernel<LAYOUT, QT, LPR, CPL, U, L2P>, kThreads, smem);
         if (e != cudaSuccess) return e;
         if (occ < 1) return cudaErrorLaunchOutOfResources;
         if (occ > 2) occ = 2;
         if (dev >= 0 && dev < 64) resident[dev] = occ;
     }
     grid = (grid / 2) * occ;  // the caller passes 2 CTAs per SM, the bucket layout's upper bound
-    gemv_kernel<LAYOUT, QT, LPR, CPL, U><<<grid, kThreads, smem, st>>>(a, mode);
+    gemv_kernel<LAYOUT, QT, LPR, CPL, U, L2P><<<grid, kThreads, smem, st>>>(a, mode);
     count_launch();
     return cudaGetLastError();
 }
 
-template <int LAYOUT, int QT>
+template <int LAYOUT, int QT, bool L2P>
 cudaError_t launch_gemv_qt(cudaStream_t st, int grid, const GemvArgs& a, int mode, const GemvShape& s) {
 #define MB200_SHAPE(L, C) \
-    if (s.lpr == L && s.cpl == C) return launch_gemv_shape<LAYOUT, QT, L, C>(st, grid, a, mode);
+    if (s.lpr == L && s.cpl == C) return launch_gemv_shape<LAYOUT, QT, L, C, L2P>(st, grid, a, mode);
     MB200_SHAPE(8, 1) MB200_SHAPE(8, 2) MB200_SHAPE(8, 3) MB200_SHAPE(8, 4)
     MB200_SHAPE(16, 1) MB200_SHAPE(16, 2) MB200_SHAPE(16, 3) MB200_SHAPE(16, 4)
     MB200_SHAPE(32, 1) MB200_SHAPE(32, 2) MB200_SHAPE(32, 3) MB200_SHAPE(32, 4)
@@ -600,9 +602,16 @@ cudaError_t launch_gemv_layout(cudaStream_t st, int sm_count, const GemvArgs& a,
     const int grid = gemv_grid_size(sm_count);
     int qt = a.qt;
     if (s.cpl == 8 && qt != 1) return cudaErrorInvalidValue;
-    if (qt == 1) return launch_gemv_qt<LAYOUT, 1>(st, grid, a, mode, s);
-    if (qt == 2) return launch_gemv_qt<LAYOUT, 2>(st, grid, a, mode, s);
-    return launch_gemv_qt<LAYOUT, 4>(st, grid, a, mode, s);
+    if constexpr (LAYOUT != MANTA_B200_LAYOUT_F16) {
+        if (mode == kModeTopk && a.metric == MANTA_B200_METRIC_L2_DISTANCE && a.order == MANTA_B200_ORDER_SMALLEST) {
+            if (qt == 1) return launch_gemv_qt<LAYOUT, 1, true>(st, grid, a, mode, s);
+            if (qt == 2) return launch_gemv_qt<LAYOUT, 2, true>(st, grid, a, mode, s);
+            return launch_gemv_qt<LAYOUT, 4, true>(st, grid, a, mode, s);
+        }
+    }
+    if (qt == 1) return launch_gemv_qt<LAYOUT, 1, false>(st, grid, a, mode, s);
+    if (qt == 2) return launch_gemv_qt<LAYOUT, 2, false>(st, grid, a, mode, s);
+    return launch_gemv_qt<LAYOUT, 4, false>(st, grid, a, mode, s);
 }
 
 cudaError_t launch_gemv_f16(cudaStream_t st, int sm_count, const GemvArgs& a, int mode);
