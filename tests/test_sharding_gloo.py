@@ -84,3 +84,65 @@ def test_shard_bounds_cover_rows_exactly():
             assert b[0][0] == 0 and b[-1][1] == rows
             assert all(b[i][1] == b[i + 1][0] for i in range(world - 1))
             assert max(e - s for s, e in b) - min(e - s for s, e in b) <= 1
+
+
+class _FakeRuntime:
+    """Stands in for native.Runtime in the host logic of the peer exchange: records calls, fails on request."""
+
+    def __init__(self, fail_create=False, fail_connect=False):
+        self.fail_create, self.fail_connect = fail_create, fail_connect
+        self.created = self.connected = self.destroyed = 0
+
+    def exchange_create(self, world, rank, nq_max, k_max):
+        if self.fail_create:
+            raise RuntimeError("no IPC here")
+        self.created += 1
+        return object(), bytes([rank]) * 64
+
+    def exchange_connect(self, ex, handles):
+        if self.fail_connect:
+            raise RuntimeError("cannot map a peer")
+        assert len(handles) == 2 and handles[0] == bytes([0]) * 64 and handles[1] == bytes([1]) * 64
+        self.connected += 1
+
+    def exchange_destroy(self, ex):
+        self.destroyed += 1
+
+    def synchronize(self):
+        pass
+
+
+def _exchange_worker(rank, world, port, scenario, ret):
+    sys.path.insert(0, ROOT)
+    from manta_b200 import sharding
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        rt = _FakeRuntime(fail_create=(scenario == "create" and rank == 1), fail_connect=(scenario == "connect" and rank == 0))
+        px = sharding.PeerExchange.try_create(rt, dist, 4, 10)
+        if scenario == "ok":
+            assert px is not None and rt.created == 1 and rt.connected == 1
+            px.close()
+            assert rt.destroyed == 1
+        else:
+            # one rank failed: EVERY rank falls back, and a rank that had created its inbox releases it
+            assert px is None
+            assert rt.destroyed == rt.created
+        ret[rank] = True
+    finally:
+        dist.destroy_process_group()
+
+
+def _run_exchange(scenario, port):
+    with mp.Manager() as mgr:
+        ret = mgr.dict()
+        mp.spawn(_exchange_worker, args=(2, port, scenario, ret), nprocs=2, join=True)
+        assert all(ret.get(r) for r in range(2))
+
+
+def test_peer_exchange_setup_and_agreed_fallback():
+    _run_exchange("ok", 29631)
+    _run_exchange("create", 29632)
+    _run_exchange("connect", 29633)
