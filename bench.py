@@ -337,6 +337,9 @@ def run_ours(args, wl: Workload):
             dq = ln.d_q
         else:
             dq = d_queries[i % nsets]
+        if ln.px is not None:  # shard pass, exchange over peer memory and merge as one stream-ordered chain
+            ln.px.score_topk_merge(cands, wl.metric, dq, nq, k, ln.m_ids, ln.m_scores, smallest=wl.smallest, sync=False)
+            return
         ln.rt.score_topk_device(cands, wl.metric, dq, nq, k, ln.d_ids, ln.d_scores, smallest=wl.smallest, sync=False)
         if world > 1:
             ln.merge(False)
@@ -414,8 +417,11 @@ def run_ours(args, wl: Workload):
                 hb["s_q"].copy_(hb["queries"][i % nsets], non_blocking=True)
         if wl.embed:
             rt.embed_device(emb, hb["s_tokens"], hb["s_mask"], nq, wl.embed[2], hb["s_q"], sync=False)
-        rt.score_topk_device(cands, wl.metric, hb["s_q"], nq, k, d_ids, d_scores, smallest=wl.smallest, sync=False)
-        lanes[0].merge(False)
+        if lanes[0].px is not None:
+            lanes[0].px.score_topk_merge(cands, wl.metric, hb["s_q"], nq, k, m_ids, m_scores, smallest=wl.smallest, sync=False)
+        else:
+            rt.score_topk_device(cands, wl.metric, hb["s_q"], nq, k, d_ids, d_scores, smallest=wl.smallest, sync=False)
+            lanes[0].merge(False)
         with torch.cuda.stream(stream):
             hb["ids"].copy_(m_ids, non_blocking=True)
             hb["scores"].copy_(m_scores, non_blocking=True)

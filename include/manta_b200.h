@@ -194,6 +194,14 @@ int manta_b200_exchange_create(MantaB200Runtime* rt, int world, int rank, int nq
 int manta_b200_exchange_connect(MantaB200Runtime* rt, MantaB200Exchange* ex, const unsigned char* handles /* world x 64 */,
                                 char** err);
 int manta_b200_exchange_destroy(MantaB200Runtime* rt, MantaB200Exchange* ex, char** err);
+/* The whole sharded step on the runtime's stream: fused score + top-k over this rank's shard whose selection kernel
+ * stores the lists straight into every rank's inbox (peer stores) and publishes the epoch, then the merge whose
+ * selection kernel waits for all ranks' lists.  The shard pass is asynchronous: a pool overflow is reported by the next
+ * synchronisation and the step must then be redone with manta_b200_score_topk_device(sync != 0) +
+ * manta_b200_topk_exchange_merge_device. */
+int manta_b200_score_topk_exchange_device(MantaB200Runtime* rt, MantaB200Exchange* ex, const MantaB200Candidates* set,
+                                          int metric, int order, const void* d_queries, int nq, int k,
+                                          int32_t* d_out_ids, float* d_out_scores, int sync, char** err);
 int manta_b200_topk_exchange_merge_device(MantaB200Runtime* rt, MantaB200Exchange* ex, int order, const int32_t* d_ids,
                                           const float* d_scores, int nq, int k, int32_t* d_out_ids, float* d_out_scores,
                                           int sync, char** err);

@@ -647,7 +647,7 @@ static int scan_rows(MantaB200Runtime* rt, const CandView& cv, const QueryPrep& 
 
 static int score_topk_locked(MantaB200Runtime* rt, const MantaB200Candidates* set, int metric, int order,
                              const void* d_queries, int nq, int k, int32_t* d_out_ids, float* d_out_scores, int sync,
-                             char** err) {
+                             char** err, const ExchangeSink* sink = nullptr) {
     const CandView& cv = set->cv;
     // a multiple of four, so that every query's bucket row starts on a 16-byte boundary
     const uint32_t nb = ((uint32_t)std::max(gemv_bucket_count(rt->sm_count), mma_bucket_count(rt->sm_count)) + 3u) & ~3u;
@@ -667,6 +667,7 @@ static int score_topk_locked(MantaB200Runtime* rt, const MantaB200Candidates* se
     sa.write_back = 0;
     sa.out_ids = d_out_ids;
     sa.out_scores = d_out_scores;
+    if (sink) sa.sink = *sink;
     cudaError_t e = launch_select(rt->stream, sa);
     rt->stats.kernel_launches++;
     if (e != cudaSuccess) return fail_cuda(err, "launch select kernel", e);
@@ -715,6 +716,24 @@ static int check_topk_args(const MantaB200Candidates* set, int order, int k, cha
     if (k > kMaxK) return fail(err, "topk limit %d exceeds the fused pass maximum %d", k, kMaxK);
     return 0;
 }
+
+extern "C++" {
+namespace mb200 {
+// The shard pass of a sharded step (exchange.cu): fused score + top-k whose selection stores the lists into every
+// rank's inbox.  Always asynchronous: a pool overflow is reported by the next synchronisation, not redone in chunks
+// (the peers would already hold the incomplete list).  Takes the runtime's lock itself.
+int score_topk_into_sink(MantaB200Runtime* rt, const MantaB200Candidates* set, int metric, int order, const void* d_queries, int nq,
+                         int k, const ExchangeSink& sink, char** err) {
+    if (check_score_args(rt, set, metric, nq, err)) return 1;
+    if (check_topk_args(set, order, k, err)) return 1;
+    if (!d_queries) return fail(err, "score_topk: NULL buffer");
+    std::lock_guard<std::mutex> lk(rt->mu);
+    CU_TRY(cudaSetDevice(rt->device));
+    rt->stats.score_topk_calls++;
+    return score_topk_locked(rt, set, metric, order, d_queries, nq, k, nullptr, nullptr, 0, err, &sink);
+}
+}  // namespace mb200
+}  // extern "C++"
 
 int manta_b200_score_topk_device(MantaB200Runtime* rt, const MantaB200Candidates* set, int metric, int order,
                                  const void* d_queries, int nq, int k, int32_t* d_out_ids, float* d_out_scores,

@@ -71,6 +71,8 @@ __global__ void exchange_push_kernel(PeerTable peers, const int32_t* __restrict_
 }  // namespace
 
 namespace mb200 {
+int score_topk_into_sink(MantaB200Runtime* rt, const MantaB200Candidates* set, int metric, int order, const void* d_queries, int nq,
+                         int k, const ExchangeSink& sink, char** err);  // api.cu
 int exchange_select_ws(MantaB200Runtime* rt, int nq, uint32_t cap, SelectWs* ws, char** err);  // api.cu
 void exchange_note_async_flags(MantaB200Runtime* rt, const SelectWs& ws, int sync, char** err, int* rc);  // api.cu
 }
@@ -95,7 +97,7 @@ int manta_b200_exchange_create(MantaB200Runtime* rt, int world, int rank, int nq
     ex->nq_max = nq_max;
     ex->k_max = k_max;
     ex->slot_words = ((size_t)2 * nq_max * k_max + 63) / 64 * 64;
-    ex->inbox_bytes = (size_t)2 * world * ex->slot_words * 4 + (size_t)2 * world * 64;
+    ex->inbox_bytes = (size_t)2 * world * ex->slot_words * 4 + (size_t)2 * world * 64 + 64;   // slots, epoch words, block counter
     e = cudaMalloc((void**)&ex->inbox, ex->inbox_bytes);
     if (e == cudaSuccess) e = cudaMemset(ex->inbox, 0, ex->inbox_bytes);
     cudaIpcMemHandle_t h;
@@ -144,6 +146,61 @@ int manta_b200_exchange_destroy(MantaB200Runtime* rt, MantaB200Exchange* ex, cha
     if (ex->inbox) cudaFree(ex->inbox);
     delete ex;
     return 0;
+}
+
+// Waits for the lists of this epoch and selects (shared by the two entry points below); the caller holds nothing.
+static int exchange_merge_tail(MantaB200Runtime* rt, MantaB200Exchange* ex, const mb200::SelectWs& ws, int order, int nq, int k,
+                               int parity, uint32_t epoch, int32_t* d_out_ids, float* d_out_scores, int sync, char** err) {
+    mb200::RuntimeInfo ri = mb200::runtime_info(rt);
+    std::lock_guard<std::mutex> lk(*ri.mu);
+    cudaError_t e = cudaSetDevice(ri.device);
+    if (e != cudaSuccess) return fail(err, "topk_exchange_merge: %s", cudaGetErrorString(e));
+    mb200::SelectArgs sa{};
+    sa.ws = ws;
+    sa.nq = nq;
+    sa.k = k;
+    sa.order = order;
+    sa.out_ids = d_out_ids;
+    sa.out_scores = d_out_scores;
+    sa.src.inbox = ex->inbox;   // the selection kernel waits for the lists of all ranks, then selects
+    sa.src.slot_words = ex->slot_words;
+    sa.src.world = ex->world;
+    sa.src.parity = parity;
+    sa.src.epoch = epoch;
+    sa.src.spin_limit = 10000000u;   // about two seconds of 200 ns naps before a missing list is reported
+    e = mb200::launch_select(ri.stream, sa);
+    if (e != cudaSuccess) return fail(err, "topk_exchange_merge: select launch failed: %s", cudaGetErrorString(e));
+    int rc = 0;
+    mb200::exchange_note_async_flags(rt, ws, sync, err, &rc);
+    return rc;
+}
+
+int manta_b200_score_topk_exchange_device(MantaB200Runtime* rt, MantaB200Exchange* ex, const MantaB200Candidates* set, int metric,
+                                          int order, const void* d_queries, int nq, int k, int32_t* d_out_ids,
+                                          float* d_out_scores, int sync, char** err) {
+    if (!rt || !ex || !set || !d_queries || !d_out_ids || !d_out_scores) return fail(err, "score_topk_exchange: NULL argument");
+    if (!ex->connected && ex->world > 1) return fail(err, "score_topk_exchange: the exchange is not connected to its peers");
+    if (nq <= 0 || k <= 0 || nq > ex->nq_max || k > ex->k_max || (size_t)2 * nq * k > ex->slot_words)
+        return fail(err, "score_topk_exchange: list shape [%d,%d] exceeds the exchange's [%d,%d]", nq, k, ex->nq_max, ex->k_max);
+    mb200::RuntimeInfo ri = mb200::runtime_info(rt);
+    if (ri.device != ex->device) return fail(err, "score_topk_exchange: the exchange lives on device %d, the runtime on %d", ex->device, ri.device);
+    const uint32_t epoch = ex->epoch + 1;
+    const int parity = (int)(epoch & 1u);
+    mb200::ExchangeSink sink;
+    for (int r = 0; r < ex->world; ++r) sink.inbox[r] = ex->peer[r];
+    sink.slot_words = ex->slot_words;
+    sink.world = ex->world;
+    sink.rank = ex->rank;
+    sink.parity = parity;
+    sink.epoch = epoch;
+    sink.done = reinterpret_cast<uint32_t*>(ex->inbox + ex->inbox_bytes - 64);
+    // shard pass: the selection kernel stores this rank's lists into every inbox and publishes the epoch
+    if (mb200::score_topk_into_sink(rt, set, metric, order, d_queries, nq, k, sink, err)) return 1;
+    ex->epoch = epoch;
+    // merge: the same workspace, stream-ordered behind the shard pass (world * k <= the shard pass's pool)
+    mb200::SelectWs ws;
+    if (mb200::exchange_select_ws(rt, nq, (uint32_t)(ex->world * k), &ws, err)) return 1;
+    return exchange_merge_tail(rt, ex, ws, order, nq, k, parity, epoch, d_out_ids, d_out_scores, sync, err);
 }
 
 int manta_b200_topk_exchange_merge_device(MantaB200Runtime* rt, MantaB200Exchange* ex, int order, const int32_t* d_ids,

@@ -106,6 +106,18 @@ struct ExchangeSource {
     uint32_t spin_limit = 0; // 200 ns naps before a missing list is reported
 };
 
+// Where a shard's selection also stores its k results: slot [parity][rank] of every rank's exchange inbox (peer
+// stores), followed by the epoch word of that slot once all queries are written.  world == 0: no sink.
+struct ExchangeSink {
+    unsigned char* inbox[16] = {};
+    size_t slot_words = 0;
+    int world = 0;
+    int rank = 0;
+    int parity = 0;
+    uint32_t epoch = 0;
+    uint32_t* done = nullptr;   // device counter of the blocks that have stored their query (returns to 0)
+};
+
 struct SelectArgs {
     SelectWs ws;
     int nq;
@@ -115,6 +127,7 @@ struct SelectArgs {
     int32_t* out_ids;    // [nq][k] or null
     float* out_scores;   // [nq][k] or null
     ExchangeSource src;  // optional: fill the pool from the exchange inbox first
+    ExchangeSink sink;   // optional: also store the results into every rank's inbox
 };
 cudaError_t launch_select(cudaStream_t st, const SelectArgs& a);
 

@@ -113,8 +113,31 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectArgs a)
     for (uint32_t i = tid; i < k; i += blockDim.x) {
         const uint64_t key = (i < n) ? s_keys[i] : 0;
         const bool have = key != 0;
-        if (a.out_ids) a.out_ids[(size_t)q * k + i] = have ? key_id(key) : -1;
-        if (a.out_scores) a.out_scores[(size_t)q * k + i] = have ? (key_goodness(key) * sign + 0.0f) : 0.0f;
+        const int32_t rid = have ? key_id(key) : -1;
+        const float rsc = have ? (key_goodness(key) * sign + 0.0f) : 0.0f;
+        if (a.out_ids) a.out_ids[(size_t)q * k + i] = rid;
+        if (a.out_scores) a.out_scores[(size_t)q * k + i] = rsc;
+        // sharded: the same pair goes straight into every rank's inbox over peer memory
+        for (int r = 0; r < a.sink.world; ++r) {
+            int32_t* dst = reinterpret_cast<int32_t*>(a.sink.inbox[r] + exchange_slot_offset(a.sink.slot_words, a.sink.world, a.sink.parity, a.sink.rank));
+            dst[(size_t)q * k + i] = rid;
+            dst[(size_t)a.nq * k + (size_t)q * k + i] = __float_as_int(rsc);
+        }
+    }
+    if (a.sink.world > 0) {
+        // the block that stores the last query publishes the epoch to every rank
+        __threadfence_system();
+        __syncthreads();
+        if (tid == 0) {
+            const uint32_t prev = atomicAdd(a.sink.done, 1u);
+            if (prev + 1u == (uint32_t)a.nq) {
+                *a.sink.done = 0u;
+                __threadfence_system();
+                for (int r = 0; r < a.sink.world; ++r)
+                    st_release_sys_u32(reinterpret_cast<uint32_t*>(a.sink.inbox[r] + exchange_flag_offset(a.sink.slot_words, a.sink.world, a.sink.parity, a.sink.rank)),
+                                       a.sink.epoch);
+            }
+        }
     }
     if (a.write_back) {
         __syncthreads();  // every read of the pool is done

@@ -37,7 +37,7 @@ EXPORTS = [
     "manta_b200_embed_device", "manta_b200_score_batched", "manta_b200_score_topk_batched",
     "manta_b200_candidates_save", "manta_b200_candidates_load", "manta_b200_packed_file_info",
     "manta_b200_exchange_create", "manta_b200_exchange_connect", "manta_b200_exchange_destroy",
-    "manta_b200_topk_exchange_merge_device",
+    "manta_b200_topk_exchange_merge_device", "manta_b200_score_topk_exchange_device",
 ]
 
 
@@ -98,6 +98,8 @@ def load() -> ctypes.CDLL:
         "manta_b200_exchange_create": [c_void_p, c_int, c_int, c_int, c_int, POINTER(c_void_p), c_void_p, E],
         "manta_b200_exchange_connect": [c_void_p, c_void_p, c_void_p, E],
         "manta_b200_exchange_destroy": [c_void_p, c_void_p, E],
+        "manta_b200_score_topk_exchange_device": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                                                  c_int, E],
         "manta_b200_topk_exchange_merge_device": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, E],
         "manta_b200_candidates_save": [c_void_p, c_void_p, c_char_p, E],
         "manta_b200_candidates_load": [c_void_p, c_char_p, c_int64, c_int64, c_int, POINTER(c_void_p), E],
@@ -244,6 +246,13 @@ class Runtime:
 
     def exchange_destroy(self, ex) -> None:
         call("manta_b200_exchange_destroy", self.handle, ex)
+
+    def score_topk_exchange_device(self, ex, cands: "Candidates", metric: str, d_queries, nq: int, k: int, d_out_ids, d_out_scores,
+                                   smallest: bool = False, sync: bool = False):
+        """Shard pass + exchange over peer memory + merge, one stream-ordered chain."""
+        call("manta_b200_score_topk_exchange_device", self.handle, ex, cands.handle, c_int(METRICS[metric]),
+             c_int(ORDER_SMALLEST if smallest else ORDER_LARGEST), _ptr(d_queries), c_int(nq), c_int(k), _ptr(d_out_ids),
+             _ptr(d_out_scores), c_int(1 if sync else 0))
 
     def topk_exchange_merge_device(self, ex, d_ids, d_scores, nq: int, k: int, d_out_ids, d_out_scores, smallest: bool = False,
                                    sync: bool = False):

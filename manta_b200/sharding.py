@@ -86,6 +86,12 @@ class PeerExchange:
     def merge(self, d_ids, d_scores, nq: int, k: int, d_out_ids, d_out_scores, smallest: bool = False, sync: bool = False):
         self.rt.topk_exchange_merge_device(self.ex, d_ids, d_scores, nq, k, d_out_ids, d_out_scores, smallest=smallest, sync=sync)
 
+    def score_topk_merge(self, cands, metric: str, d_queries, nq: int, k: int, d_out_ids, d_out_scores, smallest: bool = False,
+                         sync: bool = False):
+        """The whole sharded step: this rank's fused pass stores its lists into every inbox, then the merge."""
+        self.rt.score_topk_exchange_device(self.ex, cands, metric, d_queries, nq, k, d_out_ids, d_out_scores, smallest=smallest,
+                                           sync=sync)
+
     def close(self):
         if self.ex is not None:
             self.rt.synchronize()

@@ -40,6 +40,11 @@ def test_single_rank_exchange_equals_direct_pass():
         ex.merge(d_ids, d_sc, 5, k, o_ids, o_sc, sync=True)
         np.testing.assert_array_equal(o_ids.cpu().numpy(), want_ids)
         np.testing.assert_array_equal(o_sc.cpu().numpy(), want_sc)
+    for _ in range(3):  # the fused step: the shard's selection kernel stores into the inbox itself
+        o_ids.zero_()
+        ex.score_topk_merge(cands, "cosine", dq, 5, k, o_ids, o_sc, sync=True)
+        np.testing.assert_array_equal(o_ids.cpu().numpy(), want_ids)
+        np.testing.assert_array_equal(o_sc.cpu().numpy(), want_sc)
     with pytest.raises(native.MantaError, match="exceeds the exchange"):
         ex.merge(d_ids, d_sc, 9, k, o_ids, o_sc, sync=True)
     ex.close()
@@ -81,6 +86,15 @@ for step in range(4):
     ex.merge(d_ids, d_sc, nq, k, o_ids, o_sc, sync=True)
     assert np.array_equal(o_ids.cpu().numpy(), want_ids), (rank, step)
     assert np.array_equal(o_sc.cpu().numpy(), want_sc), (rank, step)
+for step in range(5):  # the fused step, mixed with the two-call form so that epochs and parities interleave
+    o_ids.zero_()
+    ex.score_topk_merge(shard, "cosine", dq, nq, k, o_ids, o_sc, sync=True)
+    assert np.array_equal(o_ids.cpu().numpy(), want_ids), (rank, "fused", step)
+    assert np.array_equal(o_sc.cpu().numpy(), want_sc), (rank, "fused", step)
+    if step == 2:
+        rt.score_topk_device(shard, "cosine", dq, nq, k, d_ids, d_sc, sync=False)
+        ex.merge(d_ids, d_sc, nq, k, o_ids, o_sc, sync=True)
+        assert np.array_equal(o_ids.cpu().numpy(), want_ids), (rank, "mixed")
 ex.close()
 shard.unbind(); whole.unbind(); rt.close()
 dist.destroy_process_group()
