@@ -116,10 +116,15 @@ def build():
          step("score_batch", "return", "return", None, ["scores"])])
     eb = "rerank_candidates_packed_batch"
     mods["retrieval_bundle"] = module("retrieval_bundle", [],
-        [{"name": eb, "kind": "pipeline", "inputs": qb_in + [{"name": "candidate_ids", "type": ttype("i64", ["Q", "N"])}],
+        [{"name": "rerank_candidates_packed", "kind": "pipeline", "inputs": cand_inputs,
+          "outputs": [{"name": "candidates", "type": {"kind": "candidate_pack", "candidate_pack": {"shape": ["2", "D"]}}}]},
+         {"name": eb, "kind": "pipeline", "inputs": qb_in + [{"name": "candidate_ids", "type": ttype("i64", ["Q", "N"])}],
           "outputs": [{"name": "candidates", "type": {"kind": "candidate_pack", "candidate_pack": {"shape": ["Q", "2", "D"]}}}]}],
-        [cos_batch],
-        [step(eb, "launch_kernel", "cosine_batch", ["queries", "docs"], ["scores"], "cosine_batch"),
+        cos + [cos_batch],
+        cand_steps("rerank_candidates_packed") +
+        [step("rerank_candidates_packed", "pack_candidates", "pack_candidates", ["top_candidate_ids", "top_scores", "top_docs"], ["candidates"]),
+         step("rerank_candidates_packed", "return", "return", None, ["candidates"]),
+         step(eb, "launch_kernel", "cosine_batch", ["queries", "docs"], ["scores"], "cosine_batch"),
          step(eb, "topk", "topk", ["scores"], ["top_indices"], None, {"k": "2"}),
          step(eb, "gather", "gather", ["candidate_ids", "top_indices"], ["top_candidate_ids"]),
          step(eb, "gather", "gather", ["scores", "top_indices"], ["top_scores"]),

@@ -280,3 +280,42 @@ def test_batched_abi_errors(rt):
         rt.score_batched("dot", q, np.zeros((2, 3, 5), np.float32))
     with pytest.raises(native.MantaError, match="topk limit 4 out of range for row width 3"):
         rt.score_topk_batched("dot", q, np.zeros((2, 3, 4), np.float32), 4)
+
+
+# ---- manifest-backed serving handles ------------------------------------------------------------------------------
+def test_score_model_score_and_score_batch(rt):
+    # TestScoreModelScore / TestScoreModelScoreBatch, runtime/score_model_test.go:55-131
+    from manta_b200.serving import ScoreManifest, ScoreModel, ServingError
+
+    model = ScoreModel(rt, load("score_bundle"), ScoreManifest(name="score_bundle", entry="score", output_name="scores",
+                                                               batch_entry="score_batch", batch_output_name="scores"))
+    res = model.score([1, 0], [[1, 0], [0, 1]])
+    assert res.output_name == "scores" and res.dtype == "f32"
+    np.testing.assert_allclose(res.scores, [1, 0], atol=TOL)
+    res = model.score_batch([[1, 0], [0, 1]], [[[1, 0], [0, 1], [1, 1]], [[0, 1], [1, 0], [1, 1]]])
+    np.testing.assert_allclose(res.scores, [[1, 0, 0.70710677], [1, 0, 0.70710677]], atol=TOL)
+    with pytest.raises(ServingError, match="doc 1 shape"):
+        model.score([1, 0], [[1, 0], [0, 1, 2]])
+    single = ScoreModel(rt, load("score_bundle"), {"entry": "score"})
+    with pytest.raises(ServingError, match="does not declare a batch entrypoint"):
+        single.score_batch([[1, 0]], [[[1, 0]]])
+    with pytest.raises(ServingError, match='unknown entrypoint "score"'):  # TestLoadScoreValidatesManifest
+        ScoreModel(rt, load("tiny_rerank"), {})
+
+
+def test_retrieval_model_retrieve_and_retrieve_batch(rt):
+    # TestRetrievalModelRetrieve / RetrieveBatch, runtime/retrieval_model_test.go:55-150
+    from manta_b200.serving import RetrievalManifest, RetrievalModel
+
+    model = RetrievalModel(rt, load("retrieval_bundle"), RetrievalManifest(
+        name="retrieval_bundle", output_name="candidates", batch_entry="rerank_candidates_packed_batch", batch_output_name="candidates"))
+    res = model.retrieve([1, 0], [(1001, [1, 0]), (2002, [0, 1]), (3003, [1, 1])])
+    assert len(res.batches) == 1
+    assert [c.id for c in res.batches[0]] == [1001, 3003]
+    np.testing.assert_allclose([c.score for c in res.batches[0]], [1, 0.70710677], atol=TOL)
+    np.testing.assert_allclose(res.batches[0][1].doc, [1, 1], atol=TOL)
+    res = model.retrieve_batch([[1, 0], [0, 1]], [[(1001, [1, 0]), (2002, [0, 1]), (3003, [1, 1])],
+                                                  [(4004, [0, 1]), (5005, [1, 0]), (6006, [1, 1])]])
+    assert len(res.batches) == 2
+    assert res.batches[1][0].id == 4004
+    assert [c.id for c in res.batches[0]] == [1001, 3003]
