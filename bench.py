@@ -350,10 +350,34 @@ def run_ours(args, wl: Workload):
         torch.cuda.synchronize()
 
     # ---- device-resident timing ------------------------------------------------------------------
-    for i in range(max(args.warmup, n_lanes)):
-        step_device(i)
-    for ln in lanes:
-        ln.rt.synchronize()  # raises if a warm-up pass overflowed its pool
+    def warm_up():
+        """Runs the warm-up steps; returns the first error text (None if every lane finished cleanly)."""
+        problem = None
+        for i in range(max(args.warmup, n_lanes)):
+            step_device(i)
+        for ln in lanes:
+            try:
+                ln.rt.synchronize()  # raises if a warm-up pass overflowed its pool or a peer's list never arrived
+            except native.MantaError as exc:
+                problem = problem or str(exc)
+        return problem
+
+    problem = warm_up()
+    if world > 1 and any(ln.px is not None for ln in lanes):
+        # If the peer exchange misbehaved on ANY rank, every rank drops it and the run continues over NCCL.
+        bad = torch.tensor([1 if problem else 0], dtype=torch.int32, device="cuda")
+        dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+        if int(bad.item()):
+            for ln in lanes:
+                try:
+                    ln.px.close()
+                except native.MantaError:
+                    pass
+                ln.px = None
+            args.exchange = "nccl (the peer exchange failed during warm-up: %s)" % (problem or "on another rank")
+            problem = warm_up()
+    if problem:
+        raise SystemExit("bench.py: warm-up failed: " + problem)
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()

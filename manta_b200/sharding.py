@@ -93,9 +93,18 @@ class PeerExchange:
                                            sync=sync)
 
     def close(self):
-        if self.ex is not None:
+        """Every rank reaches the barrier and releases its inbox even when its last pass reported an error (the
+        error is raised afterwards), so a failing rank cannot strand the others."""
+        if self.ex is None:
+            return
+        pending = None
+        try:
             self.rt.synchronize()
-            if self.world > 1:
-                self.dist.barrier()  # no rank unmaps an inbox a peer may still store into
-            self.rt.exchange_destroy(self.ex)
-            self.ex = None
+        except Exception as exc:  # reported below, after the collective part
+            pending = exc
+        if self.world > 1:
+            self.dist.barrier()  # no rank unmaps an inbox a peer may still store into
+        self.rt.exchange_destroy(self.ex)
+        self.ex = None
+        if pending is not None:
+            raise pending
