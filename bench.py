@@ -411,6 +411,31 @@ def run_ours(args, wl: Workload):
     final_ids = (last.m_ids if world > 1 else last.d_ids).cpu().numpy().copy()
     stats_device = rt.stats()
 
+    # ---- sharded runs over the peer exchange check themselves against the NCCL path (one extra, untimed step) -------
+    exchange_verified = None
+    if world > 1 and lanes[0].px is not None:
+        ln = lanes[0]
+        step_no = args.steps + 7
+        dq_chk = None
+        if wl.embed:
+            ln.rt.embed_device(emb, d_tokens[step_no % nsets], d_mask[step_no % nsets], nq, wl.embed[2], ln.d_q, sync=False)
+            dq_chk = ln.d_q
+        else:
+            dq_chk = d_queries[step_no % nsets]
+        ln.px.score_topk_merge(cands, wl.metric, dq_chk, nq, k, ln.m_ids, ln.m_scores, smallest=wl.smallest, sync=True)
+        peer_ids, peer_scores = ln.m_ids.cpu().numpy().copy(), ln.m_scores.cpu().numpy().copy()
+        ln.rt.score_topk_device(cands, wl.metric, dq_chk, nq, k, ln.d_ids, ln.d_scores, smallest=wl.smallest, sync=False)
+        with torch.cuda.stream(ln.stream):
+            sharding.gather_pairs(ln.d_pair, ln.g_pair, dist)
+        ln.rt.topk_merge_device(ln.g_ids, ln.g_scores, world, nq, k, ln.m_ids, ln.m_scores, smallest=wl.smallest, sync=True,
+                                list_stride=ln.g_stride)
+        same = bool(np.array_equal(peer_ids, ln.m_ids.cpu().numpy()) and np.array_equal(peer_scores, ln.m_scores.cpu().numpy()))
+        flag = torch.tensor([1 if same else 0], dtype=torch.int32, device="cuda")
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        exchange_verified = bool(int(flag.item()))
+        if not exchange_verified:
+            raise SystemExit("bench.py: the peer exchange and the NCCL path disagree on the merged top-k")
+
     # ---- end to end through the host-buffer ABI call ------------------------------------------------
     hb = {}  # pinned host / staging buffers of the sharded end-to-end step (released before the streams they used)
     if world > 1:
@@ -511,7 +536,7 @@ def run_ours(args, wl: Workload):
             "data": "synthetic",
             "config": {"workload": wl.describe(), "rows": wl.rows, "cols": wl.cols, "k": k, "queries_per_step": nq,
                        "layout": wl.layout, "shards": world, "note": wl.note, "lanes": n_lanes,
-                       "exchange": (args.exchange if world > 1 else None),
+                       "exchange": (args.exchange if world > 1 else None), "exchange_equals_nccl_path": exchange_verified,
                        "l2": f"inputs larger than L2: {algo_bytes / 1e9:.3f} GB scanned per pass and GPU" if algo_bytes > 2.5e8
                              else "inputs smaller than L2 (latency-bound configuration, not a roofline point)"},
             "candidates_dim_per_s": value * wl.rows * wl.cols,
