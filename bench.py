@@ -7,8 +7,8 @@ Default workload `c3` is the configuration the headline metric is quoted on: q8 
 768 (int8 codes + one f32 scale per row, 7.72 GB), one f16 query per step, k = 10.  A step is one pass of the
 hot path over all candidates for one query batch.  With N GPUs the rows are sharded (strong scaling: the rows
 are split), each rank scans its shard and the per-shard lists are all-gathered (NCCL) and merged on every rank.
-Other workloads (`--workload`) are the remaining configurations of the survey, used for profiles and parity at
-size; they print the same JSON line.
+Other workloads (`--workload`) are the remaining benchmark configurations (batched f16 dot, q8 at query batch 256,
+q4 l2 nearest neighbours, embed + score), used for profiles and parity at size; they print the same JSON line.
 
 Prints ONE JSON line.  `value` is measured with candidates and queries resident in HBM (CUDA events on the
 launching stream, max over ranks); `e2e` goes through the host-buffer C-ABI call (queries copied H2D from pinned
@@ -212,8 +212,9 @@ def cpu_reference_pass(wl: Workload, sample_rows: int, threads: int, steps: int,
 
 
 def _sample_rows_for(wl: Workload) -> int:
-    # about 1 GB of f32 rows, at most the whole set; the timed CPU work stays in the 10-30 s range
-    return int(min(wl.rows, max(10_000, 250_000_000 // wl.cols // max(1, wl.nq // 4))))
+    # about 1 GB of f32 rows for small batches, never fewer than 100,000 rows (the parity spot check runs on the same
+    # sample), at most the whole set; the timed CPU work stays in the 10-30 s range
+    return int(min(wl.rows, max(100_000, 250_000_000 // wl.cols // max(1, wl.nq // 4))))
 
 
 def run_reference(args, wl: Workload):
@@ -226,20 +227,29 @@ def run_reference(args, wl: Workload):
     sample_rows = _sample_rows_for(wl)
     nsets = max(1, min(N_QUERY_SET, 4096 // wl.nq))
     t0 = time.perf_counter()
+    # every step is one pass over the bounded sample; the run is capped so that it ends within a few minutes
     steps = max(1, min(args.steps, 10))
-    qps, sec, _ = cpu_reference_pass(wl, sample_rows, threads, steps, min(args.warmup, 1), nsets)
+    warm = max(1, min(args.warmup, 2))
+    qps, sec, _ = cpu_reference_pass(wl, sample_rows, threads, steps, warm, nsets)
+    factor = wl.rows / sample_rows
     line = {
         "impl": "reference", "metric": METRIC_NAME if wl.name == "c3" else f"{wl.describe()} queries/s",
-        "value": qps, "unit": "queries/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "value": qps, "unit": "queries/s", "n_gpus": args.gpus, "steps": steps, "warmup": warm,
+        "steps_requested": args.steps, "warmup_requested": args.warmup,
         "ms_per_step": wl.nq / qps * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f64 accumulate / f32 result" if wl.metric != "dot" else "f32",
         "data": "synthetic",
-        "config": {"workload": wl.describe() + " (reference f32 layout, host cores)", "rows": wl.rows, "cols": wl.cols,
-                   "k": wl.k, "queries_per_step": wl.nq},
+        "config": {"workload": wl.describe(), "rows": wl.rows, "cols": wl.cols, "k": wl.k, "queries_per_step": wl.nq,
+                   "layout": "f32 rows as the reference holds them (the same values the packed set de-quantises to)",
+                   "where": "host cores"},
+        "extrapolated": factor != 1.0, "extrapolation_factor": factor, "sample_rows": sample_rows,
+        "sample_seconds_per_pass": sec, "sample_ms_per_step_measured": sec * 1e3,
         "cpu_baseline": {"value": qps, "unit": "queries/s", "cores": threads, "kind": "port",
-                         "sample": f"{sample_rows} of {wl.rows} rows per step as f32, {steps} timed steps, score builtin + "
-                                   f"full-sort topKTensor restated in C with OpenMP over rows; queries/s extrapolated "
-                                   f"x{wl.rows / sample_rows:g}; the Go toolchain is unavailable so the reference itself cannot run"},
+                         "sample": f"{sample_rows} of {wl.rows} rows per step as f32, {steps} timed steps after {warm} warm-up "
+                                   f"(at most 10 / 2 whatever was asked, to stay within minutes), {sec:.3f} s measured per "
+                                   f"sample pass; score builtin + full-sort topKTensor restated in C with OpenMP over rows; "
+                                   f"queries/s and ms_per_step extrapolated x{factor:g} to the full row count; the Go "
+                                   f"toolchain is unavailable so the reference itself cannot run"},
         "e2e": {"value": qps, "unit": "queries/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0, "oracle_threads": oracle.num_threads(), "wall_s": time.perf_counter() - t0,
     }
@@ -381,33 +391,62 @@ def run_ours(args, wl: Workload):
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    rt.profile(True)
+    # The scan kernel is timed by CUDA events inside the timed region when one lane runs; with two lanes the lanes'
+    # kernels overlap, so the per-kernel time is taken from a single-lane pass after the timed region instead.
+    profile_inside = n_lanes == 1
+    if profile_inside:
+        rt.profile(True)
     barrier()  # after the sampler's start-up delay, so that all ranks enter the timed region together
     launches0 = native.kernel_launch_count()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_begin = time.perf_counter()
-    ev0.record(stream)
-    for i in range(args.steps):
-        step_device(i)
-    for ln in lanes[1:]:  # the closing event waits for every lane
-        done = torch.cuda.Event()
-        done.record(ln.stream)
-        stream.wait_event(done)
-    ev1.record(stream)
-    barrier()
+    repeat_ms = []
+    launches = 0
+    for rep in range(max(1, args.repeats)):
+        # one repeat = exactly `steps` steps between a barrier + synchronize on both sides, CUDA events on the stream
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record(stream)
+        for i in range(args.steps):
+            step_device(rep * args.steps + i)
+        for ln in lanes[1:]:  # the closing event waits for every lane
+            done = torch.cuda.Event()
+            done.record(ln.stream)
+            stream.wait_event(done)
+        ev1.record(stream)
+        barrier()
+        for ln in lanes:
+            ln.rt.synchronize()
+        if rep == 0:
+            launches = native.kernel_launch_count() - launches0
+        repeat_ms.append(ev0.elapsed_time(ev1))
     t_end = time.perf_counter()
-    for ln in lanes:
-        ln.rt.synchronize()
-    launches = native.kernel_launch_count() - launches0
-    total_ms = ev0.elapsed_time(ev1)
-    scan_ms, scan_passes = rt.scan_time()
+    scan_ms, scan_passes = rt.scan_time() if profile_inside else (0.0, 0)
     rt.profile(False)
     clocks = sampler.stop(t_begin, t_end) if rank == 0 else None
-    t = torch.tensor([total_ms, scan_ms / max(scan_passes, 1)], dtype=torch.float64, device="cuda")
+    if not profile_inside:
+        lanes[0].rt.profile(True)
+        for i in range(min(args.steps, 20)):
+            ln = lanes[0]
+            if wl.embed:
+                ln.rt.embed_device(emb, d_tokens[i % nsets], d_mask[i % nsets], nq, wl.embed[2], ln.d_q, sync=False)
+            dq1 = ln.d_q if wl.embed else d_queries[i % nsets]
+            if ln.px is not None:
+                ln.px.score_topk_merge(cands, wl.metric, dq1, nq, k, ln.m_ids, ln.m_scores, smallest=wl.smallest, sync=False)
+            else:
+                ln.rt.score_topk_device(cands, wl.metric, dq1, nq, k, ln.d_ids, ln.d_scores, smallest=wl.smallest, sync=False)
+                ln.merge(False)
+        scan_ms, scan_passes = lanes[0].rt.scan_time()
+        lanes[0].rt.profile(False)
+        barrier()
+    t = torch.tensor(repeat_ms + [scan_ms / max(scan_passes, 1)], dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    total_ms, scan_ms_per_pass = float(t[0]), float(t[1])
-    last = lanes[(args.steps - 1) % n_lanes]
+    repeat_ms = [float(x) for x in t[:-1]]
+    scan_ms_per_pass = float(t[-1])
+    # the value comes from the median repeat (each repeat is `steps` steps, max over ranks)
+    order_ms = sorted(repeat_ms)
+    total_ms = order_ms[len(order_ms) // 2]
+    total_steps = args.steps * len(repeat_ms)
+    last = lanes[(total_steps - 1) % n_lanes]
     final_ids = (last.m_ids if world > 1 else last.d_ids).cpu().numpy().copy()
     stats_device = rt.stats()
 
@@ -415,7 +454,7 @@ def run_ours(args, wl: Workload):
     exchange_verified = None
     if world > 1 and lanes[0].px is not None:
         ln = lanes[0]
-        step_no = args.steps + 7
+        step_no = total_steps + 7
         dq_chk = None
         if wl.embed:
             ln.rt.embed_device(emb, d_tokens[step_no % nsets], d_mask[step_no % nsets], nq, wl.embed[2], ln.d_q, sync=False)
@@ -497,13 +536,13 @@ def run_ours(args, wl: Workload):
         sample_rows = _sample_rows_for(wl)
         threads = os.cpu_count() or 1
         qps, sec, ref_ids = cpu_reference_pass(wl, sample_rows, threads, 3, 1, nsets)
-        qps1, sec1, _ = cpu_reference_pass(wl, sample_rows, 1, 1, 0, nsets)
+        qps1 = cpu_reference_pass(wl, sample_rows, 1, 1, 0, nsets)[0] if nq <= 4 else None  # bounded: small batches only
         cpu = {"value": qps, "unit": "queries/s", "cores": threads, "kind": "port",
                "sample": f"first {sample_rows} of {wl.rows} rows as f32 per pass, 3 timed passes after 1 warm-up, "
                          f"C restatement of the score builtin + full-sort topKTensor with OpenMP over rows; queries/s "
                          f"extrapolated x{wl.rows / sample_rows:g}; single thread (the reference's own threading): "
-                         f"{qps1:.4f} queries/s",
-               "single_thread_value": qps1, "sample_seconds_per_pass": sec}
+                         + (f"{qps1:.4f} queries/s" if qps1 is not None else "not timed for this batch size"),
+               "single_thread_value": qps1, "sample_seconds_per_pass": sec, "extrapolated": wl.rows != sample_rows}
         sub = rt.bind(wl.layout, data[:sample_rows], None if scales is None else scales[:sample_rows], row_base=0,
                       rows=sample_rows, cols=wl.cols)
         kk = min(k, sample_rows)
@@ -511,8 +550,21 @@ def run_ours(args, wl: Workload):
             ids, sc = rt.embed_score_topk(emb, sub, h_tokens[1], h_mask[1], wl.metric, kk, smallest=wl.smallest)
         else:
             ids, sc = rt.score_topk(sub, wl.metric, h_queries[(1 + 3 - 1) % nsets], kk, smallest=wl.smallest)
-        same = (np.asarray(ids).reshape(nq, kk) == ref_ids.reshape(nq, kk))
-        parity = {"sample_rows": sample_rows, "ids_equal_oracle": bool(same.all()), "ids_equal_fraction": float(same.mean())}
+        # the comparison rule of tests/helpers.py: ids equal to topKTensor's except across score gaps below twice the
+        # tolerance, returned scores within tolerance of the oracle's
+        sys.path.insert(0, os.path.join(ROOT, "tests"))
+        from helpers import FLOOR, REL_TOL, topk_parity_report
+
+        docs_f32, q_sets = _cpu_sample(wl, sample_rows, nsets)
+        if wl.embed:
+            table, proj, tokens, mask = q_sets
+            q_chk = oracle.half_to_float(oracle.float_to_half(oracle.embed_pooled(table, proj, tokens[1], mask[1], 0)))
+        else:
+            q_chk = q_sets[(1 + 3 - 1) % nsets]
+        parity = topk_parity_report(wl.metric, q_chk, docs_f32, np.asarray(ids).reshape(nq, kk), np.asarray(sc).reshape(nq, kk), kk,
+                                    wl.smallest)
+        parity.update({"sample_rows": sample_rows, "rel_tol": REL_TOL, "floor": FLOOR,
+                       "ids_equal_fraction": float((np.asarray(ids).reshape(nq, kk) == ref_ids.reshape(nq, kk)).mean())})
         sub.unbind()
 
     if rank == 0:
@@ -520,17 +572,22 @@ def run_ours(args, wl: Workload):
         shard_rows = r1 - r0
         algo_bytes = shard_rows * wl.row_bytes()
         achieved = algo_bytes / (scan_ms_per_pass * 1e-3) / 1e9
-        # DRAM traffic per launch from the committed ncu capture of the same kernel on a 2 M-row case
-        # (the summary under profiles/ for q8 cosine 2M x 768: dram__bytes_read+write = 1.5477e9 B for 2e6 rows), scaled by rows;
-        # traffic grows in proportion because every row is read exactly once.
-        traffic = None
+        # DRAM traffic per launch is not read live: it is the dram__bytes_read + dram__bytes_write of one ncu capture of
+        # the same kernel on a 2 M-row case (1.5480e9 B for 2e6 rows), scaled by rows -- every row is read exactly once,
+        # so traffic grows in proportion.
+        traffic, traffic_source = None, None
         if wl.layout == "q8" and wl.metric == "cosine" and wl.cols == 768 and nq <= 4:
             traffic = shard_rows * (1.544046e9 + 3.98e6) / 2e6
+            traffic_source = "from_profile: profiles/stream_scan_q8_cosine_2Mx768.md (ncu, 2 M rows), scaled by rows; not measured in this run"
         value = args.steps * nq / (total_ms * 1e-3)
         line = {
             "metric": METRIC_NAME if wl.name == "c3" else f"{wl.describe()} queries/s",
             "value": value, "unit": "queries/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "ms_per_step": total_ms / args.steps,
+            "repeats": {"count": len(repeat_ms), "ms_per_step": [x / args.steps for x in repeat_ms],
+                        "median_ms_per_step": total_ms / args.steps, "min_ms_per_step": min(repeat_ms) / args.steps,
+                        "max_ms_per_step": max(repeat_ms) / args.steps,
+                        "note": "each repeat times exactly `steps` steps between barriers; value is the median repeat"}, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": {"q8": "int8 x int8 -> int32 (two int8 query planes), f32 epilogue",
                       "q4": "int4 x int8 -> int32 per block, f32 across blocks", "f16": "f16 x f16 -> f32"}[wl.layout],
             "data": "synthetic",
@@ -541,15 +598,18 @@ def run_ours(args, wl: Workload):
                              else "inputs smaller than L2 (latency-bound configuration, not a roofline point)"},
             "candidates_dim_per_s": value * wl.rows * wl.cols,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": traffic, "peak_source": peak_src,
-                         "kernel": "tcgen05 scan (mma.cu)" if stats_device["mma_passes"] else "gemv_kernel (gemv.cuh)",
-                         "kernel_ms": scan_ms_per_pass, "algorithmic_bytes_per_launch": algo_bytes,
+                         "traffic": traffic, "traffic_source": traffic_source, "peak_source": peak_src,
+                         "kernel": "mma_scan_kernel (mma.cu, tcgen05)" if stats_device["mma_passes"] else "stream_scan_kernel (stream_scan.cuh)",
+                         "kernel_ms": scan_ms_per_pass,
+                         "kernel_ms_source": "CUDA events around the scan kernel inside the timed region" if profile_inside else
+                                             "CUDA events around the scan kernel in a single-lane pass after the timed region (two lanes overlap inside it)", "algorithmic_bytes_per_launch": algo_bytes,
                          "frac_of_nominal_8TBs": achieved / 8000.0},
             "e2e": {"value": args.steps * nq / e2e_s, "unit": "queries/s", "h2d_bytes_per_step": (2 * nq * wl.embed[2] * 4) if wl.embed else nq * wl.cols * 2,
                     "d2h_bytes_per_step": nq * k * 8, "ms_per_step": e2e_s / args.steps * 1e3,
                     "note": "host-buffer C-ABI call per step; candidates stay bound (resident) as plan parameters"
                             if world == 1 else "inputs from pinned host memory, results to pinned host memory, one synchronisation per "
-                            "step (upload, shard pass, NCCL all-gather, merge, download on one stream)"},
+                            "step (upload, shard pass, " + ("peer-store exchange fused with the merge" if str(args.exchange) == "peer"
+                                                            else "NCCL all-gather, merge") + ", download on one stream)"},
             "gpu_launches": int(launches), "clocks": clocks, "cpu_baseline": cpu, "parity_check": parity,
             "result_checksum": int(np.asarray(final_ids, dtype=np.int64).sum()),
             "stats": rt.stats(),
@@ -590,6 +650,7 @@ def main():
     ap.add_argument("--exchange", default="peer", choices=["nccl", "peer"],
                     help="sharded runs: how the per-shard lists meet (NCCL all-gather + merge, or peer stores over NVLink fused "
                          "with the merge)")
+    ap.add_argument("--repeats", type=int, default=5, help="timed repeats of `steps` steps; the value is the median repeat")
     ap.add_argument("--lanes", type=int, default=0,
                     help="runtimes alternating steps (0: one on a single GPU, two when sharded so that merge and scan overlap)")
     args = ap.parse_args()

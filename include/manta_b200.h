@@ -193,6 +193,17 @@ int manta_b200_exchange_create(MantaB200Runtime* rt, int world, int rank, int nq
                                unsigned char* handle_out /* 64 bytes */, char** err);
 int manta_b200_exchange_connect(MantaB200Runtime* rt, MantaB200Exchange* ex, const unsigned char* handles /* world x 64 */,
                                 char** err);
+/* Same for ranks that live in ONE process (one process driving several GPUs, or several exchanges on one GPU): takes
+ * the ranks' exchange handles (ranks[r] for every r != own rank) instead of IPC handles; peer access between the
+ * devices is enabled when they differ. */
+int manta_b200_exchange_connect_local(MantaB200Runtime* rt, MantaB200Exchange* ex, MantaB200Exchange* const* ranks, char** err);
+/* How long a merge waits for a list that has not arrived, in naps of 200 ns (default 10,000,000: about two seconds). */
+int manta_b200_exchange_set_wait_limit(MantaB200Exchange* ex, uint32_t naps_200ns, char** err);
+/* Tear-down is two steps with a host barrier between them: EVERY rank first disconnects (synchronises its stream and
+ * unmaps the peers' inboxes), the ranks meet at a barrier, and only then does each rank destroy its exchange, which
+ * frees its own inbox.  Freeing an inbox a peer still has mapped is undefined behaviour of CUDA IPC.  destroy on an
+ * exchange that was never disconnected unmaps first (correct for a single rank, and for peers known to be gone). */
+int manta_b200_exchange_disconnect(MantaB200Runtime* rt, MantaB200Exchange* ex, char** err);
 int manta_b200_exchange_destroy(MantaB200Runtime* rt, MantaB200Exchange* ex, char** err);
 /* The whole sharded step on the runtime's stream: fused score + top-k over this rank's shard whose selection kernel
  * stores the lists straight into every rank's inbox (peer stores) and publishes the epoch, then the merge whose

@@ -27,6 +27,7 @@ struct MantaB200Exchange {
     unsigned char* peer[kMaxWorld] = {};      // every rank's inbox as mapped into this process (peer[rank] == inbox)
     bool opened[kMaxWorld] = {};
     uint32_t epoch = 0;
+    uint32_t spin_limit = 10000000u;   // 200 ns naps a merge waits for a missing list: about two seconds
     bool connected = false;
 };
 
@@ -134,18 +135,72 @@ int manta_b200_exchange_connect(MantaB200Runtime* rt, MantaB200Exchange* ex, con
     return 0;
 }
 
-int manta_b200_exchange_destroy(MantaB200Runtime* rt, MantaB200Exchange* ex, char** err) {
+int manta_b200_exchange_connect_local(MantaB200Runtime* rt, MantaB200Exchange* ex, MantaB200Exchange* const* ranks, char** err) {
+    if (!rt || !ex || !ranks) return fail(err, "exchange_connect_local: NULL argument");
+    mb200::RuntimeInfo ri = mb200::runtime_info(rt);
+    std::lock_guard<std::mutex> lk(*ri.mu);
+    for (int r = 0; r < ex->world; ++r) {
+        if (r == ex->rank) continue;
+        const MantaB200Exchange* other = ranks[r];
+        if (!other || !other->inbox) return fail(err, "exchange_connect_local: rank %d has no exchange", r);
+        if (other->world != ex->world || other->rank != r || other->slot_words != ex->slot_words)
+            return fail(err, "exchange_connect_local: rank %d's exchange was created with another shape", r);
+        if (other->device != ex->device) {
+            int can = 0;
+            cudaError_t e = cudaDeviceCanAccessPeer(&can, ex->device, other->device);
+            if (e != cudaSuccess || !can) return fail(err, "exchange_connect_local: device %d cannot store into device %d's memory", ex->device, other->device);
+            e = cudaSetDevice(ex->device);
+            if (e == cudaSuccess) e = cudaDeviceEnablePeerAccess(other->device, 0);
+            if (e == cudaErrorPeerAccessAlreadyEnabled) {
+                cudaGetLastError();
+                e = cudaSuccess;
+            }
+            if (e != cudaSuccess) return fail(err, "exchange_connect_local: %s", cudaGetErrorString(e));
+        }
+        ex->peer[r] = other->inbox;   // same address space: no IPC mapping, nothing to close later
+    }
+    ex->connected = true;
+    return 0;
+}
+
+int manta_b200_exchange_set_wait_limit(MantaB200Exchange* ex, uint32_t naps_200ns, char** err) {
+    if (!ex) return fail(err, "exchange_set_wait_limit: NULL exchange");
+    if (naps_200ns == 0) return fail(err, "exchange_set_wait_limit: the limit must be positive");
+    ex->spin_limit = naps_200ns;
+    return 0;
+}
+
+int manta_b200_exchange_disconnect(MantaB200Runtime* rt, MantaB200Exchange* ex, char** err) {
     if (!ex) return 0;
-    if (!rt) return fail(err, "exchange_destroy: NULL runtime");
+    if (!rt) return fail(err, "exchange_disconnect: NULL runtime");
     mb200::RuntimeInfo ri = mb200::runtime_info(rt);
     std::lock_guard<std::mutex> lk(*ri.mu);
     cudaSetDevice(ri.device);
-    cudaStreamSynchronize(ri.stream);
-    for (int r = 0; r < ex->world; ++r)
-        if (ex->opened[r]) cudaIpcCloseMemHandle(ex->peer[r]);
+    cudaError_t e = cudaStreamSynchronize(ri.stream);
+    for (int r = 0; r < ex->world; ++r) {
+        if (ex->opened[r]) {
+            cudaError_t c = cudaIpcCloseMemHandle(ex->peer[r]);
+            if (e == cudaSuccess) e = c;
+            ex->opened[r] = false;
+        }
+        if (r != ex->rank) ex->peer[r] = nullptr;
+    }
+    ex->connected = false;
+    if (e != cudaSuccess) return fail(err, "exchange_disconnect: %s", cudaGetErrorString(e));
+    return 0;
+}
+
+int manta_b200_exchange_destroy(MantaB200Runtime* rt, MantaB200Exchange* ex, char** err) {
+    if (!ex) return 0;
+    if (!rt) return fail(err, "exchange_destroy: NULL runtime");
+    // unmaps whatever is still mapped (a caller that skipped the disconnect step), then frees this rank's inbox
+    int rc = manta_b200_exchange_disconnect(rt, ex, err);
+    mb200::RuntimeInfo ri = mb200::runtime_info(rt);
+    std::lock_guard<std::mutex> lk(*ri.mu);
+    cudaSetDevice(ri.device);
     if (ex->inbox) cudaFree(ex->inbox);
     delete ex;
-    return 0;
+    return rc;
 }
 
 // Waits for the lists of this epoch and selects (shared by the two entry points below); the caller holds nothing.
@@ -167,7 +222,7 @@ static int exchange_merge_tail(MantaB200Runtime* rt, MantaB200Exchange* ex, cons
     sa.src.world = ex->world;
     sa.src.parity = parity;
     sa.src.epoch = epoch;
-    sa.src.spin_limit = 10000000u;   // about two seconds of 200 ns naps before a missing list is reported
+    sa.src.spin_limit = ex->spin_limit;   // 200 ns naps before a missing list is reported
     e = mb200::launch_select(ri.stream, sa);
     if (e != cudaSuccess) return fail(err, "topk_exchange_merge: select launch failed: %s", cudaGetErrorString(e));
     int rc = 0;
@@ -239,7 +294,7 @@ int manta_b200_topk_exchange_merge_device(MantaB200Runtime* rt, MantaB200Exchang
     sa.src.world = ex->world;
     sa.src.parity = parity;
     sa.src.epoch = epoch;
-    sa.src.spin_limit = 10000000u;   // about two seconds of 200 ns naps before a missing list is reported
+    sa.src.spin_limit = ex->spin_limit;   // 200 ns naps before a missing list is reported
     e = mb200::launch_select(ri.stream, sa);
     if (e != cudaSuccess) return fail(err, "topk_exchange_merge: select launch failed: %s", cudaGetErrorString(e));
     int rc = 0;

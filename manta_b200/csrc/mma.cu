@@ -148,7 +148,6 @@ struct KernelArgs {
     int observe_tiles;            // tiles per CTA scored before the first bound exists (replayed at the end)
     int64_t row_begin;
     int64_t row_end;
-    unsigned long long* dbg;      // debugging: cycle counts of one epilogue warp (null in normal use)
 };
 
 // Scores of N consecutive queries for one candidate row (one lane).  METRIC is a compile-time constant so that
@@ -245,7 +244,6 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    const long long t_start = (a.dbg != nullptr) ? clock64() : 0;
     auto tile_of = [&](int it) { return cta + ((it < n_my) ? it : it - n_my) * grid; };
 
     if (n_my > 0) {
@@ -321,18 +319,13 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             // every (metric, order) has a pre-filter except "largest l2 distance", which takes the exact path throughout
             constexpr bool kL2 = METRIC == MANTA_B200_METRIC_L2_DISTANCE;
             const bool cheap = !(kL2 && a.order == MANTA_B200_ORDER_LARGEST);
-            unsigned long long c_wait = 0, c_ld = 0, c_math = 0, c_slow = 0, c_house = 0, n_slow = 0, c_thr = 0;
-            const bool timing = a.dbg != nullptr && cta == 0 && warp == 4;
-            (void)c_ld; (void)c_slow;
             for (int it = 0; it < n_iters; ++it) {
-                long long t0 = timing ? clock64() : 0;
                 const bool observe = it < n_obs;            // score and record maxima only
                 const bool replay = it >= n_my;             // append only
                 if (a.filtered && it == n_obs && n_obs > 0) {
                     // the first bounds must exist before anything is appended (bounded wait on the refresher)
                     for (uint32_t spin = 0; spin < 40000u && !*thr_ready_s && !*abort_s; ++spin) __nanosleep(100);
                 }
-                if (timing) { long long t1 = clock64(); c_thr += t1 - t0; t0 = t1; }
                 const int acc = it & 1;
                 // row constants of this tile (issued before the wait so their latency hides behind it)
                 const int64_t row = a.row_begin + (int64_t)tile_of(it) * kTileRows + quad * 32 + lane;
@@ -345,8 +338,6 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 if (METRIC == MANTA_B200_METRIC_COSINE) rinv = I8 ? q8_row_inv_norm((int)stat) : float_row_inv_norm(__uint_as_float(stat));
                 if (!mbar_wait(&tfull[acc], (uint32_t)(it >> 1) & 1u, abort_s)) break;
                 tc_fence_after();
-                if (timing && it == 0 && lane == 0) a.dbg[11] = (unsigned long long)(clock64() - t_start);   // first accumulator ready
-                if (timing) { long long t1 = clock64(); c_wait += t1 - t0; t0 = t1; }
                 const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)acc * kMmaCols;
                 const int32_t my_id = (int32_t)(a.cv.row_base + row);
                 // row factor of the pre-filter; NaN for rows past the end makes every comparison false
@@ -421,7 +412,6 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         groups = ((hit & 0x000Fu) ? 1u : 0u) | ((hit & 0x00F0u) ? 2u : 0u) | ((hit & 0x0F00u) ? 4u : 0u) |
                                  ((hit & 0xF000u) ? 8u : 0u);
                     }
-                    n_slow++;
                     {
                         // The accumulators of a group that passed are re-read four queries at a time instead of keeping
                         // sixteen finished scores live: the epilogue stays under 104 registers, which is what lets four
@@ -449,7 +439,6 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         }
                     }
                 }
-                if (timing) { long long t1 = clock64(); c_math += t1 - t0; t0 = t1; }
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&tempty[acc]);
@@ -476,11 +465,6 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         if (lane == 0) atomicAdd(a.ready, 1u);
                     }
                 }
-                if (timing) { long long t1 = clock64(); c_house += t1 - t0; t0 = t1; }
-            }
-            if (timing && lane == 0) {
-                a.dbg[0] = c_thr; a.dbg[1] = c_wait; a.dbg[2] = c_ld; a.dbg[3] = c_math; a.dbg[4] = c_slow; a.dbg[5] = c_house;
-                a.dbg[6] = n_slow; a.dbg[7] = (unsigned long long)n_iters;
             }
             __syncwarp();
             if (lane == 0) atomicAdd((uint32_t*)done_s, 1u);
@@ -495,7 +479,6 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 seen = ld_relaxed_u32(a.ready);
                 if (seen < want) __nanosleep(64);
             }
-            if (a.dbg != nullptr && cta == 0 && lane == 0) a.dbg[8] = (unsigned long long)(clock64() - t_start);   // all CTAs published
             const uint32_t nb = min(a.ws.nb, (uint32_t)kRefStage);
             for (uint32_t round = 0; *done_s < (uint32_t)kEpiWarps && !*abort_s; ++round) {
                 const int j = (int)(((uint64_t)cta + (uint64_t)round * grid) % (uint64_t)a.qn);
@@ -520,7 +503,6 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 #pragma unroll
                         for (int u = 0; u < 5; ++u) m[u0 + u] = max(max(tmp[u].x, tmp[u].y), max(tmp[u].z, tmp[u].w));
                     }
-                    if (a.dbg != nullptr && cta == 0 && lane == 0 && round == 0) a.dbg[12] = (unsigned long long)(clock64() - t_start);
                     for (int bit = 31; bit >= 12; --bit) {
                         const uint32_t cand = t | (1u << bit);
                         uint32_t c0 = 0, c1 = 0, c2 = 0, c3 = 0;
@@ -548,7 +530,6 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         if (cnt >= (uint32_t)a.k) t = cand;
                     }
                 }
-                if (a.dbg != nullptr && cta == 0 && lane == 0 && round == 0) a.dbg[13] = (unsigned long long)(clock64() - t_start);
                 if (lane == 0 && t != 0) atomicMax(a.ws.thr + a.q0 + j, t);
                 __syncwarp();
                 bool allset = true;
@@ -593,14 +574,7 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     zq_s[jj] = c;
                 }
                 allset = __all_sync(0xffffffffu, allset);
-                if (a.dbg != nullptr && cta == 0 && lane == 0 && round == 0) a.dbg[14] = (unsigned long long)(clock64() - t_start);
-                if (allset && lane == 0) {
-                    if (a.dbg != nullptr && cta == 0 && !*thr_ready_s) {
-                        a.dbg[9] = (unsigned long long)(clock64() - t_start);   // first complete set of bounds
-                        a.dbg[10] = round;
-                    }
-                    *thr_ready_s = 1u;
-                }
+                if (allset && lane == 0) *thr_ready_s = 1u;
                 if (round > (uint32_t)(4 * a.qn)) __nanosleep(1000);   // steady state: refresh at a relaxed pace
             }
         }
@@ -648,7 +622,6 @@ struct MmaState {
     unsigned char* d_b = nullptr;     // operand B staging
     size_t d_b_bytes = 0;
     uint32_t* d_ready = nullptr;
-    unsigned long long* d_dbg = nullptr;
     bool attr_set[12] = {};
 };
 
@@ -672,7 +645,6 @@ void mma_state_destroy(MmaState* s) {
     if (!s) return;
     if (s->d_b) cudaFree(s->d_b);
     if (s->d_ready) cudaFree(s->d_ready);
-    if (s->d_dbg) cudaFree(s->d_dbg);
     delete s;
 }
 
@@ -804,8 +776,7 @@ cudaError_t launch_mma_topk(cudaStream_t stream, int sm_count, MmaState** state,
         const size_t budget = kSmemLimit - fixed;
         // Operand B stays resident when it leaves room for at least four candidate stages: the ring then carries
         // only candidate bytes instead of re-reading the queries from L2 for every tile.
-        static const bool no_resident = getenv("MANTA_B200_MMA_NO_RESIDENT_B") != nullptr;  // debugging switch
-        const int b_resident = (!no_resident && b_stage * kchunks + 4 * a_stage <= budget) ? 1 : 0;
+        const int b_resident = (b_stage * kchunks + 4 * a_stage <= budget) ? 1 : 0;
         int stages = b_resident ? (int)((budget - b_stage * kchunks) / a_stage) : (int)(budget / (a_stage + b_stage));
         if (stages > 8) stages = 8;
         if (stages < 2) { *why = "not enough shared memory for two pipeline stages"; return cudaErrorInvalidValue; }
@@ -824,8 +795,7 @@ cudaError_t launch_mma_topk(cudaStream_t stream, int sm_count, MmaState** state,
         ka.stages = stages;
         ka.b_resident = b_resident;
         // Four epilogue warps per quadrant pay off when a tile carries many 16-query chunks and few K chunks.
-        static const char* subs_env = getenv("MANTA_B200_MMA_SUBS");  // debugging switch
-        ka.epi_subs = subs_env ? (atoi(subs_env) == 4 ? 4 : 2) : ((qn >= 96 && kchunks <= 4) ? 4 : 2);
+        ka.epi_subs = (qn >= 96 && kchunks <= 4) ? 4 : 2;
         ka.metric = a.metric;
         ka.order = a.order;
         ka.k = a.k;
@@ -833,28 +803,12 @@ cudaError_t launch_mma_topk(cudaStream_t stream, int sm_count, MmaState** state,
         ka.observe_tiles = observe;
         ka.row_begin = a.row_begin;
         ka.row_end = a.row_end;
-        ka.dbg = nullptr;
-        static const bool timing = getenv("MANTA_B200_MMA_TIMING") != nullptr;  // debugging switch
-        if (timing) {
-            if (!st->d_dbg) cudaMalloc(&st->d_dbg, 128);
-            cudaMemsetAsync(st->d_dbg, 0, 128, stream);
-            ka.dbg = st->d_dbg;
-        }
         e = launch_scan_variant(st, i8, a.metric, grid, smem, stream, map_a, map_b, ka, why);
         if (e != cudaSuccess) return e;
         count_launch();
         ++*launches;
         e = cudaGetLastError();
         if (e != cudaSuccess) { *why = "tensor-core scan launch"; return e; }
-        if (timing) {
-            unsigned long long h[16];
-            cudaStreamSynchronize(stream);
-            cudaMemcpy(h, st->d_dbg, 128, cudaMemcpyDeviceToHost);
-            fprintf(stderr, "[mma timing, CTA 0, cycles since kernel start] first accumulator %llu, all CTAs published %llu, first bounds %llu (refresher pass %llu); pass 0: staged %llu, counted %llu, bounds re-read %llu\n",
-                    h[11], h[8], h[9], h[10], h[12], h[13], h[14]);
-            fprintf(stderr, "[mma timing, CTA 0 warp 4, cycles] thr_wait %llu tfull_wait %llu tmem_ld %llu math %llu slow %llu house %llu | slow chunks %llu iters %llu\n",
-                    h[0], h[1], h[2], h[3], h[4], h[5], h[6], h[7]);
-        }
     }
     return cudaSuccess;
 }

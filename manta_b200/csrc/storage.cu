@@ -15,6 +15,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
+#include <climits>
 #include <cstring>
 #include <vector>
 
@@ -91,9 +92,16 @@ int read_header(const char* path, int fd, PackedFileHeader* h, int64_t* file_siz
     int erb = 0, srb = 0;
     if (h->rows < 0 || h->cols <= 0 || geometry((int)h->layout, h->cols, &erb, &srb) || erb != h->elem_row_bytes || srb != h->scale_row_bytes)
         return fail(err, "packed file %s: header geometry is inconsistent (layout %u, cols %d)", path, h->layout, h->cols);
-    if (h->data_offset < (int64_t)sizeof *h || (h->data_offset & 255) || (h->scales_offset & 255) ||
-        h->data_offset + h->rows * erb > *file_size || (srb && (h->scales_offset < h->data_offset + h->rows * erb || h->scales_offset + h->rows * srb > *file_size)))
+    // Bounds are checked by division, so that a corrupt row count cannot wrap the products.
+    if (h->data_offset < (int64_t)sizeof *h || (h->data_offset & 255) || (h->scales_offset & 255) || h->data_offset > *file_size ||
+        h->rows > (*file_size - h->data_offset) / erb)
         return fail(err, "packed file %s: sections exceed the file (%lld bytes)", path, (long long)*file_size);
+    if (srb && (h->scales_offset < h->data_offset + h->rows * erb || h->scales_offset > *file_size ||
+                h->rows > (*file_size - h->scales_offset) / srb))
+        return fail(err, "packed file %s: sections exceed the file (%lld bytes)", path, (long long)*file_size);
+    if (h->row_base < 0 || h->row_base > (int64_t)INT32_MAX || h->rows > (int64_t)INT32_MAX - h->row_base)
+        return fail(err, "packed file %s: row ids [%lld, %lld + %lld) do not fit int32", path, (long long)h->row_base, (long long)h->row_base,
+                    (long long)h->rows);
     return 0;
 }
 

@@ -37,6 +37,7 @@ EXPORTS = [
     "manta_b200_embed_device", "manta_b200_score_batched", "manta_b200_score_topk_batched",
     "manta_b200_candidates_save", "manta_b200_candidates_load", "manta_b200_packed_file_info",
     "manta_b200_exchange_create", "manta_b200_exchange_connect", "manta_b200_exchange_destroy",
+    "manta_b200_exchange_connect_local", "manta_b200_exchange_set_wait_limit", "manta_b200_exchange_disconnect",
     "manta_b200_topk_exchange_merge_device", "manta_b200_score_topk_exchange_device",
 ]
 
@@ -98,6 +99,9 @@ def load() -> ctypes.CDLL:
         "manta_b200_exchange_create": [c_void_p, c_int, c_int, c_int, c_int, POINTER(c_void_p), c_void_p, E],
         "manta_b200_exchange_connect": [c_void_p, c_void_p, c_void_p, E],
         "manta_b200_exchange_destroy": [c_void_p, c_void_p, E],
+        "manta_b200_exchange_disconnect": [c_void_p, c_void_p, E],
+        "manta_b200_exchange_connect_local": [c_void_p, c_void_p, POINTER(c_void_p), E],
+        "manta_b200_exchange_set_wait_limit": [c_void_p, ctypes.c_uint32, E],
         "manta_b200_score_topk_exchange_device": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p,
                                                   c_int, E],
         "manta_b200_topk_exchange_merge_device": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, E],
@@ -243,6 +247,18 @@ class Runtime:
         blob = b"".join(handles)
         buf = (ctypes.c_ubyte * len(blob)).from_buffer_copy(blob)
         call("manta_b200_exchange_connect", self.handle, ex, buf)
+
+    def exchange_connect_local(self, ex, ranks) -> None:
+        """Connects exchanges that live in this process: ``ranks[r]`` is rank r's exchange handle."""
+        arr = (c_void_p * len(ranks))(*[r.value if isinstance(r, c_void_p) else r for r in ranks])
+        call("manta_b200_exchange_connect_local", self.handle, ex, arr)
+
+    def exchange_set_wait_limit(self, ex, naps_200ns: int) -> None:
+        call("manta_b200_exchange_set_wait_limit", ex, ctypes.c_uint32(naps_200ns))
+
+    def exchange_disconnect(self, ex) -> None:
+        """First half of the tear-down: unmaps the peers' inboxes.  A host barrier belongs between this and destroy."""
+        call("manta_b200_exchange_disconnect", self.handle, ex)
 
     def exchange_destroy(self, ex) -> None:
         call("manta_b200_exchange_destroy", self.handle, ex)

@@ -77,6 +77,10 @@ class PeerExchange:
         flag = torch.tensor([ok], dtype=torch.int32, device="cuda" if dist.get_backend() == "nccl" else "cpu")
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
         if int(flag.item()) == 0:
+            # every rank is here (the all-reduce above): unmap, meet, and only then free the inboxes
+            if self.ex is not None:
+                rt.exchange_disconnect(self.ex)
+            dist.barrier()
             if self.ex is not None:
                 rt.exchange_destroy(self.ex)
             return None
@@ -102,8 +106,16 @@ class PeerExchange:
             self.rt.synchronize()
         except Exception as exc:  # reported below, after the collective part
             pending = exc
+        # CUDA IPC wants every importer to unmap before the exporter frees: all ranks finish their work, unmap the
+        # peers' inboxes, meet again, and only then free their own
         if self.world > 1:
             self.dist.barrier()  # no rank unmaps an inbox a peer may still store into
+        try:
+            self.rt.exchange_disconnect(self.ex)
+        except Exception as exc:
+            pending = pending or exc
+        if self.world > 1:
+            self.dist.barrier()  # no rank frees an inbox a peer still has mapped
         self.rt.exchange_destroy(self.ex)
         self.ex = None
         if pending is not None:

@@ -55,3 +55,19 @@ def test_inconsistent_geometry_and_truncation(tmp_path):
     open(p, "wb").write(b"MB2PACK\0")
     with pytest.raises(native.MantaError, match="shorter than its header"):
         native.packed_file_info(p)
+
+
+def test_huge_row_count_and_bad_row_base_are_refused(tmp_path):
+    # a row count whose products with the row sizes wrap 64 bits must not pass the bounds check
+    p = str(tmp_path / "wrap.mb2")
+    _write(p, _header(LAYOUT_Q8, (1 << 62) + 10, 100, 100, 4, 256, 1280), 2000)
+    with pytest.raises(native.MantaError, match="sections exceed the file"):
+        native.packed_file_info(p)
+    p = str(tmp_path / "neg_base.mb2")
+    _write(p, _header(LAYOUT_Q8, 10, 100, 100, 4, 256, 1280, row_base=-1), 1024 + 40)
+    with pytest.raises(native.MantaError, match="do not fit int32"):
+        native.packed_file_info(p)
+    p = str(tmp_path / "big_base.mb2")
+    _write(p, _header(LAYOUT_Q8, 10, 100, 100, 4, 256, 1280, row_base=2**31 - 5), 1024 + 40)
+    with pytest.raises(native.MantaError, match="do not fit int32"):
+        native.packed_file_info(p)

@@ -91,7 +91,8 @@ class _FakeRuntime:
 
     def __init__(self, fail_create=False, fail_connect=False):
         self.fail_create, self.fail_connect = fail_create, fail_connect
-        self.created = self.connected = self.destroyed = 0
+        self.created = self.connected = self.destroyed = self.disconnected = 0
+        self.log = []  # call order, shared with the barrier spy
 
     def exchange_create(self, world, rank, nq_max, k_max):
         if self.fail_create:
@@ -105,11 +106,30 @@ class _FakeRuntime:
         assert len(handles) == 2 and handles[0] == bytes([0]) * 64 and handles[1] == bytes([1]) * 64
         self.connected += 1
 
+    def exchange_disconnect(self, ex):
+        self.disconnected += 1
+        self.log.append("disconnect")
+
     def exchange_destroy(self, ex):
         self.destroyed += 1
+        self.log.append("destroy")
 
     def synchronize(self):
-        pass
+        self.log.append("synchronize")
+
+
+class _DistSpy:
+    """torch.distributed with every barrier noted in the fake runtime's call log."""
+
+    def __init__(self, real, log):
+        self._real, self._log = real, log
+
+    def barrier(self, *a, **kw):
+        self._log.append("barrier")
+        return self._real.barrier(*a, **kw)
+
+    def __getattr__(self, name):
+        return getattr(self._real, name)
 
 
 def _exchange_worker(rank, world, port, scenario, ret):
@@ -121,15 +141,22 @@ def _exchange_worker(rank, world, port, scenario, ret):
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         rt = _FakeRuntime(fail_create=(scenario == "create" and rank == 1), fail_connect=(scenario == "connect" and rank == 0))
-        px = sharding.PeerExchange.try_create(rt, dist, 4, 10)
+        spy = _DistSpy(dist, rt.log)
+        px = sharding.PeerExchange.try_create(rt, spy, 4, 10)
         if scenario == "ok":
             assert px is not None and rt.created == 1 and rt.connected == 1
+            del rt.log[:]
             px.close()
             assert rt.destroyed == 1
+            # an inbox is freed only after every rank has unmapped it: unmap, barrier, free
+            assert rt.log == ["synchronize", "barrier", "disconnect", "barrier", "destroy"]
         else:
-            # one rank failed: EVERY rank falls back, and a rank that had created its inbox releases it
+            # one rank failed: EVERY rank falls back, and a rank that had created its inbox releases it, again with a
+            # barrier between the unmapping and the freeing
             assert px is None
             assert rt.destroyed == rt.created
+            assert rt.log[-1 - rt.created:] == (["disconnect"] * rt.created + ["barrier"] + ["destroy"] * rt.created)[-1 - rt.created:]
+            assert "barrier" in rt.log and (not rt.created or rt.log.index("disconnect") < len(rt.log) - 1 - rt.log[::-1].index("barrier") < rt.log.index("destroy"))
         ret[rank] = True
     finally:
         dist.destroy_process_group()
