@@ -103,6 +103,17 @@ int manta_b200_runtime_stats(MantaB200Runtime* rt, MantaB200Stats* out, char** e
  * summed device milliseconds and the number of passes measured since the last call, and clears the record. */
 int manta_b200_runtime_profile(MantaB200Runtime* rt, int enable, char** err);
 int manta_b200_runtime_scan_time(MantaB200Runtime* rt, double* total_ms, int* passes, char** err);
+/* Launch configuration of the scan kernel the runtime's last score / fused pass issued: the truthful counterpart of
+ * nativeLaunchConfig's launch_* metadata (runtime/backend/native_kernel.go:65-112), which the host executor attaches
+ * to the values a score step produces.  kernel is the __global__ function's name. */
+typedef struct {
+    char kernel[48];
+    int grid;          /* thread blocks (one-dimensional grid) */
+    int block;         /* threads per block */
+    int shared_bytes;  /* dynamic shared memory per block */
+    int launches;      /* scan launches of that pass (query groups, row chunks) */
+} MantaB200LaunchInfo;
+int manta_b200_runtime_last_launch(MantaB200Runtime* rt, MantaB200LaunchInfo* out, char** err);
 /* Number of kernels this library has launched in this process (all runtimes). */
 uint64_t manta_b200_kernel_launch_count(void);
 

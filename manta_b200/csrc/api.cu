@@ -16,6 +16,15 @@ namespace mb200 {
 static std::atomic<uint64_t> g_launches{0};
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
+static thread_local MantaB200LaunchInfo t_last_scan{};
+void note_scan_launch(const char* kernel, int grid, int block, size_t shared_bytes) {
+    snprintf(t_last_scan.kernel, sizeof t_last_scan.kernel, "%s", kernel);
+    t_last_scan.grid = grid;
+    t_last_scan.block = block;
+    t_last_scan.shared_bytes = (int)shared_bytes;
+    t_last_scan.launches++;
+}
+
 cudaError_t launch_gemv_f16(cudaStream_t st, int sm_count, const GemvArgs& a, int mode);
 cudaError_t launch_gemv_q8(cudaStream_t st, int sm_count, const GemvArgs& a, int mode);
 cudaError_t launch_gemv_q4(cudaStream_t st, int sm_count, const GemvArgs& a, int mode);
@@ -96,6 +105,7 @@ struct MantaB200Runtime {
     bool async_exchange_pending = false;  // a sync == 0 exchange merge copied its flags to h_flags[4..7]
     bool async_embed_pending = false;  // a sync == 0 embed pass copied its bad-token word to h_flags[10..11]
     bool async_flags_pending = false;  // a sync == 0 pass copied its flags to h_flags; checked at synchronize
+    MantaB200LaunchInfo last_launch{};  // configuration of the last pass's scan kernel
 };
 
 static void prof_mark(MantaB200Runtime* rt, int which) {
@@ -265,6 +275,13 @@ int manta_b200_runtime_stats(MantaB200Runtime* rt, MantaB200Stats* out, char** e
     if (!rt || !out) return fail(err, "runtime_stats: NULL argument");
     std::lock_guard<std::mutex> lk(rt->mu);
     *out = rt->stats;
+    return 0;
+}
+
+int manta_b200_runtime_last_launch(MantaB200Runtime* rt, MantaB200LaunchInfo* out, char** err) {
+    if (!rt || !out) return fail(err, "runtime_last_launch: NULL argument");
+    std::lock_guard<std::mutex> lk(rt->mu);
+    *out = rt->last_launch;
     return 0;
 }
 
@@ -592,8 +609,17 @@ static int check_score_args(const MantaB200Runtime* rt, const MantaB200Candidate
 }
 
 // Streams the row range [r0, r1) through the scoring kernels for all queries (no reset, no selection).
+static int scan_rows_impl(MantaB200Runtime* rt, const CandView& cv, const QueryPrep& qp, int metric, int order, int k,
+                          int64_t r0, int64_t r1, const SelectWs& ws, int nq, bool allow_mma, char** err);
 static int scan_rows(MantaB200Runtime* rt, const CandView& cv, const QueryPrep& qp, int metric, int order, int k,
                      int64_t r0, int64_t r1, const SelectWs& ws, int nq, bool allow_mma, char** err) {
+    t_last_scan = MantaB200LaunchInfo{};
+    const int rc = scan_rows_impl(rt, cv, qp, metric, order, k, r0, r1, ws, nq, allow_mma, err);
+    rt->last_launch = t_last_scan;
+    return rc;
+}
+static int scan_rows_impl(MantaB200Runtime* rt, const CandView& cv, const QueryPrep& qp, int metric, int order, int k,
+                          int64_t r0, int64_t r1, const SelectWs& ws, int nq, bool allow_mma, char** err) {
     if (allow_mma && mma_supported(cv, nq)) {
         MmaArgs m;
         m.cv = cv;
@@ -797,6 +823,7 @@ int manta_b200_score(MantaB200Runtime* rt, const MantaB200Candidates* set, int m
     SelectWs ws{};
     QueryPrep qp;
     if (prepare_queries(rt, cv, rt->queries.p, nq, ws, 0, &qp, err)) return 1;
+    t_last_scan = MantaB200LaunchInfo{};
     for (int q0 = 0; q0 < nq;) {
         int left = nq - q0;
         int qt = left >= 4 ? 4 : (left >= 2 ? 2 : 1);
@@ -817,6 +844,7 @@ int manta_b200_score(MantaB200Runtime* rt, const MantaB200Candidates* set, int m
         if (e != cudaSuccess) return fail_cuda(err, "launch score kernel", e);
         q0 += qt;
     }
+    rt->last_launch = t_last_scan;
     CU_TRY(cudaMemcpyAsync(out_scores, rt->misc.p, obytes, cudaMemcpyDeviceToHost, rt->stream));
     CU_TRY(cudaStreamSynchronize(rt->stream));
     rt->stats.h2d_bytes += qbytes;
@@ -865,7 +893,9 @@ static int batched_common(MantaB200Runtime* rt, int metric, int order, const flo
     }
     SelectWs ws{};
     if (topk && ensure_select_ws(rt, nq, (uint32_t)rows, 1, &ws, err)) return 1;
+    t_last_scan = MantaB200LaunchInfo{};
     cudaError_t e = launch_score_batched(rt->stream, rt->sm_count, metric, d_q, d_d, nq, rows, cols, order, d_full, ws, topk ? 1 : 0);
+    rt->last_launch = t_last_scan;
     rt->stats.kernel_launches++;
     rt->stats.score_calls++;
     if (e != cudaSuccess) return fail_cuda(err, "launch batched score kernel", e);

@@ -102,6 +102,7 @@ cudaError_t launch_score_batched(cudaStream_t st, int sm_count, int metric, cons
             break;
     }
     count_launch();
+    note_scan_launch("score_batched_kernel", grid, kBatchedThreads, 0);
     return cudaGetLastError();
 }
 

@@ -578,6 +578,7 @@ cudaError_t launch_gemv_shape(cudaStream_t st, int grid, const GemvArgs& a, int 
     grid = (grid / 2) * occ;  // the caller passes 2 CTAs per SM, the bucket layout's upper bound
     gemv_kernel<LAYOUT, QT, LPR, CPL, U, L2P><<<grid, kThreads, smem, st>>>(a, mode);
     count_launch();
+    note_scan_launch("gemv_kernel", grid, kThreads, smem);
     return cudaGetLastError();
 }
 

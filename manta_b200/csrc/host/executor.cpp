@@ -16,6 +16,7 @@
 #include "../../../include/manta_b200_host.h"
 #include "half.h"
 #include "json.h"
+#include "sha256.h"
 
 namespace {
 
@@ -60,11 +61,20 @@ struct EntryPoint {
 };
 struct Variant {
     std::string backend, entry, source;
+    std::map<std::string, std::string> meta;
+    bool has_backend = false;
+};
+struct Hints {  // ScheduleHints, artifact/manta/module.go:168-176 (the fields the launch configuration reads)
+    std::vector<int> tile, tile_2d;
+    int vector_width = 0;
+    std::string memory;
 };
 struct Kernel {
     std::string name, op;  // op = body[0].op
     std::vector<Binding> inputs, outputs;
     std::vector<Variant> variants;
+    Hints hints;
+    bool empty_body_op = false;
 };
 struct Step {
     std::string entry, kind, name, kernel;
@@ -73,6 +83,7 @@ struct Step {
 };
 struct Module {
     std::string version, name;
+    std::vector<std::string> supported_backends;
     std::vector<Param> params;
     std::vector<EntryPoint> entries;
     std::vector<Kernel> kernels;
@@ -146,6 +157,7 @@ bool parse_module(const std::string& text, Module* m, std::string* err) {
     if (!root.is_object()) { *err = "module JSON is not an object"; return false; }
     m->version = root.get_string("version");
     m->name = root.get_string("name");
+    if (const Value* rq = root.get("requirements")) m->supported_backends = strings_of(rq->get("supported_backends"));
     if (const Value* ps = root.get("params"))
         for (const auto& e : ps->items()) {
             Param p{e.get_string("name"), e.get_string("binding"), parse_type(e.get("type"))};
@@ -161,10 +173,36 @@ bool parse_module(const std::string& text, Module* m, std::string* err) {
             k.name = e.get_string("name");
             k.inputs = parse_bindings(e.get("inputs"));
             k.outputs = parse_bindings(e.get("outputs"));
-            if (const Value* body = e.get("body"))
+            if (const Value* body = e.get("body")) {
                 if (!body->items().empty()) k.op = body->items()[0].get_string("op");
+                for (const auto& op : body->items()) k.empty_body_op = k.empty_body_op || op.get_string("op").empty();
+            }
+            if (const Value* h = e.get("hints")) {
+                auto ints = [](const Value* a) {
+                    std::vector<int> out;
+                    if (a)
+                        for (const auto& x : a->items())
+                            if (x.kind == Value::Number) out.push_back((int)x.num);
+                    return out;
+                };
+                k.hints.tile = ints(h->get("tile"));
+                k.hints.tile_2d = ints(h->get("tile_2d"));
+                if (const Value* vw = h->get("vector_width"))
+                    if (vw->kind == Value::Number) k.hints.vector_width = (int)vw->num;
+                k.hints.memory = h->get_string("memory");
+            }
             if (const Value* vs = e.get("variants"))
-                for (const auto& v : vs->items()) k.variants.push_back(Variant{v.get_string("backend"), v.get_string("entry"), v.get_string("source")});
+                for (const auto& v : vs->items()) {
+                    Variant var;
+                    var.backend = v.get_string("backend");
+                    var.entry = v.get_string("entry");
+                    var.source = v.get_string("source");
+                    if (const Value* mt = v.get("meta"))
+                        if (mt->is_object())
+                            for (const auto& kv : *mt->obj)
+                                if (kv.second.is_string()) var.meta[kv.first] = kv.second.str;
+                    k.variants.push_back(var);
+                }
             m->kernels.push_back(k);
         }
     if (const Value* ss = root.get("steps"))
@@ -210,26 +248,93 @@ const Variant* cuda_variant(const Kernel& k) {
     return nullptr;
 }
 
-// Module.Validate, the part that concerns this path (artifact/manta/module.go:256-449).
+// validateKernelVariants (artifact/manta/module.go:426-449): one variant per backend, each with an entry and a
+// source, and a variant for every backend the module says it supports (all five for a compiler-made module).
+bool validate_kernel_variants(const std::vector<std::string>& required, const Kernel& k, std::string* err) {
+    std::set<std::string> seen;
+    for (const auto& v : k.variants) {
+        if (v.backend.empty()) { *err = "kernel \"" + k.name + "\" variant backend is required"; return false; }
+        if (!seen.insert(v.backend).second) { *err = "kernel \"" + k.name + "\" has duplicate variant for backend \"" + v.backend + "\""; return false; }
+        if (v.entry.empty()) { *err = "kernel \"" + k.name + "\" variant entry is required for backend \"" + v.backend + "\""; return false; }
+        if (v.source.empty()) { *err = "kernel \"" + k.name + "\" variant source is required for backend \"" + v.backend + "\""; return false; }
+    }
+    for (const auto& b : required)
+        if (!seen.count(b)) { *err = "kernel \"" + k.name + "\" is missing variant for backend \"" + b + "\""; return false; }
+    return true;
+}
+
+// Module.Validate, the part that concerns this path (artifact/manta/module.go:256-449), followed by what loading on
+// the CUDA backend adds: the module must list "cuda" (Backend.CanLoad, runtime/backends/cuda/cuda.go:53-56), every
+// kernel must carry a cuda variant (CompileVariants, runtime/backend/backend.go:275-296) whose source defines its
+// entry (validateCompiledKernelSource, runtime/backend/native_kernel.go:37-63).
 bool validate_module(const Module& m, std::string* err) {
-    if (m.version != kVersion) { *err = "unsupported artifact version \"" + m.version + "\""; return false; }
     if (m.name.empty()) { *err = "module name is required"; return false; }
+    if (m.version.empty()) { *err = "module version is required"; return false; }
+    if (m.version != kVersion) { *err = "module version \"" + m.version + "\" is not supported, want \"" + kVersion + "\""; return false; }
+    if (m.supported_backends.empty()) { *err = "at least one supported backend is required"; return false; }
+    {
+        std::set<std::string> seen;
+        for (const auto& b : m.supported_backends) {
+            if (b.empty()) { *err = "supported backend is required"; return false; }
+            if (!seen.insert(b).second) { *err = "duplicate supported backend \"" + b + "\""; return false; }
+        }
+    }
     if (m.entries.empty()) { *err = "module requires at least one entry point"; return false; }
     std::set<std::string> seen;
     for (const auto& e : m.entries) {
         if (e.name.empty()) { *err = "entry point name is required"; return false; }
         if (!seen.insert(e.name).second) { *err = "duplicate entry point \"" + e.name + "\""; return false; }
     }
+    std::set<std::string> kernel_names;
+    for (const auto& k : m.kernels) {
+        if (k.name.empty()) { *err = "kernel name is required"; return false; }
+        if (!kernel_names.insert(k.name).second) { *err = "duplicate kernel \"" + k.name + "\""; return false; }
+        if (k.empty_body_op) { *err = "kernel \"" + k.name + "\" has body op with empty op name"; return false; }
+        if (!validate_kernel_variants(m.supported_backends, k, err)) return false;
+    }
     for (const auto& s : m.steps) {
         if (!entry_by_name(m, s.entry)) { *err = "step \"" + s.name + "\" references unknown entry point \"" + s.entry + "\""; return false; }
         if (s.kind == "launch_kernel") {
             const Kernel* k = kernel_by_name(m, s.kernel);
             if (!k) { *err = "step \"" + s.name + "\" references unknown kernel \"" + s.kernel + "\""; return false; }
-            const Variant* v = cuda_variant(*k);
-            if (!v || v->entry.empty()) { *err = "kernel \"" + k->name + "\" is missing a cuda variant"; return false; }
+        }
+    }
+    // loading on the CUDA backend
+    if (std::find(m.supported_backends.begin(), m.supported_backends.end(), "cuda") == m.supported_backends.end()) {
+        *err = "cuda: unsupported backend";  // Runtime.Load's reason for a backend that cannot load the module (runtime.go:62-64)
+        return false;
+    }
+    for (const auto& k : m.kernels) {
+        const Variant* v = cuda_variant(k);
+        if (!v) { *err = "kernel \"" + k.name + "\" missing variant for backend \"cuda\""; return false; }
+        if (v->source.find("__global__ void " + v->entry + "(") == std::string::npos) {
+            *err = "kernel \"" + k.name + "\" CUDA source does not define entry \"" + v->entry + "\"";
+            return false;
         }
     }
     return true;
+}
+
+// firstTileSize / estimatedSharedBytes (runtime/backend/native_kernel.go:114-148): what the plan's hints ask for.
+int first_tile_size(const Kernel& k, const Variant& v) {
+    if (!k.hints.tile.empty() && k.hints.tile[0] > 0) return k.hints.tile[0];
+    auto it = v.meta.find("tile");
+    if (it != v.meta.end()) {
+        std::string raw = it->second;
+        if (!raw.empty() && raw.front() == '[') raw.erase(0, 1);
+        if (!raw.empty() && raw.back() == ']') raw.pop_back();
+        const int n = atoi(raw.c_str());
+        if (n > 0) return n;
+    }
+    return 1;
+}
+int estimated_shared_bytes(const Kernel& k, int tile) {
+    if (tile <= 0) tile = 1;
+    if (k.hints.memory != "workgroup_local") return 0;
+    const int width = k.hints.vector_width > 0 ? k.hints.vector_width : 1;
+    int values = (int)(k.inputs.size() + k.outputs.size());
+    if (values == 0) values = 1;
+    return tile * width * values * 4;
 }
 
 // ---- candidate sets bound from float32-labelled tensors --------------------------------------------------------
@@ -369,6 +474,7 @@ struct Fusion {
     std::vector<int> gather_steps;    // gather(scores, ids)
     bool need_full_scores = false;    // scores are returned or read by a step that is not fused
     std::string scores_name, ids_name, query_name, docs_name, op;
+    std::string bind_name;            // the value the candidate set is bound from: docs_name seen through dequant steps
     int k = 0;
 };
 
@@ -393,6 +499,20 @@ std::vector<Fusion> plan_fusions(const Module& m, const std::vector<const Step*>
         f.query_name = s.inputs[0];
         f.docs_name = s.inputs[1];
         f.scores_name = s.outputs[0];
+        // score(q, dequant(docs_q)): dequant only relabels (tensor_ops.go:136-148), so the pass binds docs_q itself, in
+        // the packed layout its own label names
+        f.bind_name = f.docs_name;
+        for (bool again = true; again;) {
+            again = false;
+            for (size_t j = 0; j < i; ++j) {
+                const Step& d = *steps[j];
+                if (d.kind == "dequant" && d.inputs.size() == 1 && d.outputs.size() == 1 && d.outputs[0] == f.bind_name) {
+                    f.bind_name = d.inputs[0];
+                    again = true;
+                    break;
+                }
+            }
+        }
         for (size_t j = i + 1; j < steps.size(); ++j) {
             const Step& t = *steps[j];
             const bool reads_scores = std::find(t.inputs.begin(), t.inputs.end(), f.scores_name) != t.inputs.end();
@@ -430,6 +550,7 @@ Value fusion_json(const std::vector<const Step*>& steps, const std::vector<Fusio
                 if ((int)i == g) how = "fused_with_score";
         }
         if (steps[i]->kind == "pack_candidates") how = "host";
+        if (steps[i]->kind == "dequant") how = "relabel";
         o.set("execution", Value::make_string(how));
         arr.push(o);
     }
@@ -754,14 +875,14 @@ int manta_b200_program_run(MantaB200Program* prog, const char* entry_name, const
                 cleanup();
                 return fail(err, "entrypoint \"%s\" step \"%s\" missing runtime input \"%s\"", entry->name.c_str(), step.name.c_str(), name.c_str());
             }
-        std::string variant_entry;
+        std::string variant_entry, source_hash;
         std::vector<RValue> produced;
         auto base_meta = [&](RValue* v) {
             v->metadata.set("backend", Value::make_string("cuda"));
             v->metadata.set("step", Value::make_string(step.kind));
             v->metadata.set("kernel", Value::make_string(step.kernel));
             v->metadata.set("variant_entry", Value::make_string(variant_entry));
-            v->metadata.set("source_hash", Value::make_string(""));
+            v->metadata.set("source_hash", Value::make_string(source_hash));
             v->producer = !step.kernel.empty() ? "kernel:" + step.kernel : (!step.name.empty() ? step.kind + ":" + step.name : step.kind);
             v->inputs = step.inputs;
         };
@@ -785,7 +906,22 @@ int manta_b200_program_run(MantaB200Program* prog, const char* entry_name, const
         if (step.kind == "launch_kernel") {
             const Kernel* k = kernel_by_name(mod, step.kernel);
             if (!k) STEP_FAIL("unknown kernel \"%s\"", step.kernel.c_str());
-            variant_entry = cuda_variant(*k) ? cuda_variant(*k)->entry : "";
+            const Variant* var = cuda_variant(*k);
+            variant_entry = var ? var->entry : "";
+            source_hash = var ? mb200_host::sha256_hex(var->source) : "";  // CompileVariants, backend.go:286-293
+            if (k->op == "dequant") {
+                // kernel op dequant (tensor_ops.go:556-563): a clone relabelled f16; nothing to compute
+                if (step.inputs.size() != 1 || step.outputs.size() != 1) STEP_FAIL("kernel \"%s\" expects 1 input and 1 output", k->name.c_str());
+                const RValue& in = env[step.inputs[0]];
+                if (!in.tensor) STEP_FAIL("value \"%s\" is not a tensor", step.inputs[0].c_str());
+                RValue v;
+                v.tensor = std::make_shared<Tensor>(*in.tensor);
+                v.tensor->dtype = "f16";
+                v.type = out_type(0, *v.tensor);
+                base_meta(&v);
+                v.metadata.set("execution_mode", Value::make_string("relabel"));
+                produced.push_back(v);
+            } else {
             if (!is_score_op(k->op)) STEP_FAIL("kernel op \"%s\" is outside the score/select path this backend implements", k->op.c_str());
             const Fusion* f = nullptr;
             for (const auto& c : fusions)
@@ -859,24 +995,27 @@ int manta_b200_program_run(MantaB200Program* prog, const char* entry_name, const
             if (!float_like(query.dtype) || !float_like(docs.dtype)) STEP_FAIL("score inputs must be float-like tensors");
             // candidate set: resident for params, bound for this call for request inputs
             BoundSet bs;
-            auto rit = prog->residency.find(f->docs_name);
+            // the set is bound from the value behind any dequant steps, with that value's own dtype label
+            const std::string& bind_name = f->bind_name;
+            const std::string bind_dtype = (env.count(bind_name) && env[bind_name].tensor) ? env[bind_name].tensor->dtype : docs.dtype;
+            auto rit = prog->residency.find(bind_name);
             const bool keep_resident = rit == prog->residency.end() || rit->second.empty() || rit->second == "device_resident";
-            if (param_by_name(mod, f->docs_name) && keep_resident) {
-                auto it = prog->resident.find(f->docs_name);
+            if (param_by_name(mod, bind_name) && keep_resident) {
+                auto it = prog->resident.find(bind_name);
                 if (it == prog->resident.end()) {
                     char* berr = nullptr;
-                    if (bind_docs(prog->rt, docs.f32.data(), n, (int)d, docs.dtype, &bs, &berr)) {
+                    if (bind_docs(prog->rt, docs.f32.data(), n, (int)d, bind_dtype, &bs, &berr)) {
                         std::string m = berr ? berr : "bind failed";
                         free(berr);
                         STEP_FAIL("%s", m.c_str());
                     }
-                    prog->resident[f->docs_name] = bs;
+                    prog->resident[bind_name] = bs;
                 } else {
                     bs = it->second;
                 }
             } else {
                 char* berr = nullptr;
-                if (bind_docs(prog->rt, docs.f32.data(), n, (int)d, docs.dtype, &bs, &berr)) {
+                if (bind_docs(prog->rt, docs.f32.data(), n, (int)d, bind_dtype, &bs, &berr)) {
                     std::string m = berr ? berr : "bind failed";
                     free(berr);
                     STEP_FAIL("%s", m.c_str());
@@ -884,6 +1023,7 @@ int manta_b200_program_run(MantaB200Program* prog, const char* entry_name, const
                 temp_sets.push_back(bs);
             }
             set_of_value[f->docs_name] = bs;
+            set_of_value[bind_name] = bs;
             std::vector<uint16_t> qbits((size_t)nq * bs.stored_cols, 0);
             for (int q = 0; q < nq; ++q)
                 for (int64_t c = 0; c < d; ++c) qbits[(size_t)q * bs.stored_cols + c] = half_bits(query.f32[(size_t)q * d + c]);
@@ -941,6 +1081,49 @@ int manta_b200_program_run(MantaB200Program* prog, const char* entry_name, const
             device_meta(&sv, f->topk_step >= 0 ? "launch_kernel+topk+gather" : "launch_kernel");
             produced.push_back(sv);
             }  // shared / rank-1 candidate set
+            {
+                // nativeLaunchConfig (native_kernel.go:65-112): the plan-side keys as the reference derives them from
+                // the variant, the launch_* keys from the kernel that really ran
+                RValue& sv = produced.back();
+                MantaB200LaunchInfo li{};
+                manta_b200_runtime_last_launch(prog->rt, &li, nullptr);
+                auto meta_of = [&](const char* key) {
+                    if (!var) return std::string();
+                    auto it = var->meta.find(key);
+                    return it == var->meta.end() ? std::string() : it->second;
+                };
+                const int tile = var ? first_tile_size(*k, *var) : 1;
+                sv.metadata.set("dispatch_backend", Value::make_string("cuda"));
+                sv.metadata.set("launch_entry", Value::make_string(variant_entry));
+                sv.metadata.set("launch_tile", Value::make_string(meta_of("tile")));
+                sv.metadata.set("launch_tile_2d", Value::make_string(meta_of("tile_2d")));
+                sv.metadata.set("launch_vector_width", Value::make_string(meta_of("vector_width")));
+                sv.metadata.set("launch_memory", Value::make_string(meta_of("memory")));
+                sv.metadata.set("launch_subgroup", Value::make_string(meta_of("subgroup")));
+                sv.metadata.set("launch_subgroup_2d", Value::make_string(meta_of("subgroup_2d")));
+                sv.metadata.set("launch_halo", Value::make_string(meta_of("halo")));
+                sv.metadata.set("plan_block_size", Value::make_number(tile));
+                sv.metadata.set("plan_shared_bytes", Value::make_number(estimated_shared_bytes(*k, tile)));
+                sv.metadata.set("launch_grid", Value::make_string("1d"));
+                sv.metadata.set("launch_kernel", Value::make_string(li.kernel));
+                sv.metadata.set("launch_grid_size", Value::make_number(li.grid));
+                sv.metadata.set("launch_block_size", Value::make_number(li.block));
+                sv.metadata.set("launch_shared_bytes", Value::make_number(li.shared_bytes));
+                sv.metadata.set("launch_count", Value::make_number(li.launches));
+            }
+            }  // score op
+        } else if (step.kind == "dequant") {
+            // StepDequant (tensor_ops.go:136-148): a clone of the input relabelled f16, values unchanged
+            if (step.inputs.size() != 1 || step.outputs.size() != 1) STEP_FAIL("dequant step \"%s\" expects 1 input and 1 output", step.name.c_str());
+            const RValue& in = env[step.inputs[0]];
+            if (!in.tensor) STEP_FAIL("value \"%s\" is not a tensor", step.inputs[0].c_str());
+            RValue v;
+            v.tensor = std::make_shared<Tensor>(*in.tensor);
+            if (v.tensor->dtype != "f16") v.tensor->dtype = "f16";
+            v.type = out_type(0, *v.tensor);
+            base_meta(&v);
+            v.metadata.set("execution_mode", Value::make_string("relabel"));
+            produced.push_back(v);
         } else if (step.kind == "topk") {
             if (step.inputs.size() != 1 || step.outputs.size() != 1) STEP_FAIL("topk step \"%s\" expects 1 input and 1 output", step.name.c_str());
             auto it = fused.find(step.inputs[0]);

@@ -6,6 +6,8 @@
 namespace mb200 {
 
 void count_launch();
+// Records the configuration of a scan launch issued by the calling thread (read back by the runtime that issued it).
+void note_scan_launch(const char* kernel, int grid, int block, size_t shared_bytes);
 
 struct QueryPrep {
     const QueryHeader* headers;  // [nq]

@@ -674,6 +674,7 @@ static cudaError_t launch_scan_subs(MmaState* st, int slot, int grid, size_t sme
         st->attr_set[idx] = true;
     }
     mma_scan_kernel<I8, METRIC, SUBS><<<grid, mma_threads(SUBS), smem, stream>>>(map_a, map_b, ka);
+    note_scan_launch("mma_scan_kernel", grid, mma_threads(SUBS), smem);
     return cudaSuccess;
 }
 

@@ -19,7 +19,8 @@ def ttype(dtype, shape):
 def variants(op):
     src = ("extern \"C\" __global__ void %s_cuda(const float* query, const float* docs, float* out0, int rows, int cols) "
            "{ /* vestigial: replaced by AOT sm_100a kernels */ }" % op)
-    return [{"backend": b, "entry": "%s_%s" % (op, b), "source": src if b == "cuda" else "// %s" % b, "meta": {}}
+    meta = {"tile": "[128]", "vector_width": "4", "subgroup": "true", "memory": "workgroup_local"}
+    return [{"backend": b, "entry": "%s_%s" % (op, b), "source": src if b == "cuda" else "// %s" % b, "meta": dict(meta)}
             for b in ["cuda", "metal", "vulkan", "directml", "webgpu"]]
 
 
@@ -131,6 +132,16 @@ def build():
          step(eb, "gather", "gather", ["docs", "top_indices"], ["top_docs"]),
          step(eb, "pack_candidates", "pack_candidates", ["top_candidate_ids", "top_scores", "top_docs"], ["candidates"]),
          step(eb, "return", "return", None, ["candidates"])])
+    # score(query, dequant(docs_q)): the dequant step only relabels, the pass still binds docs_q packed
+    docs_q8 = [{"name": "docs_q", "type": ttype("q8", ["N", "D"]), "binding": "weights/docs_q"}]
+    mods["dequant_rerank"] = module("dequant_rerank", docs_q8,
+        [{"name": "rerank", "kind": "pipeline", "inputs": q_in,
+          "outputs": [{"name": "top_ids", "type": ttype("i32", ["2"])}, {"name": "top_scores", "type": ttype("f32", ["2"])}]}], cos,
+        [step("rerank", "dequant", "dequant", ["docs_q"], ["docs"]),
+         step("rerank", "launch_kernel", "cosine", ["query", "docs"], ["scores"], "cosine"),
+         step("rerank", "topk", "topk", ["scores"], ["top_ids"], None, {"k": "2"}),
+         step("rerank", "gather", "gather", ["scores", "top_ids"], ["top_scores"]),
+         step("rerank", "return", "return", None, ["top_ids", "top_scores"])])
     for op in ("dot", "cosine", "l2_distance"):
         mods["direct_" + op] = module(op, [],
             [{"name": "score", "kind": "pipeline",

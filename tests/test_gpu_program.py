@@ -319,3 +319,41 @@ def test_retrieval_model_retrieve_and_retrieve_batch(rt):
     assert len(res.batches) == 2
     assert res.batches[1][0].id == 4004
     assert [c.id for c in res.batches[0]] == [1001, 3003]
+
+
+def test_dequant_step_keeps_docs_packed(rt):
+    """score(query, dequant(docs_q)) (StepDequant, runtime/backend/tensor_ops.go:136-148: a clone relabelled f16): the
+    fused pass binds docs_q itself, packed by its own label, and the result equals the plan without the dequant step."""
+    import hashlib
+
+    from manta_b200.program import Program
+
+    rng = np.random.default_rng(77)
+    x = make_rows(rng, 3000, 64)
+    deq = oracle.unpack_q8_rows(*oracle.pack_q8_rows(x))  # what a q8-labelled float32 tensor of the reference holds
+    q = make_rows(rng, 1, 64)[0]
+    mod = load("dequant_rerank")
+    prog = Program(rt, mod)
+    prog.bind_weight("docs_q", T("q8", list(deq.shape), deq))
+    res = prog.run("rerank", {"query": T("f16", [64], q)})
+    assert [t["kind"] for t in res.trace] == ["dequant", "launch_kernel", "topk", "gather", "return"]
+    ids, scores = res.outputs["top_ids"].data, res.outputs["top_scores"].data
+    assert_topk_matches("cosine", q, deq, ids, scores, 2)
+    plain = Program(rt, load("tiny_rerank"))
+    plain.bind_weight("docs", T("q8", list(deq.shape), deq))
+    res2 = plain.run("rerank", {"query": T("f16", [64], q)})
+    np.testing.assert_array_equal(ids, res2.outputs["top_ids"].data)
+    np.testing.assert_array_equal(scores.view(np.uint32), res2.outputs["top_scores"].data.view(np.uint32))
+    # CompileVariants' source hash (runtime/backend/backend.go:286-293) and the launch configuration of the kernel
+    # that really ran, beside the plan-side keys of nativeLaunchConfig (runtime/backend/native_kernel.go:65-112)
+    mod2 = load("tiny_score")
+    prog = Program(rt, mod2)
+    prog.bind_weight("docs", T("q4", [2, 2], [1, 0, 0, 1]))
+    md = prog.run("score", {"query": T("f16", [2], [1, 0])}).outputs["scores"].metadata
+    src = [v for v in mod2["kernels"][0]["variants"] if v["backend"] == "cuda"][0]["source"]
+    assert md["source_hash"] == hashlib.sha256(src.encode()).hexdigest()
+    assert md["dispatch_mode"] == "backend_native" and md["dispatch_backend"] == "cuda" and md["launch_entry"] == "cosine_cuda"
+    assert md["launch_tile"] == "[128]" and md["launch_vector_width"] == "4" and md["launch_memory"] == "workgroup_local"
+    assert md["plan_block_size"] == 128 and md["plan_shared_bytes"] == 128 * 4 * 3 * 4  # estimatedSharedBytes
+    assert md["launch_grid"] == "1d" and md["launch_kernel"].endswith("_kernel")
+    assert md["launch_block_size"] >= 32 and md["launch_grid_size"] >= 1 and md["launch_count"] >= 1

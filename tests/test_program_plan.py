@@ -54,7 +54,7 @@ def test_scores_returned_next_to_topk_forces_full_scores():
 def test_validation_errors():
     mod = load("tiny_rerank")
     bad = dict(mod, version="manta/v9")
-    with pytest.raises(MantaError, match="unsupported artifact version"):
+    with pytest.raises(MantaError, match='module version "manta/v9" is not supported, want "manta/v0alpha1"'):
         Program(None, bad)
     bad = dict(mod, entry_points=[])
     with pytest.raises(MantaError, match="at least one entry point"):
@@ -63,15 +63,64 @@ def test_validation_errors():
     bad["steps"][0]["kernel"] = "nope"
     with pytest.raises(MantaError, match='unknown kernel "nope"'):
         Program(None, bad)
-    bad = json.loads(json.dumps(mod))
-    bad["kernels"][0]["variants"] = [v for v in bad["kernels"][0]["variants"] if v["backend"] != "cuda"]
-    with pytest.raises(MantaError, match="missing a cuda variant"):
-        Program(None, bad)
     with pytest.raises(MantaError, match="json:"):
         Program(None, "{not json")
     prog = Program(None, mod)
     with pytest.raises(MantaError, match='unknown entrypoint "nope"'):
         prog.plan("nope")
+
+
+def test_kernel_variant_rules():
+    """validateKernelVariants (artifact/manta/module.go:426-449) and what loading on the CUDA backend adds."""
+    mod = load("tiny_rerank")
+
+    def broken(edit):
+        bad = json.loads(json.dumps(mod))
+        edit(bad)
+        return bad
+
+    # a compiler-made module supports five backends and every kernel carries all five variants
+    assert sorted(v["backend"] for v in mod["kernels"][0]["variants"]) == ["cuda", "directml", "metal", "vulkan", "webgpu"]
+    for backend in ("cuda", "metal", "vulkan", "directml", "webgpu"):
+        bad = broken(lambda m: m["kernels"][0].__setitem__("variants", [v for v in m["kernels"][0]["variants"] if v["backend"] != backend]))
+        with pytest.raises(MantaError, match=f'kernel "cosine" is missing variant for backend "{backend}"'):
+            Program(None, bad)
+    bad = broken(lambda m: m["kernels"][0]["variants"].append(dict(m["kernels"][0]["variants"][0])))
+    with pytest.raises(MantaError, match='has duplicate variant for backend "cuda"'):
+        Program(None, bad)
+    bad = broken(lambda m: m["kernels"][0]["variants"][1].__setitem__("entry", ""))
+    with pytest.raises(MantaError, match='variant entry is required for backend "metal"'):
+        Program(None, bad)
+    bad = broken(lambda m: m["kernels"][0]["variants"][2].__setitem__("source", ""))
+    with pytest.raises(MantaError, match='variant source is required for backend "vulkan"'):
+        Program(None, bad)
+    bad = broken(lambda m: m["kernels"][0]["variants"][0].__setitem__("backend", ""))
+    with pytest.raises(MantaError, match="variant backend is required"):
+        Program(None, bad)
+    bad = broken(lambda m: m["requirements"].__setitem__("supported_backends", []))
+    with pytest.raises(MantaError, match="at least one supported backend is required"):
+        Program(None, bad)
+    bad = broken(lambda m: m["requirements"].__setitem__("supported_backends", ["cuda", "cuda"]))
+    with pytest.raises(MantaError, match='duplicate supported backend "cuda"'):
+        Program(None, bad)
+    # a module that does not list cuda cannot load on this backend
+    bad = broken(lambda m: m["requirements"].__setitem__("supported_backends", ["metal"]))
+    with pytest.raises(MantaError, match="cuda: unsupported backend"):
+        Program(None, bad)
+    # the cuda variant's source must define its entry (validateCompiledKernelSource)
+    bad = broken(lambda m: m["kernels"][0]["variants"][0].__setitem__("entry", "other_name"))
+    with pytest.raises(MantaError, match='CUDA source does not define entry "other_name"'):
+        Program(None, bad)
+    # a module limited to cuda needs only the cuda variant
+    ok = broken(lambda m: (m["requirements"].__setitem__("supported_backends", ["cuda"]),
+                           m["kernels"][0].__setitem__("variants", m["kernels"][0]["variants"][:1])))
+    Program(None, ok)
+
+
+def test_dequant_step_is_seen_through():
+    plan = Program(None, load("dequant_rerank")).plan("rerank")
+    assert [s["kind"] for s in plan] == ["dequant", "launch_kernel", "topk", "gather", "return"]
+    assert [s["execution"] for s in plan] == ["relabel", "fused_pass", "fused_with_score", "fused_with_score", "host"]
 
 
 def test_run_without_runtime_fails_loudly():
