@@ -105,6 +105,7 @@ struct MantaB200Runtime {
     bool async_exchange_pending = false;  // a sync == 0 exchange merge copied its flags to h_flags[4..7]
     bool async_embed_pending = false;  // a sync == 0 embed pass copied its bad-token word to h_flags[10..11]
     bool async_flags_pending = false;  // a sync == 0 pass copied its flags to h_flags; checked at synchronize
+    bool async_static_pending = false;  // a sync == 0 allocation-free pass copied its flags to h_flags[12..15]
     MantaB200LaunchInfo last_launch{};  // configuration of the last pass's scan kernel
 };
 
@@ -136,7 +137,9 @@ struct MantaB200Candidates {
 };
 
 namespace mb200 {
-RuntimeInfo runtime_info(MantaB200Runtime* rt) { return RuntimeInfo{rt->device, rt->sm_count, rt->stream, rt->h_flags, &rt->mu}; }
+RuntimeInfo runtime_info(MantaB200Runtime* rt) {
+    return RuntimeInfo{rt->device, rt->sm_count, rt->stream, rt->h_flags, &rt->async_static_pending, &rt->mu};
+}
 const CandView* candidates_view(const MantaB200Candidates* set) { return &set->cv; }
 int candidates_device(const MantaB200Candidates* set) { return set->device; }
 }  // namespace mb200
@@ -259,6 +262,12 @@ int manta_b200_runtime_synchronize(MantaB200Runtime* rt, char** err) {
     if (rt->async_embed_pending) {
         rt->async_embed_pending = false;
         if (rt->h_flags[10]) return fail(err, "gather index %d out of range", (int32_t)rt->h_flags[11]);
+    }
+    if (rt->async_static_pending) {
+        rt->async_static_pending = false;
+        if (rt->h_flags[12 + kFlagTimeout]) return fail(err, "runtime_synchronize: a bounded device wait gave up in an allocation-free pass");
+        if (rt->h_flags[12 + kFlagOverflow] || rt->h_flags[12 + kFlagInternal])
+            return fail(err, "runtime_synchronize: the last allocation-free pass found fewer than k candidates");
     }
     if (rt->async_flags_pending) {
         rt->async_flags_pending = false;

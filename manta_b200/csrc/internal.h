@@ -11,7 +11,9 @@ struct RuntimeInfo {
     int device;
     int sm_count;
     cudaStream_t stream;
-    uint32_t* h_flags;  // 16 pinned host words owned by the runtime; words 4..7 are free for callers of this header
+    uint32_t* h_flags;  // 16 pinned host words owned by the runtime: 0..3 fused pass, 4..7 exchange merge, 8..9 row
+                        // gather, 10..11 embedding front end, 12..15 the allocation-free entry point
+    bool* static_flags_pending;  // set when an asynchronous allocation-free pass has copied its flags to words 12..15
     std::mutex* mu;
 };
 RuntimeInfo runtime_info(MantaB200Runtime* rt);

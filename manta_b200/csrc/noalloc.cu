@@ -158,10 +158,18 @@ extern "C" int manta_b200_score_topk_static(MantaB200Runtime* rt, const MantaB20
         e = launch_select(ri.stream, sa);
         if (e != cudaSuccess) return fail(err, "score_topk_static: select launch: %s", cudaGetErrorName(e));
     }
-    if (!sync) return 0;
-    e = cudaMemcpyAsync(ri.h_flags + 4, ws.flags, kNumFlags * 4, cudaMemcpyDeviceToHost, ri.stream);
-    if (e == cudaSuccess) e = cudaStreamSynchronize(ri.stream);
+    // The pass's flag words go to the runtime's pinned host words 12..15 (this entry point's own slot): read here
+    // when the call is synchronous, by the next manta_b200_runtime_synchronize otherwise.
+    e = cudaMemcpyAsync(ri.h_flags + 12, ws.flags, kNumFlags * 4, cudaMemcpyDeviceToHost, ri.stream);
     if (e != cudaSuccess) return fail(err, "score_topk_static: %s (%s)", cudaGetErrorName(e), cudaGetErrorString(e));
-    if (ri.h_flags[4 + kFlagOverflow] || ri.h_flags[4 + kFlagInternal]) return fail(err, "score_topk_static: selection found fewer than k candidates");
+    if (!sync) {
+        *ri.static_flags_pending = true;
+        return 0;
+    }
+    e = cudaStreamSynchronize(ri.stream);
+    if (e != cudaSuccess) return fail(err, "score_topk_static: %s (%s)", cudaGetErrorName(e), cudaGetErrorString(e));
+    *ri.static_flags_pending = false;
+    if (ri.h_flags[12 + kFlagTimeout]) return fail(err, "score_topk_static: a bounded device wait gave up");
+    if (ri.h_flags[12 + kFlagOverflow] || ri.h_flags[12 + kFlagInternal]) return fail(err, "score_topk_static: selection found fewer than k candidates");
     return 0;
 }

@@ -27,7 +27,7 @@ MEM_HOST, MEM_DEVICE_COPY, MEM_DEVICE_ADOPT = 0, 1, 2
 EXPORTS = [
     "manta_b200_runtime_create", "manta_b200_runtime_destroy", "manta_b200_free_cstring",
     "manta_b200_runtime_stream", "manta_b200_runtime_synchronize", "manta_b200_runtime_stats",
-    "manta_b200_runtime_profile", "manta_b200_runtime_scan_time",
+    "manta_b200_runtime_profile", "manta_b200_runtime_scan_time", "manta_b200_runtime_last_launch",
     "manta_b200_kernel_launch_count", "manta_b200_candidates_bind", "manta_b200_candidates_unbind",
     "manta_b200_candidates_bytes", "manta_b200_pack_q8_rows", "manta_b200_pack_q4_b32",
     "manta_b200_pack_q8_rows_device", "manta_b200_pack_q4_b32_device", "manta_b200_score",
@@ -44,6 +44,10 @@ EXPORTS = [
 
 class MantaError(RuntimeError):
     pass
+
+
+class LaunchInfo(ctypes.Structure):
+    _fields_ = [("kernel", ctypes.c_char * 48), ("grid", c_int), ("block", c_int), ("shared_bytes", c_int), ("launches", c_int)]
 
 
 class Stats(ctypes.Structure):
@@ -79,6 +83,7 @@ def load() -> ctypes.CDLL:
         "manta_b200_runtime_synchronize": [c_void_p, E],
         "manta_b200_runtime_stats": [c_void_p, POINTER(Stats), E],
         "manta_b200_runtime_profile": [c_void_p, c_int, E],
+        "manta_b200_runtime_last_launch": [c_void_p, POINTER(LaunchInfo), E],
         "manta_b200_runtime_scan_time": [c_void_p, POINTER(ctypes.c_double), POINTER(c_int), E],
         "manta_b200_candidates_bind": [c_void_p, c_int, c_int64, c_int, c_void_p, c_void_p, c_int64, c_int,
                                        POINTER(c_void_p), E],
@@ -234,6 +239,12 @@ class Runtime:
         s = Stats()
         call("manta_b200_runtime_stats", self.handle, byref(s))
         return s.as_dict()
+
+    def last_launch(self) -> dict:
+        """Launch configuration of the scan kernel of the last score / fused pass."""
+        li = LaunchInfo()
+        call("manta_b200_runtime_last_launch", self.handle, byref(li))
+        return {"kernel": li.kernel.decode(), "grid": li.grid, "block": li.block, "shared_bytes": li.shared_bytes, "launches": li.launches}
 
     # ---- exchange of per-shard lists over peer memory ---------------------------------------------
     def exchange_create(self, world: int, rank: int, nq_max: int, k_max: int):

@@ -52,6 +52,61 @@ def test_single_rank_exchange_equals_direct_pass():
     rt.close()
 
 
+def test_missing_list_runs_into_the_wait_limit_and_the_runtime_stays_usable():
+    """A bounded device wait running out, made on the host: two ranks' exchanges live in this process on one GPU, only
+    rank 0 ever pushes, so the merge of rank 0 waits for a list nothing will write.  With a limit of a few
+    milliseconds the selection kernel gives up, raises its time-out flag and returns; the call reports it, and the
+    same runtime then serves an ordinary pass.  Nothing faults and no kernel waits on another kernel."""
+    import torch
+
+    from manta_b200 import native, sharding
+
+    rt = native.Runtime(0)
+    rng = np.random.default_rng(33)
+    data, scales, _ = pack("q8", make_rows(rng, 20000, 64))
+    cands = rt.bind("q8", data, scales)
+    q = make_rows(rng, 2, 64)
+    k = 8
+    want_ids, want_sc = rt.score_topk(cands, "cosine", q, k)
+    stream = torch.cuda.ExternalStream(rt.stream)
+    with torch.cuda.stream(stream):
+        dq = torch.from_numpy(q.astype(np.float16)).cuda()
+        _, d_ids, d_sc = sharding.new_pair(2, k, "cuda")
+        o_ids = torch.empty((2, k), dtype=torch.int32, device="cuda")
+        o_sc = torch.empty((2, k), dtype=torch.float32, device="cuda")
+    stream.synchronize()
+    ex0, _ = rt.exchange_create(2, 0, 4, 16)
+    ex1, _ = rt.exchange_create(2, 1, 4, 16)
+    rt.exchange_connect_local(ex0, [ex0, ex1])
+    rt.exchange_connect_local(ex1, [ex0, ex1])
+    rt.exchange_set_wait_limit(ex0, 25_000)  # 25,000 naps of 200 ns: about 5 ms
+    try:
+        # synchronous form: the call itself fails
+        with pytest.raises(native.MantaError, match="did not arrive"):
+            rt.score_topk_exchange_device(ex0, cands, "cosine", dq, 2, k, o_ids, o_sc, sync=True)
+        ids, sc = rt.score_topk(cands, "cosine", q, k)
+        np.testing.assert_array_equal(ids, want_ids)
+        np.testing.assert_array_equal(sc, want_sc)
+        # two-call form, asynchronous: the next synchronisation reports it
+        rt.score_topk_device(cands, "cosine", dq, 2, k, d_ids, d_sc, sync=False)
+        rt.topk_exchange_merge_device(ex0, d_ids, d_sc, 2, k, o_ids, o_sc, sync=False)
+        with pytest.raises(native.MantaError, match="did not arrive"):
+            rt.synchronize()
+        rt.synchronize()  # the report is delivered once
+        ids, sc = rt.score_topk(cands, "cosine", q, k)
+        np.testing.assert_array_equal(ids, want_ids)
+        np.testing.assert_array_equal(sc, want_sc)
+        with pytest.raises(native.MantaError, match="must be positive"):
+            rt.exchange_set_wait_limit(ex0, 0)
+    finally:
+        rt.exchange_disconnect(ex0)
+        rt.exchange_disconnect(ex1)
+        rt.exchange_destroy(ex0)
+        rt.exchange_destroy(ex1)
+        cands.unbind()
+        rt.close()
+
+
 _CHILD = r"""
 import os, sys
 import numpy as np

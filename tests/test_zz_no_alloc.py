@@ -44,6 +44,12 @@ def test_static_scratch_entry_point_matches_regular_path_twice():
             np.testing.assert_array_equal(got_s.cpu().numpy().view(np.uint32), ref_s.cpu().numpy().view(np.uint32),
                                           err_msg=f"call {call_no}")
             assert got_i.min().item() >= 7
+            # asynchronous form: the pass's status words are checked by the next synchronisation of the runtime
+            with torch.cuda.stream(stream):
+                got_i.fill_(-5)
+            rt.score_topk_static(cands, metric, d_q, nq, k, got_i, got_s, smallest=smallest, sync=False)
+            rt.synchronize()
+            np.testing.assert_array_equal(got_i.cpu().numpy(), ref_i.cpu().numpy(), err_msg=f"asynchronous call {call_no}")
         # sizes beyond the fixed scratch are refused with a clear message
         with pytest.raises(native.MantaError, match="exceed the fixed scratch"):
             rt.score_topk_static(cands, "cosine", d_q, 5, k, got_i, got_s)
