@@ -553,6 +553,7 @@ def run_ours(args, wl: Workload):
         # the comparison rule of tests/helpers.py: ids equal to topKTensor's except across score gaps below twice the
         # tolerance, returned scores within tolerance of the oracle's
         sys.path.insert(0, os.path.join(ROOT, "tests"))
+        import oracle
         from helpers import FLOOR, REL_TOL, topk_parity_report
 
         docs_f32, q_sets = _cpu_sample(wl, sample_rows, nsets)

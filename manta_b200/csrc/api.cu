@@ -25,23 +25,15 @@ void note_scan_launch(const char* kernel, int grid, int block, size_t shared_byt
     t_last_scan.launches++;
 }
 
-cudaError_t launch_gemv_f16(cudaStream_t st, int sm_count, const GemvArgs& a, int mode);
-cudaError_t launch_gemv_q8(cudaStream_t st, int sm_count, const GemvArgs& a, int mode);
-cudaError_t launch_gemv_q4(cudaStream_t st, int sm_count, const GemvArgs& a, int mode);
+cudaError_t launch_stream_scan_f16(cudaStream_t st, int sm_count, const StreamArgs& a);
+cudaError_t launch_stream_scan_q8(cudaStream_t st, int sm_count, const StreamArgs& a);
+cudaError_t launch_stream_scan_q4(cudaStream_t st, int sm_count, const StreamArgs& a);
 
-int gemv_grid_size(int sm_count) { return sm_count * 2; }
-int gemv_bucket_count(int sm_count) { return gemv_grid_size(sm_count) * kWarpsPerCta; }
-int gemv_first_burst_rows(int sm_count, int chunks) {
-    GemvShape s;
-    if (!pick_gemv_shape(chunks, &s)) return 0;
-    return gemv_bucket_count(sm_count) * (32 / s.lpr) * s.u * 4;
-}
-
-cudaError_t launch_gemv(cudaStream_t st, int sm_count, const GemvArgs& a, int mode) {
+cudaError_t launch_stream_scan(cudaStream_t st, int sm_count, const StreamArgs& a) {
     switch (a.cv.layout) {
-        case MANTA_B200_LAYOUT_F16: return launch_gemv_f16(st, sm_count, a, mode);
-        case MANTA_B200_LAYOUT_Q8_ROW_F32: return launch_gemv_q8(st, sm_count, a, mode);
-        case MANTA_B200_LAYOUT_Q4_B32_F16: return launch_gemv_q4(st, sm_count, a, mode);
+        case MANTA_B200_LAYOUT_F16: return launch_stream_scan_f16(st, sm_count, a);
+        case MANTA_B200_LAYOUT_Q8_ROW_F32: return launch_stream_scan_q8(st, sm_count, a);
+        case MANTA_B200_LAYOUT_Q4_B32_F16: return launch_stream_scan_q4(st, sm_count, a);
     }
     return cudaErrorInvalidValue;
 }
@@ -107,6 +99,7 @@ struct MantaB200Runtime {
     bool async_flags_pending = false;  // a sync == 0 pass copied its flags to h_flags; checked at synchronize
     bool async_static_pending = false;  // a sync == 0 allocation-free pass copied its flags to h_flags[12..15]
     MantaB200LaunchInfo last_launch{};  // configuration of the last pass's scan kernel
+    bool ws_dirty = true;  // the selection workspace is not in the all-zero state a fused streaming pass starts from
 };
 
 static void prof_mark(MantaB200Runtime* rt, int which) {
@@ -155,6 +148,7 @@ static int ensure(MantaB200Runtime* rt, DevBuf& b, size_t bytes, char** err) {
     size_t want = bytes + bytes / 4 + 256;
     CU_TRY(cudaMalloc(&b.p, want));
     b.bytes = want;
+    rt->ws_dirty = true;   // fresh memory is not the zeroed workspace a fused streaming pass expects
     return 0;
 }
 
@@ -253,30 +247,49 @@ int manta_b200_runtime_synchronize(MantaB200Runtime* rt, char** err) {
     std::lock_guard<std::mutex> lk(rt->mu);
     CU_TRY(cudaSetDevice(rt->device));
     CU_TRY(cudaStreamSynchronize(rt->stream));
+    // every pending report is read and cleared first, then the first failure (if any) is returned
+    const char* msg = nullptr;
     if (rt->async_exchange_pending) {
         rt->async_exchange_pending = false;
-        if (rt->h_flags[4 + kFlagTimeout])
-            return fail(err, "runtime_synchronize: a peer's top-k list did not arrive within the wait limit of the exchange");
-        if (rt->h_flags[4 + kFlagInternal]) return fail(err, "runtime_synchronize: the exchange merge found fewer than k candidates");
+        uint32_t fl[kNumFlags];
+        for (int f = 0; f < kNumFlags; ++f) {
+            fl[f] = rt->h_flags[4 + f];
+            rt->h_flags[4 + f] = 0;
+        }
+        if (fl[kFlagTimeout]) msg = "runtime_synchronize: a peer's top-k list did not arrive within the wait limit of the exchange";
+        else if (fl[kFlagPeerOverflow] || rt->h_flags[kFlagOverflow])
+            msg = "runtime_synchronize: a shard's candidate pool overflowed during an exchange step, the merged result is incomplete on "
+                  "every rank; redo the step with manta_b200_score_topk_device(sync != 0) + manta_b200_topk_exchange_merge_device";
+        else if (fl[kFlagInternal]) msg = "runtime_synchronize: the exchange merge found fewer than k candidates";
     }
     if (rt->async_embed_pending) {
         rt->async_embed_pending = false;
-        if (rt->h_flags[10]) return fail(err, "gather index %d out of range", (int32_t)rt->h_flags[11]);
+        if (rt->h_flags[10] && !msg) return fail(err, "gather index %d out of range", (int32_t)rt->h_flags[11]);
     }
     if (rt->async_static_pending) {
         rt->async_static_pending = false;
-        if (rt->h_flags[12 + kFlagTimeout]) return fail(err, "runtime_synchronize: a bounded device wait gave up in an allocation-free pass");
-        if (rt->h_flags[12 + kFlagOverflow] || rt->h_flags[12 + kFlagInternal])
-            return fail(err, "runtime_synchronize: the last allocation-free pass found fewer than k candidates");
+        if (!msg) {
+            if (rt->h_flags[12 + kFlagTimeout]) msg = "runtime_synchronize: a bounded device wait gave up in an allocation-free pass";
+            else if (rt->h_flags[12 + kFlagOverflow] || rt->h_flags[12 + kFlagInternal])
+                msg = "runtime_synchronize: the last allocation-free pass found fewer than k candidates";
+        }
     }
     if (rt->async_flags_pending) {
         rt->async_flags_pending = false;
-        if (rt->h_flags[kFlagTimeout]) return fail(err, "runtime_synchronize: a bounded device wait gave up in an asynchronous pass");
-        if (rt->h_flags[kFlagOverflow])
-            return fail(err, "runtime_synchronize: the last asynchronous fused pass overflowed its candidate pool; its "
-                             "result is incomplete, reissue it with sync != 0 (which redoes it in chunks)");
-        if (rt->h_flags[kFlagInternal]) return fail(err, "runtime_synchronize: selection found fewer than k candidates");
+        uint32_t fl[kNumFlags];
+        for (int f = 0; f < kNumFlags; ++f) {
+            fl[f] = rt->h_flags[f];
+            rt->h_flags[f] = 0;
+        }
+        if (!msg) {
+            if (fl[kFlagTimeout]) msg = "runtime_synchronize: a bounded device wait gave up in an asynchronous pass";
+            else if (fl[kFlagOverflow])
+                msg = "runtime_synchronize: an asynchronous fused pass overflowed its candidate pool; its result is incomplete, reissue it "
+                      "with sync != 0 (which redoes it in chunks)";
+            else if (fl[kFlagInternal]) msg = "runtime_synchronize: selection found fewer than k candidates";
+        }
     }
+    if (msg) return fail(err, "%s", msg);
     return 0;
 }
 
@@ -357,8 +370,15 @@ int manta_b200_candidates_bind(MantaB200Runtime* rt, int layout, int64_t rows, i
         return fail(err, "candidates_bind: row ids [%lld, %lld) do not fit int32", (long long)row_base,
                     (long long)(row_base + rows));
     if (rows > 0 && (!data || (scale_row_bytes && !scales))) return fail(err, "candidates_bind: NULL data or scales");
-    if (!pick_gemv_shape(chunks, nullptr))
-        return fail(err, "candidates_bind: row of %d columns is wider than the kernels support for this layout", cols);
+    {
+        CandView probe{};
+        probe.layout = layout;
+        probe.chunks = chunks;
+        ScanGeometry g;
+        size_t smem = 0;
+        if (!stream_scan_geometry(probe, 1, 0, &g, &smem))
+            return fail(err, "candidates_bind: row of %d columns is wider than the kernels support for this layout", cols);
+    }
 
     std::lock_guard<std::mutex> lk(rt->mu);
     CU_TRY(cudaSetDevice(rt->device));
@@ -532,11 +552,9 @@ static uint32_t pool_cap_for(const MantaB200Runtime* rt, const CandView& cv, int
         if (cap < k) cap = k;
         return (uint32_t)cap;
     } else {
-        // Every row streamed before the first threshold lands enters the pool.  That takes on the order of ten
-        // microseconds whatever the row size, so the allowance is a byte budget (HBM rate x ~20 us), in rows.
-        cap = (int64_t)gemv_first_burst_rows(rt->sm_count, cv.chunks) * 2;
-        const int64_t by_time = (int64_t)130000000 / (cv.row_bytes + 8);
-        if (cap < by_time) cap = by_time;
+        // The streaming scan appends only rows that pass the running threshold (tiles seen before a threshold exists
+        // are observed and re-read), so the pool holds a small multiple of k; a set smaller than this is held whole.
+        cap = 64ll * k;
     }
     if (cap < 32ll * k) cap = 32ll * k;
     if (cap < (1 << 16)) cap = 1 << 16;
@@ -570,7 +588,7 @@ static int ensure_select_ws(MantaB200Runtime* rt, int nq, uint32_t cap, uint32_t
     if (ensure(rt, rt->count, (size_t)nq * 4, err)) return 1;
     if (ensure(rt, rt->thr, (size_t)nq * 4, err)) return 1;
     if (ensure(rt, rt->bucket, (size_t)nq * nb * 4, err)) return 1;
-    if (ensure(rt, rt->flags, kNumFlags * 4, err)) return 1;
+    if (ensure(rt, rt->flags, 64, err)) return 1;   // [0..3] flags, [4] blocks that have finished the current scan
     ws->pool = (uint64_t*)rt->pool.p;
     ws->count = (uint32_t*)rt->count.p;
     ws->thr = (uint32_t*)rt->thr.p;
@@ -579,6 +597,14 @@ static int ensure_select_ws(MantaB200Runtime* rt, int nq, uint32_t cap, uint32_t
     ws->cap = cap;
     ws->nb = nb;
     return 0;
+}
+
+// Reads and clears the sticky host flag words [first, first + 4); the stream must be synchronised.
+static void take_host_flags(MantaB200Runtime* rt, int first, uint32_t out[kNumFlags]) {
+    for (int f = 0; f < kNumFlags; ++f) {
+        out[f] = rt->h_flags[first + f];
+        rt->h_flags[first + f] = 0;
+    }
 }
 
 extern "C++" {
@@ -590,21 +616,35 @@ int exchange_select_ws(MantaB200Runtime* rt, int nq, uint32_t cap, SelectWs* ws,
     rt->stats.kernel_launches += 2;
     return ensure_select_ws(rt, nq, cap, 1, ws, err);
 }
-// Reads the merge's flags into host words 4..7 (the fused pass keeps 0..3); the caller holds the lock.
+// The exchange merge raises its flags in the pinned host words 4..7 (the fused pass keeps 0..3).
+uint32_t* exchange_host_flags(MantaB200Runtime* rt) { return rt->h_flags + 4; }
+// After the merge's selection kernel is queued: with sync the words are read (and cleared) here, otherwise by the next
+// runtime_synchronize.  The caller holds the lock.
 void exchange_note_async_flags(MantaB200Runtime* rt, const SelectWs& ws, int sync, char** err, int* rc) {
+    (void)ws;
     *rc = 0;
-    cudaError_t e = cudaMemcpyAsync(rt->h_flags + 4, ws.flags, kNumFlags * 4, cudaMemcpyDeviceToHost, rt->stream);
-    if (e == cudaSuccess && sync) e = cudaStreamSynchronize(rt->stream);
-    if (e != cudaSuccess) {
-        *rc = fail_cuda(err, "topk_exchange_merge", e);
-        return;
-    }
     if (!sync) {
         rt->async_exchange_pending = true;
         return;
     }
-    if (rt->h_flags[4 + kFlagTimeout]) *rc = fail(err, "topk_exchange_merge: a peer's top-k list did not arrive within the wait limit");
-    else if (rt->h_flags[4 + kFlagInternal]) *rc = fail(err, "topk_exchange_merge: selection found fewer than k candidates");
+    cudaError_t e = cudaStreamSynchronize(rt->stream);
+    if (e != cudaSuccess) {
+        *rc = fail_cuda(err, "topk_exchange_merge", e);
+        return;
+    }
+    rt->async_exchange_pending = false;
+    uint32_t fl[kNumFlags];
+    take_host_flags(rt, 4, fl);
+    const bool own_overflow = rt->h_flags[kFlagOverflow] != 0;   // this rank's shard pass (its words stay for the next synchronize)
+    if (fl[kFlagTimeout]) *rc = fail(err, "topk_exchange_merge: a peer's top-k list did not arrive within the wait limit");
+    else if (fl[kFlagPeerOverflow] || own_overflow)
+        *rc = fail(err, "topk_exchange_merge: a shard's candidate pool overflowed, the merged result is incomplete on every rank; redo the "
+                        "step with manta_b200_score_topk_device(sync != 0) + manta_b200_topk_exchange_merge_device");
+    else if (fl[kFlagInternal]) *rc = fail(err, "topk_exchange_merge: selection found fewer than k candidates");
+    if (*rc && own_overflow) {
+        for (int f = 0; f < kNumFlags; ++f) rt->h_flags[f] = 0;   // reported here
+        rt->async_flags_pending = false;
+    }
 }
 }  // namespace mb200
 }  // extern "C++"
@@ -617,61 +657,43 @@ static int check_score_args(const MantaB200Runtime* rt, const MantaB200Candidate
     return 0;
 }
 
-// Streams the row range [r0, r1) through the scoring kernels for all queries (no reset, no selection).
-static int scan_rows_impl(MantaB200Runtime* rt, const CandView& cv, const QueryPrep& qp, int metric, int order, int k,
-                          int64_t r0, int64_t r1, const SelectWs& ws, int nq, bool allow_mma, char** err);
-static int scan_rows(MantaB200Runtime* rt, const CandView& cv, const QueryPrep& qp, int metric, int order, int k,
-                     int64_t r0, int64_t r1, const SelectWs& ws, int nq, bool allow_mma, char** err) {
-    t_last_scan = MantaB200LaunchInfo{};
-    const int rc = scan_rows_impl(rt, cv, qp, metric, order, k, r0, r1, ws, nq, allow_mma, err);
-    rt->last_launch = t_last_scan;
-    return rc;
-}
-static int scan_rows_impl(MantaB200Runtime* rt, const CandView& cv, const QueryPrep& qp, int metric, int order, int k,
-                          int64_t r0, int64_t r1, const SelectWs& ws, int nq, bool allow_mma, char** err) {
-    if (allow_mma && mma_supported(cv, nq)) {
-        MmaArgs m;
-        m.cv = cv;
-        m.qp = qp;
-        m.metric = metric;
-        m.order = order;
-        m.k = k;
-        m.row_begin = r0;
-        m.row_end = r1;
-        m.ws = ws;
-        m.nq = nq;
-        int launches = 0;
-        const char* why = nullptr;
-        cudaError_t e = launch_mma_topk(rt->stream, rt->sm_count, &rt->mma, m, &launches, &why);
-        rt->stats.kernel_launches += launches;
-        if (e == cudaSuccess) {
-            rt->stats.mma_passes++;
-            return 0;
-        }
-        if (e != cudaErrorNotSupported)
-            return fail(err, "score_topk(%s): tensor-core pass: %s (%s)", metric_name(metric), why ? why : "launch failed", cudaGetErrorName(e));
-        // shapes the tensor-core pass declines go to the streaming kernel below
-    }
+// What the tail of a fused streaming pass does with the selected lists.
+struct FusedTail {
+    int32_t* d_out_ids = nullptr;
+    float* d_out_scores = nullptr;
+    const ExchangeSink* sink = nullptr;
+};
+
+// Streams the row range [r0, r1) through the streaming kernel for all queries, four at a time.  With a tail the
+// last block of every launch selects its queries' top k (one launch per query group is the whole pass); without one
+// the pools are left for a selection kernel.
+static int stream_rows(MantaB200Runtime* rt, const CandView& cv, const void* d_queries, int metric, int order, int k, int64_t r0,
+                       int64_t r1, const SelectWs& ws, int nq, const FusedTail* tail, char** err) {
     for (int q0 = 0; q0 < nq;) {
-        int left = nq - q0;
-        int qt = left >= 4 ? 4 : (left >= 2 ? 2 : 1);
-        GemvShape s;
-        pick_gemv_shape(cv.chunks, &s);
-        if (s.cpl == 8) qt = 1;
-        GemvArgs a{};
+        const int left = nq - q0;
+        const int qt = left >= 4 ? 4 : (left >= 2 ? 2 : 1);
+        StreamArgs a{};
         a.cv = cv;
-        a.qp = qp;
+        a.queries = (const __half*)d_queries;
         a.q0 = q0;
         a.qt = qt;
         a.metric = metric;
         a.order = order;
         a.k = k;
+        a.mode = kModeTopk;
         a.row_begin = r0;
         a.row_end = r1;
         a.ws = ws;
-        static const bool no_wait = getenv("MANTA_B200_NO_STARTUP_WAIT") != nullptr;  // debugging switch
-        a.no_startup_wait = no_wait ? 1 : 0;
-        cudaError_t e = launch_gemv(rt->stream, rt->sm_count, a, kModeTopk);
+        a.nq_total = nq;
+        a.done_blocks = (uint32_t*)rt->flags.p + 4;
+        a.host_flags = rt->h_flags;
+        if (tail) {
+            a.fused_select = 1;
+            a.out_ids = tail->d_out_ids;
+            a.out_topk_scores = tail->d_out_scores;
+            if (tail->sink) a.sink = *tail->sink;
+        }
+        cudaError_t e = launch_stream_scan(rt->stream, rt->sm_count, a);
         rt->stats.kernel_launches++;
         if (e != cudaSuccess) return fail_cuda(err, "launch score kernel", e);
         q0 += qt;
@@ -680,42 +702,103 @@ static int scan_rows_impl(MantaB200Runtime* rt, const CandView& cv, const QueryP
     return 0;
 }
 
-static int score_topk_locked(MantaB200Runtime* rt, const MantaB200Candidates* set, int metric, int order,
-                             const void* d_queries, int nq, int k, int32_t* d_out_ids, float* d_out_scores, int sync,
-                             char** err, const ExchangeSink* sink = nullptr) {
-    const CandView& cv = set->cv;
-    // a multiple of four, so that every query's bucket row starts on a 16-byte boundary
-    const uint32_t nb = ((uint32_t)std::max(gemv_bucket_count(rt->sm_count), mma_bucket_count(rt->sm_count)) + 3u) & ~3u;
-    uint32_t cap = pool_cap_for(rt, cv, nq, k);
-    SelectWs ws;
-    if (ensure_select_ws(rt, nq, cap, nb, &ws, err)) return 1;
+static int reset_ws(MantaB200Runtime* rt, const SelectWs& ws, int nq, char** err) {
+    cudaError_t e = launch_ws_reset(rt->stream, ws, nq, (uint32_t*)rt->flags.p + 4);
+    rt->stats.kernel_launches++;
+    if (e != cudaSuccess) return fail_cuda(err, "launch workspace reset", e);
+    return 0;
+}
+
+// The tensor-core pass: query preparation kernel, scan, selection kernel; flags copied to the host words.
+static int mma_pass(MantaB200Runtime* rt, const CandView& cv, const void* d_queries, int metric, int order, int k, const SelectWs& ws,
+                    int nq, int32_t* d_out_ids, float* d_out_scores, const ExchangeSink* sink, bool* declined, char** err) {
+    *declined = false;
     QueryPrep qp;
     if (prepare_queries(rt, cv, d_queries, nq, ws, 1, &qp, err)) return 1;
+    rt->ws_dirty = true;
+    MmaArgs m;
+    m.cv = cv;
+    m.qp = qp;
+    m.metric = metric;
+    m.order = order;
+    m.k = k;
+    m.row_begin = 0;
+    m.row_end = cv.rows;
+    m.ws = ws;
+    m.nq = nq;
+    int launches = 0;
+    const char* why = nullptr;
     prof_mark(rt, 0);
-    if (scan_rows(rt, cv, qp, metric, order, k, 0, cv.rows, ws, nq, true, err)) return 1;
+    cudaError_t e = launch_mma_topk(rt->stream, rt->sm_count, &rt->mma, m, &launches, &why);
+    rt->stats.kernel_launches += launches;
+    if (e == cudaErrorNotSupported) {
+        *declined = true;   // shapes the tensor-core pass declines go to the streaming kernel
+        return 0;
+    }
+    if (e != cudaSuccess)
+        return fail(err, "score_topk(%s): tensor-core pass: %s (%s)", metric_name(metric), why ? why : "launch failed", cudaGetErrorName(e));
     prof_mark(rt, 1);
+    rt->stats.mma_passes++;
     SelectArgs sa{};
     sa.ws = ws;
     sa.nq = nq;
     sa.k = k;
     sa.order = order;
-    sa.write_back = 0;
     sa.out_ids = d_out_ids;
     sa.out_scores = d_out_scores;
     if (sink) sa.sink = *sink;
-    cudaError_t e = launch_select(rt->stream, sa);
+    e = launch_select(rt->stream, sa);
     rt->stats.kernel_launches++;
     if (e != cudaSuccess) return fail_cuda(err, "launch select kernel", e);
+    // the pass's flags join the sticky host words (the copy overwrites: an earlier unsynchronised pass's report in
+    // these words is replaced, as before)
     CU_TRY(cudaMemcpyAsync(rt->h_flags, ws.flags, kNumFlags * 4, cudaMemcpyDeviceToHost, rt->stream));
+    return 0;
+}
+
+static int score_topk_locked(MantaB200Runtime* rt, const MantaB200Candidates* set, int metric, int order,
+                             const void* d_queries, int nq, int k, int32_t* d_out_ids, float* d_out_scores, int sync,
+                             char** err, const ExchangeSink* sink = nullptr) {
+    const CandView& cv = set->cv;
+    // a multiple of four, so that every query's bucket row starts on a 16-byte boundary
+    const uint32_t nb = ((uint32_t)std::max(stream_bucket_count(rt->sm_count), mma_bucket_count(rt->sm_count)) + 3u) & ~3u;
+    uint32_t cap = pool_cap_for(rt, cv, nq, k);
+    SelectWs ws;
+    if (ensure_select_ws(rt, nq, cap, nb, &ws, err)) return 1;
+    t_last_scan = MantaB200LaunchInfo{};
+    bool streamed = true;
+    if (mma_supported(cv, nq)) {
+        bool declined = false;
+        if (mma_pass(rt, cv, d_queries, metric, order, k, ws, nq, d_out_ids, d_out_scores, sink, &declined, err)) return 1;
+        streamed = declined;
+    }
+    if (streamed) {
+        // one launch per group of four queries does everything: query preparation, scan, selection, clean-up
+        if (rt->ws_dirty && reset_ws(rt, ws, nq, err)) return 1;
+        rt->ws_dirty = false;
+        FusedTail tail;
+        tail.d_out_ids = d_out_ids;
+        tail.d_out_scores = d_out_scores;
+        tail.sink = sink;
+        prof_mark(rt, 0);
+        if (stream_rows(rt, cv, d_queries, metric, order, k, 0, cv.rows, ws, nq, &tail, err)) {
+            rt->ws_dirty = true;
+            return 1;
+        }
+        prof_mark(rt, 1);
+    }
+    rt->last_launch = t_last_scan;
     if (!sync) {
         rt->async_flags_pending = true;
         return 0;
     }
     CU_TRY(cudaStreamSynchronize(rt->stream));
     rt->async_flags_pending = false;
-    if (rt->h_flags[kFlagTimeout]) return fail(err, "score_topk(%s): a bounded device wait gave up", metric_name(metric));
-    if (!rt->h_flags[kFlagOverflow]) {
-        if (rt->h_flags[kFlagInternal]) return fail(err, "score_topk(%s): selection found fewer than k candidates", metric_name(metric));
+    uint32_t fl[kNumFlags];
+    take_host_flags(rt, 0, fl);
+    if (fl[kFlagTimeout]) return fail(err, "score_topk(%s): a bounded device wait gave up", metric_name(metric));
+    if (!fl[kFlagOverflow]) {
+        if (fl[kFlagInternal]) return fail(err, "score_topk(%s): selection found fewer than k candidates", metric_name(metric));
         return 0;
     }
     // The candidate pool overflowed (scores arrive in an order that keeps beating the threshold).  Redo the
@@ -724,23 +807,32 @@ static int score_topk_locked(MantaB200Runtime* rt, const MantaB200Candidates* se
     int64_t chunk = std::min<int64_t>(cv.rows, (int64_t)1 << 20);
     cap = (uint32_t)(chunk + k);
     if (ensure_select_ws(rt, nq, cap, nb, &ws, err)) return 1;
-    if (prepare_queries(rt, cv, d_queries, nq, ws, 1, &qp, err)) return 1;
+    rt->ws_dirty = true;
+    if (reset_ws(rt, ws, nq, err)) return 1;
+    SelectArgs sa{};
+    sa.nq = nq;
+    sa.k = k;
+    sa.order = order;
+    if (sink) sa.sink = *sink;
     for (int64_t r0 = 0; r0 < cv.rows; r0 += chunk) {
         int64_t r1 = std::min(cv.rows, r0 + chunk);
-        if (scan_rows(rt, cv, qp, metric, order, k, r0, r1, ws, nq, false, err)) return 1;
+        if (stream_rows(rt, cv, d_queries, metric, order, k, r0, r1, ws, nq, nullptr, err)) return 1;
         sa.ws = ws;
         sa.write_back = (r1 < cv.rows) ? 1 : 0;
         sa.out_ids = sa.write_back ? nullptr : d_out_ids;
         sa.out_scores = sa.write_back ? nullptr : d_out_scores;
-        e = launch_select(rt->stream, sa);
+        ExchangeSink none;
+        if (sa.write_back) sa.sink = none;
+        else if (sink) sa.sink = *sink;
+        cudaError_t e = launch_select(rt->stream, sa);
         rt->stats.kernel_launches++;
         if (e != cudaSuccess) return fail_cuda(err, "launch select kernel", e);
     }
     CU_TRY(cudaMemcpyAsync(rt->h_flags, ws.flags, kNumFlags * 4, cudaMemcpyDeviceToHost, rt->stream));
     CU_TRY(cudaStreamSynchronize(rt->stream));
-    if (rt->h_flags[kFlagOverflow] || rt->h_flags[kFlagInternal])
-        return fail(err, "score_topk(%s): chunked selection failed (flags %u %u)", metric_name(metric),
-                    rt->h_flags[kFlagOverflow], rt->h_flags[kFlagInternal]);
+    take_host_flags(rt, 0, fl);
+    if (fl[kFlagOverflow] || fl[kFlagInternal])
+        return fail(err, "score_topk(%s): chunked selection failed (flags %u %u)", metric_name(metric), fl[kFlagOverflow], fl[kFlagInternal]);
     return 0;
 }
 
@@ -829,26 +921,21 @@ int manta_b200_score(MantaB200Runtime* rt, const MantaB200Candidates* set, int m
     if (ensure(rt, rt->queries, qbytes, err)) return 1;
     if (ensure(rt, rt->misc, obytes, err)) return 1;
     CU_TRY(cudaMemcpyAsync(rt->queries.p, queries, qbytes, cudaMemcpyHostToDevice, rt->stream));
-    SelectWs ws{};
-    QueryPrep qp;
-    if (prepare_queries(rt, cv, rt->queries.p, nq, ws, 0, &qp, err)) return 1;
     t_last_scan = MantaB200LaunchInfo{};
     for (int q0 = 0; q0 < nq;) {
-        int left = nq - q0;
-        int qt = left >= 4 ? 4 : (left >= 2 ? 2 : 1);
-        GemvShape s;
-        pick_gemv_shape(cv.chunks, &s);
-        if (s.cpl == 8) qt = 1;
-        GemvArgs a{};
+        const int left = nq - q0;
+        const int qt = left >= 4 ? 4 : (left >= 2 ? 2 : 1);
+        StreamArgs a{};
         a.cv = cv;
-        a.qp = qp;
+        a.queries = (const __half*)rt->queries.p;
         a.q0 = q0;
         a.qt = qt;
         a.metric = metric;
+        a.mode = kModeScores;
         a.row_begin = 0;
         a.row_end = cv.rows;
         a.out_scores = (float*)rt->misc.p;
-        cudaError_t e = launch_gemv(rt->stream, rt->sm_count, a, kModeScores);
+        cudaError_t e = launch_stream_scan(rt->stream, rt->sm_count, a);
         rt->stats.kernel_launches++;
         if (e != cudaSuccess) return fail_cuda(err, "launch score kernel", e);
         q0 += qt;
@@ -929,6 +1016,7 @@ static int batched_common(MantaB200Runtime* rt, int metric, int order, const flo
         sa.order = order;
         sa.out_ids = d_ids;
         sa.out_scores = d_sc;
+        sa.reset_after = 1;
         e = launch_select(rt->stream, sa);
         rt->stats.kernel_launches++;
         if (e != cudaSuccess) return fail_cuda(err, "launch select kernel", e);
@@ -1113,19 +1201,17 @@ int manta_b200_q8_accumulators(MantaB200Runtime* rt, const MantaB200Candidates* 
     if (ensure(rt, rt->queries, qbytes, err)) return 1;
     if (ensure(rt, rt->misc, obytes, err)) return 1;
     CU_TRY(cudaMemcpyAsync(rt->queries.p, query, qbytes, cudaMemcpyHostToDevice, rt->stream));
-    SelectWs ws{};
-    QueryPrep qp;
-    if (prepare_queries(rt, cv, rt->queries.p, 1, ws, 0, &qp, err)) return 1;
-    GemvArgs a{};
+    StreamArgs a{};
     a.cv = cv;
-    a.qp = qp;
+    a.queries = (const __half*)rt->queries.p;
     a.q0 = 0;
     a.qt = 1;
     a.metric = MANTA_B200_METRIC_COSINE;
+    a.mode = kModeAccum;
     a.row_begin = 0;
     a.row_end = cv.rows;
     a.out_acc = (int32_t*)rt->misc.p;
-    cudaError_t e = launch_gemv(rt->stream, rt->sm_count, a, kModeAccum);
+    cudaError_t e = launch_stream_scan(rt->stream, rt->sm_count, a);
     rt->stats.kernel_launches++;
     if (e != cudaSuccess) return fail_cuda(err, "launch score kernel", e);
     CU_TRY(cudaMemcpyAsync(out_acc, rt->misc.p, obytes, cudaMemcpyDeviceToHost, rt->stream));
@@ -1154,10 +1240,19 @@ int manta_b200_topk_merge_device(MantaB200Runtime* rt, int order, const int32_t*
     sa.order = order;
     sa.out_ids = d_out_ids;
     sa.out_scores = d_out_scores;
+    sa.reset_after = 1;
+    sa.flags_out = rt->h_flags + 4;   // "fewer than k entries in the lists" is raised in the merge's host words
     e = launch_select(rt->stream, sa);
     rt->stats.kernel_launches++;
     if (e != cudaSuccess) return fail_cuda(err, "launch select kernel", e);
-    if (sync) CU_TRY(cudaStreamSynchronize(rt->stream));
+    if (!sync) {
+        rt->async_exchange_pending = true;
+        return 0;
+    }
+    CU_TRY(cudaStreamSynchronize(rt->stream));
+    uint32_t fl[kNumFlags];
+    take_host_flags(rt, 4, fl);
+    if (fl[kFlagInternal]) return fail(err, "topk_merge: the lists hold fewer than k entries");
     return 0;
 }
 
@@ -1172,11 +1267,12 @@ int manta_b200_gather_rows(MantaB200Runtime* rt, const MantaB200Candidates* set,
     const size_t ibytes = (size_t)n * 4, obytes = (size_t)n * cv.cols * 4;
     if (ensure(rt, rt->out_ids, ibytes + 64, err)) return 1;
     if (ensure(rt, rt->misc, obytes, err)) return 1;
-    if (ensure(rt, rt->flags, kNumFlags * 4, err)) return 1;
-    // out_ids: [n ids][pad][bad id]; flags[3] doubles as the "bad id seen" word
+    if (ensure(rt, rt->embed_flag, 16, err)) return 1;
+    // out_ids: [n ids][pad][bad id]; the "bad id seen" word is word 2 of the small flag buffer the embedding front
+    // end keeps its own two words in
     int32_t* d_ids = (int32_t*)rt->out_ids.p;
     int32_t* d_bad = d_ids + n + 8;
-    uint32_t* d_flag = (uint32_t*)rt->flags.p + 3;
+    uint32_t* d_flag = (uint32_t*)rt->embed_flag.p + 2;
     CU_TRY(cudaMemcpyAsync(d_ids, ids, ibytes, cudaMemcpyHostToDevice, rt->stream));
     CU_TRY(cudaMemsetAsync(d_flag, 0, 4, rt->stream));
     launch_gather_rows(rt->stream, cv, d_ids, n, (float*)rt->misc.p, d_bad, d_flag);

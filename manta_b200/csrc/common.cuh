@@ -52,12 +52,12 @@ struct SelectWs {
     uint32_t* count;      // [nq]
     uint32_t* thr;        // [nq]
     uint32_t* bucket;     // [nq][nb]
-    uint32_t* flags;      // [0] pool overflow, [1] bounded wait gave up, [2] internal check failed
+    uint32_t* flags;      // [0] pool overflow, [1] bounded wait gave up, [2] internal check failed, [3] a peer's list is incomplete
     uint32_t cap;
     uint32_t nb;
 };
 
-enum { kFlagOverflow = 0, kFlagTimeout = 1, kFlagInternal = 2, kNumFlags = 4 };
+enum { kFlagOverflow = 0, kFlagTimeout = 1, kFlagInternal = 2, kFlagPeerOverflow = 3, kNumFlags = 4 };
 
 struct CandView {
     const uint8_t* data;     // packed rows
@@ -124,14 +124,6 @@ __device__ __forceinline__ float float_finish(int metric, float dotv, float dn2,
     return res + 0.0f;
 }
 
-__device__ __forceinline__ uint4 ld_stream16(const void* p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.L2::128B.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(p));
-    return v;
-}
-
 __device__ __forceinline__ uint32_t ld_relaxed_u32(const uint32_t* p) {
     uint32_t v;
     asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p));
@@ -140,31 +132,6 @@ __device__ __forceinline__ uint32_t ld_relaxed_u32(const uint32_t* p) {
 
 __device__ __forceinline__ void st_relaxed_u32(uint32_t* p, uint32_t v) {
     asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v));
-}
-
-// Appends one candidate to a query's pool.  Overflow only raises a flag: the host redoes the pass in
-// row chunks small enough that the pool cannot overflow.
-__device__ __forceinline__ void pool_append(const SelectWs& ws, int q, uint64_t key) {
-    uint32_t pos = atomicAdd(&ws.count[q], 1u);
-    if (pos < ws.cap) {
-        ws.pool[(size_t)q * ws.cap + pos] = key;
-    } else {
-        ws.flags[kFlagOverflow] = 1u;
-    }
-}
-
-// One warp: largest t such that at least k of the nb bucket maxima of query q are >= t (0 if fewer than k
-// buckets have reported).  Built bit by bit from the top; 32 counting passes over nb values.
-__device__ __forceinline__ uint32_t warp_kth_largest_bucket(const uint32_t* bucket, uint32_t nb, uint32_t k, int lane) {
-    uint32_t t = 0;
-    for (int bit = 31; bit >= 0; --bit) {
-        uint32_t cand = t | (1u << bit);
-        uint32_t cnt = 0;
-        for (uint32_t i = lane; i < nb; i += 32) cnt += (ld_relaxed_u32(bucket + i) >= cand) ? 1u : 0u;
-        cnt = __reduce_add_sync(0xffffffffu, cnt);
-        if (cnt >= k) t = cand;
-    }
-    return t;
 }
 
 }  // namespace mb200

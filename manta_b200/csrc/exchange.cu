@@ -52,11 +52,9 @@ struct PeerTable {
     unsigned char* inbox[kMaxWorld];
 };
 
-// Block p stores this rank's list into peer p's inbox slot [parity][rank], then publishes the epoch.  Block 0 also
-// clears the flags of the merge that follows on this stream.
+// Block p stores this rank's list into peer p's inbox slot [parity][rank], then publishes the status and the epoch.
 __global__ void exchange_push_kernel(PeerTable peers, const int32_t* __restrict__ ids, const float* __restrict__ scores, int n,
-                                     size_t slot_words, int world, int rank, int parity, uint32_t epoch, uint32_t* ws_flags) {
-    if (blockIdx.x == 0 && threadIdx.x < mb200::kNumFlags) ws_flags[threadIdx.x] = 0;
+                                     size_t slot_words, int world, int rank, int parity, uint32_t epoch) {
     unsigned char* box = peers.inbox[blockIdx.x];
     int32_t* dst = reinterpret_cast<int32_t*>(box + mb200::exchange_slot_offset(slot_words, world, parity, rank));
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
@@ -65,8 +63,11 @@ __global__ void exchange_push_kernel(PeerTable peers, const int32_t* __restrict_
     }
     __threadfence_system();
     __syncthreads();
-    if (threadIdx.x == 0)
-        mb200::st_release_sys_u32(reinterpret_cast<uint32_t*>(box + mb200::exchange_flag_offset(slot_words, world, parity, rank)), epoch);
+    if (threadIdx.x == 0) {
+        uint32_t* word = reinterpret_cast<uint32_t*>(box + mb200::exchange_flag_offset(slot_words, world, parity, rank));
+        word[1] = 0u;   // status: a list handed over by the caller is complete
+        mb200::st_release_sys_u32(word, epoch);
+    }
 }
 
 }  // namespace
@@ -76,6 +77,7 @@ int score_topk_into_sink(MantaB200Runtime* rt, const MantaB200Candidates* set, i
                          int k, const ExchangeSink& sink, char** err);  // api.cu
 int exchange_select_ws(MantaB200Runtime* rt, int nq, uint32_t cap, SelectWs* ws, char** err);  // api.cu
 void exchange_note_async_flags(MantaB200Runtime* rt, const SelectWs& ws, int sync, char** err, int* rc);  // api.cu
+uint32_t* exchange_host_flags(MantaB200Runtime* rt);  // api.cu
 }
 
 extern "C" {
@@ -223,6 +225,8 @@ static int exchange_merge_tail(MantaB200Runtime* rt, MantaB200Exchange* ex, cons
     sa.src.parity = parity;
     sa.src.epoch = epoch;
     sa.src.spin_limit = ex->spin_limit;   // 200 ns naps before a missing list is reported
+    sa.flags_out = mb200::exchange_host_flags(rt);   // pinned host words: no copy after the kernel
+    sa.reset_after = 1;                               // the workspace is clean again for the next fused pass
     e = mb200::launch_select(ri.stream, sa);
     if (e != cudaSuccess) return fail(err, "topk_exchange_merge: select launch failed: %s", cudaGetErrorString(e));
     int rc = 0;
@@ -277,8 +281,7 @@ int manta_b200_topk_exchange_merge_device(MantaB200Runtime* rt, MantaB200Exchang
     const int parity = (int)(epoch & 1u);
     PeerTable pt;
     for (int r = 0; r < kMaxWorld; ++r) pt.inbox[r] = ex->peer[r];
-    exchange_push_kernel<<<ex->world, 256, 0, ri.stream>>>(pt, d_ids, d_scores, nq * k, ex->slot_words, ex->world, ex->rank, parity, epoch,
-                                                          ws.flags);
+    exchange_push_kernel<<<ex->world, 256, 0, ri.stream>>>(pt, d_ids, d_scores, nq * k, ex->slot_words, ex->world, ex->rank, parity, epoch);
     mb200::count_launch();
     e = cudaGetLastError();
     if (e != cudaSuccess) return fail(err, "topk_exchange_merge: launch failed: %s", cudaGetErrorString(e));
@@ -295,6 +298,8 @@ int manta_b200_topk_exchange_merge_device(MantaB200Runtime* rt, MantaB200Exchang
     sa.src.parity = parity;
     sa.src.epoch = epoch;
     sa.src.spin_limit = ex->spin_limit;   // 200 ns naps before a missing list is reported
+    sa.flags_out = mb200::exchange_host_flags(rt);   // pinned host words: no copy after the kernel
+    sa.reset_after = 1;                               // the workspace is clean again for the next fused pass
     e = mb200::launch_select(ri.stream, sa);
     if (e != cudaSuccess) return fail(err, "topk_exchange_merge: select launch failed: %s", cudaGetErrorString(e));
     int rc = 0;

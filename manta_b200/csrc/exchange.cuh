@@ -25,21 +25,29 @@ __device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
 
 // Called by all threads of the block that selects for query q.  Waits (bounded) until every rank's slot of this
 // parity carries the epoch, then writes the keys of all lists into the query's pool (entries a shard could not
-// fill, id < 0, rank below everything).  A list that does not arrive raises the time-out flag and empties the pool.
-__device__ __forceinline__ void exchange_collect(const ExchangeSource& src, int q, int nq, int k, int order, const SelectWs& ws) {
-    __shared__ int ok_s;
-    if (threadIdx.x == 0) ok_s = 1;
+// fill, id < 0, rank below everything).  A list that does not arrive raises the time-out flag and empties the pool;
+// a list whose sender marked it incomplete (its candidate pool overflowed) raises the peer-overflow flag.
+__device__ __forceinline__ void exchange_collect(const ExchangeSource& src, int q, int nq, int k, int order, const SelectWs& ws,
+                                                 uint32_t* flags) {
+    __shared__ int ok_s, bad_s;
+    if (threadIdx.x == 0) {
+        ok_s = 1;
+        bad_s = 0;
+    }
     __syncthreads();
     if ((int)threadIdx.x < src.world) {
         const uint32_t* flag = reinterpret_cast<const uint32_t*>(src.inbox + exchange_flag_offset(src.slot_words, src.world, src.parity, threadIdx.x));
         uint32_t spin = 0;
+        bool arrived = true;
         while (ld_acquire_sys_u32(flag) != src.epoch) {
             if (++spin > src.spin_limit) {
                 ok_s = 0;
+                arrived = false;
                 break;
             }
             __nanosleep(200);
         }
+        if (arrived && __ldcv(flag + 1) != 0u) bad_s = 1;
     }
     __syncthreads();
     const float sign = (order == MANTA_B200_ORDER_SMALLEST) ? -1.0f : 1.0f;
@@ -57,8 +65,10 @@ __device__ __forceinline__ void exchange_collect(const ExchangeSource& src, int 
     if (threadIdx.x == 0) {
         ws.count[q] = ok_s ? (uint32_t)per : 0u;
         ws.thr[q] = 0;
-        if (!ok_s) ws.flags[kFlagTimeout] = 1u;
+        if (!ok_s) flags[kFlagTimeout] = 1u;
+        if (bad_s) flags[kFlagPeerOverflow] = 1u;
     }
+    __threadfence();
     __syncthreads();
 }
 

@@ -40,60 +40,130 @@ cudaError_t launch_embed_pooled(cudaStream_t st, const void* table_f16, int voca
                                 const int32_t* d_tokens, const int32_t* d_mask, int batch, int seq, int order, float* d_out_f32,
                                 void* d_out_f16, int32_t* d_bad_token, uint32_t* d_bad_flag);
 
-// Streaming (GEMV) scoring kernel.  mode: what the epilogue does with a score.
+// Streaming scoring kernel (stream_scan.cuh).  mode: what the epilogue does with a score.
 enum { kModeScores = 0, kModeTopk = 1, kModeAccum = 2 };
-struct GemvArgs {
+constexpr int kScanStages = 3;          // ring depth: kScanStages - 1 tiles in flight per warp
+constexpr int kScanMaxWarps = 8;        // warps per block (fewer when a row is very wide)
+constexpr int kScanBucketSlots = 2;     // running maxima per warp (tiles alternate between them)
+constexpr int kScanRefreshWords = 4864; // bucket maxima a threshold refresh can stage in shared memory
+constexpr int kScanObserveMax = 48;     // tiles a warp observes at most before it appends without a threshold
+constexpr int kSelSmemKeys = 4096;      // keys the selection sorts in shared memory
+// shared memory a block needs for select_block: keys, a 256-bin histogram, four scalars
+constexpr size_t kSelSmemBytes = (size_t)kSelSmemKeys * 8 + 256 * 4 + 16;
+
+// Where a shard's selection also stores its k results: slot [parity][rank] of every rank's exchange inbox (peer
+// stores), followed by the status and epoch words of that slot once all queries are written.  world == 0: no sink.
+struct ExchangeSink {
+    unsigned char* inbox[16] = {};
+    size_t slot_words = 0;
+    int world = 0;
+    int rank = 0;
+    int parity = 0;
+    uint32_t epoch = 0;
+    uint32_t* done = nullptr;   // device counter of the queries that have been stored (returns to 0)
+};
+
+// Geometry of a launch, chosen on the host (stream_scan_geometry).
+struct ScanGeometry {
+    int rows_per_tile;   // R
+    int lpr_shift;       // log2(32 / R)
+    int cstride;         // row stride inside a stage, in 16-byte chunks (>= chunks, padded against bank conflicts)
+    int stage_bytes;     // codes + per-row values, multiple of 16
+    int scale_off;       // q4: byte offset of the block scales inside a stage
+    int scale_unit;      // q4: 16 or 4 = size of the asynchronous copies that bring the block scales, 0 = read them from global memory
+    int stat_off;        // byte offset of the R row statistics
+    int rscale_off;      // q8: byte offset of the R row scales
+    int q_bytes;         // shared memory per query (planes or f32 values), multiple of 128
+    int warps;           // warps per block
+};
+
+struct StreamArgs {
     CandView cv;
-    QueryPrep qp;
-    int q0;            // first query of this pass
-    int qt;            // queries in this pass (1, 2 or 4)
+    const __half* queries;   // [nq][cols] device, IEEE half
+    int q0;                  // first query of this launch
+    int qt;                  // queries in this launch (<= QT)
     int metric;
     int order;
     int k;
-    int64_t row_begin; // rows [row_begin, row_end) of the set are scanned
+    int mode;                // kModeScores / kModeTopk / kModeAccum
+    int64_t row_begin;       // rows [row_begin, row_end) of the set are scanned
     int64_t row_end;
-    SelectWs ws;       // kModeTopk
-    float* out_scores; // kModeScores: [nq][rows]
-    int32_t* out_acc;  // kModeAccum: [rows][3]
-    int no_startup_wait; // debugging: do not wait for the first threshold after two unfiltered tiles
+    SelectWs ws;             // kModeTopk
+    float* out_scores;       // kModeScores: [nq][rows]
+    int32_t* out_acc;        // kModeAccum: [rows][3]
+    ScanGeometry g;
+    // tail of a fused pass (kModeTopk): the last block selects, stores and cleans the workspace
+    int fused_select;
+    int nq_total;            // queries of the whole pass (the exchange's epoch goes out after the last one)
+    uint32_t* done_blocks;   // device counter, zero between launches
+    uint32_t* host_flags;    // pinned host words that receive the pass's raised flags (sticky until the host clears them)
+    int32_t* out_ids;        // [nq][k]
+    float* out_topk_scores;  // [nq][k]
+    ExchangeSink sink;
 };
-// How a row of `chunks` 16-byte chunks is split over lanes: lpr lanes per row, cpl chunks per lane, u rows in
-// flight per lane group.  Smallest padded footprint first, then the wider group.
-struct GemvShape {
-    int lpr, cpl, u;
-};
-inline bool pick_gemv_shape(int chunks, GemvShape* out) {
-    const int lprs[3] = {32, 16, 8};
-    int best_cost = 1 << 30;
-    GemvShape best{0, 0, 0};
-    bool ok = false;
-    for (int i = 0; i < 3; ++i) {
-        int lpr = lprs[i];
-        int cpl = (chunks + lpr - 1) / lpr;
-        if (cpl > 4 && !(lpr == 32 && cpl <= 8)) continue;
-        if (cpl > 4) cpl = 8;
-        int cost = lpr * cpl;
-        if (cost < best_cost) {
-            best_cost = cost;
-            best.lpr = lpr;
-            best.cpl = cpl;
-            ok = true;
-        }
-    }
-    if (ok) {
-        best.u = (best.cpl == 1) ? 8 : (best.cpl == 2) ? 4 : (best.cpl <= 4) ? 2 : 1;
-        if (out) *out = best;
-    }
-    return ok;
+
+// Bytes a stage may take for the candidate codes of one tile; a row wider than this gets a tile of its own.
+constexpr int kScanStageBudget = 6656;
+
+inline int scan_padded_stride(int chunks, int lpr) {
+    if (lpr >= 8) return chunks;
+    // the 8 lanes that share a shared-memory wavefront read rows r, r+1, ... at chunk offsets 0..lpr-1: they fall into
+    // distinct 16-byte bank groups when the stride is congruent to lpr modulo 2*lpr
+    const int m = 2 * lpr;
+    return chunks + ((lpr - chunks % m) + m) % m;
 }
 
-// Number of buckets (running maxima) the kernel keeps per query for a given grid; the workspace must
-// provide at least this many.
-int gemv_grid_size(int sm_count);
-int gemv_bucket_count(int sm_count);
-// Rows that can be scanned before a useful threshold exists (every one of them is appended).
-int gemv_first_burst_rows(int sm_count, int chunks);
-cudaError_t launch_gemv(cudaStream_t st, int sm_count, const GemvArgs& a, int mode);
+// Picks the tile geometry for a candidate layout; returns false when even one warp with one row per tile does not fit.
+inline bool stream_scan_geometry(const CandView& cv, int qt, int64_t row_begin, ScanGeometry* g, size_t* smem_bytes) {
+    const int C = cv.chunks;
+    if (C <= 0) return false;
+    int R = 32;
+    while (R > 1 && (size_t)R * scan_padded_stride(C, 32 / R) * 16 > (size_t)kScanStageBudget) R >>= 1;
+    const int lpr = 32 / R;
+    int shift = 0;
+    while ((1 << shift) < lpr) ++shift;
+    g->rows_per_tile = R;
+    g->lpr_shift = shift;
+    g->cstride = scan_padded_stride(C, lpr);
+    int off = R * g->cstride * 16;
+    g->scale_off = 0;
+    g->scale_unit = 0;
+    if (cv.layout == MANTA_B200_LAYOUT_Q4_B32_F16) {
+        const uintptr_t sp = (uintptr_t)cv.scales;
+        if (C % 8 == 0 && (sp & 15) == 0) g->scale_unit = 16;
+        else if (C % 2 == 0 && (sp & 3) == 0) g->scale_unit = 4;
+        (void)row_begin;   // a row's block scales start on a multiple of 2*C bytes, so any first row is aligned for these units
+        if (g->scale_unit) {
+            g->scale_off = off;
+            off += (R * C * 2 + 15) / 16 * 16;
+        }
+    }
+    g->stat_off = off;
+    off += (R * 4 + 15) / 16 * 16;
+    g->rscale_off = off;
+    if (cv.layout == MANTA_B200_LAYOUT_Q8_ROW_F32) off += (R * 4 + 15) / 16 * 16;
+    g->stage_bytes = off;
+    const int per_chunk = (cv.layout == MANTA_B200_LAYOUT_Q4_B32_F16) ? 64 : 32;   // q8: two planes of 16 bytes; q4: two of 32; f16: 8 floats
+    g->q_bytes = (C * per_chunk + 127) / 128 * 128;
+    const size_t fixed = 256 + (size_t)qt * g->q_bytes + (size_t)kScanRefreshWords * 4;
+    const size_t limit = 232448;   // 227 KB of dynamic shared memory per block
+    int warps = kScanMaxWarps;
+    while (warps > 1 && fixed + (size_t)warps * kScanStages * g->stage_bytes > limit) warps >>= 1;
+    size_t total = fixed + (size_t)warps * kScanStages * g->stage_bytes;
+    if (total > limit) return false;
+    const size_t ring_min = kSelSmemBytes;   // the tail's selection reuses the ring
+    if ((size_t)warps * kScanStages * g->stage_bytes < ring_min) total = fixed + ring_min;
+    g->warps = warps;
+    *smem_bytes = total;
+    return true;
+}
+
+// Buckets (running maxima) per query the workspace must provide for any launch of the scan on this device.
+inline int stream_bucket_count(int sm_count) { return sm_count * kScanMaxWarps * kScanBucketSlots; }
+// Runs the scan for a.qt <= 4 queries; the geometry is filled in by the launcher.
+cudaError_t launch_stream_scan(cudaStream_t st, int sm_count, const StreamArgs& a);
+// Zeroes the selection workspace of nq queries (fill counts, thresholds, bucket maxima, flags, the block counter).
+cudaError_t launch_ws_reset(cudaStream_t st, const SelectWs& ws, int nq, uint32_t* done_blocks);
 
 // Final selection: best k keys of each query's pool, sorted best first.  With write_back the k keys are
 // also written to the front of the pool, count becomes k and the threshold becomes the k-th goodness
@@ -108,18 +178,6 @@ struct ExchangeSource {
     uint32_t spin_limit = 0; // 200 ns naps before a missing list is reported
 };
 
-// Where a shard's selection also stores its k results: slot [parity][rank] of every rank's exchange inbox (peer
-// stores), followed by the epoch word of that slot once all queries are written.  world == 0: no sink.
-struct ExchangeSink {
-    unsigned char* inbox[16] = {};
-    size_t slot_words = 0;
-    int world = 0;
-    int rank = 0;
-    int parity = 0;
-    uint32_t epoch = 0;
-    uint32_t* done = nullptr;   // device counter of the blocks that have stored their query (returns to 0)
-};
-
 struct SelectArgs {
     SelectWs ws;
     int nq;
@@ -130,6 +188,8 @@ struct SelectArgs {
     float* out_scores;   // [nq][k] or null
     ExchangeSource src;  // optional: fill the pool from the exchange inbox first
     ExchangeSink sink;   // optional: also store the results into every rank's inbox
+    uint32_t* flags_out = nullptr;  // where this selection raises its flags (null: ws.flags); may be pinned host memory
+    int reset_after = 0; // leave the query's fill count and threshold at zero (the workspace is clean for the next pass)
 };
 cudaError_t launch_select(cudaStream_t st, const SelectArgs& a);
 

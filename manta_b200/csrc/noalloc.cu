@@ -21,22 +21,14 @@ constexpr int kStaticMaxQueries = 4;
 constexpr int kStaticMaxK = 256;
 constexpr int kStaticMaxCols = 4096;
 constexpr uint32_t kStaticPoolCap = 1u << 17;   // candidate keys per query
-constexpr uint32_t kStaticBuckets = 4096;       // running maxima per query
-constexpr int kStaticPlaneStride = 4096;        // bytes per query in one int8 plane
-
+constexpr uint32_t kStaticBuckets = 8192;       // running maxima per query
 // carve-up of the scratch array (every offset is a multiple of 256)
-constexpr size_t kOffHeaders = 0;
-constexpr size_t kOffQf32 = 256;
-constexpr size_t kOffPlaneHi = kOffQf32 + (size_t)kStaticMaxQueries * kStaticMaxCols * 4;
-constexpr size_t kOffPlaneLo = kOffPlaneHi + (size_t)kStaticMaxQueries * kStaticPlaneStride;
-constexpr size_t kOffCount = kOffPlaneLo + (size_t)kStaticMaxQueries * kStaticPlaneStride;
+constexpr size_t kOffCount = 0;
 constexpr size_t kOffThr = kOffCount + 256;
-constexpr size_t kOffFlags = kOffThr + 256;
+constexpr size_t kOffFlags = kOffThr + 256;      // [0..3] flags, [4] counter of finished blocks
 constexpr size_t kOffBucket = kOffFlags + 256;
 constexpr size_t kOffPool = kOffBucket + (size_t)kStaticMaxQueries * kStaticBuckets * 4;
-constexpr size_t kScratchBytes = kOffPool + (size_t)kStaticMaxQueries * kStaticPoolCap * 8;  // about 4.4 MB
-
-static_assert(sizeof(QueryHeader) * kStaticMaxQueries <= 256, "headers must fit their slot");
+constexpr size_t kScratchBytes = kOffPool + (size_t)kStaticMaxQueries * kStaticPoolCap * 8;  // about 4.3 MB
 
 // The scratch itself.  In host code this name is only a handle for the runtime API, not a device address:
 // the address is fetched per device with cudaGetSymbolAddress below and only that pointer goes to kernels.
@@ -77,13 +69,13 @@ extern "C" int manta_b200_score_topk_static(MantaB200Runtime* rt, const MantaB20
     if (k <= 0 || k > cv.rows) return fail(err, "topk limit %d out of range for %lld scores", k, (long long)cv.rows);
     if (k > kStaticMaxK) return fail(err, "score_topk_static: k = %d exceeds the fixed scratch (at most %d)", k, kStaticMaxK);
     if (cv.cols > kStaticMaxCols) return fail(err, "score_topk_static: %d columns exceed the fixed scratch (at most %d)", cv.cols, kStaticMaxCols);
-    const int plane_bytes = (cv.layout == MANTA_B200_LAYOUT_Q4_B32_F16) ? cv.chunks * 32 : cv.chunks * 16;
-    if (plane_bytes > kStaticPlaneStride) return fail(err, "score_topk_static: query planes of %d bytes exceed the fixed scratch", plane_bytes);
-    if (gemv_bucket_count(ri.sm_count) > (int)kStaticBuckets) return fail(err, "score_topk_static: this GPU needs more bucket slots than the fixed scratch holds");
+    if (stream_bucket_count(ri.sm_count) > (int)kStaticBuckets) return fail(err, "score_topk_static: this GPU needs more bucket slots than the fixed scratch holds");
     if (ri.device < 0 || ri.device >= kMaxDevices) return fail(err, "score_topk_static: device ordinal %d out of range", ri.device);
-    GemvShape shape;
-    if (!pick_gemv_shape(cv.chunks, &shape)) return fail(err, "score_topk_static: row too wide");
-    if (shape.cpl == 8 && nq != 1) return fail(err, "score_topk_static: rows this wide are scored one query per call");
+    {
+        ScanGeometry geo;
+        size_t smem = 0;
+        if (!stream_scan_geometry(cv, nq <= 1 ? 1 : (nq <= 2 ? 2 : 4), 0, &geo, &smem)) return fail(err, "score_topk_static: row too wide");
+    }
 
     std::lock_guard<std::mutex> lk(*ri.mu);
     cudaError_t e = cudaSetDevice(ri.device);
@@ -109,20 +101,12 @@ extern "C" int manta_b200_score_topk_static(MantaB200Runtime* rt, const MantaB20
     ws.flags = (uint32_t*)(base + kOffFlags);
     ws.cap = kStaticPoolCap;
     ws.nb = kStaticBuckets;
-    QueryPrep qp;
-    qp.headers = (const QueryHeader*)(base + kOffHeaders);
-    qp.qf32 = (const float*)(base + kOffQf32);
-    qp.plane_hi = (const int8_t*)(base + kOffPlaneHi);
-    qp.plane_lo = (const int8_t*)(base + kOffPlaneLo);
-    qp.plane_stride = kStaticPlaneStride;
-    qp.nq = nq;
-
-    // The prep kernel clears what must start at zero (fill counts, thresholds, bucket maxima, flags); the pool
-    // itself may keep the previous call's keys, only the first `count` entries are ever read.
-    launch_query_prep(ri.stream, d_queries, nq, cv.cols, cv.layout, kStaticPlaneStride, (QueryHeader*)(base + kOffHeaders),
-                      (float*)(base + kOffQf32), (int8_t*)(base + kOffPlaneHi), (int8_t*)(base + kOffPlaneLo), ws, 1);
-    e = cudaGetLastError();
-    if (e != cudaSuccess) return fail(err, "score_topk_static: query prep launch: %s", cudaGetErrorName(e));
+    uint32_t* done_blocks = ws.flags + 4;
+    // What must start at zero (fill counts, thresholds, bucket maxima, flags, the block counter) is cleared by a
+    // small kernel; the pool itself may keep the previous call's keys, only the first `count` entries are ever read.
+    // The queries are prepared inside the scan, in shared memory: no scratch for them.
+    e = launch_ws_reset(ri.stream, ws, nq, done_blocks);
+    if (e != cudaSuccess) return fail(err, "score_topk_static: workspace reset launch: %s", cudaGetErrorName(e));
     // Rows are scanned in chunks of (pool capacity - k) rows and the pool is compacted to the best k between
     // chunks, so the fixed pool cannot overflow whatever order the scores arrive in.
     const int64_t chunk = (int64_t)ws.cap - k > 0 ? (int64_t)ws.cap - k : cv.rows;
@@ -131,18 +115,20 @@ extern "C" int manta_b200_score_topk_static(MantaB200Runtime* rt, const MantaB20
         for (int q0 = 0; q0 < nq;) {
             const int left = nq - q0;
             const int qt = left >= 4 ? 4 : (left >= 2 ? 2 : 1);
-            GemvArgs a{};
+            StreamArgs a{};
             a.cv = cv;
-            a.qp = qp;
+            a.queries = (const __half*)d_queries;
             a.q0 = q0;
             a.qt = qt;
             a.metric = metric;
             a.order = order;
             a.k = k;
+            a.mode = kModeTopk;
             a.row_begin = r0;
             a.row_end = r1;
             a.ws = ws;
-            e = launch_gemv(ri.stream, ri.sm_count, a, kModeTopk);
+            a.nq_total = nq;
+            e = launch_stream_scan(ri.stream, ri.sm_count, a);
             if (e != cudaSuccess) return fail(err, "score_topk_static: scan launch: %s", cudaGetErrorName(e));
             q0 += qt;
         }

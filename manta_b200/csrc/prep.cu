@@ -277,6 +277,27 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(CandView cv, const int
     }
 }
 
+// ---- workspace reset ---------------------------------------------------------------------------------------------
+// One block per query: fill count, threshold and bucket maxima to zero; block 0 also clears the flags and the counter
+// of finished blocks.  The fused scan leaves its workspace clean by itself; this kernel runs only after a pass that
+// did not (the tensor-core pass, a chunked rerun, an error).
+__global__ void __launch_bounds__(256) ws_reset_kernel(SelectWs ws, uint32_t* done_blocks) {
+    const int q = blockIdx.x;
+    if (threadIdx.x == 0) {
+        ws.count[q] = 0;
+        ws.thr[q] = 0;
+    }
+    for (uint32_t i = threadIdx.x; i < ws.nb; i += blockDim.x) ws.bucket[(size_t)q * ws.nb + i] = 0;
+    if (q == 0 && threadIdx.x < kNumFlags) ws.flags[threadIdx.x] = 0;
+    if (q == 0 && threadIdx.x == 0 && done_blocks != nullptr) *done_blocks = 0;
+}
+
+cudaError_t launch_ws_reset(cudaStream_t st, const SelectWs& ws, int nq, uint32_t* done_blocks) {
+    ws_reset_kernel<<<nq, 256, 0, st>>>(ws, done_blocks);
+    count_launch();
+    return cudaGetLastError();
+}
+
 // ---- launchers ----------------------------------------------------------------------------------------------
 void launch_query_prep(cudaStream_t st, const void* d_queries_f16, int nq, int cols, int layout, int plane_stride,
                        QueryHeader* headers, float* qf32, int8_t* plane_hi, int8_t* plane_lo, const SelectWs& ws,

@@ -1,0 +1,616 @@
+// Streaming scoring kernel: 1, 2 or 4 queries against packed candidate rows, every stored byte read once.
+//
+// Data movement.  A warp owns "tiles" of R consecutive rows (R a power of two, 1..32) and strides over the row range.
+// The tile's bytes are contiguous in HBM; the 32 lanes copy them 16 bytes at a time, lane after lane, with
+// asynchronous copies (cp.async.cg, no registers held in flight) into the warp's own three-stage ring in shared
+// memory, so every global access is a fully coalesced 512-byte warp request.  The copy lays rows out with a padded
+// stride chosen so that the reads below are free of bank conflicts.  Two tiles are in flight per warp while one is
+// consumed.  The small per-row values (row scale, row statistic, q4 block scales) travel through the same ring.
+//
+// Arithmetic.  A row is consumed by LPR = 32/R adjacent lanes, each taking every LPR-th 16-byte chunk of the row
+// from shared memory; the query (for q8/q4 two int8 planes q ~= s_hi*hi + s_lo*lo, for f16 candidates f32 values)
+// is prepared by the block itself at start-up and read from shared memory as a broadcast.  q8/q4 accumulate with
+// dp4a into int32 (exact, order-free), f16 with fma.  log2(LPR) shuffle steps finish a row, one lane per row runs
+// the score epilogue.  Warps never synchronise with each other inside the loop.
+//
+// Top-k.  A row's score enters the query's pool when it is not below the query's threshold.  The threshold is the
+// k-th largest of the per-warp running maxima ("buckets": disjoint row sets, so k bucket maxima >= t prove that k
+// rows score >= t); it can only be too low, never too high, so the pool always contains the true top k.  Until a
+// first threshold exists a warp only observes (scores, bucket maxima); once it exists the warp re-reads the tiles it
+// observed (still in L2) and appends what passes, so nothing waits and the pool never sees an unfiltered burst.
+// The last block to finish selects the exact top k of the launch's queries (select.cuh), stores them (sharded: also
+// into every rank's exchange inbox) and leaves the workspace zeroed for the next pass: a fused step is one launch.
+#pragma once
+
+#include "select.cuh"
+
+namespace mb200 {
+
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global.L2::128B [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async4(void* smem_dst, const void* gmem_src) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// ---- query preparation inside the scan ------------------------------------------------------------------------
+// One warp prepares one query into shared memory: header, and either the two int8 planes in the order the consumer
+// reads them (q8: element order; q4: per 32-element block, per 8-element group the even elements then the odd ones,
+// matching the nibble unpack) or the f32 values (f16 candidates), zero padded to whole chunks.
+// ||q||^2 is summed in f64: lane l adds elements l, l+32, ... in order, then the 32 partial sums are combined by an
+// xor butterfly (16, 8, 4, 2, 1); the squared norm of the query the planes represent is summed the same way.  The
+// stand-alone preparation kernel (prep.cu) and the CPU model of the packed path use the same order.
+__device__ __forceinline__ void quantise_query_element(float v, float sh, float sl, bool zero, float* h, float* l) {
+    *h = 0.0f;
+    *l = 0.0f;
+    if (zero) return;
+    float hh = roundf(__fdiv_rn(v, sh));
+    hh = fminf(fmaxf(hh, -127.0f), 127.0f);
+    const float rem = __fmaf_rn(-hh, sh, v);
+    float ll = 0.0f;
+    if (sl != 0.0f) {
+        ll = roundf(__fdiv_rn(rem, sl));
+        ll = fminf(fmaxf(ll, -127.0f), 127.0f);
+    }
+    *h = hh;
+    *l = ll;
+}
+
+template <int LAYOUT>
+__device__ __forceinline__ void prepare_query_warp(const __half* __restrict__ src, int cols, int chunks, int lane, QueryHeader* hdr,
+                                                   unsigned char* q_s) {
+    constexpr bool kF16 = LAYOUT == MANTA_B200_LAYOUT_F16;
+    constexpr bool kQ4 = LAYOUT == MANTA_B200_LAYOUT_Q4_B32_F16;
+    float amax = 0.0f;
+    double part = 0.0;
+    for (int c = lane; c < cols; c += 32) {
+        const float v = __half2float(src[c]);
+        amax = fmaxf(amax, fabsf(v));
+        part = __dadd_rn(part, __dmul_rn((double)v, (double)v));
+    }
+    for (int off = 16; off > 0; off >>= 1) {
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+        part = __dadd_rn(part, __shfl_xor_sync(0xffffffffu, part, off));
+    }
+    QueryHeader h;
+    h.qn = __double2float_rn(__dsqrt_rn(part));
+    h.qinv = (h.qn > 0.0f) ? __fdiv_rn(1.0f, h.qn) : 0.0f;
+    h.qn2d = part;
+    h.qhat2 = part;
+    h.s_hi = 0.0f;
+    h.s_lo = 0.0f;
+    if (amax > 0.0f) {
+        h.s_hi = __fdiv_rn(amax, 127.0f);
+        h.s_lo = __fdiv_rn(h.s_hi, 254.0f);
+    }
+    if constexpr (kF16) {
+        float* qf = reinterpret_cast<float*>(q_s);
+        for (int c = lane; c < chunks * 8; c += 32) qf[c] = (c < cols) ? __half2float(src[c]) : 0.0f;
+    } else {
+        const bool zero = !(amax > 0.0f);
+        const int plane = kQ4 ? chunks * 32 : chunks * 16;   // bytes of one plane
+        int8_t* hi = reinterpret_cast<int8_t*>(q_s);
+        int8_t* lo = hi + plane;
+        for (int c = lane; c < plane; c += 32) {
+            int e = c;   // c indexes the plane in storage order; e is the query element stored there
+            if constexpr (kQ4) {
+                const int blk = c >> 5, w = (c >> 2) & 7, b = c & 3;
+                e = blk * 32 + (w >> 1) * 8 + 2 * b + (w & 1);
+            }
+            float hh = 0.0f, ll = 0.0f;
+            if (e < cols) quantise_query_element(__half2float(src[e]), h.s_hi, h.s_lo, zero, &hh, &ll);
+            hi[c] = (int8_t)hh;
+            lo[c] = (int8_t)ll;
+        }
+        double p2 = 0.0;
+        for (int c = lane; c < cols; c += 32) {
+            float hh, ll;
+            quantise_query_element(__half2float(src[c]), h.s_hi, h.s_lo, zero, &hh, &ll);
+            const double v = zero ? 0.0 : __dadd_rn(__dmul_rn((double)hh, (double)h.s_hi), __dmul_rn((double)ll, (double)h.s_lo));
+            p2 = __dadd_rn(p2, __dmul_rn(v, v));
+        }
+        for (int off = 16; off > 0; off >>= 1) p2 = __dadd_rn(p2, __shfl_xor_sync(0xffffffffu, p2, off));
+        h.qhat2 = p2;
+    }
+    if (lane == 0) *hdr = h;
+}
+
+template <int LAYOUT, int QT>
+__global__ void __launch_bounds__(kScanMaxWarps * 32, 1) stream_scan_kernel(const StreamArgs a) {
+    constexpr bool kQ8 = LAYOUT == MANTA_B200_LAYOUT_Q8_ROW_F32;
+    constexpr bool kQ4 = LAYOUT == MANTA_B200_LAYOUT_Q4_B32_F16;
+    constexpr bool kF16 = LAYOUT == MANTA_B200_LAYOUT_F16;
+    constexpr int S = kScanStages;
+
+    extern __shared__ __align__(128) unsigned char smem[];
+    QueryHeader* hdr_s = reinterpret_cast<QueryHeader*>(smem);                   // [QT], 256 bytes reserved
+    unsigned char* q_s = smem + 256;                                             // [QT][q_bytes]
+    uint32_t* s_stage = reinterpret_cast<uint32_t*>(q_s + (size_t)QT * a.g.q_bytes);   // [kScanRefreshWords]
+    unsigned char* ring = reinterpret_cast<unsigned char*>(s_stage + kScanRefreshWords);
+    __shared__ int s_last;
+
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int W = blockDim.x >> 5;
+    const CandView& cv = a.cv;
+    const ScanGeometry& g = a.g;
+    const int R = g.rows_per_tile;
+    const int lpr = 1 << g.lpr_shift;
+    const int r_in = lane >> g.lpr_shift;    // row of the tile this lane works on
+    const int part = lane & (lpr - 1);       // which chunks of the row: part, part + lpr, ...
+    const bool leader = part == 0;           // the lane that finishes the row
+    const int C = cv.chunks;
+    const int Cs = g.cstride;
+    unsigned char* my_ring = ring + (size_t)warp * S * g.stage_bytes;
+
+    const int64_t nrows = a.row_end - a.row_begin;
+    const int64_t n_tiles = (nrows + R - 1) / R;
+    const int64_t gw = (int64_t)blockIdx.x * W + warp;
+    const int64_t nwarps = (int64_t)gridDim.x * W;
+    const int my_tiles = (gw < n_tiles) ? (int)((n_tiles - gw + nwarps - 1) / nwarps) : 0;
+    const bool topk = a.mode == kModeTopk;
+
+    // ---- the asynchronous copy of one tile: lane l copies chunks l, l + 32, ... of the tile's contiguous bytes
+    const int step_r = 32 / C, step_c = 32 % C;
+    const int row0 = lane / C, col0 = lane % C;
+    auto issue = [&](int tile_local, int stage) {
+        if (tile_local >= 0 && tile_local < my_tiles) {
+            const int64_t first = a.row_begin + (gw + (int64_t)tile_local * nwarps) * R;
+            const int rows_here = (int)min((int64_t)R, a.row_end - first);
+            const int n_chunks = rows_here * C;
+            const unsigned char* src = cv.data + (size_t)first * cv.row_bytes;
+            unsigned char* dst = my_ring + (size_t)stage * g.stage_bytes;
+            int rr = row0, cc = col0;
+            for (int i = lane; i < n_chunks; i += 32) {
+                cp_async16(dst + ((size_t)rr * Cs + cc) * 16, src + (size_t)i * 16);
+                cc += step_c;
+                rr += step_r;
+                if (cc >= C) {
+                    cc -= C;
+                    ++rr;
+                }
+            }
+            if constexpr (kQ4) {
+                if (g.scale_unit != 0) {
+                    const unsigned char* ssrc = reinterpret_cast<const unsigned char*>(cv.scales) + (size_t)first * C * 2;
+                    const int n_units = rows_here * C * 2 / g.scale_unit;
+                    if (g.scale_unit == 16) {
+                        for (int i = lane; i < n_units; i += 32) cp_async16(dst + g.scale_off + i * 16, ssrc + (size_t)i * 16);
+                    } else {
+                        for (int i = lane; i < n_units; i += 32) cp_async4(dst + g.scale_off + i * 4, ssrc + (size_t)i * 4);
+                    }
+                }
+            }
+            if (lane < rows_here) {
+                if (cv.stats != nullptr) cp_async4(dst + g.stat_off + lane * 4, reinterpret_cast<const uint32_t*>(cv.stats) + first + lane);
+                if constexpr (kQ8) cp_async4(dst + g.rscale_off + lane * 4, reinterpret_cast<const float*>(cv.scales) + first + lane);
+            }
+        }
+        cp_async_commit();
+    };
+    // Tile processed in iteration i.  A warp observes its first T tiles (T unknown while it observes); when the first
+    // threshold arrives at the top of iteration T the two tiles already in flight (T, T+1) are consumed in append mode,
+    // then the T observed tiles are read again and appended, then the scan goes on.
+    int T = topk ? 0x3fffffff : 0;
+    auto tile_of = [&](int i) -> int {
+        if (i < T + 2) return (i < my_tiles) ? i : -1;
+        if (i < 2 * T + 2) return i - (T + 2);
+        return (i - T < my_tiles) ? i - T : -1;
+    };
+
+    // start the stream before anything else, then prepare the queries while the first tiles are on their way
+#pragma unroll
+    for (int p = 0; p < S - 1; ++p) issue(tile_of(p), p);
+    for (int q = warp; q < QT; q += W) {
+        const int qi = a.q0 + ((q < a.qt) ? q : 0);   // unused slots repeat query 0 of the launch
+        prepare_query_warp<LAYOUT>(a.queries + (size_t)qi * cv.cols, cv.cols, C, lane, hdr_s + q, q_s + (size_t)q * g.q_bytes);
+    }
+    __syncthreads();
+    QueryHeader hdr[QT];
+    float q4_sh[QT], q4_sl[QT];
+#pragma unroll
+    for (int q = 0; q < QT; ++q) {
+        hdr[q] = hdr_s[q];
+        q4_sh[q] = hdr[q].s_hi * 0.0625f;  // the nibble unpack yields 16*code
+        q4_sl[q] = hdr[q].s_lo * 0.0625f;
+    }
+
+    const float sign = (a.order == MANTA_B200_ORDER_SMALLEST) ? -1.0f : 1.0f;
+    // Nearest-neighbour l2 on packed rows finishes a score in f64 (square root included).  In top-k mode a row is
+    // first tested in f32: dist <= B  <=>  dot >= (||q||^2 - B^2 + ||row||^2) / 2, with B the current bound and a few
+    // ulps of slack; a tile in which no row passes skips the exact evaluation.  Rows that do not pass are below the
+    // bound, so leaving them out of the bucket maxima keeps those maxima valid lower bounds.
+    const bool l2_pref = !kF16 && topk && a.metric == MANTA_B200_METRIC_L2_DISTANCE && a.order == MANTA_B200_ORDER_SMALLEST;
+    uint32_t thr[QT], bmax[QT][kScanBucketSlots], published[QT][kScanBucketSlots];
+    float l2_ch[QT];   // (||q||^2 - B^2) / 2 per query, lowered; -inf while no bound exists
+#pragma unroll
+    for (int q = 0; q < QT; ++q) {
+        thr[q] = 0;
+        l2_ch[q] = -INFINITY;
+#pragma unroll
+        for (int s = 0; s < kScanBucketSlots; ++s) bmax[q][s] = published[q][s] = 0;
+    }
+    auto load_bounds = [&]() {
+#pragma unroll
+        for (int q = 0; q < QT; ++q) {
+            thr[q] = ld_relaxed_u32(a.ws.thr + a.q0 + ((q < a.qt) ? q : 0));
+            float ch = -INFINITY;
+            if (l2_pref && thr[q] > 1u) {
+                const float bnd = fmaxf(-float_from_ord(thr[q]), 0.0f);
+                const double b2 = (double)bnd * (double)bnd * (1.0 + 4e-6) + 1e-30;
+                ch = (float)((hdr[q].qhat2 - b2) * 0.5);
+                ch = ch - fabsf(ch) * 1e-6f - 1e-30f;
+            }
+            l2_ch[q] = ch;
+        }
+    };
+    // one reservation per call for all lanes that pass
+    auto append = [&](int q, bool pass, uint64_t key) {
+        const uint32_t ballot = __ballot_sync(0xffffffffu, pass);
+        if (ballot == 0) return;
+        uint32_t base = 0;
+        if (lane == 0) base = atomicAdd(a.ws.count + a.q0 + q, (uint32_t)__popc(ballot));
+        base = __shfl_sync(0xffffffffu, base, 0);
+        if (pass) {
+            const uint32_t pos = base + __popc(ballot & ((1u << lane) - 1u));
+            if (pos < a.ws.cap)
+                a.ws.pool[(size_t)(a.q0 + q) * a.ws.cap + pos] = key;
+            else
+                a.ws.flags[kFlagOverflow] = 1u;
+        }
+    };
+
+    bool observing = topk;
+    int total = topk ? 0x3fffffff : max(my_tiles, 2);
+    uint32_t fresh = 0;            // fresh (not re-read) tiles consumed so far: drives the refresh duty
+    uint32_t overflow_seen = 0;
+    for (int i = 0; i < total; ++i) {
+        if (topk) {
+            // the bounds move fast only at the start: reread them every tile early on, every eighth tile later
+            if (observing || i <= 16 || (i & 7) == 0) load_bounds();
+            if (observing) {
+                bool have = true;
+#pragma unroll
+                for (int q = 0; q < QT; ++q) have = have && thr[q] != 0u;
+                if (have || i >= my_tiles || i >= kScanObserveMax) {
+                    observing = false;
+                    T = min(i, my_tiles);
+                    total = max(2 * T + 2, my_tiles + T);
+                }
+            }
+            // a pool that overflowed makes the host redo the pass in chunks: stop streaming.  The flag is loaded in
+            // one check and tested in the next, so its latency never stalls the stream.
+            if ((i & 63) == 63) {
+                if (overflow_seen != 0) break;
+                overflow_seen = ld_relaxed_u32(a.ws.flags + kFlagOverflow);
+            }
+        }
+        const int stage = i % S;
+        cp_async_wait<S - 2>();   // the copies of this iteration's tile have landed
+        __syncwarp();             // ... for every lane, and every lane is done with the stage refilled next
+        issue(tile_of(i + S - 1), (i + S - 1) % S);
+        const int tile_local = tile_of(i);
+        if (tile_local < 0) continue;
+        const bool observe = i < T;
+        const bool replay = i >= T + 2 && i < 2 * T + 2;
+        const unsigned char* st = my_ring + (size_t)stage * g.stage_bytes;
+        const int64_t first = a.row_begin + (gw + (int64_t)tile_local * nwarps) * R;
+        const int64_t my_row = first + r_in;
+        const bool rv = leader && my_row < a.row_end;
+
+        // ---- accumulate this lane's chunks of its row
+        int ih[QT], il[QT];
+        float fa[QT], fb[QT];
+#pragma unroll
+        for (int q = 0; q < QT; ++q) {
+            ih[q] = il[q] = 0;
+            fa[q] = fb[q] = 0.0f;
+        }
+        const uint4* rowp = reinterpret_cast<const uint4*>(st) + (size_t)r_in * Cs;
+        if constexpr (kQ8) {
+#pragma unroll 4
+            for (int c = part; c < C; c += lpr) {
+                const uint4 d = rowp[c];
+#pragma unroll
+                for (int q = 0; q < QT; ++q) {
+                    const uint4 qh = reinterpret_cast<const uint4*>(q_s + (size_t)q * g.q_bytes)[c];
+                    const uint4 ql = reinterpret_cast<const uint4*>(q_s + (size_t)q * g.q_bytes)[C + c];
+                    int h = ih[q], l = il[q];
+                    h = __dp4a((int)d.x, (int)qh.x, h);
+                    l = __dp4a((int)d.x, (int)ql.x, l);
+                    h = __dp4a((int)d.y, (int)qh.y, h);
+                    l = __dp4a((int)d.y, (int)ql.y, l);
+                    h = __dp4a((int)d.z, (int)qh.z, h);
+                    l = __dp4a((int)d.z, (int)ql.z, l);
+                    h = __dp4a((int)d.w, (int)qh.w, h);
+                    l = __dp4a((int)d.w, (int)ql.w, l);
+                    ih[q] = h;
+                    il[q] = l;
+                }
+            }
+        } else if constexpr (kQ4) {
+            const __half* srow = (g.scale_unit != 0) ? reinterpret_cast<const __half*>(st + g.scale_off) + (size_t)r_in * C
+                                                     : reinterpret_cast<const __half*>(cv.scales) + (size_t)min(my_row, a.row_end - 1) * C;
+#pragma unroll 2
+            for (int c = part; c < C; c += lpr) {
+                const uint4 d = rowp[c];
+                const uint32_t w[4] = {d.x, d.y, d.z, d.w};
+                int ev[4], od[4];
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    ev[t] = (int)((w[t] << 4) & 0xF0F0F0F0u);
+                    od[t] = (int)(w[t] & 0xF0F0F0F0u);
+                }
+                const float bs = __half2float(srow[c]);
+#pragma unroll
+                for (int q = 0; q < QT; ++q) {
+                    const uint4* qh = reinterpret_cast<const uint4*>(q_s + (size_t)q * g.q_bytes) + 2 * c;
+                    const uint4* ql = qh + 2 * C;
+                    const uint4 h0 = qh[0], h1 = qh[1], l0 = ql[0], l1 = ql[1];
+                    const uint32_t ph[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+                    const uint32_t pl[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
+                    int h = 0, l = 0;
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) {
+                        h = __dp4a(ev[t], (int)ph[2 * t], h);
+                        l = __dp4a(ev[t], (int)pl[2 * t], l);
+                        h = __dp4a(od[t], (int)ph[2 * t + 1], h);
+                        l = __dp4a(od[t], (int)pl[2 * t + 1], l);
+                    }
+                    fa[q] = __fmaf_rn((float)h, bs, fa[q]);
+                    fb[q] = __fmaf_rn((float)l, bs, fb[q]);
+                }
+            }
+        } else {
+            const bool l2 = a.metric == MANTA_B200_METRIC_L2_DISTANCE;
+#pragma unroll 2
+            for (int c = part; c < C; c += lpr) {
+                const uint4 d = rowp[c];
+                const __half2* hp = reinterpret_cast<const __half2*>(&d);
+                float f[8];
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    const float2 p = __half22float2(hp[t]);
+                    f[2 * t] = p.x;
+                    f[2 * t + 1] = p.y;
+                }
+#pragma unroll
+                for (int q = 0; q < QT; ++q) {
+                    const float4* qf = reinterpret_cast<const float4*>(q_s + (size_t)q * g.q_bytes) + 2 * c;
+                    const float4 q0 = qf[0], q1 = qf[1];
+                    const float qv[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+                    float acc = fa[q];
+                    if (l2) {
+                        // sum (q - d)^2 directly, as the reference does: no cancellation near zero distance
+#pragma unroll
+                        for (int t = 0; t < 8; ++t) {
+                            const float df = __fsub_rn(qv[t], f[t]);
+                            acc = __fmaf_rn(df, df, acc);
+                        }
+                    } else {
+#pragma unroll
+                        for (int t = 0; t < 8; ++t) acc = __fmaf_rn(f[t], qv[t], acc);
+                    }
+                    fa[q] = acc;
+                }
+            }
+        }
+        // ---- finish the row: log2(lpr) exchange steps, then the row's leader lane holds the sums
+#pragma unroll
+        for (int q = 0; q < QT; ++q) {
+            for (int off = lpr >> 1; off > 0; off >>= 1) {
+                if constexpr (kQ8) {
+                    ih[q] += __shfl_xor_sync(0xffffffffu, ih[q], off);
+                    il[q] += __shfl_xor_sync(0xffffffffu, il[q], off);
+                } else if constexpr (kQ4) {
+                    fa[q] += __shfl_xor_sync(0xffffffffu, fa[q], off);
+                    fb[q] += __shfl_xor_sync(0xffffffffu, fb[q], off);
+                } else {
+                    fa[q] += __shfl_xor_sync(0xffffffffu, fa[q], off);
+                }
+            }
+        }
+        const uint32_t stat = (cv.stats != nullptr) ? reinterpret_cast<const uint32_t*>(st + g.stat_off)[r_in] : 0u;
+        const int nn = (int)stat;
+        const float dn2 = __uint_as_float(stat);
+        float sd = 0.0f;
+        if constexpr (kQ8) sd = reinterpret_cast<const float*>(st + g.rscale_off)[r_in];
+        float rinv = 0.0f;
+        if (a.metric == MANTA_B200_METRIC_COSINE) rinv = kQ8 ? q8_row_inv_norm(nn) : float_row_inv_norm(dn2);
+        const int slot = (int)(fresh & (kScanBucketSlots - 1));
+#pragma unroll
+        for (int q = 0; q < QT; ++q) {
+            float score;
+            if constexpr (kQ8) {
+                if (a.mode == kModeAccum) {
+                    if (rv && q == 0) {
+                        int32_t* o = a.out_acc + (size_t)(my_row - a.row_begin) * 3;
+                        o[0] = ih[q];
+                        o[1] = il[q];
+                        o[2] = nn;
+                    }
+                    continue;
+                }
+                if (l2_pref && !observe) {
+                    const float t = __fmaf_rn((float)il[q], hdr[q].s_lo, __fmul_rn((float)ih[q], hdr[q].s_hi));
+                    float dc = __fmul_rn(t, sd);
+                    dc = dc + 4e-7f * fabsf(dc);   // the exact path forms this product in f64
+                    const float dn2c = __fmul_rn(__fmul_rn(sd, sd), (float)nn);
+                    const bool pass = rv && dc >= __fmaf_rn(dn2c, 0.4999995f, l2_ch[q]);
+                    if (!__any_sync(0xffffffffu, pass)) continue;
+                }
+                score = q8_finish(a.metric, ih[q], il[q], nn, rinv, sd, hdr[q]);
+            } else if constexpr (kQ4) {
+                const float dotv = __fmaf_rn(fb[q], q4_sl[q], __fmul_rn(fa[q], q4_sh[q]));
+                if (l2_pref && !observe) {
+                    const bool pass = rv && dotv >= __fmaf_rn(dn2, 0.4999995f, l2_ch[q]);
+                    if (!__any_sync(0xffffffffu, pass)) continue;
+                }
+                score = float_finish(a.metric, dotv, dn2, rinv, hdr[q], hdr[q].qhat2);
+            } else {
+                if (a.metric == MANTA_B200_METRIC_L2_DISTANCE)
+                    score = __fsqrt_rn(fa[q]) + 0.0f;  // fa holds sum (q - d)^2 here
+                else
+                    score = float_finish(a.metric, fa[q], dn2, rinv, hdr[q], hdr[q].qn2d);
+            }
+            const bool mine = rv && q < a.qt;
+            if (a.mode == kModeScores) {
+                if (mine) a.out_scores[(size_t)(a.q0 + q) * cv.rows + my_row] = score;
+            } else if (topk) {
+                const float gd = score * sign + 0.0f;
+                const uint32_t o = ord_from_float(gd);
+                if (mine && !replay) bmax[q][slot] = max(bmax[q][slot], o);
+                if (!observe) append(q, mine && o >= thr[q], make_key(gd, (int32_t)(cv.row_base + my_row)));
+            }
+        }
+        if (!topk || replay) continue;
+        ++fresh;
+        // ---- publish this warp's running maximum of the slot when it changed
+#pragma unroll
+        for (int q = 0; q < QT; ++q) {
+            uint32_t m = bmax[q][slot];
+            if (__any_sync(0xffffffffu, m > published[q][slot])) {
+                m = __reduce_max_sync(0xffffffffu, m);
+                published[q][slot] = m;
+                bmax[q][slot] = m;
+                if (lane == 0 && q < a.qt)
+                    st_relaxed_u32(a.ws.bucket + (size_t)(a.q0 + q) * a.ws.nb + (size_t)gw * kScanBucketSlots + slot, m);
+            }
+        }
+        // ---- threshold refresh duty: warp 0, at power-of-two tile counts, one block in eight per count (plus tile
+        // counts 3 and 6 early on).  The bound is built from the top 20 bits only: rounding it down keeps it valid
+        // and costs a fraction of a percent of selectivity.
+        const bool duty_iter = (fresh & (fresh - 1)) == 0 || fresh == 3 || fresh == 6;
+        if (warp == 0 && duty_iter && ((blockIdx.x & 7) == ((fresh == 3 || fresh == 6) ? 7 - (fresh / 3) : ((31 - __clz(fresh)) & 7)))) {
+            for (int q = 0; q < a.qt; ++q) {
+                const uint32_t* b = a.ws.bucket + (size_t)(a.q0 + q) * a.ws.nb;
+                // A bound needs k buckets; for small k the first 256 buckets are plenty (any subset of buckets gives a
+                // valid, slightly lower bound) and fit in eight registers per lane.
+                const uint32_t nb_all = min(min(a.ws.nb, (uint32_t)kScanRefreshWords), (uint32_t)(nwarps * kScanBucketSlots));
+                uint32_t t = 0;
+                if (2u * (uint32_t)a.k <= 256u) {
+                    const uint32_t nb = min(nb_all, 256u);
+                    uint32_t v[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) v[u] = ((uint32_t)(u * 32 + lane) < nb) ? __ldcg(b + u * 32 + lane) : 0u;
+                    for (int bit = 31; bit >= 12; --bit) {
+                        const uint32_t cand = t | (1u << bit);
+                        uint32_t cnt = 0;
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) cnt += (v[u] >= cand) ? 1u : 0u;
+                        cnt = __reduce_add_sync(0xffffffffu, cnt);
+                        if (cnt >= (uint32_t)a.k) t = cand;
+                    }
+                } else {
+                    const uint32_t nb = nb_all;
+                    // eight independent loads at a time (a volatile load per element would serialise on its store)
+                    for (uint32_t i0 = lane; i0 < nb; i0 += 256) {
+                        uint32_t v[8];
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) v[u] = (i0 + u * 32 < nb) ? __ldcg(b + i0 + u * 32) : 0u;
+#pragma unroll
+                        for (int u = 0; u < 8; ++u)
+                            if (i0 + u * 32 < nb) s_stage[i0 + u * 32] = v[u];
+                    }
+                    __syncwarp();
+                    for (int bit = 31; bit >= 12; --bit) {
+                        const uint32_t cand = t | (1u << bit);
+                        uint32_t cnt = 0;
+                        for (uint32_t j = lane; j < nb; j += 32) cnt += (s_stage[j] >= cand) ? 1u : 0u;
+                        cnt = __reduce_add_sync(0xffffffffu, cnt);
+                        if (cnt >= (uint32_t)a.k) t = cand;
+                    }
+                    __syncwarp();
+                }
+                if (lane == 0 && t != 0) atomicMax(a.ws.thr + a.q0 + q, t);
+                __syncwarp();
+            }
+        }
+    }
+    cp_async_wait<0>();
+
+    // ---- tail of a fused pass: the last block to arrive selects the exact top k of this launch's queries
+    if (!a.fused_select) return;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const uint32_t prev = atomicAdd(a.done_blocks, 1u);
+        s_last = (prev + 1u == gridDim.x) ? 1 : 0;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    SelectArgs sa{};
+    sa.ws = a.ws;
+    sa.nq = a.nq_total;
+    sa.k = a.k;
+    sa.order = a.order;
+    sa.write_back = 0;
+    sa.out_ids = a.out_ids;
+    sa.out_scores = a.out_topk_scores;
+    sa.sink = a.sink;
+    for (int q = 0; q < a.qt; ++q) {
+        select_block(sa, a.q0 + q, ring);   // the ring is free: every warp of this block has drained its copies
+        // leave the query's workspace zeroed: the next pass starts from a clean state without a reset launch
+        uint32_t* b = a.ws.bucket + (size_t)(a.q0 + q) * a.ws.nb;
+        const uint32_t nb_used = min(a.ws.nb, (uint32_t)(nwarps * kScanBucketSlots));
+        for (uint32_t j = threadIdx.x; j < nb_used; j += blockDim.x) b[j] = 0u;
+        if (threadIdx.x == 0) {
+            a.ws.count[a.q0 + q] = 0u;
+            a.ws.thr[a.q0 + q] = 0u;
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        *a.done_blocks = 0u;
+        for (int f = 0; f < kNumFlags; ++f) {
+            if (a.ws.flags[f] != 0u) {
+                a.host_flags[f] = 1u;   // sticky on the host until it reads and clears them
+                a.ws.flags[f] = 0u;
+            }
+        }
+    }
+}
+
+// ---- host side ---------------------------------------------------------------------------------------------------
+template <int LAYOUT, int QT>
+cudaError_t launch_stream_scan_qt(cudaStream_t st, int sm_count, const StreamArgs& a, size_t smem) {
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(stream_scan_kernel<LAYOUT, QT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448);
+        if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+    }
+    // one persistent block per SM; every warp is a bucket owner, so the grid is exactly what is resident at once
+    const int grid = sm_count;
+    stream_scan_kernel<LAYOUT, QT><<<grid, a.g.warps * 32, smem, st>>>(a);
+    count_launch();
+    note_scan_launch("stream_scan_kernel", grid, a.g.warps * 32, smem);
+    return cudaGetLastError();
+}
+
+template <int LAYOUT>
+cudaError_t launch_stream_scan_layout(cudaStream_t st, int sm_count, StreamArgs a) {
+    size_t smem = 0;
+    const int qt_slots = a.qt <= 1 ? 1 : (a.qt <= 2 ? 2 : 4);
+    if (!stream_scan_geometry(a.cv, qt_slots, a.row_begin, &a.g, &smem)) return cudaErrorInvalidValue;
+    if (qt_slots == 1) return launch_stream_scan_qt<LAYOUT, 1>(st, sm_count, a, smem);
+    if (qt_slots == 2) return launch_stream_scan_qt<LAYOUT, 2>(st, sm_count, a, smem);
+    return launch_stream_scan_qt<LAYOUT, 4>(st, sm_count, a, smem);
+}
+
+cudaError_t launch_stream_scan_f16(cudaStream_t st, int sm_count, const StreamArgs& a);
+cudaError_t launch_stream_scan_q8(cudaStream_t st, int sm_count, const StreamArgs& a);
+cudaError_t launch_stream_scan_q4(cudaStream_t st, int sm_count, const StreamArgs& a);
+
+}  // namespace mb200

@@ -1,0 +1,10 @@
+// Instantiations of the streaming scan for q8 candidate rows.
+#include "stream_scan.cuh"
+
+namespace mb200 {
+
+cudaError_t launch_stream_scan_q8(cudaStream_t st, int sm_count, const StreamArgs& a) {
+    return launch_stream_scan_layout<MANTA_B200_LAYOUT_Q8_ROW_F32>(st, sm_count, a);
+}
+
+}  // namespace mb200

@@ -161,7 +161,10 @@ class Program:
 
     def close(self):
         if self.handle is not None:
-            native.call("manta_b200_program_destroy", self.handle)
+            # a program whose runtime is already closed cannot release its resident sets through it: the handle is
+            # dropped (the runtime's destruction has freed the device)
+            if self.rt is None or getattr(self.rt, "handle", None) is not None:
+                native.call("manta_b200_program_destroy", self.handle)
             self.handle = None
 
     def __del__(self):

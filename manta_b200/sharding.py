@@ -92,9 +92,24 @@ class PeerExchange:
 
     def score_topk_merge(self, cands, metric: str, d_queries, nq: int, k: int, d_out_ids, d_out_scores, smallest: bool = False,
                          sync: bool = False):
-        """The whole sharded step: this rank's fused pass stores its lists into every inbox, then the merge."""
-        self.rt.score_topk_exchange_device(self.ex, cands, metric, d_queries, nq, k, d_out_ids, d_out_scores, smallest=smallest,
-                                           sync=sync)
+        """The whole sharded step: this rank's fused pass stores its lists into every inbox, then the merge.
+
+        A shard whose candidate pool overflows (rows arriving in an order that defeats the in-scan filter) marks its list
+        incomplete, and the merge fails on EVERY rank.  With ``sync`` the step is then redone here, on all ranks alike, in
+        the form that cannot overflow: the chunked synchronous pass followed by the two-call exchange.  Without ``sync``
+        the failure is reported by the runtime's next ``synchronize``."""
+        from .native import MantaError
+
+        try:
+            self.rt.score_topk_exchange_device(self.ex, cands, metric, d_queries, nq, k, d_out_ids, d_out_scores, smallest=smallest,
+                                               sync=sync)
+        except MantaError as exc:
+            if not sync or "candidate pool overflowed" not in str(exc):
+                raise
+            pair = torch.empty((2, nq, k), dtype=torch.int32, device=d_out_ids.device)
+            self.rt.score_topk_device(cands, metric, d_queries, nq, k, pair[0], pair[1].view(torch.float32), smallest=smallest, sync=True)
+            self.rt.topk_exchange_merge_device(self.ex, pair[0], pair[1].view(torch.float32), nq, k, d_out_ids, d_out_scores,
+                                               smallest=smallest, sync=True)
 
     def close(self):
         """Every rank reaches the barrier and releases its inbox even when its last pass reported an error (the

@@ -107,6 +107,50 @@ def test_missing_list_runs_into_the_wait_limit_and_the_runtime_stays_usable():
         rt.close()
 
 
+def test_overflowing_shard_pass_is_reported_and_redone():
+    """A shard whose candidate pool overflows (rows sorted so that every row beats all earlier ones) holds an
+    incomplete list.  The fused exchange step must not return it as a success: the list travels with a status word, the
+    merge fails with a message that says so, and PeerExchange redoes the step with the chunked pass + two-call exchange."""
+    import torch
+
+    from helpers import f16_round
+    from manta_b200 import native, sharding
+
+    rt = native.Runtime(0)
+    rows, cols, k = 900000, 128, 10
+    rng = np.random.default_rng(9)
+    q = make_rows(rng, 1, cols)
+    x = rng.standard_normal((rows, cols), dtype=np.float32) * np.float32(1e-4)
+    x += (np.arange(rows, dtype=np.float32) / rows)[:, None] * q[0][None, :]
+    data, scales, _ = pack("f16", f16_round(x))
+    cands = rt.bind("f16", data, scales)
+    want_ids, want_sc = rt.score_topk(cands, "dot", q, k)   # the host-buffer call redoes the pass in chunks by itself
+    stream = torch.cuda.ExternalStream(rt.stream)
+    with torch.cuda.stream(stream):
+        dq = torch.from_numpy(q.astype(np.float16)).cuda()
+        o_ids = torch.zeros((1, k), dtype=torch.int32, device="cuda")
+        o_sc = torch.zeros((1, k), dtype=torch.float32, device="cuda")
+    stream.synchronize()
+    ex = sharding.PeerExchange(rt, None, 2, 16)
+    try:
+        with pytest.raises(native.MantaError, match="candidate pool overflowed"):
+            rt.score_topk_exchange_device(ex.ex, cands, "dot", dq, 1, k, o_ids, o_sc, sync=True)
+        # asynchronous form: the next synchronisation reports it
+        rt.score_topk_exchange_device(ex.ex, cands, "dot", dq, 1, k, o_ids, o_sc, sync=False)
+        with pytest.raises(native.MantaError, match="candidate pool overflowed"):
+            rt.synchronize()
+        # the wrapper redoes the step in the form that cannot overflow
+        before = rt.stats()["chunked_reruns"]
+        ex.score_topk_merge(cands, "dot", dq, 1, k, o_ids, o_sc, sync=True)
+        assert rt.stats()["chunked_reruns"] == before + 1
+        np.testing.assert_array_equal(o_ids.cpu().numpy(), np.atleast_2d(want_ids))
+        np.testing.assert_array_equal(o_sc.cpu().numpy(), np.atleast_2d(want_sc))
+    finally:
+        ex.close()
+        cands.unbind()
+        rt.close()
+
+
 _CHILD = r"""
 import os, sys
 import numpy as np

@@ -339,7 +339,9 @@ def test_dequant_step_keeps_docs_packed(rt):
     assert [t["kind"] for t in res.trace] == ["dequant", "launch_kernel", "topk", "gather", "return"]
     ids, scores = res.outputs["top_ids"].data, res.outputs["top_scores"].data
     assert_topk_matches("cosine", q, deq, ids, scores, 2)
-    plain = Program(rt, load("tiny_rerank"))
+    plain_mod = load("tiny_rerank")
+    plain_mod["params"][0]["type"]["tensor"]["dtype"] = "q8"
+    plain = Program(rt, plain_mod)
     plain.bind_weight("docs", T("q8", list(deq.shape), deq))
     res2 = plain.run("rerank", {"query": T("f16", [64], q)})
     np.testing.assert_array_equal(ids, res2.outputs["top_ids"].data)
