@@ -95,7 +95,7 @@ class ClockSampler:
     """Samples nvidia-smi clocks / throttle reasons during the timed region."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-         "clocks_event_reasons.sw_power_cap")
+         "clocks_event_reasons.sw_power_cap,clocks.mem")
 
     def __init__(self, gpu_index: int):
         self.gpu, self.proc, self.lines = gpu_index, None, []
@@ -123,7 +123,7 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
-        sm, mx, reasons, power = [], [], set(), []
+        sm, mx, reasons, power, mem = [], [], set(), [], []
         inside = [ln for (t, ln) in self.lines if t_begin <= t <= t_end + 0.05] or [ln for (_, ln) in self.lines]
         for ln in inside:
             f = [x.strip() for x in ln.split(",")]
@@ -133,6 +133,8 @@ class ClockSampler:
                 sm.append(float(f[1]))
                 mx.append(float(f[2]))
                 power.append(float(f[3]))
+                if len(f) > 9:
+                    mem.append(float(f[9]))
             except ValueError:
                 continue
             for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
@@ -140,7 +142,8 @@ class ClockSampler:
                     reasons.add(name)
         sm.sort()
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm), "power_w_max": max(power) if power else None}
+                "reasons": sorted(reasons), "samples": len(sm), "power_w_max": max(power) if power else None,
+                "mem_mhz_min": min(mem) if mem else None}
 
 
 # ------------------------------------------------------------------------------------------------------------
@@ -402,7 +405,14 @@ def run_ours(args, wl: Workload):
     repeat_ms = []
     launches = 0
     for rep in range(max(1, args.repeats)):
-        # one repeat = exactly `steps` steps between a barrier + synchronize on both sides, CUDA events on the stream
+        # One repeat = one independent measurement of the timed region: `warmup` untimed steps, then exactly `steps`
+        # steps between a barrier + synchronize on both sides, CUDA events on the stream.  Repeats are a quarter of a
+        # second apart, so that one does not inherit the power / thermal state the previous one left.
+        if rep > 0:
+            time.sleep(0.25)
+            for i in range(max(args.warmup, n_lanes)):
+                step_device(i)
+            barrier()
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         ev0.record(stream)
         for i in range(args.steps):
@@ -588,7 +598,8 @@ def run_ours(args, wl: Workload):
             "repeats": {"count": len(repeat_ms), "ms_per_step": [x / args.steps for x in repeat_ms],
                         "median_ms_per_step": total_ms / args.steps, "min_ms_per_step": min(repeat_ms) / args.steps,
                         "max_ms_per_step": max(repeat_ms) / args.steps,
-                        "note": "each repeat times exactly `steps` steps between barriers; value is the median repeat"}, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                        "note": "each repeat is an independent measurement (warm-up steps, then exactly `steps` timed steps between "
+                                "barriers), 0.25 s apart; value is the median repeat"}, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": {"q8": "int8 x int8 -> int32 (two int8 query planes), f32 epilogue",
                       "q4": "int4 x int8 -> int32 per block, f32 across blocks", "f16": "f16 x f16 -> f32"}[wl.layout],
             "data": "synthetic",
@@ -644,6 +655,7 @@ def main():
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline / parity spot check")
     ap.add_argument("--rows", type=int, default=0, help="override the workload's row count (smaller cases for profiling)")
+    ap.add_argument("--cols", type=int, default=0, help="override the workload's row width")
     ap.add_argument("--nq", type=int, default=0, help="override the workload's query batch")
     ap.add_argument("--k", type=int, default=0, help="override the workload's k")
     ap.add_argument("--metric", default="", choices=["", "dot", "cosine", "l2_distance"], help="override the workload's metric")
@@ -660,6 +672,8 @@ def main():
     wl = WORKLOADS[args.workload]
     if args.rows:
         wl.rows = args.rows
+    if args.cols:
+        wl.cols = args.cols
     if args.nq:
         wl.nq = args.nq
     if args.k:

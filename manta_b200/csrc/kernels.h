@@ -1,6 +1,8 @@
 // Host-side launchers of the kernels (one translation unit per kernel family).
 #pragma once
 
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace mb200 {
@@ -42,11 +44,14 @@ cudaError_t launch_embed_pooled(cudaStream_t st, const void* table_f16, int voca
 
 // Streaming scoring kernel (stream_scan.cuh).  mode: what the epilogue does with a score.
 enum { kModeScores = 0, kModeTopk = 1, kModeAccum = 2 };
-constexpr int kScanStages = 3;          // ring depth: kScanStages - 1 tiles in flight per warp
-constexpr int kScanMaxWarps = 8;        // warps per block (fewer when a row is very wide)
-constexpr int kScanBucketSlots = 2;     // running maxima per warp (tiles alternate between them)
-constexpr int kScanRefreshWords = 4864; // bucket maxima a threshold refresh can stage in shared memory
-constexpr int kScanObserveMax = 48;     // tiles a warp observes at most before it appends without a threshold
+// One query per launch runs 16 warps per block on a two-stage ring (one tile in flight per warp while one is consumed:
+// 16 tiles per SM); two or four queries per launch need more registers per thread and run 8 warps on a three-stage
+// ring.  Every warp owns one bucket (running maximum) per query, two when a block has 8 warps, so that a grid of one
+// block per SM always offers more buckets than the largest k.
+constexpr int scan_warps(int qt) { return qt == 1 ? 16 : 8; }
+constexpr int scan_bucket_slots(int qt) { return qt == 1 ? 1 : 2; }
+constexpr int kScanMaxBucketsPerBlock = 16;   // scan_warps * scan_bucket_slots for either form
+constexpr int kScanRefreshWords = 2560; // bucket maxima a threshold refresh can stage in shared memory
 constexpr int kSelSmemKeys = 4096;      // keys the selection sorts in shared memory
 // shared memory a block needs for select_block: keys, a 256-bin histogram, four scalars
 constexpr size_t kSelSmemBytes = (size_t)kSelSmemKeys * 8 + 256 * 4 + 16;
@@ -75,6 +80,7 @@ struct ScanGeometry {
     int rscale_off;      // q8: byte offset of the R row scales
     int q_bytes;         // shared memory per query (planes or f32 values), multiple of 128
     int warps;           // warps per block
+    int stages;          // ring depth per warp (2..4): stages - 1 tiles in flight while one is consumed
 };
 
 struct StreamArgs {
@@ -102,64 +108,90 @@ struct StreamArgs {
     ExchangeSink sink;
 };
 
-// Bytes a stage may take for the candidate codes of one tile; a row wider than this gets a tile of its own.
-constexpr int kScanStageBudget = 6656;
+// Dynamic shared memory a block of the scan may ask for: the 227 KB a block can have, less 1 KB for the kernel's static
+// shared variables.
+constexpr size_t kScanSmemLimit = 232448 - 1024;
 
-inline int scan_padded_stride(int chunks, int lpr) {
+__host__ __device__ constexpr int scan_padded_stride(int chunks, int lpr) {
     if (lpr >= 8) return chunks;
     // the 8 lanes that share a shared-memory wavefront read rows r, r+1, ... at chunk offsets 0..lpr-1: they fall into
     // distinct 16-byte bank groups when the stride is congruent to lpr modulo 2*lpr
-    const int m = 2 * lpr;
-    return chunks + ((lpr - chunks % m) + m) % m;
+    return chunks + ((lpr - chunks % (2 * lpr)) + 2 * lpr) % (2 * lpr);
 }
 
-// Picks the tile geometry for a candidate layout; returns false when even one warp with one row per tile does not fit.
+// Picks the tile geometry for a candidate layout and a launch of qt (1, 2 or 4) queries: as many rows per tile as the
+// block's share of shared memory allows (up to 32), fewer warps only when a single row does not fit otherwise.
+// Returns false when even one warp with one row per tile does not fit.
 inline bool stream_scan_geometry(const CandView& cv, int qt, int64_t row_begin, ScanGeometry* g, size_t* smem_bytes) {
     const int C = cv.chunks;
     if (C <= 0) return false;
-    int R = 32;
-    while (R > 1 && (size_t)R * scan_padded_stride(C, 32 / R) * 16 > (size_t)kScanStageBudget) R >>= 1;
-    const int lpr = 32 / R;
-    int shift = 0;
-    while ((1 << shift) < lpr) ++shift;
-    g->rows_per_tile = R;
-    g->lpr_shift = shift;
-    g->cstride = scan_padded_stride(C, lpr);
-    int off = R * g->cstride * 16;
-    g->scale_off = 0;
-    g->scale_unit = 0;
-    if (cv.layout == MANTA_B200_LAYOUT_Q4_B32_F16) {
-        const uintptr_t sp = (uintptr_t)cv.scales;
-        if (C % 8 == 0 && (sp & 15) == 0) g->scale_unit = 16;
-        else if (C % 2 == 0 && (sp & 3) == 0) g->scale_unit = 4;
-        (void)row_begin;   // a row's block scales start on a multiple of 2*C bytes, so any first row is aligned for these units
-        if (g->scale_unit) {
-            g->scale_off = off;
-            off += (R * C * 2 + 15) / 16 * 16;
-        }
-    }
-    g->stat_off = off;
-    off += (R * 4 + 15) / 16 * 16;
-    g->rscale_off = off;
-    if (cv.layout == MANTA_B200_LAYOUT_Q8_ROW_F32) off += (R * 4 + 15) / 16 * 16;
-    g->stage_bytes = off;
+    (void)row_begin;   // a row's block scales start on a multiple of 2*C bytes, so any first row is aligned for the copy units below
     const int per_chunk = (cv.layout == MANTA_B200_LAYOUT_Q4_B32_F16) ? 64 : 32;   // q8: two planes of 16 bytes; q4: two of 32; f16: 8 floats
     g->q_bytes = (C * per_chunk + 127) / 128 * 128;
-    const size_t fixed = 256 + (size_t)qt * g->q_bytes + (size_t)kScanRefreshWords * 4;
-    const size_t limit = 232448;   // 227 KB of dynamic shared memory per block
-    int warps = kScanMaxWarps;
-    while (warps > 1 && fixed + (size_t)warps * kScanStages * g->stage_bytes > limit) warps >>= 1;
-    size_t total = fixed + (size_t)warps * kScanStages * g->stage_bytes;
-    if (total > limit) return false;
-    const size_t ring_min = kSelSmemBytes;   // the tail's selection reuses the ring
-    if ((size_t)warps * kScanStages * g->stage_bytes < ring_min) total = fixed + ring_min;
-    g->warps = warps;
-    *smem_bytes = total;
-    return true;
+    const size_t fixed = 256 + (size_t)qt * g->q_bytes + (size_t)(kScanRefreshWords + 256) * 4;   // headers, queries, staged maxima + histogram
+    if (fixed >= kScanSmemLimit) return false;
+    auto stage_bytes_for = [&](int R, ScanGeometry* out) {
+        const int lpr = 32 / R;
+        int shift = 0;
+        while ((1 << shift) < lpr) ++shift;
+        out->rows_per_tile = R;
+        out->lpr_shift = shift;
+        out->cstride = scan_padded_stride(C, lpr);
+        int off = R * out->cstride * 16;
+        out->scale_off = 0;
+        out->scale_unit = 0;
+        if (cv.layout == MANTA_B200_LAYOUT_Q4_B32_F16) {
+            const uintptr_t sp = (uintptr_t)cv.scales;
+            if (C % 8 == 0 && (sp & 15) == 0) out->scale_unit = 16;
+            else if (C % 2 == 0 && (sp & 3) == 0) out->scale_unit = 4;
+            if (out->scale_unit) {
+                out->scale_off = off;
+                off += (R * C * 2 + 15) / 16 * 16;
+            }
+        }
+        out->stat_off = off;
+        off += (R * 4 + 15) / 16 * 16;
+        out->rscale_off = off;
+        if (cv.layout == MANTA_B200_LAYOUT_Q8_ROW_F32) off += (R * 4 + 15) / 16 * 16;
+        out->stage_bytes = off;
+    };
+    // Measured on B200: what counts is the height of the tile (the per-tile work of a warp -- epilogue, bookkeeping,
+    // one round trip of latency -- is paid once per tile whatever its size), not the depth of the ring, so the ring is
+    // two stages deep (one tile in flight per warp while one is consumed, 16 warps per SM) and the tile as tall as the
+    // block's shared memory allows.  Deeper rings with shorter tiles were 1.4x to 1.7x slower on every layout.
+    const char* env_s = getenv("MB200_SCAN_S");
+    const char* env_r = getenv("MB200_SCAN_R");
+    for (int warps = scan_warps(qt); warps >= 1; warps >>= 1) {
+        long best = -1;
+        ScanGeometry pick{};
+        for (int S = 2; S <= 4 && best < 0; ++S) {
+            if (env_s && atoi(env_s) != S) continue;
+            if (!env_s && S != (qt == 1 ? 2 : 3)) continue;
+            const size_t budget = (kScanSmemLimit - fixed) / ((size_t)warps * S);
+            for (int R = 32; R >= 1; R >>= 1) {
+                if (env_r && atoi(env_r) != R) continue;
+                ScanGeometry t = *g;
+                stage_bytes_for(R, &t);
+                if ((size_t)t.stage_bytes > budget) continue;
+                best = (long)(S - 1) * R * C * 16;
+                pick = t;
+                pick.stages = S;
+                break;
+            }
+        }
+        if (best < 0) continue;
+        pick.warps = warps;
+        *g = pick;
+        size_t ring = (size_t)warps * pick.stages * pick.stage_bytes;
+        if (ring < kSelSmemBytes) ring = kSelSmemBytes;   // the tail's selection reuses the ring
+        *smem_bytes = fixed + ring;
+        return true;
+    }
+    return false;
 }
 
 // Buckets (running maxima) per query the workspace must provide for any launch of the scan on this device.
-inline int stream_bucket_count(int sm_count) { return sm_count * kScanMaxWarps * kScanBucketSlots; }
+inline int stream_bucket_count(int sm_count) { return sm_count * kScanMaxBucketsPerBlock; }
 // Runs the scan for a.qt <= 4 queries; the geometry is filled in by the launcher.
 cudaError_t launch_stream_scan(cudaStream_t st, int sm_count, const StreamArgs& a);
 // Zeroes the selection workspace of nq queries (fill counts, thresholds, bucket maxima, flags, the block counter).

@@ -2,10 +2,11 @@
 //
 // Data movement.  A warp owns "tiles" of R consecutive rows (R a power of two, 1..32) and strides over the row range.
 // The tile's bytes are contiguous in HBM; the 32 lanes copy them 16 bytes at a time, lane after lane, with
-// asynchronous copies (cp.async.cg, no registers held in flight) into the warp's own three-stage ring in shared
-// memory, so every global access is a fully coalesced 512-byte warp request.  The copy lays rows out with a padded
-// stride chosen so that the reads below are free of bank conflicts.  Two tiles are in flight per warp while one is
-// consumed.  The small per-row values (row scale, row statistic, q4 block scales) travel through the same ring.
+// asynchronous copies (cp.async.cg, no registers held in flight) into the warp's own ring in shared memory (two
+// stages with 16 warps per block, three with 8), so every global access is a fully coalesced 512-byte warp request.
+// The copy lays rows out with a padded stride chosen so that the reads below are free of bank conflicts.  The next
+// tile(s) of a warp are in flight while one is consumed: 16 tiles per SM at any time.  The small per-row values (row
+// scale, row statistic, q4 block scales) travel through the same ring.
 //
 // Arithmetic.  A row is consumed by LPR = 32/R adjacent lanes, each taking every LPR-th 16-byte chunk of the row
 // from shared memory; the query (for q8/q4 two int8 planes q ~= s_hi*hi + s_lo*lo, for f16 candidates f32 values)
@@ -123,18 +124,22 @@ __device__ __forceinline__ void prepare_query_warp(const __half* __restrict__ sr
     if (lane == 0) *hdr = h;
 }
 
-template <int LAYOUT, int QT>
-__global__ void __launch_bounds__(kScanMaxWarps * 32, 1) stream_scan_kernel(const StreamArgs a) {
+// LPR, CPL: lanes per row and 16-byte chunks per lane and row as compile-time constants (a row is exactly LPR * CPL
+// chunks: the loops unroll and every shared-memory access is a base register plus an immediate), or LPR == 0 for the
+// generic form that takes both from the launch geometry.
+template <int LAYOUT, int QT, int LPR, int CPL>
+__global__ void __launch_bounds__(scan_warps(QT) * 32, 1) stream_scan_kernel(const StreamArgs a) {
+    constexpr bool kSpec = LPR > 0;
     constexpr bool kQ8 = LAYOUT == MANTA_B200_LAYOUT_Q8_ROW_F32;
     constexpr bool kQ4 = LAYOUT == MANTA_B200_LAYOUT_Q4_B32_F16;
     constexpr bool kF16 = LAYOUT == MANTA_B200_LAYOUT_F16;
-    constexpr int S = kScanStages;
+    const int S = a.g.stages;
 
     extern __shared__ __align__(128) unsigned char smem[];
     QueryHeader* hdr_s = reinterpret_cast<QueryHeader*>(smem);                   // [QT], 256 bytes reserved
     unsigned char* q_s = smem + 256;                                             // [QT][q_bytes]
     uint32_t* s_stage = reinterpret_cast<uint32_t*>(q_s + (size_t)QT * a.g.q_bytes);   // [kScanRefreshWords]
-    unsigned char* ring = reinterpret_cast<unsigned char*>(s_stage + kScanRefreshWords);
+    unsigned char* ring = reinterpret_cast<unsigned char*>(s_stage + kScanRefreshWords + 256);   // 256 histogram bins follow the staged maxima
     __shared__ int s_last;
 
     const int lane = threadIdx.x & 31;
@@ -142,13 +147,13 @@ __global__ void __launch_bounds__(kScanMaxWarps * 32, 1) stream_scan_kernel(cons
     const int W = blockDim.x >> 5;
     const CandView& cv = a.cv;
     const ScanGeometry& g = a.g;
-    const int R = g.rows_per_tile;
-    const int lpr = 1 << g.lpr_shift;
-    const int r_in = lane >> g.lpr_shift;    // row of the tile this lane works on
+    const int lpr = kSpec ? LPR : (1 << g.lpr_shift);
+    const int R = kSpec ? 32 / (kSpec ? LPR : 1) : g.rows_per_tile;
+    const int r_in = kSpec ? lane / (kSpec ? LPR : 1) : (lane >> g.lpr_shift);    // row of the tile this lane works on
     const int part = lane & (lpr - 1);       // which chunks of the row: part, part + lpr, ...
     const bool leader = part == 0;           // the lane that finishes the row
-    const int C = cv.chunks;
-    const int Cs = g.cstride;
+    const int C = kSpec ? LPR * CPL : cv.chunks;
+    const int Cs = kSpec ? scan_padded_stride(LPR * CPL, kSpec ? LPR : 1) : g.cstride;
     unsigned char* my_ring = ring + (size_t)warp * S * g.stage_bytes;
 
     const int64_t nrows = a.row_end - a.row_begin;
@@ -159,8 +164,10 @@ __global__ void __launch_bounds__(kScanMaxWarps * 32, 1) stream_scan_kernel(cons
     const bool topk = a.mode == kModeTopk;
 
     // ---- the asynchronous copy of one tile: lane l copies chunks l, l + 32, ... of the tile's contiguous bytes
-    const int step_r = 32 / C, step_c = 32 % C;
-    const int row0 = lane / C, col0 = lane % C;
+    // chunk i of the tile lands at ((i / C) * Cs + i % C) * 16 = (i + (i / C) * (Cs - C)) * 16; the division is a
+    // multiply-high by ceil(2^32 / C), exact for every chunk index a tile can have
+    const uint32_t c_magic = (uint32_t)((0x100000000ull + (uint32_t)C - 1u) / (uint32_t)C);
+    const int c_pad = Cs - C;
     auto issue = [&](int tile_local, int stage) {
         if (tile_local >= 0 && tile_local < my_tiles) {
             const int64_t first = a.row_begin + (gw + (int64_t)tile_local * nwarps) * R;
@@ -168,14 +175,19 @@ __global__ void __launch_bounds__(kScanMaxWarps * 32, 1) stream_scan_kernel(cons
             const int n_chunks = rows_here * C;
             const unsigned char* src = cv.data + (size_t)first * cv.row_bytes;
             unsigned char* dst = my_ring + (size_t)stage * g.stage_bytes;
-            int rr = row0, cc = col0;
-            for (int i = lane; i < n_chunks; i += 32) {
-                cp_async16(dst + ((size_t)rr * Cs + cc) * 16, src + (size_t)i * 16);
-                cc += step_c;
-                rr += step_r;
-                if (cc >= C) {
-                    cc -= C;
-                    ++rr;
+            if constexpr (kSpec) {
+                // a full tile is exactly CPL copies per lane
+#pragma unroll
+                for (int j = 0; j < CPL; ++j) {
+                    const int i = lane + 32 * j;
+                    const int rr = i / (LPR * CPL);
+                    if (i < n_chunks) cp_async16(dst + (size_t)(i + rr * c_pad) * 16, src + (size_t)i * 16);
+                }
+            } else {
+#pragma unroll 4
+                for (int i = lane; i < n_chunks; i += 32) {
+                    const int rr = (C == 1) ? i : (int)__umulhi((uint32_t)i, c_magic);
+                    cp_async16(dst + (size_t)(i + rr * c_pad) * 16, src + (size_t)i * 16);
                 }
             }
             if constexpr (kQ4) {
@@ -197,17 +209,17 @@ __global__ void __launch_bounds__(kScanMaxWarps * 32, 1) stream_scan_kernel(cons
         cp_async_commit();
     };
     // Tile processed in iteration i.  A warp observes its first T tiles (T unknown while it observes); when the first
-    // threshold arrives at the top of iteration T the two tiles already in flight (T, T+1) are consumed in append mode,
-    // then the T observed tiles are read again and appended, then the scan goes on.
+    // threshold arrives at the top of iteration T the F = S - 1 tiles whose copies were already issued (T .. T+F-1) are
+    // consumed in append mode, then the T observed tiles are read again and appended, then the scan goes on.
+    const int F = S - 1;
     int T = topk ? 0x3fffffff : 0;
     auto tile_of = [&](int i) -> int {
-        if (i < T + 2) return (i < my_tiles) ? i : -1;
-        if (i < 2 * T + 2) return i - (T + 2);
+        if (i < T + F) return (i < my_tiles) ? i : -1;
+        if (i < 2 * T + F) return i - (T + F);
         return (i - T < my_tiles) ? i - T : -1;
     };
 
     // start the stream before anything else, then prepare the queries while the first tiles are on their way
-#pragma unroll
     for (int p = 0; p < S - 1; ++p) issue(tile_of(p), p);
     for (int q = warp; q < QT; q += W) {
         const int qi = a.q0 + ((q < a.qt) ? q : 0);   // unused slots repeat query 0 of the launch
@@ -229,14 +241,15 @@ __global__ void __launch_bounds__(kScanMaxWarps * 32, 1) stream_scan_kernel(cons
     // ulps of slack; a tile in which no row passes skips the exact evaluation.  Rows that do not pass are below the
     // bound, so leaving them out of the bucket maxima keeps those maxima valid lower bounds.
     const bool l2_pref = !kF16 && topk && a.metric == MANTA_B200_METRIC_L2_DISTANCE && a.order == MANTA_B200_ORDER_SMALLEST;
-    uint32_t thr[QT], bmax[QT][kScanBucketSlots], published[QT][kScanBucketSlots];
+    constexpr int kSlots = scan_bucket_slots(QT);
+    uint32_t thr[QT], bmax[QT][kSlots], published[QT][kSlots];
     float l2_ch[QT];   // (||q||^2 - B^2) / 2 per query, lowered; -inf while no bound exists
 #pragma unroll
     for (int q = 0; q < QT; ++q) {
         thr[q] = 0;
         l2_ch[q] = -INFINITY;
 #pragma unroll
-        for (int s = 0; s < kScanBucketSlots; ++s) bmax[q][s] = published[q][s] = 0;
+        for (int s = 0; s < kSlots; ++s) bmax[q][s] = published[q][s] = 0;
     }
     auto load_bounds = [&]() {
 #pragma unroll
@@ -268,8 +281,10 @@ __global__ void __launch_bounds__(kScanMaxWarps * 32, 1) stream_scan_kernel(cons
         }
     };
 
+    int stage = 0;                 // ring slot of the tile consumed in this iteration
+    int next_stage = S - 1;        // ring slot the copies issued in this iteration go to
     bool observing = topk;
-    int total = topk ? 0x3fffffff : max(my_tiles, 2);
+    int total = topk ? 0x3fffffff : max(my_tiles, F);
     uint32_t fresh = 0;            // fresh (not re-read) tiles consumed so far: drives the refresh duty
     uint32_t overflow_seen = 0;
     for (int i = 0; i < total; ++i) {
@@ -280,10 +295,10 @@ __global__ void __launch_bounds__(kScanMaxWarps * 32, 1) stream_scan_kernel(cons
                 bool have = true;
 #pragma unroll
                 for (int q = 0; q < QT; ++q) have = have && thr[q] != 0u;
-                if (have || i >= my_tiles || i >= kScanObserveMax) {
+                if (have || i >= my_tiles) {
                     observing = false;
                     T = min(i, my_tiles);
-                    total = max(2 * T + 2, my_tiles + T);
+                    total = max(2 * T + F, my_tiles + T);
                 }
             }
             // a pool that overflowed makes the host redo the pass in chunks: stop streaming.  The flag is loaded in
@@ -293,15 +308,20 @@ __global__ void __launch_bounds__(kScanMaxWarps * 32, 1) stream_scan_kernel(cons
                 overflow_seen = ld_relaxed_u32(a.ws.flags + kFlagOverflow);
             }
         }
-        const int stage = i % S;
-        cp_async_wait<S - 2>();   // the copies of this iteration's tile have landed
+        // the copies of this iteration's tile have landed once at most S - 2 younger groups are still pending
+        if (S == 2) cp_async_wait<0>();
+        else if (S == 3) cp_async_wait<1>();
+        else cp_async_wait<2>();
         __syncwarp();             // ... for every lane, and every lane is done with the stage refilled next
-        issue(tile_of(i + S - 1), (i + S - 1) % S);
+        issue(tile_of(i + S - 1), next_stage);
+        next_stage = stage;       // the stage consumed now is refilled in the next iteration
+        stage = (stage + 1 == S) ? 0 : stage + 1;
+        const int cur_stage = next_stage;
         const int tile_local = tile_of(i);
         if (tile_local < 0) continue;
         const bool observe = i < T;
-        const bool replay = i >= T + 2 && i < 2 * T + 2;
-        const unsigned char* st = my_ring + (size_t)stage * g.stage_bytes;
+        const bool replay = i >= T + F && i < 2 * T + F;
+        const unsigned char* st = my_ring + (size_t)cur_stage * g.stage_bytes;
         const int64_t first = a.row_begin + (gw + (int64_t)tile_local * nwarps) * R;
         const int64_t my_row = first + r_in;
         const bool rv = leader && my_row < a.row_end;
@@ -314,33 +334,55 @@ __global__ void __launch_bounds__(kScanMaxWarps * 32, 1) stream_scan_kernel(cons
             ih[q] = il[q] = 0;
             fa[q] = fb[q] = 0.0f;
         }
-        const uint4* rowp = reinterpret_cast<const uint4*>(st) + (size_t)r_in * Cs;
-        if constexpr (kQ8) {
+        const uint4* rowp = reinterpret_cast<const uint4*>(st) + (size_t)r_in * Cs + part;
+        // body(j) consumes chunk part + j * lpr of the row; compile-time j in the specialised form
+        auto for_each_chunk = [&](auto&& body) {
+            if constexpr (kSpec) {
+#pragma unroll
+                for (int j = 0; j < CPL; ++j) body(j * LPR);
+            } else {
 #pragma unroll 4
-            for (int c = part; c < C; c += lpr) {
+                for (int c = 0; part + c < C; c += lpr) body(c);
+            }
+        };
+        if constexpr (kQ8) {
+            // two independent accumulator chains per plane (.x/.z and .y/.w words) keep the integer pipe busy
+            int ih2[QT], il2[QT];
+#pragma unroll
+            for (int q = 0; q < QT; ++q) ih2[q] = il2[q] = 0;
+            const uint4* qbase = reinterpret_cast<const uint4*>(q_s) + part;
+            const int q_stride = g.q_bytes / 16;
+            for_each_chunk([&](int c) {
                 const uint4 d = rowp[c];
 #pragma unroll
                 for (int q = 0; q < QT; ++q) {
-                    const uint4 qh = reinterpret_cast<const uint4*>(q_s + (size_t)q * g.q_bytes)[c];
-                    const uint4 ql = reinterpret_cast<const uint4*>(q_s + (size_t)q * g.q_bytes)[C + c];
-                    int h = ih[q], l = il[q];
-                    h = __dp4a((int)d.x, (int)qh.x, h);
-                    l = __dp4a((int)d.x, (int)ql.x, l);
-                    h = __dp4a((int)d.y, (int)qh.y, h);
-                    l = __dp4a((int)d.y, (int)ql.y, l);
-                    h = __dp4a((int)d.z, (int)qh.z, h);
-                    l = __dp4a((int)d.z, (int)ql.z, l);
-                    h = __dp4a((int)d.w, (int)qh.w, h);
-                    l = __dp4a((int)d.w, (int)ql.w, l);
-                    ih[q] = h;
-                    il[q] = l;
+                    const uint4 qh = qbase[q * q_stride + c];
+                    const uint4 ql = qbase[q * q_stride + C + c];
+                    ih[q] = __dp4a((int)d.x, (int)qh.x, ih[q]);
+                    ih2[q] = __dp4a((int)d.y, (int)qh.y, ih2[q]);
+                    il[q] = __dp4a((int)d.x, (int)ql.x, il[q]);
+                    il2[q] = __dp4a((int)d.y, (int)ql.y, il2[q]);
+                    ih[q] = __dp4a((int)d.z, (int)qh.z, ih[q]);
+                    ih2[q] = __dp4a((int)d.w, (int)qh.w, ih2[q]);
+                    il[q] = __dp4a((int)d.z, (int)ql.z, il[q]);
+                    il2[q] = __dp4a((int)d.w, (int)ql.w, il2[q]);
                 }
+            });
+#pragma unroll
+            for (int q = 0; q < QT; ++q) {
+                ih[q] += ih2[q];
+                il[q] += il2[q];
             }
         } else if constexpr (kQ4) {
-            const __half* srow = (g.scale_unit != 0) ? reinterpret_cast<const __half*>(st + g.scale_off) + (size_t)r_in * C
-                                                     : reinterpret_cast<const __half*>(cv.scales) + (size_t)min(my_row, a.row_end - 1) * C;
-#pragma unroll 2
-            for (int c = part; c < C; c += lpr) {
+            const __half* srow = (g.scale_unit != 0) ? reinterpret_cast<const __half*>(st + g.scale_off) + (size_t)r_in * C + part
+                                                     : reinterpret_cast<const __half*>(cv.scales) + (size_t)min(my_row, a.row_end - 1) * C + part;
+            // a row of eight blocks handled by one lane: its eight block scales are one 16-byte read
+            uint4 sc8 = make_uint4(0u, 0u, 0u, 0u);
+            constexpr bool kRowScales = kSpec && LPR == 1 && CPL == 8;
+            if constexpr (kRowScales) sc8 = *reinterpret_cast<const uint4*>(srow);
+            const uint4* qbase = reinterpret_cast<const uint4*>(q_s) + 2 * part;
+            const int q_stride = g.q_bytes / 16;
+            for_each_chunk([&](int c) {
                 const uint4 d = rowp[c];
                 const uint32_t w[4] = {d.x, d.y, d.z, d.w};
                 int ev[4], od[4];
@@ -349,10 +391,16 @@ __global__ void __launch_bounds__(kScanMaxWarps * 32, 1) stream_scan_kernel(cons
                     ev[t] = (int)((w[t] << 4) & 0xF0F0F0F0u);
                     od[t] = (int)(w[t] & 0xF0F0F0F0u);
                 }
-                const float bs = __half2float(srow[c]);
+                float bs;
+                if constexpr (kRowScales) {
+                    const uint32_t pair = (c < 2) ? sc8.x : (c < 4) ? sc8.y : (c < 6) ? sc8.z : sc8.w;
+                    bs = __half2float(__ushort_as_half((unsigned short)((c & 1) ? (pair >> 16) : (pair & 0xffffu))));
+                } else {
+                    bs = __half2float(srow[c]);
+                }
 #pragma unroll
                 for (int q = 0; q < QT; ++q) {
-                    const uint4* qh = reinterpret_cast<const uint4*>(q_s + (size_t)q * g.q_bytes) + 2 * c;
+                    const uint4* qh = qbase + q * q_stride + 2 * c;
                     const uint4* ql = qh + 2 * C;
                     const uint4 h0 = qh[0], h1 = qh[1], l0 = ql[0], l1 = ql[1];
                     const uint32_t ph[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
@@ -368,11 +416,12 @@ __global__ void __launch_bounds__(kScanMaxWarps * 32, 1) stream_scan_kernel(cons
                     fa[q] = __fmaf_rn((float)h, bs, fa[q]);
                     fb[q] = __fmaf_rn((float)l, bs, fb[q]);
                 }
-            }
+            });
         } else {
             const bool l2 = a.metric == MANTA_B200_METRIC_L2_DISTANCE;
-#pragma unroll 2
-            for (int c = part; c < C; c += lpr) {
+            const float4* qbase = reinterpret_cast<const float4*>(q_s) + 2 * part;
+            const int q_stride = g.q_bytes / 16;
+            for_each_chunk([&](int c) {
                 const uint4 d = rowp[c];
                 const __half2* hp = reinterpret_cast<const __half2*>(&d);
                 float f[8];
@@ -384,7 +433,7 @@ __global__ void __launch_bounds__(kScanMaxWarps * 32, 1) stream_scan_kernel(cons
                 }
 #pragma unroll
                 for (int q = 0; q < QT; ++q) {
-                    const float4* qf = reinterpret_cast<const float4*>(q_s + (size_t)q * g.q_bytes) + 2 * c;
+                    const float4* qf = qbase + q * q_stride + 2 * c;
                     const float4 q0 = qf[0], q1 = qf[1];
                     const float qv[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
                     float acc = fa[q];
@@ -401,11 +450,12 @@ __global__ void __launch_bounds__(kScanMaxWarps * 32, 1) stream_scan_kernel(cons
                     }
                     fa[q] = acc;
                 }
-            }
+            });
         }
         // ---- finish the row: log2(lpr) exchange steps, then the row's leader lane holds the sums
 #pragma unroll
         for (int q = 0; q < QT; ++q) {
+#pragma unroll
             for (int off = lpr >> 1; off > 0; off >>= 1) {
                 if constexpr (kQ8) {
                     ih[q] += __shfl_xor_sync(0xffffffffu, ih[q], off);
@@ -425,7 +475,7 @@ __global__ void __launch_bounds__(kScanMaxWarps * 32, 1) stream_scan_kernel(cons
         if constexpr (kQ8) sd = reinterpret_cast<const float*>(st + g.rscale_off)[r_in];
         float rinv = 0.0f;
         if (a.metric == MANTA_B200_METRIC_COSINE) rinv = kQ8 ? q8_row_inv_norm(nn) : float_row_inv_norm(dn2);
-        const int slot = (int)(fresh & (kScanBucketSlots - 1));
+        const int slot = (int)(fresh & (kSlots - 1));
 #pragma unroll
         for (int q = 0; q < QT; ++q) {
             float score;
@@ -482,57 +532,102 @@ __global__ void __launch_bounds__(kScanMaxWarps * 32, 1) stream_scan_kernel(cons
                 published[q][slot] = m;
                 bmax[q][slot] = m;
                 if (lane == 0 && q < a.qt)
-                    st_relaxed_u32(a.ws.bucket + (size_t)(a.q0 + q) * a.ws.nb + (size_t)gw * kScanBucketSlots + slot, m);
+                    st_relaxed_u32(a.ws.bucket + (size_t)(a.q0 + q) * a.ws.nb + (size_t)gw * kSlots + slot, m);
             }
         }
         // ---- threshold refresh duty: warp 0, at power-of-two tile counts, one block in eight per count (plus tile
-        // counts 3 and 6 early on).  The bound is built from the top 20 bits only: rounding it down keeps it valid
-        // and costs a fraction of a percent of selectivity.
+        // counts 3 and 6 early on); the blocks on duty at a count share the launch's queries among them, one query
+        // each.  The bound is built from the top 20 bits only: rounding it down keeps it valid and costs a fraction of
+        // a percent of selectivity.
         const bool duty_iter = (fresh & (fresh - 1)) == 0 || fresh == 3 || fresh == 6;
         if (warp == 0 && duty_iter && ((blockIdx.x & 7) == ((fresh == 3 || fresh == 6) ? 7 - (fresh / 3) : ((31 - __clz(fresh)) & 7)))) {
-            for (int q = 0; q < a.qt; ++q) {
-                const uint32_t* b = a.ws.bucket + (size_t)(a.q0 + q) * a.ws.nb;
-                // A bound needs k buckets; for small k the first 256 buckets are plenty (any subset of buckets gives a
-                // valid, slightly lower bound) and fit in eight registers per lane.
-                const uint32_t nb_all = min(min(a.ws.nb, (uint32_t)kScanRefreshWords), (uint32_t)(nwarps * kScanBucketSlots));
-                uint32_t t = 0;
-                if (2u * (uint32_t)a.k <= 256u) {
-                    const uint32_t nb = min(nb_all, 256u);
+            const int q = (int)((blockIdx.x >> 3) % (unsigned)a.qt);
+            const uint32_t* b = a.ws.bucket + (size_t)(a.q0 + q) * a.ws.nb;
+            // A bound needs k buckets; for small k the first 256 buckets are plenty (any subset of buckets gives a
+            // valid, slightly lower bound) and fit in eight registers per lane.
+            const uint32_t nb_all = min(min(a.ws.nb, (uint32_t)kScanRefreshWords), (uint32_t)(nwarps * kSlots));
+            uint32_t t = 0;
+            if (2u * (uint32_t)a.k <= 256u) {
+                const uint32_t nb = min(nb_all, 256u);
+                uint32_t v[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) v[u] = ((uint32_t)(u * 32 + lane) < nb) ? __ldcg(b + u * 32 + lane) : 0u;
+                for (int bit = 31; bit >= 12; --bit) {
+                    const uint32_t cand = t | (1u << bit);
+                    uint32_t cnt = 0;
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) cnt += (v[u] >= cand) ? 1u : 0u;
+                    cnt = __reduce_add_sync(0xffffffffu, cnt);
+                    if (cnt >= (uint32_t)a.k) t = cand;
+                }
+            } else if (nb_all >= (uint32_t)a.k) {
+                // Larger k: the maxima are staged in shared memory and the top 20 bits of the k-th largest are found by
+                // a radix select (8 + 8 + 4 bits, one histogram pass each).
+                const uint32_t nb = nb_all;
+                for (uint32_t i0 = lane; i0 < nb; i0 += 256) {   // eight independent loads at a time
                     uint32_t v[8];
 #pragma unroll
-                    for (int u = 0; u < 8; ++u) v[u] = ((uint32_t)(u * 32 + lane) < nb) ? __ldcg(b + u * 32 + lane) : 0u;
-                    for (int bit = 31; bit >= 12; --bit) {
-                        const uint32_t cand = t | (1u << bit);
-                        uint32_t cnt = 0;
+                    for (int u = 0; u < 8; ++u) v[u] = (i0 + u * 32 < nb) ? __ldcg(b + i0 + u * 32) : 0u;
 #pragma unroll
-                        for (int u = 0; u < 8; ++u) cnt += (v[u] >= cand) ? 1u : 0u;
-                        cnt = __reduce_add_sync(0xffffffffu, cnt);
-                        if (cnt >= (uint32_t)a.k) t = cand;
-                    }
-                } else {
-                    const uint32_t nb = nb_all;
-                    // eight independent loads at a time (a volatile load per element would serialise on its store)
-                    for (uint32_t i0 = lane; i0 < nb; i0 += 256) {
-                        uint32_t v[8];
-#pragma unroll
-                        for (int u = 0; u < 8; ++u) v[u] = (i0 + u * 32 < nb) ? __ldcg(b + i0 + u * 32) : 0u;
-#pragma unroll
-                        for (int u = 0; u < 8; ++u)
-                            if (i0 + u * 32 < nb) s_stage[i0 + u * 32] = v[u];
+                    for (int u = 0; u < 8; ++u)
+                        if (i0 + u * 32 < nb) s_stage[i0 + u * 32] = v[u];
+                }
+                uint32_t* hist = s_stage + kScanRefreshWords;   // 256 bins behind the staged values
+                uint32_t prefix = 0, mask = 0, need = (uint32_t)a.k;
+                bool ok = true;
+#pragma unroll 1
+                for (int pass = 0; pass < 3 && ok; ++pass) {
+                    const int shift = (pass == 0) ? 24 : (pass == 1) ? 16 : 12;
+                    const uint32_t bin_mask = (pass == 2) ? 15u : 255u;
+                    for (int h = lane; h < 256; h += 32) hist[h] = 0u;
+                    __syncwarp();
+                    for (uint32_t j = lane; j < nb; j += 32) {
+                        const uint32_t v = s_stage[j];
+                        if ((v & mask) == prefix) atomicAdd(&hist[(v >> shift) & bin_mask], 1u);
                     }
                     __syncwarp();
-                    for (int bit = 31; bit >= 12; --bit) {
-                        const uint32_t cand = t | (1u << bit);
-                        uint32_t cnt = 0;
-                        for (uint32_t j = lane; j < nb; j += 32) cnt += (s_stage[j] >= cand) ? 1u : 0u;
-                        cnt = __reduce_add_sync(0xffffffffu, cnt);
-                        if (cnt >= (uint32_t)a.k) t = cand;
+                    // lane l owns digits 8l .. 8l+7; counts of all higher digits come from a suffix sum over the lanes
+                    uint32_t c[8], mine = 0;
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        c[u] = hist[lane * 8 + u];
+                        mine += c[u];
+                    }
+                    uint32_t incl = mine;   // becomes the count of values whose digit is in this lane's range or above
+#pragma unroll
+                    for (int off = 1; off < 32; off <<= 1) {
+                        const uint32_t up = __shfl_down_sync(0xffffffffu, incl, off);
+                        if (lane + off < 32) incl += up;
+                    }
+                    int hit = -1;
+                    uint32_t run = incl - mine, above_digit = 0;
+#pragma unroll
+                    for (int u = 7; u >= 0; --u) {
+                        if (hit < 0) {
+                            if (run + c[u] >= need) {
+                                hit = u;
+                                above_digit = run;
+                            } else {
+                                run += c[u];
+                            }
+                        }
+                    }
+                    const uint32_t ballot = __ballot_sync(0xffffffffu, hit >= 0);
+                    if (ballot == 0u) {
+                        ok = false;
+                    } else {
+                        const int src = 31 - __clz(ballot);   // the highest digit range that reaches the rank
+                        const uint32_t digit = (uint32_t)__shfl_sync(0xffffffffu, lane * 8 + hit, src);
+                        need -= __shfl_sync(0xffffffffu, above_digit, src);
+                        prefix |= digit << shift;
+                        mask |= bin_mask << shift;
                     }
                     __syncwarp();
                 }
-                if (lane == 0 && t != 0) atomicMax(a.ws.thr + a.q0 + q, t);
-                __syncwarp();
+                if (ok) t = prefix;
             }
+            if (lane == 0 && t != 0) atomicMax(a.ws.thr + a.q0 + q, t);
+            __syncwarp();
         }
     }
     cp_async_wait<0>();
@@ -561,7 +656,7 @@ __global__ void __launch_bounds__(kScanMaxWarps * 32, 1) stream_scan_kernel(cons
         select_block(sa, a.q0 + q, ring);   // the ring is free: every warp of this block has drained its copies
         // leave the query's workspace zeroed: the next pass starts from a clean state without a reset launch
         uint32_t* b = a.ws.bucket + (size_t)(a.q0 + q) * a.ws.nb;
-        const uint32_t nb_used = min(a.ws.nb, (uint32_t)(nwarps * kScanBucketSlots));
+        const uint32_t nb_used = min(a.ws.nb, (uint32_t)(nwarps * kSlots));
         for (uint32_t j = threadIdx.x; j < nb_used; j += blockDim.x) b[j] = 0u;
         if (threadIdx.x == 0) {
             a.ws.count[a.q0 + q] = 0u;
@@ -581,22 +676,36 @@ __global__ void __launch_bounds__(kScanMaxWarps * 32, 1) stream_scan_kernel(cons
 }
 
 // ---- host side ---------------------------------------------------------------------------------------------------
-template <int LAYOUT, int QT>
-cudaError_t launch_stream_scan_qt(cudaStream_t st, int sm_count, const StreamArgs& a, size_t smem) {
+template <int LAYOUT, int QT, int LPR, int CPL>
+cudaError_t launch_stream_scan_form(cudaStream_t st, int sm_count, const StreamArgs& a, size_t smem) {
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(stream_scan_kernel<LAYOUT, QT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448);
+        cudaError_t e = cudaFuncSetAttribute(stream_scan_kernel<LAYOUT, QT, LPR, CPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kScanSmemLimit);
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
     // one persistent block per SM; every warp is a bucket owner, so the grid is exactly what is resident at once
     const int grid = sm_count;
-    stream_scan_kernel<LAYOUT, QT><<<grid, a.g.warps * 32, smem, st>>>(a);
+    stream_scan_kernel<LAYOUT, QT, LPR, CPL><<<grid, a.g.warps * 32, smem, st>>>(a);
     count_launch();
     note_scan_launch("stream_scan_kernel", grid, a.g.warps * 32, smem);
     return cudaGetLastError();
+}
+
+// One query per launch has specialised forms for the row shapes that matter most (768-byte rows: q8 x 768 and
+// f16 x 384; 384-byte rows: q8 x 384; 128-byte rows: q4 x 256); everything else runs the generic form.
+template <int LAYOUT, int QT>
+cudaError_t launch_stream_scan_qt(cudaStream_t st, int sm_count, const StreamArgs& a, size_t smem) {
+    if constexpr (QT == 1) {
+        const int lpr = 1 << a.g.lpr_shift;
+        const int C = a.cv.chunks;
+        if (lpr == 4 && C == 48) return launch_stream_scan_form<LAYOUT, 1, 4, 12>(st, sm_count, a, smem);
+        if (lpr == 2 && C == 24) return launch_stream_scan_form<LAYOUT, 1, 2, 12>(st, sm_count, a, smem);
+        if (lpr == 1 && C == 8) return launch_stream_scan_form<LAYOUT, 1, 1, 8>(st, sm_count, a, smem);
+    }
+    return launch_stream_scan_form<LAYOUT, QT, 0, 0>(st, sm_count, a, smem);
 }
 
 template <int LAYOUT>
