@@ -486,52 +486,75 @@ def run_ours(args, wl: Workload):
             raise SystemExit("bench.py: the peer exchange and the NCCL path disagree on the merged top-k")
 
     # ---- end to end through the host-buffer ABI call ------------------------------------------------
-    hb = {}  # pinned host / staging buffers of the sharded end-to-end step (released before the streams they used)
+    # Sharded: every lane has its own pinned host buffers and staging buffers; steps alternate between the lanes, and
+    # a step's result is read (its lane synchronised) while the next step is already on the other lane, so that the
+    # selection, exchange and merge of one step overlap the scan of the next -- like the device-timed loop.  Every step's
+    # host-to-device and device-to-host copies stay inside the timed region.
+    hbs = []  # released before the streams they used
     if world > 1:
-        if wl.embed:
-            hb["tokens"] = torch.from_numpy(h_tokens)
-            hb["mask"] = torch.from_numpy(h_mask)
-            hb["s_tokens"] = torch.empty((nq, wl.embed[2]), dtype=torch.int32, device="cuda")
-            hb["s_mask"] = torch.empty((nq, wl.embed[2]), dtype=torch.int32, device="cuda")
-            hb["s_q"] = torch.empty((nq, wl.cols), dtype=torch.float16, device="cuda")
-        else:
-            hb["queries"] = torch.from_numpy(h_queries.view(np.int16)).pin_memory()
-            hb["s_q"] = torch.empty((nq, wl.cols), dtype=torch.int16, device="cuda")
-        hb["ids"] = torch.empty((nq, k), dtype=torch.int32).pin_memory()
-        hb["scores"] = torch.empty((nq, k), dtype=torch.float32).pin_memory()
+        for ln in lanes:
+            hb = {}
+            with torch.cuda.stream(ln.stream):
+                if wl.embed:
+                    hb["tokens"] = torch.from_numpy(h_tokens)
+                    hb["mask"] = torch.from_numpy(h_mask)
+                    hb["s_tokens"] = torch.empty((nq, wl.embed[2]), dtype=torch.int32, device="cuda")
+                    hb["s_mask"] = torch.empty((nq, wl.embed[2]), dtype=torch.int32, device="cuda")
+                    hb["s_q"] = torch.empty((nq, wl.cols), dtype=torch.float16, device="cuda")
+                else:
+                    hb["queries"] = torch.from_numpy(h_queries.view(np.int16)).pin_memory()
+                    hb["s_q"] = torch.empty((nq, wl.cols), dtype=torch.int16, device="cuda")
+                hb["ids"] = torch.empty((nq, k), dtype=torch.int32).pin_memory()
+                hb["scores"] = torch.empty((nq, k), dtype=torch.float32).pin_memory()
+            ln.stream.synchronize()
+            hbs.append(hb)
 
-    def step_host(i):
-        if world == 1:
-            if wl.embed:
-                return rt.embed_score_topk(emb, cands, h_tokens[i % nsets], h_mask[i % nsets], wl.metric, k, smallest=wl.smallest)
-            return rt.score_topk(cands, wl.metric, h_queries[i % nsets], k, smallest=wl.smallest)
-        # sharded: inputs from pinned host memory, one stream-ordered chain (upload, shard pass, all-gather, merge,
-        # download), one synchronisation at the end
-        with torch.cuda.stream(stream):
+    def enqueue_host_step(i):
+        """Upload, shard pass, exchange + merge, download of step i on lane i % n_lanes; returns the lane index."""
+        li = i % n_lanes
+        ln, hb = lanes[li], hbs[li]
+        with torch.cuda.stream(ln.stream):
             if wl.embed:
                 hb["s_tokens"].copy_(hb["tokens"][i % nsets], non_blocking=True)
                 hb["s_mask"].copy_(hb["mask"][i % nsets], non_blocking=True)
             else:
                 hb["s_q"].copy_(hb["queries"][i % nsets], non_blocking=True)
         if wl.embed:
-            rt.embed_device(emb, hb["s_tokens"], hb["s_mask"], nq, wl.embed[2], hb["s_q"], sync=False)
-        if lanes[0].px is not None:
-            lanes[0].px.score_topk_merge(cands, wl.metric, hb["s_q"], nq, k, m_ids, m_scores, smallest=wl.smallest, sync=False)
+            ln.rt.embed_device(emb, hb["s_tokens"], hb["s_mask"], nq, wl.embed[2], hb["s_q"], sync=False)
+        if ln.px is not None:
+            ln.px.score_topk_merge(cands, wl.metric, hb["s_q"], nq, k, ln.m_ids, ln.m_scores, smallest=wl.smallest, sync=False)
         else:
-            rt.score_topk_device(cands, wl.metric, hb["s_q"], nq, k, d_ids, d_scores, smallest=wl.smallest, sync=False)
-            lanes[0].merge(False)
-        with torch.cuda.stream(stream):
-            hb["ids"].copy_(m_ids, non_blocking=True)
-            hb["scores"].copy_(m_scores, non_blocking=True)
-        rt.synchronize()  # also raises if the pass overflowed its pool
-        return hb["ids"].numpy(), hb["scores"].numpy()
+            ln.rt.score_topk_device(cands, wl.metric, hb["s_q"], nq, k, ln.d_ids, ln.d_scores, smallest=wl.smallest, sync=False)
+            ln.merge(False)
+        with torch.cuda.stream(ln.stream):
+            hb["ids"].copy_(ln.m_ids, non_blocking=True)
+            hb["scores"].copy_(ln.m_scores, non_blocking=True)
+        return li
 
-    for i in range(args.warmup):
-        step_host(i)
+    def finish_host_step(li):
+        lanes[li].rt.synchronize()  # also raises if the pass overflowed its pool or a list never arrived
+        return hbs[li]["ids"].numpy(), hbs[li]["scores"].numpy()
+
+    def host_steps(first, count):
+        if world == 1:
+            for i in range(first, first + count):
+                if wl.embed:
+                    rt.embed_score_topk(emb, cands, h_tokens[i % nsets], h_mask[i % nsets], wl.metric, k, smallest=wl.smallest)
+                else:
+                    rt.score_topk(cands, wl.metric, h_queries[i % nsets], k, smallest=wl.smallest)
+            return
+        pending = []
+        for i in range(first, first + count):
+            pending.append(enqueue_host_step(i))
+            if len(pending) == n_lanes:  # the oldest step's lane is needed again: read its result first
+                finish_host_step(pending.pop(0))
+        while pending:
+            finish_host_step(pending.pop(0))
+
+    host_steps(0, args.warmup)
     barrier()
     t0 = time.perf_counter()
-    for i in range(args.steps):
-        step_host(args.warmup + i)
+    host_steps(args.warmup, args.steps)
     barrier()
     e2e_s = time.perf_counter() - t0
     te = torch.tensor([e2e_s], dtype=torch.float64, device="cuda")
@@ -620,7 +643,7 @@ def run_ours(args, wl: Workload):
                     "d2h_bytes_per_step": nq * k * 8, "ms_per_step": e2e_s / args.steps * 1e3,
                     "note": "host-buffer C-ABI call per step; candidates stay bound (resident) as plan parameters"
                             if world == 1 else "inputs from pinned host memory, results to pinned host memory, one synchronisation per "
-                            "step (upload, shard pass, " + ("peer-store exchange fused with the merge" if str(args.exchange) == "peer"
+                            "step, steps alternating over the lanes (upload, shard pass, " + ("peer-store exchange fused with the merge" if str(args.exchange) == "peer"
                                                             else "NCCL all-gather, merge") + ", download on one stream)"},
             "gpu_launches": int(launches), "clocks": clocks, "cpu_baseline": cpu, "parity_check": parity,
             "result_checksum": int(np.asarray(final_ids, dtype=np.int64).sum()),
@@ -631,7 +654,7 @@ def run_ours(args, wl: Workload):
     for ln in lanes:
         if ln.px is not None:
             ln.px.close()
-    hb.clear()
+    hbs.clear()
     if wl.embed:
         h_tokens = h_mask = None  # pinned: released while the streams that read them still exist
     import gc

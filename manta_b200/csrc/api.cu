@@ -543,10 +543,10 @@ static int plane_stride_for(const CandView& cv) {
 }
 
 // Pool capacity per query for the optimistic single-launch pass.
-static uint32_t pool_cap_for(const MantaB200Runtime* rt, const CandView& cv, int nq, int k) {
+static uint32_t pool_cap_for(const MantaB200Runtime* rt, const CandView& cv, int nq, int k, int metric) {
     const int64_t rows = cv.rows;
     int64_t cap;
-    if (mma_supported(cv, nq)) {
+    if (mma_supported(cv, nq, metric)) {
         cap = mma_pool_cap(k);  // observed tiles are replayed, so nothing enters the pool unfiltered
         if (cap > rows) cap = rows;
         if (cap < k) cap = k;
@@ -762,12 +762,12 @@ static int score_topk_locked(MantaB200Runtime* rt, const MantaB200Candidates* se
     const CandView& cv = set->cv;
     // a multiple of four, so that every query's bucket row starts on a 16-byte boundary
     const uint32_t nb = ((uint32_t)std::max(stream_bucket_count(rt->sm_count), mma_bucket_count(rt->sm_count)) + 3u) & ~3u;
-    uint32_t cap = pool_cap_for(rt, cv, nq, k);
+    uint32_t cap = pool_cap_for(rt, cv, nq, k, metric);
     SelectWs ws;
     if (ensure_select_ws(rt, nq, cap, nb, &ws, err)) return 1;
     t_last_scan = MantaB200LaunchInfo{};
     bool streamed = true;
-    if (mma_supported(cv, nq)) {
+    if (mma_supported(cv, nq, metric)) {
         bool declined = false;
         if (mma_pass(rt, cv, d_queries, metric, order, k, ws, nq, d_out_ids, d_out_scores, sink, &declined, err)) return 1;
         streamed = declined;

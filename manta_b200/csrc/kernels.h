@@ -1,8 +1,6 @@
 // Host-side launchers of the kernels (one translation unit per kernel family).
 #pragma once
 
-#include <stdlib.h>
-
 #include "common.cuh"
 
 namespace mb200 {
@@ -159,25 +157,19 @@ inline bool stream_scan_geometry(const CandView& cv, int qt, int64_t row_begin, 
     // one round trip of latency -- is paid once per tile whatever its size), not the depth of the ring, so the ring is
     // two stages deep (one tile in flight per warp while one is consumed, 16 warps per SM) and the tile as tall as the
     // block's shared memory allows.  Deeper rings with shorter tiles were 1.4x to 1.7x slower on every layout.
-    const char* env_s = getenv("MB200_SCAN_S");
-    const char* env_r = getenv("MB200_SCAN_R");
     for (int warps = scan_warps(qt); warps >= 1; warps >>= 1) {
         long best = -1;
         ScanGeometry pick{};
-        for (int S = 2; S <= 4 && best < 0; ++S) {
-            if (env_s && atoi(env_s) != S) continue;
-            if (!env_s && S != (qt == 1 ? 2 : 3)) continue;
-            const size_t budget = (kScanSmemLimit - fixed) / ((size_t)warps * S);
-            for (int R = 32; R >= 1; R >>= 1) {
-                if (env_r && atoi(env_r) != R) continue;
-                ScanGeometry t = *g;
-                stage_bytes_for(R, &t);
-                if ((size_t)t.stage_bytes > budget) continue;
-                best = (long)(S - 1) * R * C * 16;
-                pick = t;
-                pick.stages = S;
-                break;
-            }
+        const int S = (qt == 1) ? 2 : 3;
+        const size_t budget = (kScanSmemLimit - fixed) / ((size_t)warps * S);
+        for (int R = 32; R >= 1; R >>= 1) {
+            ScanGeometry t = *g;
+            stage_bytes_for(R, &t);
+            if ((size_t)t.stage_bytes > budget) continue;
+            best = (long)R;
+            pick = t;
+            pick.stages = S;
+            break;
         }
         if (best < 0) continue;
         pick.warps = warps;

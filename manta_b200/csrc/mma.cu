@@ -28,7 +28,11 @@ constexpr int kTileRows = 128;
 constexpr int kChunkBytes = 128;      // K extent of one pipeline stage, in bytes (one 128-byte swizzle span)
 // SUBS (template parameter of the kernel) = epilogue warps per tensor-memory quadrant; warp s of a quadrant takes the
 // 16-query chunks s, s + SUBS, ...
-constexpr int mma_threads(int subs) { return 32 * (2 + 4 * subs + 1); }
+constexpr int kConvWarps = 4;          // q4 candidates: warps that unpack nibbles to f16 into the operand ring
+constexpr int mma_threads(int subs, bool conv = false) { return 32 * (2 + 4 * subs + 1 + (conv ? kConvWarps : 0)); }
+constexpr int kRawStages = 3;         // q4 candidates: ring of raw (packed) tiles in front of the converter warps
+constexpr int kRawStageBytes = kTileRows * kChunkBytes;   // one swizzled 128 x 128-byte box of nibbles
+constexpr int kQ4Blocks = 8;          // q4 rows the tensor-core pass takes are 256 columns = eight blocks = one raw chunk
 constexpr int kMmaCols = 256;         // N of one MMA
 constexpr int kBucketSlots = 4;       // bucket slots per epilogue warp (tiles rotate through them)
 constexpr uint32_t kSpinLimit = 1u << 22;
@@ -75,6 +79,13 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
         : "memory");
 }
 
+// Plain (untiled) bulk copy global -> shared; both addresses 16-byte aligned, bytes a multiple of 16.
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+
 __device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t cols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(cols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -109,6 +120,11 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
         : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
           "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
         : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t* v) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                 : "r"(taddr));
 }
 __device__ __forceinline__ void tmem_ld4(uint32_t taddr, uint32_t (&v)[4]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];"
@@ -146,6 +162,7 @@ struct KernelArgs {
     int k;
     int filtered;                 // 0: everything enters the pool (small sets)
     int observe_tiles;            // tiles per CTA scored before the first bound exists (replayed at the end)
+    int raw_chunks;               // q4: 128-byte chunks of packed nibbles per row (each becomes four f16 K chunks)
     int64_t row_begin;
     int64_t row_end;
 };
@@ -168,8 +185,16 @@ __device__ __forceinline__ void score_n(const uint32_t (&vh)[N], const uint32_t 
     }
 }
 
-template <bool I8, int METRIC, int SUBS>
-__global__ void __launch_bounds__(mma_threads(SUBS), 1)
+// Q4: the candidates are q4 rows of 256 columns (eight blocks of 32).  The TMA producer fills a ring of raw tiles (128
+// rows x 128 bytes of nibbles, 128-byte swizzle) and four converter warps, one thread per row, unpack each raw tile
+// into four f16 operand stages holding the CODES (small integers, exact in f16).  The MMA issuer gives every block its
+// own accumulator columns (block b, query j -> column b * ncols + j; K = 32 per block, two instructions), so tensor
+// memory holds the exact per-block sums of code * query, and the epilogue applies the row's eight block scales with
+// eight fused multiply-adds per score -- the arithmetic of the streaming kernel with the exact f16 query.
+// Within every group of eight elements the converter emits them in the order 0,4,1,5,2,6,3,7 (what the nibble
+// unpack yields pairwise); operand B is built with the same order, and a contraction does not care.
+template <bool I8, int METRIC, int SUBS, bool Q4>
+__global__ void __launch_bounds__(mma_threads(SUBS, Q4), 1)
 mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const KernelArgs a) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -180,13 +205,16 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* sA = base;
     unsigned char* sB = sA + (size_t)S * kTileRows * kChunkBytes;
-    unsigned char* p = sB + (size_t)(a.b_resident ? a.kchunks : S) * b_stage_bytes;
+    unsigned char* sRaw = sB + (size_t)(a.b_resident ? a.kchunks : S) * b_stage_bytes;   // q4 only (1024-byte aligned: every stage is)
+    unsigned char* p = sRaw + (Q4 ? (size_t)kRawStages * kRawStageBytes : 0);
     uint64_t* full = (uint64_t*)p;
     uint64_t* empty = full + 8;
     uint64_t* tfull = empty + 8;
     uint64_t* tempty = tfull + 2;
     uint64_t* bfull = tempty + 2;
-    uint32_t* tmem_slot = (uint32_t*)(bfull + 1);
+    uint64_t* rfull = bfull + 1;          // [kRawStages]
+    uint64_t* rempty = rfull + kRawStages;  // [kRawStages]
+    uint32_t* tmem_slot = (uint32_t*)(rempty + kRawStages);
     volatile uint32_t* abort_s = tmem_slot + 1;
     volatile uint32_t* done_s = tmem_slot + 2;       // epilogue warps that have finished
     volatile uint32_t* thr_ready_s = tmem_slot + 3;  // set by the refresher once every query has a bound
@@ -207,8 +235,12 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; ++s) {
-            mbar_init(&full[s], 1);
+            mbar_init(&full[s], Q4 ? kConvWarps : 1);   // q4: one arrival per converter warp instead of a TMA transaction
             mbar_init(&empty[s], 1);
+        }
+        for (int s = 0; s < kRawStages; ++s) {
+            mbar_init(&rfull[s], 1);
+            mbar_init(&rempty[s], kConvWarps);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&tfull[b], 1);
@@ -257,8 +289,19 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     for (int kc = 0; kc < a.kchunks; ++kc)
                         tma_load_2d(sB + (size_t)kc * b_stage_bytes, &map_b, kc * kChunkBytes, 0, bfull);
                 }
+                if constexpr (Q4) {
+                    // raw tiles: one 128 x 128-byte box of nibbles per tile; the converter warps make the operand stages
+                    for (int it = 0; it < n_iters && !*abort_s; ++it) {
+                        const int row0 = (int)(a.row_begin + (int64_t)tile_of(it) * kTileRows);
+                        const int rs = it % kRawStages;
+                        const uint32_t ph = (uint32_t)(it / kRawStages) & 1u;
+                        if (!mbar_wait(&rempty[rs], ph ^ 1u, abort_s)) break;
+                        mbar_expect_tx(&rfull[rs], (uint32_t)kRawStageBytes);
+                        tma_load_2d(sRaw + (size_t)rs * kRawStageBytes, &map_a, 0, row0, &rfull[rs]);
+                    }
+                }
                 const uint32_t stage_tx = (uint32_t)(kTileRows * kChunkBytes) + (a.b_resident ? 0u : b_stage_bytes);
-                for (int it = 0; it < n_iters && !*abort_s; ++it) {
+                for (int it = 0; !Q4 && it < n_iters && !*abort_s; ++it) {
                     const int row0 = (int)(a.row_begin + (int64_t)tile_of(it) * kTileRows);
                     for (int kc = 0; kc < a.kchunks; ++kc, ++g) {
                         const int s = g % S;
@@ -296,8 +339,15 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         const uint32_t b_addr = smem_u32(sB + (size_t)(a.b_resident ? kc : s) * b_stage_bytes);
 #pragma unroll
                         for (int ks = 0; ks < kChunkBytes / 32; ++ks) {
-                            tc_mma<I8>(d_tmem, smem_desc_sw128(a_addr + ks * 32), smem_desc_sw128(b_addr + ks * 32), idesc,
-                                       (kc > 0 || ks > 0) ? 1u : 0u);
+                            if constexpr (Q4) {
+                                // 32 bytes = 16 codes: two steps per block, each block into its own columns
+                                const uint32_t blk = (uint32_t)(kc * 2 + (ks >> 1));
+                                tc_mma<I8>(d_tmem + blk * (uint32_t)a.ncols, smem_desc_sw128(a_addr + ks * 32), smem_desc_sw128(b_addr + ks * 32),
+                                           idesc, (ks & 1) ? 1u : 0u);
+                            } else {
+                                tc_mma<I8>(d_tmem, smem_desc_sw128(a_addr + ks * 32), smem_desc_sw128(b_addr + ks * 32), idesc,
+                                           (kc > 0 || ks > 0) ? 1u : 0u);
+                            }
                         }
                         tc_commit(&empty[s]);   // frees the stage when these MMAs have read it
                     }
@@ -319,6 +369,21 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             // every (metric, order) has a pre-filter except "largest l2 distance", which takes the exact path throughout
             constexpr bool kL2 = METRIC == MANTA_B200_METRIC_L2_DISTANCE;
             const bool cheap = !(kL2 && a.order == MANTA_B200_ORDER_LARGEST);
+            float nxt_sd = 0.0f;
+            uint32_t nxt_stat = 0;
+            uint4 nxt_sc = make_uint4(0u, 0u, 0u, 0u);
+            auto load_row_consts = [&](int it2) {
+                const int64_t r2 = a.row_begin + (int64_t)tile_of(it2) * kTileRows + quad * 32 + lane;
+                nxt_sd = 0.0f;
+                nxt_stat = 0;
+                nxt_sc = make_uint4(0u, 0u, 0u, 0u);
+                if (r2 < a.row_end) {
+                    if (want_scale) nxt_sd = ((const float*)a.cv.scales)[r2];
+                    if (want_stats) nxt_stat = ((const uint32_t*)a.cv.stats)[r2];
+                    if constexpr (Q4) nxt_sc = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(a.cv.scales) + (size_t)r2 * kQ4Blocks));
+                }
+            };
+            if (n_iters > 0) load_row_consts(0);
             for (int it = 0; it < n_iters; ++it) {
                 const bool observe = it < n_obs;            // score and record maxima only
                 const bool replay = it >= n_my;             // append only
@@ -327,13 +392,21 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     for (uint32_t spin = 0; spin < 40000u && !*thr_ready_s && !*abort_s; ++spin) __nanosleep(100);
                 }
                 const int acc = it & 1;
-                // row constants of this tile (issued before the wait so their latency hides behind it)
+                // Row constants (row scale, statistic, q4 block scales): the loads for the NEXT tile are issued now and
+                // used one iteration later, so their latency (these rows are cold in L2) hides behind a whole tile.
                 const int64_t row = a.row_begin + (int64_t)tile_of(it) * kTileRows + quad * 32 + lane;
                 const bool rv = row < a.row_end;
-                float sd = 0.0f;
-                uint32_t stat = 0;
-                if (rv && want_scale) sd = ((const float*)a.cv.scales)[row];
-                if (rv && want_stats) stat = ((const uint32_t*)a.cv.stats)[row];
+                const float sd = nxt_sd;
+                const uint32_t stat = nxt_stat;
+                const uint4 sc = nxt_sc;
+                if (it + 1 < n_iters) load_row_consts(it + 1);
+                float bsc[kQ4Blocks];   // q4: the row's eight block scales
+                if constexpr (Q4) {
+                    const uint32_t scw[4] = {sc.x, sc.y, sc.z, sc.w};
+#pragma unroll
+                    for (int b = 0; b < kQ4Blocks; ++b)
+                        bsc[b] = __half2float(__ushort_as_half((unsigned short)((b & 1) ? (scw[b >> 1] >> 16) : (scw[b >> 1] & 0xffffu))));
+                }
                 float rinv = 0.0f;
                 if (METRIC == MANTA_B200_METRIC_COSINE) rinv = I8 ? q8_row_inv_norm((int)stat) : float_row_inv_norm(__uint_as_float(stat));
                 if (!mbar_wait(&tfull[acc], (uint32_t)(it >> 1) & 1u, abort_s)) break;
@@ -379,14 +452,34 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     uint32_t groups = 0xFu;   // four-query groups of the chunk that need the exact evaluation
                     uint32_t vh[16], vl[16];
                     if (cheap) {
-                        tmem_ld16(t_row + c0, vh);
-                        if constexpr (I8) {
-                            tmem_ld16(t_row + a.lo_off + c0, vl);
-                        } else {
+                        if constexpr (Q4) {
+                            // dot = sum over the eight blocks of scale_b * (exact block sum), in block order; eight
+                            // queries at a time, so that the eight block reads are in flight together behind one wait
 #pragma unroll
-                            for (int jj = 0; jj < 16; ++jj) vl[jj] = 0;
+                            for (int half = 0; half < 2; ++half) {
+                                uint32_t pb[kQ4Blocks][8];
+#pragma unroll
+                                for (int b = 0; b < kQ4Blocks; ++b) tmem_ld8(t_row + (uint32_t)(b * a.ncols + c0 + 8 * half), pb[b]);
+                                tmem_ld_wait();
+#pragma unroll
+                                for (int jj = 0; jj < 8; ++jj) {
+                                    float dv = 0.0f;
+#pragma unroll
+                                    for (int b = 0; b < kQ4Blocks; ++b) dv = __fmaf_rn(bsc[b], __uint_as_float(pb[b][jj]), dv);
+                                    vh[8 * half + jj] = __float_as_uint(dv);
+                                    vl[8 * half + jj] = 0;
+                                }
+                            }
+                        } else {
+                            tmem_ld16(t_row + c0, vh);
+                            if constexpr (I8) {
+                                tmem_ld16(t_row + a.lo_off + c0, vl);
+                            } else {
+#pragma unroll
+                                for (int jj = 0; jj < 16; ++jj) vl[jj] = 0;
+                            }
+                            tmem_ld_wait();
                         }
-                        tmem_ld_wait();
                     }
                     if (cheap) {
                         // Pre-filter without finishing the scores.  With s_hi = 254 * s_lo the unscaled dot product is
@@ -422,14 +515,29 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                             if (cg >= a.qn) break;
                             if (!((groups >> gq) & 1u)) continue;
                             uint32_t h4[4], l4[4];
-                            tmem_ld4(t_row + cg, h4);
-                            if constexpr (I8) {
-                                tmem_ld4(t_row + a.lo_off + cg, l4);
-                            } else {
+                            if constexpr (Q4) {
+                                uint32_t pb[kQ4Blocks][4];
 #pragma unroll
-                                for (int jj = 0; jj < 4; ++jj) l4[jj] = 0;
+                                for (int b = 0; b < kQ4Blocks; ++b) tmem_ld4(t_row + (uint32_t)(b * a.ncols + cg), pb[b]);
+                                tmem_ld_wait();
+#pragma unroll
+                                for (int jj = 0; jj < 4; ++jj) {
+                                    float dv = 0.0f;
+#pragma unroll
+                                    for (int b = 0; b < kQ4Blocks; ++b) dv = __fmaf_rn(bsc[b], __uint_as_float(pb[b][jj]), dv);
+                                    h4[jj] = __float_as_uint(dv);
+                                    l4[jj] = 0;
+                                }
+                            } else {
+                                tmem_ld4(t_row + cg, h4);
+                                if constexpr (I8) {
+                                    tmem_ld4(t_row + a.lo_off + cg, l4);
+                                } else {
+#pragma unroll
+                                    for (int jj = 0; jj < 4; ++jj) l4[jj] = 0;
+                                }
+                                tmem_ld_wait();
                             }
-                            tmem_ld_wait();
                             float g[4];
                             uint32_t o[4];
                             score_n<I8, METRIC, 4>(h4, l4, stat, rinv, sd, hdr_s, cg, a.qn, rv, sign, g, o);
@@ -468,7 +576,54 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             }
             __syncwarp();
             if (lane == 0) atomicAdd((uint32_t*)done_s, 1u);
-        } else if (a.filtered) {
+        } else if (Q4 && warp >= 2 + kEpiWarps + 1) {
+            // ---------------- q4 converter ----------------
+            // Thread t of the four converter warps owns row t of the tile.  Per raw chunk (128 bytes of nibbles = 256
+            // elements = 8 blocks) it reads its row from the swizzled raw stage and its eight block scales from global
+            // memory, and writes four operand stages of 64 f16 each.
+            const int t = (warp - (2 + kEpiWarps + 1)) * 32 + lane;
+            const __half2 off2 = __floats2half2_rn(1032.0f, 1032.0f);
+            uint32_t g = 0;
+            for (int it = 0; it < n_iters && !*abort_s; ++it) {
+                const int rs = it % kRawStages;
+                if (!mbar_wait(&rfull[rs], (uint32_t)(it / kRawStages) & 1u, abort_s)) break;
+                const unsigned char* raw = sRaw + (size_t)rs * kRawStageBytes + (size_t)t * kChunkBytes;
+                bool ok = true;
+                for (int kc = 0; kc < 4; ++kc, ++g) {
+                    const int s = g % S;
+                    if (!mbar_wait(&empty[s], ((g / S) & 1u) ^ 1u, abort_s)) { ok = false; break; }
+                    unsigned char* dst = sA + (size_t)s * kTileRows * kChunkBytes + (size_t)t * kChunkBytes;
+                    // 32 raw bytes = two 16-byte chunks (2kc, 2kc+1), each one block of 32 codes
+#pragma unroll
+                    for (int hb = 0; hb < 2; ++hb) {
+                        const int rawc = 2 * kc + hb;
+                        const uint4 w4 = *reinterpret_cast<const uint4*>(raw + ((rawc ^ (t & 7)) << 4));
+                        const uint32_t w[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+                        for (int wi = 0; wi < 4; ++wi) {
+                            // nibble n (two's complement) ^ 8 is n + 8; 0x6400 | u is the half 1024 + u: subtract 1032
+                            const uint32_t x = w[wi] ^ 0x88888888u;
+                            uint32_t o[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const uint32_t bits = ((x >> (4 * e)) & 0x000F000Fu) | 0x64006400u;
+                                const __half2 code = __hsub2(*reinterpret_cast<const __half2*>(&bits), off2);
+                                o[e] = *reinterpret_cast<const uint32_t*>(&code);
+                            }
+                            const int outc = 4 * hb + wi;   // 16-byte chunk of the 128-byte operand row
+                            *reinterpret_cast<uint4*>(dst + ((outc ^ (t & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                        }
+                    }
+                    // make the generic-proxy stores visible to the tensor core's async proxy, then one arrival per warp
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&full[s]);
+                }
+                if (!ok) break;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&rempty[rs]);
+            }
+        } else if (a.filtered && warp == 2 + kEpiWarps) {
             // ---------------- threshold refresher ----------------
             // Waits until every epilogue warp of every active CTA has published its observed tiles, then keeps
             // recomputing, for one query per round, the k-th largest bucket maximum (top 20 bits; rounding a bound
@@ -603,9 +758,17 @@ __global__ void build_b_kernel(unsigned char* __restrict__ out, int ncols, int k
                 else if (n >= lo_off && n < lo_off + qn)
                     v = (unsigned char)qp.plane_lo[(size_t)(q0 + n - lo_off) * qp.plane_stride + kb];
             }
-        } else if (n < qn && (kb >> 1) < cols) {
-            const __half h = __float2half_rn(qp.qf32[(size_t)(q0 + n) * cols + (kb >> 1)]);
-            v = (unsigned char)((__half_as_ushort(h) >> ((kb & 1) * 8)) & 0xFF);
+        } else if (n < qn) {
+            // q4 candidates reach the MMA as f16 with every group of eight elements in the converter's order
+            int e = kb >> 1;
+            if (layout == MANTA_B200_LAYOUT_Q4_B32_F16) {
+                const int j = e & 7;
+                e = (e & ~7) + ((j & 1) ? 4 + (j >> 1) : (j >> 1));
+            }
+            if (e < cols) {
+                const __half h = __float2half_rn(qp.qf32[(size_t)(q0 + n) * cols + e]);
+                v = (unsigned char)((__half_as_ushort(h) >> ((kb & 1) * 8)) & 0xFF);
+            }
         }
         out[i] = v;
     }
@@ -622,17 +785,26 @@ struct MmaState {
     unsigned char* d_b = nullptr;     // operand B staging
     size_t d_b_bytes = 0;
     uint32_t* d_ready = nullptr;
-    bool attr_set[12] = {};
+    bool attr_set[18] = {};
 };
 
-static int mma_group_queries(const CandView& cv) { return cv.layout == MANTA_B200_LAYOUT_Q8_ROW_F32 ? kMmaCols / 2 : kMmaCols; }
+static int mma_group_queries(const CandView& cv) {
+    if (cv.layout == MANTA_B200_LAYOUT_Q4_B32_F16) return kMmaCols / kQ4Blocks;   // every block has its own columns: 8 x 32 = 256
+    return cv.layout == MANTA_B200_LAYOUT_Q8_ROW_F32 ? kMmaCols / 2 : kMmaCols;
+}
 
-bool mma_supported(const CandView& cv, int nq) {
-    if (cv.layout != MANTA_B200_LAYOUT_Q8_ROW_F32 && cv.layout != MANTA_B200_LAYOUT_F16) return false;
-    if (nq < 8) return false;               // small batches stream faster on the GEMV kernel
+bool mma_supported(const CandView& cv, int nq, int metric) {
+    if (nq < 8) return false;               // small batches stream faster on the streaming kernel
     if (cv.rows < kTileRows) return false;
     if (((uintptr_t)cv.data & 15) || (cv.row_bytes & 15)) return false;
-    return true;
+    if (cv.layout == MANTA_B200_LAYOUT_Q4_B32_F16) {
+        // q4 rows reach the tensor cores as f16 codes, one accumulator range per 32-element block, and the block scales
+        // are applied to the exact per-block sums: rows of 256 columns (eight blocks, one 128-byte chunk of nibbles)
+        // whose scale rows are 16-byte aligned.
+        (void)metric;
+        return cv.cols == 32 * kQ4Blocks && ((uintptr_t)cv.scales & 15) == 0;
+    }
+    return cv.layout == MANTA_B200_LAYOUT_Q8_ROW_F32 || cv.layout == MANTA_B200_LAYOUT_F16;
 }
 int mma_bucket_count(int sm_count) { return sm_count * 4 * kBucketSlots; }
 int mma_first_burst_rows(int) { return 0; }
@@ -664,31 +836,38 @@ static cudaError_t make_map(MmaState* st, CUtensorMap* map, const void* base, ui
     return cudaSuccess;
 }
 
-template <bool I8, int METRIC, int SUBS>
+template <bool I8, int METRIC, int SUBS, bool Q4>
 static cudaError_t launch_scan_subs(MmaState* st, int slot, int grid, size_t smem, cudaStream_t stream, const CUtensorMap& map_a,
                                     const CUtensorMap& map_b, const KernelArgs& ka, const char** why) {
     const int idx = slot * 2 + (SUBS == 4 ? 1 : 0);
     if (!st->attr_set[idx]) {
-        cudaError_t e = cudaFuncSetAttribute(mma_scan_kernel<I8, METRIC, SUBS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit);
+        cudaError_t e = cudaFuncSetAttribute(mma_scan_kernel<I8, METRIC, SUBS, Q4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit);
         if (e != cudaSuccess) { *why = "cudaFuncSetAttribute"; return e; }
         st->attr_set[idx] = true;
     }
-    mma_scan_kernel<I8, METRIC, SUBS><<<grid, mma_threads(SUBS), smem, stream>>>(map_a, map_b, ka);
-    note_scan_launch("mma_scan_kernel", grid, mma_threads(SUBS), smem);
+    mma_scan_kernel<I8, METRIC, SUBS, Q4><<<grid, mma_threads(SUBS, Q4), smem, stream>>>(map_a, map_b, ka);
+    note_scan_launch("mma_scan_kernel", grid, mma_threads(SUBS, Q4), smem);
     return cudaSuccess;
 }
 
-template <bool I8, int METRIC>
+template <bool I8, int METRIC, bool Q4 = false>
 static cudaError_t launch_scan_one(MmaState* st, int slot, int grid, size_t smem, cudaStream_t stream, const CUtensorMap& map_a,
                                    const CUtensorMap& map_b, const KernelArgs& ka, const char** why) {
-    if (ka.epi_subs == 4) return launch_scan_subs<I8, METRIC, 4>(st, slot, grid, smem, stream, map_a, map_b, ka, why);
-    return launch_scan_subs<I8, METRIC, 2>(st, slot, grid, smem, stream, map_a, map_b, ka, why);
+    if (ka.epi_subs == 4) return launch_scan_subs<I8, METRIC, 4, Q4>(st, slot, grid, smem, stream, map_a, map_b, ka, why);
+    return launch_scan_subs<I8, METRIC, 2, Q4>(st, slot, grid, smem, stream, map_a, map_b, ka, why);
 }
 
 // One instantiation per (layout, metric): the epilogue of each is straight-line code for its own metric.
-static cudaError_t launch_scan_variant(MmaState* st, bool i8, int metric, int grid, size_t smem, cudaStream_t stream,
+static cudaError_t launch_scan_variant(MmaState* st, int layout, int metric, int grid, size_t smem, cudaStream_t stream,
                                        const CUtensorMap& map_a, const CUtensorMap& map_b, const KernelArgs& ka, const char** why) {
-    const int slot = (i8 ? 0 : 3) + metric;
+    if (layout == MANTA_B200_LAYOUT_Q4_B32_F16) {
+        switch (metric) {
+            case MANTA_B200_METRIC_DOT: return launch_scan_one<false, MANTA_B200_METRIC_DOT, true>(st, 6, grid, smem, stream, map_a, map_b, ka, why);
+            case MANTA_B200_METRIC_COSINE: return launch_scan_one<false, MANTA_B200_METRIC_COSINE, true>(st, 7, grid, smem, stream, map_a, map_b, ka, why);
+            default: return launch_scan_one<false, MANTA_B200_METRIC_L2_DISTANCE, true>(st, 8, grid, smem, stream, map_a, map_b, ka, why);
+        }
+    }
+    const int slot = (layout == MANTA_B200_LAYOUT_Q8_ROW_F32 ? 0 : 3) + metric;
     switch (slot) {
         case 0: return launch_scan_one<true, MANTA_B200_METRIC_DOT>(st, slot, grid, smem, stream, map_a, map_b, ka, why);
         case 1: return launch_scan_one<true, MANTA_B200_METRIC_COSINE>(st, slot, grid, smem, stream, map_a, map_b, ka, why);
@@ -725,7 +904,10 @@ cudaError_t launch_mma_topk(cudaStream_t stream, int sm_count, MmaState** state,
     const CandView& cv = a.cv;
     const bool i8 = cv.layout == MANTA_B200_LAYOUT_Q8_ROW_F32;
     const int group = mma_group_queries(cv);
-    const int kchunks = (cv.row_bytes + kChunkBytes - 1) / kChunkBytes;
+    const bool q4 = cv.layout == MANTA_B200_LAYOUT_Q4_B32_F16;
+    // q4: a 128-byte chunk of nibbles (256 codes) becomes four 128-byte K chunks of f16
+    const int raw_chunks = (cv.row_bytes + kChunkBytes - 1) / kChunkBytes;
+    const int kchunks = q4 ? 4 * raw_chunks : raw_chunks;
     const int kpad = kchunks * kChunkBytes;
     const size_t b_bytes = (size_t)kMmaCols * kpad;
     if (st->d_b_bytes < b_bytes) {
@@ -774,14 +956,16 @@ cudaError_t launch_mma_topk(cudaStream_t stream, int sm_count, MmaState** state,
         const size_t a_stage = (size_t)kTileRows * kChunkBytes, b_stage = (size_t)ncols * kChunkBytes;
         const size_t fixed = 1024 /*alignment slack*/ + 256 /*barriers*/ + sizeof(QueryHeader) * kMmaCols + 4 * kMmaCols +
                              16 * kMmaCols + 16 * kMmaCols * kBucketSlots + 8 * kMmaCols;
-        const size_t budget = kSmemLimit - fixed;
+        const size_t raw_ring = q4 ? (size_t)kRawStages * kRawStageBytes : 0;
+        const size_t budget = kSmemLimit - fixed - raw_ring;
         // Operand B stays resident when it leaves room for at least four candidate stages: the ring then carries
         // only candidate bytes instead of re-reading the queries from L2 for every tile.
         const int b_resident = (b_stage * kchunks + 4 * a_stage <= budget) ? 1 : 0;
         int stages = b_resident ? (int)((budget - b_stage * kchunks) / a_stage) : (int)(budget / (a_stage + b_stage));
         if (stages > 8) stages = 8;
         if (stages < 2) { *why = "not enough shared memory for two pipeline stages"; return cudaErrorInvalidValue; }
-        const size_t smem = fixed + (b_resident ? b_stage * kchunks + stages * a_stage : stages * (a_stage + b_stage));
+        if (q4 && !b_resident) { *why = "q4 rows this wide do not leave room for the resident query operand"; return cudaErrorNotSupported; }
+        const size_t smem = fixed + raw_ring + (b_resident ? b_stage * kchunks + stages * a_stage : stages * (a_stage + b_stage));
 
         KernelArgs ka;
         ka.cv = cv;
@@ -804,7 +988,8 @@ cudaError_t launch_mma_topk(cudaStream_t stream, int sm_count, MmaState** state,
         ka.observe_tiles = observe;
         ka.row_begin = a.row_begin;
         ka.row_end = a.row_end;
-        e = launch_scan_variant(st, i8, a.metric, grid, smem, stream, map_a, map_b, ka, why);
+        ka.raw_chunks = raw_chunks;
+        e = launch_scan_variant(st, cv.layout, a.metric, grid, smem, stream, map_a, map_b, ka, why);
         if (e != cudaSuccess) return e;
         count_launch();
         ++*launches;

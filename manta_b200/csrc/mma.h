@@ -19,8 +19,8 @@ struct MmaArgs {
     SelectWs ws;
 };
 
-// True when the tensor-core pass handles this candidate set and query count.
-bool mma_supported(const CandView& cv, int nq);
+// True when the tensor-core pass handles this candidate set, query count and metric.
+bool mma_supported(const CandView& cv, int nq, int metric);
 int mma_bucket_count(int sm_count);
 int mma_first_burst_rows(int sm_count);
 // Pool capacity per query of a filtered tensor-core pass.

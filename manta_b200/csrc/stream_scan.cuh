@@ -17,8 +17,10 @@
 // Top-k.  A row's score enters the query's pool when it is not below the query's threshold.  The threshold is the
 // k-th largest of the per-warp running maxima ("buckets": disjoint row sets, so k bucket maxima >= t prove that k
 // rows score >= t); it can only be too low, never too high, so the pool always contains the true top k.  Until a
-// first threshold exists a warp only observes (scores, bucket maxima); once it exists the warp re-reads the tiles it
-// observed (still in L2) and appends what passes, so nothing waits and the pool never sees an unfiltered burst.
+// first threshold exists a warp only observes (scores, bucket maxima; with one query per launch it also keeps the
+// keys of its first four tiles in registers); once it exists the held keys go through the filter, or, if more tiles
+// were observed than are held, the warp re-reads them (still in L2) and appends what passes.  Nothing waits and the
+// pool never sees an unfiltered burst.
 // The last block to finish selects the exact top k of the launch's queries (select.cuh), stores them (sharded: also
 // into every rank's exchange inbox) and leaves the workspace zeroed for the next pass: a fused step is one launch.
 #pragma once
@@ -43,12 +45,15 @@ __device__ __forceinline__ void cp_async_wait() {
 }
 
 // ---- query preparation inside the scan ------------------------------------------------------------------------
-// One warp prepares one query into shared memory: header, and either the two int8 planes in the order the consumer
-// reads them (q8: element order; q4: per 32-element block, per 8-element group the even elements then the odd ones,
-// matching the nibble unpack) or the f32 values (f16 candidates), zero padded to whole chunks.
-// ||q||^2 is summed in f64: lane l adds elements l, l+32, ... in order, then the 32 partial sums are combined by an
-// xor butterfly (16, 8, 4, 2, 1); the squared norm of the query the planes represent is summed the same way.  The
-// stand-alone preparation kernel (prep.cu) and the CPU model of the packed path use the same order.
+// The whole block prepares the launch's queries into shared memory: header, and either the two int8 planes in the
+// order the consumer reads them (q8: element order; q4: per 32-element block, per 8-element group the even elements
+// then the odd ones, matching the nibble unpack) or the f32 values (f16 candidates), zero padded to whole chunks.
+//   1. all threads: max |x| of every query (any order: a maximum) -> the plane scales s_hi = max/127, s_lo = s_hi/254;
+//   2. all threads: the planes, element by element (each element is independent of the others);
+//   3. warp q: the sums of query q that must come out bit for bit on every path: ||q||^2 in f64 (lane l adds
+//      elements l, l+32, ... in order, then the 32 partial sums meet in an xor butterfly 16, 8, 4, 2, 1) and, for
+//      packed candidates, the squared norm of the query the planes represent, summed the same way.
+// The stand-alone preparation kernel (prep.cu) and the CPU model of the packed path use the same arithmetic and order.
 __device__ __forceinline__ void quantise_query_element(float v, float sh, float sl, bool zero, float* h, float* l) {
     *h = 0.0f;
     *l = 0.0f;
@@ -65,63 +70,102 @@ __device__ __forceinline__ void quantise_query_element(float v, float sh, float 
     *l = ll;
 }
 
+// Storage position inside a plane of query element e (the inverse of the order described above).
 template <int LAYOUT>
-__device__ __forceinline__ void prepare_query_warp(const __half* __restrict__ src, int cols, int chunks, int lane, QueryHeader* hdr,
-                                                   unsigned char* q_s) {
+__device__ __forceinline__ int plane_index_of_element(int e) {
+    if constexpr (LAYOUT == MANTA_B200_LAYOUT_Q4_B32_F16) {
+        const int blk = e >> 5, j = e & 31, grp = j >> 3, pos = j & 7;
+        return blk * 32 + (2 * grp + (pos & 1)) * 4 + (pos >> 1);
+    }
+    return e;
+}
+
+template <int LAYOUT, int QT>
+__device__ __forceinline__ void prepare_queries_block(const __half* __restrict__ queries, int q0, int qt, int cols, int chunks, int q_bytes,
+                                                      QueryHeader* hdr_s, unsigned char* q_s, float* s_red /* [QT][32] scratch */) {
     constexpr bool kF16 = LAYOUT == MANTA_B200_LAYOUT_F16;
     constexpr bool kQ4 = LAYOUT == MANTA_B200_LAYOUT_Q4_B32_F16;
-    float amax = 0.0f;
-    double part = 0.0;
-    for (int c = lane; c < cols; c += 32) {
-        const float v = __half2float(src[c]);
-        amax = fmaxf(amax, fabsf(v));
-        part = __dadd_rn(part, __dmul_rn((double)v, (double)v));
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, W = blockDim.x >> 5;
+    // 1. max |x| per query
+#pragma unroll
+    for (int q = 0; q < QT; ++q) {
+        const __half* src = queries + (size_t)(q0 + ((q < qt) ? q : 0)) * cols;   // unused slots repeat query 0 of the launch
+        float amax = 0.0f;
+        for (int c = threadIdx.x; c < cols; c += blockDim.x) amax = fmaxf(amax, fabsf(__half2float(src[c])));
+        for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+        if (lane == 0) s_red[q * 32 + warp] = amax;
     }
-    for (int off = 16; off > 0; off >>= 1) {
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
-        part = __dadd_rn(part, __shfl_xor_sync(0xffffffffu, part, off));
+    __syncthreads();
+    float s_hi[QT], s_lo[QT];
+    bool zero[QT];
+#pragma unroll
+    for (int q = 0; q < QT; ++q) {
+        float amax = 0.0f;
+        for (int w = 0; w < W; ++w) amax = fmaxf(amax, s_red[q * 32 + w]);
+        zero[q] = !(amax > 0.0f);
+        s_hi[q] = zero[q] ? 0.0f : __fdiv_rn(amax, 127.0f);
+        s_lo[q] = zero[q] ? 0.0f : __fdiv_rn(s_hi[q], 254.0f);
     }
-    QueryHeader h;
-    h.qn = __double2float_rn(__dsqrt_rn(part));
-    h.qinv = (h.qn > 0.0f) ? __fdiv_rn(1.0f, h.qn) : 0.0f;
-    h.qn2d = part;
-    h.qhat2 = part;
-    h.s_hi = 0.0f;
-    h.s_lo = 0.0f;
-    if (amax > 0.0f) {
-        h.s_hi = __fdiv_rn(amax, 127.0f);
-        h.s_lo = __fdiv_rn(h.s_hi, 254.0f);
-    }
-    if constexpr (kF16) {
-        float* qf = reinterpret_cast<float*>(q_s);
-        for (int c = lane; c < chunks * 8; c += 32) qf[c] = (c < cols) ? __half2float(src[c]) : 0.0f;
-    } else {
-        const bool zero = !(amax > 0.0f);
-        const int plane = kQ4 ? chunks * 32 : chunks * 16;   // bytes of one plane
-        int8_t* hi = reinterpret_cast<int8_t*>(q_s);
-        int8_t* lo = hi + plane;
-        for (int c = lane; c < plane; c += 32) {
-            int e = c;   // c indexes the plane in storage order; e is the query element stored there
-            if constexpr (kQ4) {
-                const int blk = c >> 5, w = (c >> 2) & 7, b = c & 3;
-                e = blk * 32 + (w >> 1) * 8 + 2 * b + (w & 1);
+    // 2. planes / f32 values
+#pragma unroll
+    for (int q = 0; q < QT; ++q) {
+        const __half* src = queries + (size_t)(q0 + ((q < qt) ? q : 0)) * cols;
+        unsigned char* dst = q_s + (size_t)q * q_bytes;
+        if constexpr (kF16) {
+            float* qf = reinterpret_cast<float*>(dst);
+            for (int c = threadIdx.x; c < chunks * 8; c += blockDim.x) qf[c] = (c < cols) ? __half2float(src[c]) : 0.0f;
+        } else {
+            const int plane = kQ4 ? chunks * 32 : chunks * 16;   // bytes of one plane
+            int8_t* hi = reinterpret_cast<int8_t*>(dst);
+            int8_t* lo = hi + plane;
+            for (int c = threadIdx.x; c < plane; c += blockDim.x) {
+                int e = c;   // c indexes the plane in storage order; e is the query element stored there
+                if constexpr (kQ4) {
+                    const int blk = c >> 5, w = (c >> 2) & 7, b = c & 3;
+                    e = blk * 32 + (w >> 1) * 8 + 2 * b + (w & 1);
+                }
+                float hh = 0.0f, ll = 0.0f;
+                if (e < cols) quantise_query_element(__half2float(src[e]), s_hi[q], s_lo[q], zero[q], &hh, &ll);
+                hi[c] = (int8_t)hh;
+                lo[c] = (int8_t)ll;
             }
-            float hh = 0.0f, ll = 0.0f;
-            if (e < cols) quantise_query_element(__half2float(src[e]), h.s_hi, h.s_lo, zero, &hh, &ll);
-            hi[c] = (int8_t)hh;
-            lo[c] = (int8_t)ll;
         }
-        double p2 = 0.0;
-        for (int c = lane; c < cols; c += 32) {
-            float hh, ll;
-            quantise_query_element(__half2float(src[c]), h.s_hi, h.s_lo, zero, &hh, &ll);
-            const double v = zero ? 0.0 : __dadd_rn(__dmul_rn((double)hh, (double)h.s_hi), __dmul_rn((double)ll, (double)h.s_lo));
-            p2 = __dadd_rn(p2, __dmul_rn(v, v));
-        }
-        for (int off = 16; off > 0; off >>= 1) p2 = __dadd_rn(p2, __shfl_xor_sync(0xffffffffu, p2, off));
-        h.qhat2 = p2;
     }
-    if (lane == 0) *hdr = h;
+    __syncthreads();
+    // 3. the ordered sums, one warp per query
+    for (int q = warp; q < QT; q += W) {
+        const __half* src = queries + (size_t)(q0 + ((q < qt) ? q : 0)) * cols;
+        double part = 0.0, p2 = 0.0;
+        for (int c = lane; c < cols; c += 32) {
+            const double v = (double)__half2float(src[c]);
+            part = __dadd_rn(part, __dmul_rn(v, v));
+        }
+        if constexpr (!kF16) {
+            const int plane = kQ4 ? chunks * 32 : chunks * 16;
+            const int8_t* hi = reinterpret_cast<const int8_t*>(q_s + (size_t)q * q_bytes);
+            const int8_t* lo = hi + plane;
+            const double dh = (double)s_hi[q], dl = (double)s_lo[q];
+            for (int c = lane; c < cols; c += 32) {
+                const int idx = plane_index_of_element<LAYOUT>(c);
+                const double v = __dadd_rn(__dmul_rn((double)hi[idx], dh), __dmul_rn((double)lo[idx], dl));
+                p2 = __dadd_rn(p2, __dmul_rn(v, v));
+            }
+        }
+        for (int off = 16; off > 0; off >>= 1) {
+            part = __dadd_rn(part, __shfl_xor_sync(0xffffffffu, part, off));
+            p2 = __dadd_rn(p2, __shfl_xor_sync(0xffffffffu, p2, off));
+        }
+        if (lane == 0) {
+            QueryHeader h;
+            h.qn = __double2float_rn(__dsqrt_rn(part));
+            h.qinv = (h.qn > 0.0f) ? __fdiv_rn(1.0f, h.qn) : 0.0f;
+            h.qn2d = part;
+            h.qhat2 = kF16 ? part : p2;
+            h.s_hi = s_hi[q];
+            h.s_lo = s_lo[q];
+            hdr_s[q] = h;
+        }
+    }
 }
 
 // LPR, CPL: lanes per row and 16-byte chunks per lane and row as compile-time constants (a row is exactly LPR * CPL
@@ -221,10 +265,7 @@ __global__ void __launch_bounds__(scan_warps(QT) * 32, 1) stream_scan_kernel(con
 
     // start the stream before anything else, then prepare the queries while the first tiles are on their way
     for (int p = 0; p < S - 1; ++p) issue(tile_of(p), p);
-    for (int q = warp; q < QT; q += W) {
-        const int qi = a.q0 + ((q < a.qt) ? q : 0);   // unused slots repeat query 0 of the launch
-        prepare_query_warp<LAYOUT>(a.queries + (size_t)qi * cv.cols, cv.cols, C, lane, hdr_s + q, q_s + (size_t)q * g.q_bytes);
-    }
+    prepare_queries_block<LAYOUT, QT>(a.queries, a.q0, a.qt, cv.cols, C, g.q_bytes, hdr_s, q_s, reinterpret_cast<float*>(s_stage));
     __syncthreads();
     QueryHeader hdr[QT];
     float q4_sh[QT], q4_sl[QT];
@@ -283,6 +324,17 @@ __global__ void __launch_bounds__(scan_warps(QT) * 32, 1) stream_scan_kernel(con
 
     int stage = 0;                 // ring slot of the tile consumed in this iteration
     int next_stage = S - 1;        // ring slot the copies issued in this iteration go to
+    // One query per launch: the keys of the first kHeld observed tiles are held back in registers (one per lane and
+    // tile), so the usual case -- a first threshold after two or three tiles -- needs no second read at all.
+    constexpr bool kHold = QT == 1;
+    constexpr int kHeld = 4;
+    uint64_t held_key[kHeld];
+    bool held_ok[kHeld];
+#pragma unroll
+    for (int e = 0; e < kHeld; ++e) {
+        held_key[e] = 0;
+        held_ok[e] = false;
+    }
     bool observing = topk;
     int total = topk ? 0x3fffffff : max(my_tiles, F);
     uint32_t fresh = 0;            // fresh (not re-read) tiles consumed so far: drives the refresh duty
@@ -298,6 +350,14 @@ __global__ void __launch_bounds__(scan_warps(QT) * 32, 1) stream_scan_kernel(con
                 if (have || i >= my_tiles) {
                     observing = false;
                     T = min(i, my_tiles);
+                    if (kHold && T <= kHeld) {
+                        // every observed tile's keys are still in registers: they go through the filter now and
+                        // nothing has to be read again
+#pragma unroll
+                        for (int e = 0; e < kHeld; ++e)
+                            if (e < T) append(0, held_ok[e] && (uint32_t)(held_key[e] >> 32) >= thr[0], held_key[e]);
+                        T = 0;
+                    }
                     total = max(2 * T + F, my_tiles + T);
                 }
             }
@@ -518,7 +578,17 @@ __global__ void __launch_bounds__(scan_warps(QT) * 32, 1) stream_scan_kernel(con
                 const float gd = score * sign + 0.0f;
                 const uint32_t o = ord_from_float(gd);
                 if (mine && !replay) bmax[q][slot] = max(bmax[q][slot], o);
-                if (!observe) append(q, mine && o >= thr[q], make_key(gd, (int32_t)(cv.row_base + my_row)));
+                const uint64_t key = make_key(gd, (int32_t)(cv.row_base + my_row));
+                if (!observe) {
+                    append(q, mine && o >= thr[q], key);
+                } else if (kHold) {
+#pragma unroll
+                    for (int e = 0; e < kHeld; ++e)
+                        if (i == e) {
+                            held_key[e] = key;
+                            held_ok[e] = mine;
+                        }
+                }
             }
         }
         if (!topk || replay) continue;
