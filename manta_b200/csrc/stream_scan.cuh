@@ -25,6 +25,8 @@
 // into every rank's exchange inbox) and leaves the workspace zeroed for the next pass: a fused step is one launch.
 #pragma once
 
+#include <type_traits>
+
 #include "select.cuh"
 
 namespace mb200 {
@@ -82,7 +84,8 @@ __device__ __forceinline__ int plane_index_of_element(int e) {
 
 template <int LAYOUT, int QT>
 __device__ __forceinline__ void prepare_queries_block(const __half* __restrict__ queries, int q0, int qt, int cols, int chunks, int q_bytes,
-                                                      QueryHeader* hdr_s, unsigned char* q_s, float* s_red /* [QT][32] scratch */) {
+                                                      QueryHeader* hdr_s, unsigned char* q_s, float* s_red /* [QT][32] scratch */,
+                                                      float* lo_norm_s /* [QT] out */) {
     constexpr bool kF16 = LAYOUT == MANTA_B200_LAYOUT_F16;
     constexpr bool kQ4 = LAYOUT == MANTA_B200_LAYOUT_Q4_B32_F16;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, W = blockDim.x >> 5;
@@ -135,7 +138,7 @@ __device__ __forceinline__ void prepare_queries_block(const __half* __restrict__
     // 3. the ordered sums, one warp per query
     for (int q = warp; q < QT; q += W) {
         const __half* src = queries + (size_t)(q0 + ((q < qt) ? q : 0)) * cols;
-        double part = 0.0, p2 = 0.0;
+        double part = 0.0, p2 = 0.0, lo2 = 0.0;
         for (int c = lane; c < cols; c += 32) {
             const double v = (double)__half2float(src[c]);
             part = __dadd_rn(part, __dmul_rn(v, v));
@@ -147,15 +150,21 @@ __device__ __forceinline__ void prepare_queries_block(const __half* __restrict__
             const double dh = (double)s_hi[q], dl = (double)s_lo[q];
             for (int c = lane; c < cols; c += 32) {
                 const int idx = plane_index_of_element<LAYOUT>(c);
-                const double v = __dadd_rn(__dmul_rn((double)hi[idx], dh), __dmul_rn((double)lo[idx], dl));
+                const double vl = __dmul_rn((double)lo[idx], dl);
+                const double v = __dadd_rn(__dmul_rn((double)hi[idx], dh), vl);
                 p2 = __dadd_rn(p2, __dmul_rn(v, v));
+                lo2 += vl * vl;
             }
         }
         for (int off = 16; off > 0; off >>= 1) {
             part = __dadd_rn(part, __shfl_xor_sync(0xffffffffu, part, off));
             p2 = __dadd_rn(p2, __shfl_xor_sync(0xffffffffu, p2, off));
+            lo2 += __shfl_xor_sync(0xffffffffu, lo2, off);
         }
         if (lane == 0) {
+            // norm of the low plane's part of the query, rounded up: |q_lo . d| <= lo_norm * ||d|| bounds what the low
+            // plane can add to a dot product (used by the high-plane-first filter of the q4 scan)
+            lo_norm_s[q] = (float)(sqrt(lo2) * 1.000001) + 1e-30f;
             QueryHeader h;
             h.qn = __double2float_rn(__dsqrt_rn(part));
             h.qinv = (h.qn > 0.0f) ? __fdiv_rn(1.0f, h.qn) : 0.0f;
@@ -265,13 +274,15 @@ __global__ void __launch_bounds__(scan_warps(QT) * 32, 1) stream_scan_kernel(con
 
     // start the stream before anything else, then prepare the queries while the first tiles are on their way
     for (int p = 0; p < S - 1; ++p) issue(tile_of(p), p);
-    prepare_queries_block<LAYOUT, QT>(a.queries, a.q0, a.qt, cv.cols, C, g.q_bytes, hdr_s, q_s, reinterpret_cast<float*>(s_stage));
+    float* lo_norm_s = reinterpret_cast<float*>(hdr_s + QT);   // behind the headers, inside their 256 bytes
+    prepare_queries_block<LAYOUT, QT>(a.queries, a.q0, a.qt, cv.cols, C, g.q_bytes, hdr_s, q_s, reinterpret_cast<float*>(s_stage), lo_norm_s);
     __syncthreads();
     QueryHeader hdr[QT];
-    float q4_sh[QT], q4_sl[QT];
+    float q4_sh[QT], q4_sl[QT], lo_norm[QT];
 #pragma unroll
     for (int q = 0; q < QT; ++q) {
         hdr[q] = hdr_s[q];
+        lo_norm[q] = lo_norm_s[q];
         q4_sh[q] = hdr[q].s_hi * 0.0625f;  // the nibble unpack yields 16*code
         q4_sl[q] = hdr[q].s_lo * 0.0625f;
     }
@@ -387,6 +398,7 @@ __global__ void __launch_bounds__(scan_warps(QT) * 32, 1) stream_scan_kernel(con
         const bool rv = leader && my_row < a.row_end;
 
         // ---- accumulate this lane's chunks of its row
+        bool skip_tile = false;   // q4 high-plane filter: no row of the tile can pass, nothing to finish
         int ih[QT], il[QT];
         float fa[QT], fb[QT];
 #pragma unroll
@@ -442,41 +454,80 @@ __global__ void __launch_bounds__(scan_warps(QT) * 32, 1) stream_scan_kernel(con
             if constexpr (kRowScales) sc8 = *reinterpret_cast<const uint4*>(srow);
             const uint4* qbase = reinterpret_cast<const uint4*>(q_s) + 2 * part;
             const int q_stride = g.q_bytes / 16;
-            for_each_chunk([&](int c) {
-                const uint4 d = rowp[c];
-                const uint32_t w[4] = {d.x, d.y, d.z, d.w};
-                int ev[4], od[4];
-#pragma unroll
-                for (int t = 0; t < 4; ++t) {
-                    ev[t] = (int)((w[t] << 4) & 0xF0F0F0F0u);
-                    od[t] = (int)(w[t] & 0xF0F0F0F0u);
-                }
-                float bs;
-                if constexpr (kRowScales) {
-                    const uint32_t pair = (c < 2) ? sc8.x : (c < 4) ? sc8.y : (c < 6) ? sc8.z : sc8.w;
-                    bs = __half2float(__ushort_as_half((unsigned short)((c & 1) ? (pair >> 16) : (pair & 0xffffu))));
-                } else {
-                    bs = __half2float(srow[c]);
-                }
-#pragma unroll
-                for (int q = 0; q < QT; ++q) {
-                    const uint4* qh = qbase + q * q_stride + 2 * c;
-                    const uint4* ql = qh + 2 * C;
-                    const uint4 h0 = qh[0], h1 = qh[1], l0 = ql[0], l1 = ql[1];
-                    const uint32_t ph[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
-                    const uint32_t pl[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
-                    int h = 0, l = 0;
+            // one pass over the lane's chunks for the high plane (DO_H), the low plane (DO_L) or both
+            auto q4_pass = [&](auto do_h, auto do_l) {
+                for_each_chunk([&](int c) {
+                    const uint4 d = rowp[c];
+                    const uint32_t w[4] = {d.x, d.y, d.z, d.w};
+                    int ev[4], od[4];
 #pragma unroll
                     for (int t = 0; t < 4; ++t) {
-                        h = __dp4a(ev[t], (int)ph[2 * t], h);
-                        l = __dp4a(ev[t], (int)pl[2 * t], l);
-                        h = __dp4a(od[t], (int)ph[2 * t + 1], h);
-                        l = __dp4a(od[t], (int)pl[2 * t + 1], l);
+                        ev[t] = (int)((w[t] << 4) & 0xF0F0F0F0u);
+                        od[t] = (int)(w[t] & 0xF0F0F0F0u);
                     }
-                    fa[q] = __fmaf_rn((float)h, bs, fa[q]);
-                    fb[q] = __fmaf_rn((float)l, bs, fb[q]);
+                    float bs;
+                    if constexpr (kRowScales) {
+                        const uint32_t pair = (c < 2) ? sc8.x : (c < 4) ? sc8.y : (c < 6) ? sc8.z : sc8.w;
+                        bs = __half2float(__ushort_as_half((unsigned short)((c & 1) ? (pair >> 16) : (pair & 0xffffu))));
+                    } else {
+                        bs = __half2float(srow[c]);
+                    }
+#pragma unroll
+                    for (int q = 0; q < QT; ++q) {
+                        const uint4* qh = qbase + q * q_stride + 2 * c;
+                        const uint4* ql = qh + 2 * C;
+                        if constexpr (decltype(do_h)::value) {
+                            const uint4 h0 = qh[0], h1 = qh[1];
+                            const uint32_t ph[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+                            int h = 0;
+#pragma unroll
+                            for (int t = 0; t < 4; ++t) {
+                                h = __dp4a(ev[t], (int)ph[2 * t], h);
+                                h = __dp4a(od[t], (int)ph[2 * t + 1], h);
+                            }
+                            fa[q] = __fmaf_rn((float)h, bs, fa[q]);
+                        }
+                        if constexpr (decltype(do_l)::value) {
+                            const uint4 l0 = ql[0], l1 = ql[1];
+                            const uint32_t pl[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
+                            int l = 0;
+#pragma unroll
+                            for (int t = 0; t < 4; ++t) {
+                                l = __dp4a(ev[t], (int)pl[2 * t], l);
+                                l = __dp4a(od[t], (int)pl[2 * t + 1], l);
+                            }
+                            fb[q] = __fmaf_rn((float)l, bs, fb[q]);
+                        }
+                    }
+                });
+            };
+            using yes = std::integral_constant<bool, true>;
+            using no = std::integral_constant<bool, false>;
+            if (l2_pref && !observe) {
+                // High plane first.  The low plane can change a dot product by at most ||q_lo|| * ||row||, so a tile in
+                // which no row passes the distance filter even with that much added is finished after half the work;
+                // otherwise the low plane is accumulated as well and the exact filter and evaluation follow.
+                q4_pass(yes{}, no{});
+                bool maybe = false;
+                const float dn2e = __uint_as_float((cv.stats != nullptr) ? reinterpret_cast<const uint32_t*>(st + g.stat_off)[r_in] : 0u);
+                const float dnorm = sqrtf(dn2e) * 1.000001f;
+#pragma unroll
+                for (int q = 0; q < QT; ++q) {
+                    float th = fa[q];
+#pragma unroll
+                    for (int off = lpr >> 1; off > 0; off >>= 1) th += __shfl_xor_sync(0xffffffffu, th, off);
+                    const float dot_hi = __fmul_rn(th, q4_sh[q]);
+                    const float slack = __fmaf_rn(lo_norm[q], dnorm, 1e-6f * fabsf(dot_hi));
+                    maybe = maybe || (rv && dot_hi + slack >= __fmaf_rn(dn2e, 0.4999995f, l2_ch[q]));
                 }
-            });
+                if (!__any_sync(0xffffffffu, maybe)) {
+                    skip_tile = true;
+                } else {
+                    q4_pass(no{}, yes{});
+                }
+            } else {
+                q4_pass(yes{}, yes{});
+            }
         } else {
             const bool l2 = a.metric == MANTA_B200_METRIC_L2_DISTANCE;
             const float4* qbase = reinterpret_cast<const float4*>(q_s) + 2 * part;
@@ -514,7 +565,7 @@ __global__ void __launch_bounds__(scan_warps(QT) * 32, 1) stream_scan_kernel(con
         }
         // ---- finish the row: log2(lpr) exchange steps, then the row's leader lane holds the sums
 #pragma unroll
-        for (int q = 0; q < QT; ++q) {
+        for (int q = 0; q < QT && !skip_tile; ++q) {
 #pragma unroll
             for (int off = lpr >> 1; off > 0; off >>= 1) {
                 if constexpr (kQ8) {
@@ -537,7 +588,7 @@ __global__ void __launch_bounds__(scan_warps(QT) * 32, 1) stream_scan_kernel(con
         if (a.metric == MANTA_B200_METRIC_COSINE) rinv = kQ8 ? q8_row_inv_norm(nn) : float_row_inv_norm(dn2);
         const int slot = (int)(fresh & (kSlots - 1));
 #pragma unroll
-        for (int q = 0; q < QT; ++q) {
+        for (int q = 0; q < QT && !skip_tile; ++q) {
             float score;
             if constexpr (kQ8) {
                 if (a.mode == kModeAccum) {

@@ -15,7 +15,7 @@ import numpy as np
 import pytest
 
 import oracle
-from helpers import topk_parity_report
+from helpers import EMBED_FLOOR, topk_parity_report
 
 pytestmark = pytest.mark.gpu
 
@@ -90,4 +90,4 @@ def test_embed_then_score_at_stated_size(rt):
     pooled = oracle.embed_pooled(table.float().cpu().numpy(), proj.float().cpu().numpy(), h_tok, h_mask, 0)
     q = oracle.half_to_float(oracle.float_to_half(pooled))  # the scan reads the pooled rows rounded to f16
     deq = _dequantised("q8", rows, cols, True)
-    _check(topk_parity_report("dot", q, deq, ids, scores, k), "embed + q8 dot 500k x 384, Q=128, k=50")
+    _check(topk_parity_report("dot", q, deq, ids, scores, k, floor=EMBED_FLOOR), "embed + q8 dot 500k x 384, Q=128, k=50")
