@@ -46,6 +46,7 @@ class Workload:
     normalise: bool = True
     note: str = ""
     embed: tuple = ()  # (vocab, dim, seq): queries come from the embedding front end instead of a query set
+    embed_order: int = 0  # 0: normalize(mean_pool(x @ P)); 1: mean_pool(normalize(x @ P)), every token row projected
 
     def row_bytes(self) -> float:
         """Algorithmic bytes per candidate row and pass: stored codes + the per-row values the metric reads."""
@@ -59,7 +60,7 @@ class Workload:
     def describe(self) -> str:
         order = "smallest" if self.smallest else "largest"
         front = (f"embed(tokens i32[{self.nq},{self.embed[2]}], table f16[{self.embed[0]},{self.embed[1]}], projection "
-                 f"f16[{self.embed[1]},{self.cols}], masked mean_pool, normalize) -> ") if self.embed else ""
+                 f"f16[{self.embed[1]},{self.cols}], {'normalize, masked mean_pool' if self.embed_order else 'masked mean_pool, normalize'}) -> ") if self.embed else ""
         return (f"{front}{self.layout} {self.metric} {self.rows / 1e6:g}M x {self.cols}, {self.nq} "
                 f"quer{'y' if self.nq == 1 else 'ies'} per pass, k={self.k} {order}")
 
@@ -79,6 +80,8 @@ WORKLOADS = {
                       note="one GPU's share (1/8) of the 100M x 256 q4 set, query batch 32"),
     "c5": Workload("c5", "q8", "dot", 5_000_000, 384, 128, 50, embed=(32000, 384, 128),
                    note="end to end: token batch -> embedding front end -> q8 dot score + top-k, queries never leave the device"),
+    "c5n": Workload("c5n", "q8", "dot", 5_000_000, 384, 128, 50, embed=(32000, 384, 128), embed_order=1,
+                    note="as c5 with the normalize-first step order: every token row is projected (tensor cores), normalised, then pooled"),
 }
 METRIC_NAME = "q8 cosine score+topk queries/s at 10M x 768 candidates (k=10, 1 query per pass)"
 
@@ -197,7 +200,7 @@ def cpu_reference_pass(wl: Workload, sample_rows: int, threads: int, steps: int,
         if wl.embed:
             table, proj, tokens, mask = queries
             j = i % tokens.shape[0]
-            q = oracle.half_to_float(oracle.float_to_half(oracle.embed_pooled(table, proj, tokens[j], mask[j], 0)))
+            q = oracle.half_to_float(oracle.float_to_half(oracle.embed_pooled(table, proj, tokens[j], mask[j], wl.embed_order)))
         else:
             q = queries[i % nsets]
         tq = time.perf_counter()
@@ -346,7 +349,7 @@ def run_ours(args, wl: Workload):
     def step_device(i):
         ln = lanes[i % n_lanes]
         if wl.embed:
-            ln.rt.embed_device(emb, d_tokens[i % nsets], d_mask[i % nsets], nq, wl.embed[2], ln.d_q, sync=False)
+            ln.rt.embed_device(emb, d_tokens[i % nsets], d_mask[i % nsets], nq, wl.embed[2], ln.d_q, normalize_then_pool=bool(wl.embed_order), sync=False)
             dq = ln.d_q
         else:
             dq = d_queries[i % nsets]
@@ -437,7 +440,7 @@ def run_ours(args, wl: Workload):
         for i in range(min(args.steps, 20)):
             ln = lanes[0]
             if wl.embed:
-                ln.rt.embed_device(emb, d_tokens[i % nsets], d_mask[i % nsets], nq, wl.embed[2], ln.d_q, sync=False)
+                ln.rt.embed_device(emb, d_tokens[i % nsets], d_mask[i % nsets], nq, wl.embed[2], ln.d_q, normalize_then_pool=bool(wl.embed_order), sync=False)
             dq1 = ln.d_q if wl.embed else d_queries[i % nsets]
             if ln.px is not None:
                 ln.px.score_topk_merge(cands, wl.metric, dq1, nq, k, ln.m_ids, ln.m_scores, smallest=wl.smallest, sync=False)
@@ -467,7 +470,7 @@ def run_ours(args, wl: Workload):
         step_no = total_steps + 7
         dq_chk = None
         if wl.embed:
-            ln.rt.embed_device(emb, d_tokens[step_no % nsets], d_mask[step_no % nsets], nq, wl.embed[2], ln.d_q, sync=False)
+            ln.rt.embed_device(emb, d_tokens[step_no % nsets], d_mask[step_no % nsets], nq, wl.embed[2], ln.d_q, normalize_then_pool=bool(wl.embed_order), sync=False)
             dq_chk = ln.d_q
         else:
             dq_chk = d_queries[step_no % nsets]
@@ -520,7 +523,7 @@ def run_ours(args, wl: Workload):
             else:
                 hb["s_q"].copy_(hb["queries"][i % nsets], non_blocking=True)
         if wl.embed:
-            ln.rt.embed_device(emb, hb["s_tokens"], hb["s_mask"], nq, wl.embed[2], hb["s_q"], sync=False)
+            ln.rt.embed_device(emb, hb["s_tokens"], hb["s_mask"], nq, wl.embed[2], hb["s_q"], normalize_then_pool=bool(wl.embed_order), sync=False)
         if ln.px is not None:
             ln.px.score_topk_merge(cands, wl.metric, hb["s_q"], nq, k, ln.m_ids, ln.m_scores, smallest=wl.smallest, sync=False)
         else:
@@ -539,7 +542,8 @@ def run_ours(args, wl: Workload):
         if world == 1:
             for i in range(first, first + count):
                 if wl.embed:
-                    rt.embed_score_topk(emb, cands, h_tokens[i % nsets], h_mask[i % nsets], wl.metric, k, smallest=wl.smallest)
+                    rt.embed_score_topk(emb, cands, h_tokens[i % nsets], h_mask[i % nsets], wl.metric, k, smallest=wl.smallest,
+                                        normalize_then_pool=bool(wl.embed_order))
                 else:
                     rt.score_topk(cands, wl.metric, h_queries[i % nsets], k, smallest=wl.smallest)
             return
@@ -580,7 +584,8 @@ def run_ours(args, wl: Workload):
                       rows=sample_rows, cols=wl.cols)
         kk = min(k, sample_rows)
         if wl.embed:  # the CPU pass cycles through two token batches; its last pass used batch 3 % 2
-            ids, sc = rt.embed_score_topk(emb, sub, h_tokens[1], h_mask[1], wl.metric, kk, smallest=wl.smallest)
+            ids, sc = rt.embed_score_topk(emb, sub, h_tokens[1], h_mask[1], wl.metric, kk, smallest=wl.smallest,
+                                          normalize_then_pool=bool(wl.embed_order))
         else:
             ids, sc = rt.score_topk(sub, wl.metric, h_queries[(1 + 3 - 1) % nsets], kk, smallest=wl.smallest)
         # the comparison rule of tests/helpers.py: ids equal to topKTensor's except across score gaps below twice the
@@ -592,7 +597,7 @@ def run_ours(args, wl: Workload):
         docs_f32, q_sets = _cpu_sample(wl, sample_rows, nsets)
         if wl.embed:
             table, proj, tokens, mask = q_sets
-            q_chk = oracle.half_to_float(oracle.float_to_half(oracle.embed_pooled(table, proj, tokens[1], mask[1], 0)))
+            q_chk = oracle.half_to_float(oracle.float_to_half(oracle.embed_pooled(table, proj, tokens[1], mask[1], wl.embed_order)))
         else:
             q_chk = q_sets[(1 + 3 - 1) % nsets]
         floor = EMBED_FLOOR if wl.embed else FLOOR  # the embedded queries themselves differ from the CPU's in a few f16 roundings

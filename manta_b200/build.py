@@ -17,7 +17,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(CSRC, "_obj")
 LIB = os.path.join(HERE, "libmanta_b200.so")
-SOURCES = ["api.cu", "prep.cu", "select.cu", "stream_scan_f16.cu", "stream_scan_q8.cu", "stream_scan_q4.cu", "mma.cu", "noalloc.cu", "embed.cu", "batched.cu", "storage.cu", "exchange.cu", "host/executor.cpp", "host/eval.cpp"]
+SOURCES = ["api.cu", "prep.cu", "select.cu", "stream_scan_f16.cu", "stream_scan_q8.cu", "stream_scan_q4.cu", "mma.cu", "noalloc.cu", "embed.cu", "embed_mma.cu", "batched.cu", "storage.cu", "exchange.cu", "host/executor.cpp", "host/eval.cpp"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall", "--expt-relaxed-constexpr",

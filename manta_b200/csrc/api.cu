@@ -82,7 +82,7 @@ struct MantaB200Runtime {
     std::mutex mu;
     MantaB200Stats stats{};
     // grow-only device buffers
-    DevBuf queries, headers, qf32, plane_hi, plane_lo, pool, count, thr, bucket, flags, out_ids, out_scores, misc, embed_flag, batch_in;
+    DevBuf queries, headers, qf32, plane_hi, plane_lo, pool, count, thr, bucket, flags, out_ids, out_scores, misc, embed_flag, batch_in, tok_norms;
     // pinned host staging
     void* h_stage = nullptr;
     size_t h_stage_bytes = 0;
@@ -118,6 +118,7 @@ struct MantaB200Embedder {
     int vocab = 0, dim = 0, out_dim = 0;
     void* d_table = nullptr;
     void* d_proj = nullptr;
+    void* d_proj_t = nullptr;   // [out_dim][dim], only for shapes the tensor-core projection takes
 };
 
 struct MantaB200Candidates {
@@ -224,7 +225,7 @@ int manta_b200_runtime_destroy(MantaB200Runtime* rt, char** err) {
     cudaSetDevice(rt->device);
     cudaError_t e = cudaStreamSynchronize(rt->stream);
     DevBuf* bufs[] = {&rt->queries, &rt->headers, &rt->qf32, &rt->plane_hi, &rt->plane_lo, &rt->pool, &rt->count,
-                      &rt->thr, &rt->bucket, &rt->flags, &rt->out_ids, &rt->out_scores, &rt->misc, &rt->embed_flag, &rt->batch_in};
+                      &rt->thr, &rt->bucket, &rt->flags, &rt->out_ids, &rt->out_scores, &rt->misc, &rt->embed_flag, &rt->batch_in, &rt->tok_norms};
     for (DevBuf* b : bufs) free_buf(*b);
     mma_state_destroy(rt->mma);
     for (int i = 0; i < rt->prof_created; ++i) cudaEventDestroy(rt->prof_ev[i]);
@@ -264,6 +265,7 @@ int manta_b200_runtime_synchronize(MantaB200Runtime* rt, char** err) {
     }
     if (rt->async_embed_pending) {
         rt->async_embed_pending = false;
+        if (rt->h_flags[10] == 2u && !msg) return fail(err, "embed: a bounded wait of the tensor-core projection ran out");
         if (rt->h_flags[10] && !msg) return fail(err, "gather index %d out of range", (int32_t)rt->h_flags[11]);
     }
     if (rt->async_static_pending) {
@@ -1064,10 +1066,18 @@ int manta_b200_embedder_bind(MantaB200Runtime* rt, int vocab, int dim, int out_d
     if (ce == cudaSuccess) ce = cudaMalloc(&e->d_proj, pb);
     if (ce == cudaSuccess) ce = cudaMemcpyAsync(e->d_table, table, tb, kind, rt->stream);
     if (ce == cudaSuccess) ce = cudaMemcpyAsync(e->d_proj, projection, pb, kind, rt->stream);
+    if (ce == cudaSuccess && embed_mma_supported(dim, out_dim)) {
+        ce = cudaMalloc(&e->d_proj_t, pb);
+        if (ce == cudaSuccess) {
+            ce = launch_transpose_f16(rt->stream, e->d_proj, dim, out_dim, e->d_proj_t);
+            rt->stats.kernel_launches++;
+        }
+    }
     if (ce == cudaSuccess) ce = cudaStreamSynchronize(rt->stream);
     if (ce != cudaSuccess) {
         if (e->d_table) cudaFree(e->d_table);
         if (e->d_proj) cudaFree(e->d_proj);
+        if (e->d_proj_t) cudaFree(e->d_proj_t);
         delete e;
         return fail_cuda(err, "embedder_bind", ce);
     }
@@ -1086,6 +1096,7 @@ int manta_b200_embedder_unbind(MantaB200Runtime* rt, MantaB200Embedder* emb, cha
     CU_TRY(cudaStreamSynchronize(rt->stream));
     cudaFree(emb->d_table);
     cudaFree(emb->d_proj);
+    if (emb->d_proj_t) cudaFree(emb->d_proj_t);
     delete emb;
     return 0;
 }
@@ -1098,8 +1109,18 @@ static int embed_device_locked(MantaB200Runtime* rt, const MantaB200Embedder* em
     uint32_t* d_flag = (uint32_t*)rt->embed_flag.p;
     int32_t* d_bad = (int32_t*)rt->embed_flag.p + 1;
     CU_TRY(cudaMemsetAsync(d_flag, 0, 8, rt->stream));
+    // mean_pool(normalize(x @ P)) on shapes the tensor cores take: the per-token product only yields the row norms
+    const float* d_norms = nullptr;
+    if (pool_order != 0 && emb->d_proj_t != nullptr) {
+        if (ensure(rt, rt->tok_norms, (size_t)batch * seq * 4, err)) return 1;
+        cudaError_t en = launch_embed_token_norms(rt->stream, emb->d_table, emb->vocab, emb->dim, emb->d_proj_t, emb->out_dim, d_tok,
+                                                  (int64_t)batch * seq, (float*)rt->tok_norms.p, d_flag);
+        rt->stats.kernel_launches++;
+        if (en != cudaSuccess) return fail_cuda(err, "launch embed projection kernel", en);
+        d_norms = (const float*)rt->tok_norms.p;
+    }
     cudaError_t e = launch_embed_pooled(rt->stream, emb->d_table, emb->vocab, emb->dim, emb->d_proj, emb->out_dim, d_tok, d_mask, batch,
-                                        seq, pool_order, d_out_f32, d_out_f16, d_bad, d_flag);
+                                        seq, pool_order, d_norms, d_out_f32, d_out_f16, d_bad, d_flag);
     rt->stats.kernel_launches++;
     if (e != cudaSuccess) return fail_cuda(err, "launch embed kernel", e);
     CU_TRY(cudaMemcpyAsync(&rt->h_flags[10], d_flag, 8, cudaMemcpyDeviceToHost, rt->stream));
@@ -1109,6 +1130,7 @@ static int embed_device_locked(MantaB200Runtime* rt, const MantaB200Embedder* em
     }
     CU_TRY(cudaStreamSynchronize(rt->stream));
     rt->async_embed_pending = false;
+    if (rt->h_flags[10] == 2u) return fail(err, "embed: a bounded wait of the tensor-core projection ran out");
     if (rt->h_flags[10]) return fail(err, "gather index %d out of range", (int32_t)rt->h_flags[11]);  // tensor_ops.go:803
     return 0;
 }

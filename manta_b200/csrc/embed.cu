@@ -9,7 +9,10 @@
 //    multiplied with the projection per batch element (seq times less arithmetic than the step-by-step order; the
 //    f32 sums associate differently from the reference's, a relative difference of a few 1e-7);
 //  - mean_pool(normalize(x @ P)): every kept token row is projected (f32 products and sums rounded separately, k
-//    ascending, as the reference's loop does), normalised, and added to the pool in token order.
+//    ascending, as the reference's loop does), normalised, and added to the pool in token order.  Shapes the tensor
+//    cores take (embed_mma.cu) go another way: that file computes the norm of every token's projected row, and the
+//    first kernel, given those norms, pools the embedding rows weighted by 1/norm and projects one row per batch
+//    element -- the same linearity, a relative difference of about 1e-6 from the step-by-step order.
 #include "kernels.h"
 
 namespace mb200 {
@@ -21,7 +24,8 @@ constexpr int kEmbColsPerThread = 4;
 // Warp 0 compacts the token ids of the kept positions, in order, into valid[] and checks every token's range (the
 // reference's gather rejects an out-of-range token whether or not the mask keeps it).
 __device__ __forceinline__ void count_valid_tokens(const int32_t* __restrict__ tokens, const int32_t* __restrict__ mask, int seq,
-                                                   int vocab, int32_t* valid, int* s_count, int32_t* bad_token, uint32_t* bad_flag) {
+                                                   int vocab, int32_t* valid, int* s_count, int32_t* bad_token, uint32_t* bad_flag,
+                                                   int32_t* vpos = nullptr) {
     const int lane = threadIdx.x & 31;
     int n = 0;
     for (int t0 = 0; t0 < seq; t0 += 32) {
@@ -37,7 +41,10 @@ __device__ __forceinline__ void count_valid_tokens(const int32_t* __restrict__ t
             }
         }
         const uint32_t m = __ballot_sync(0xffffffffu, keep);
-        if (keep) valid[n + __popc(m & ((1u << lane) - 1u))] = tok;
+        if (keep) {
+            valid[n + __popc(m & ((1u << lane) - 1u))] = tok;
+            if (vpos) vpos[n + __popc(m & ((1u << lane) - 1u))] = t;
+        }
         n += __popc(m);
     }
     if (lane == 0) *s_count = n;
@@ -56,21 +63,36 @@ __device__ __forceinline__ double block_sum(double ss, double* s_part) {
 
 // normalize(mean_pool(gather(table, tokens) @ proj, mask)).  One CTA per batch element; thread t owns hidden
 // elements t, t+256, ... of the token-row sum and output columns t, t+256, ...
+// WEIGHTED: token_norms[b][t] is the norm of token t's projected row; the rows are pooled with the weights 1/norm (1 for
+// a zero norm, whose row projects to zero anyway) and the result is mean_pool(normalize(...)): no final normalisation.
+template <bool WEIGHTED>
 __global__ void __launch_bounds__(kEmbThreads) embed_pool_first_kernel(const __half* __restrict__ table, int vocab, int dim,
                                                                        const __half* __restrict__ proj, int out_dim,
                                                                        const int32_t* __restrict__ tokens,
                                                                        const int32_t* __restrict__ mask, int seq,
+                                                                       const float* __restrict__ token_norms,
                                                                        float* __restrict__ out_f32, __half* __restrict__ out_f16,
                                                                        int32_t* __restrict__ bad_token, uint32_t* __restrict__ bad_flag) {
     extern __shared__ __align__(16) unsigned char emb_smem[];
     float* hsum = reinterpret_cast<float*>(emb_smem);              // [dim]
     int32_t* valid = reinterpret_cast<int32_t*>(hsum + dim);       // [seq]
+    int32_t* vpos = valid + seq;                                   // [seq], WEIGHTED only: position of each kept token
+    float* wts = reinterpret_cast<float*>(vpos + seq);             // [seq], WEIGHTED only
     __shared__ int s_count;
     __shared__ double s_part[kEmbThreads / 32];
     const int b = blockIdx.x, tid = threadIdx.x;
-    if (tid < 32) count_valid_tokens(tokens + (size_t)b * seq, mask + (size_t)b * seq, seq, vocab, valid, &s_count, bad_token, bad_flag);
+    if (tid < 32)
+        count_valid_tokens(tokens + (size_t)b * seq, mask + (size_t)b * seq, seq, vocab, valid, &s_count, bad_token, bad_flag,
+                           WEIGHTED ? vpos : nullptr);
     __syncthreads();
     const int count = s_count;
+    if constexpr (WEIGHTED) {
+        for (int n = tid; n < count; n += kEmbThreads) {
+            const float nm = token_norms[(size_t)b * seq + vpos[n]];
+            wts[n] = (nm != 0.0f) ? __fdiv_rn(1.0f, nm) : 1.0f;
+        }
+        __syncthreads();
+    }
 
     // sum of the kept token rows, token order, eight independent loads in flight per thread
     for (int k = tid; k < dim; k += kEmbThreads) {
@@ -81,9 +103,12 @@ __global__ void __launch_bounds__(kEmbThreads) embed_pool_first_kernel(const __h
 #pragma unroll
             for (int u = 0; u < 8; ++u) v[u] = __half2float(table[(size_t)valid[t + u] * dim + k]);
 #pragma unroll
-            for (int u = 0; u < 8; ++u) acc = __fadd_rn(acc, v[u]);
+            for (int u = 0; u < 8; ++u) acc = WEIGHTED ? fmaf(wts[t + u], v[u], acc) : __fadd_rn(acc, v[u]);
         }
-        for (; t < count; ++t) acc = __fadd_rn(acc, __half2float(table[(size_t)valid[t] * dim + k]));
+        for (; t < count; ++t) {
+            const float v = __half2float(table[(size_t)valid[t] * dim + k]);
+            acc = WEIGHTED ? fmaf(wts[t], v, acc) : __fadd_rn(acc, v);
+        }
         hsum[k] = acc;
     }
     __syncthreads();
@@ -109,7 +134,7 @@ __global__ void __launch_bounds__(kEmbThreads) embed_pool_first_kernel(const __h
         pooled[j] = __fmul_rn(acc, inv);
         ss = __dadd_rn(ss, __dmul_rn((double)pooled[j], (double)pooled[j]));  // columns past out_dim hold 0
     }
-    const float norm = __double2float_rn(__dsqrt_rn(block_sum(ss, s_part)));
+    const float norm = WEIGHTED ? 0.0f : __double2float_rn(__dsqrt_rn(block_sum(ss, s_part)));   // 0: values stay as they are
 #pragma unroll
     for (int j = 0; j < kEmbColsPerThread; ++j) {
         const int c = tid + j * kEmbThreads;
@@ -224,18 +249,23 @@ __global__ void __launch_bounds__(kEmbThreads) embed_normalize_first_kernel(cons
 }
 
 cudaError_t launch_embed_pooled(cudaStream_t st, const void* table_f16, int vocab, int dim, const void* proj_f16, int out_dim,
-                                const int32_t* d_tokens, const int32_t* d_mask, int batch, int seq, int order, float* d_out_f32,
-                                void* d_out_f16, int32_t* d_bad_token, uint32_t* d_bad_flag) {
+                                const int32_t* d_tokens, const int32_t* d_mask, int batch, int seq, int order,
+                                const float* d_token_norms, float* d_out_f32, void* d_out_f16, int32_t* d_bad_token,
+                                uint32_t* d_bad_flag) {
     if (out_dim > kEmbThreads * kEmbColsPerThread) return cudaErrorInvalidValue;
-    const size_t smem = (order == 0) ? (size_t)dim * 4 + (size_t)seq * 4
-                                     : (size_t)kEmbRows * dim * 4 + (size_t)kEmbRows * out_dim * 4 + (size_t)seq * 4;
+    const bool weighted = order != 0 && d_token_norms != nullptr;
+    const size_t smem = weighted ? (size_t)dim * 4 + (size_t)seq * 12
+                        : (order == 0) ? (size_t)dim * 4 + (size_t)seq * 4
+                                       : (size_t)kEmbRows * dim * 4 + (size_t)kEmbRows * out_dim * 4 + (size_t)seq * 4;
     constexpr size_t kMaxSmem = 220 * 1024;
     if (smem > kMaxSmem) return cudaErrorInvalidValue;
     static bool configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(embed_pool_first_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmem);
+        cudaError_t e = cudaFuncSetAttribute(embed_pool_first_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmem);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(embed_pool_first_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmem);
         if (e == cudaSuccess)
             e = cudaFuncSetAttribute(embed_normalize_first_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmem);
         if (e != cudaSuccess) return e;
@@ -243,9 +273,12 @@ cudaError_t launch_embed_pooled(cudaStream_t st, const void* table_f16, int voca
     }
     const __half* table = (const __half*)table_f16;
     const __half* proj = (const __half*)proj_f16;
-    if (order == 0)
-        embed_pool_first_kernel<<<batch, kEmbThreads, smem, st>>>(table, vocab, dim, proj, out_dim, d_tokens, d_mask, seq, d_out_f32,
-                                                                (__half*)d_out_f16, d_bad_token, d_bad_flag);
+    if (weighted)
+        embed_pool_first_kernel<true><<<batch, kEmbThreads, smem, st>>>(table, vocab, dim, proj, out_dim, d_tokens, d_mask, seq,
+                                                                      d_token_norms, d_out_f32, (__half*)d_out_f16, d_bad_token, d_bad_flag);
+    else if (order == 0)
+        embed_pool_first_kernel<false><<<batch, kEmbThreads, smem, st>>>(table, vocab, dim, proj, out_dim, d_tokens, d_mask, seq, nullptr,
+                                                                       d_out_f32, (__half*)d_out_f16, d_bad_token, d_bad_flag);
     else
         embed_normalize_first_kernel<<<batch, kEmbThreads, smem, st>>>(table, vocab, dim, proj, out_dim, d_tokens, d_mask, seq, d_out_f32,
                                                                      (__half*)d_out_f16, d_bad_token, d_bad_flag);

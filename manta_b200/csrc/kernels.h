@@ -36,9 +36,18 @@ cudaError_t launch_score_batched(cudaStream_t st, int sm_count, int metric, cons
 
 // Embedding front end: gather -> matmul -> masked mean_pool / normalize (order 0: normalize(mean_pool(x)),
 // 1: mean_pool(normalize(x))); writes the pooled rows as f32 and / or f16.
+// d_token_norms (order 1 only, may be NULL): [batch*seq] norms of the tokens' projected rows from
+// launch_embed_token_norms; with them the pool runs on the embedding rows and one row per batch element is projected.
 cudaError_t launch_embed_pooled(cudaStream_t st, const void* table_f16, int vocab, int dim, const void* proj_f16, int out_dim,
-                                const int32_t* d_tokens, const int32_t* d_mask, int batch, int seq, int order, float* d_out_f32,
-                                void* d_out_f16, int32_t* d_bad_token, uint32_t* d_bad_flag);
+                                const int32_t* d_tokens, const int32_t* d_mask, int batch, int seq, int order,
+                                const float* d_token_norms, float* d_out_f32, void* d_out_f16, int32_t* d_bad_token,
+                                uint32_t* d_bad_flag);
+// Tensor-core projection of every token row, reduced to the row norms (embed_mma.cu).  proj_t is the projection
+// transposed to [out_dim][dim].  A wait that runs out raises *d_flag to 2.
+bool embed_mma_supported(int dim, int out_dim);
+cudaError_t launch_transpose_f16(cudaStream_t st, const void* src, int rows, int cols, void* dst);
+cudaError_t launch_embed_token_norms(cudaStream_t st, const void* table_f16, int vocab, int dim, const void* proj_t_f16, int out_dim,
+                                     const int32_t* d_tokens, int64_t n_tokens, float* d_norms, uint32_t* d_flag);
 
 // Streaming scoring kernel (stream_scan.cuh).  mode: what the epilogue does with a score.
 enum { kModeScores = 0, kModeTopk = 1, kModeAccum = 2 };
@@ -49,6 +58,7 @@ enum { kModeScores = 0, kModeTopk = 1, kModeAccum = 2 };
 constexpr int scan_warps(int qt) { return qt == 1 ? 16 : 8; }
 constexpr int scan_bucket_slots(int qt) { return qt == 1 ? 1 : 2; }
 constexpr int kScanMaxBucketsPerBlock = 16;   // scan_warps * scan_bucket_slots for either form
+constexpr int kScanClaimMinTiles = 16;  // tiles per warp from which the last part of a fused pass is dealt on demand
 constexpr int kScanRefreshWords = 2560; // bucket maxima a threshold refresh can stage in shared memory
 constexpr int kSelSmemKeys = 4096;      // keys the selection sorts in shared memory
 // shared memory a block needs for select_block: keys, a 256-bin histogram, four scalars
@@ -99,7 +109,7 @@ struct StreamArgs {
     // tail of a fused pass (kModeTopk): the last block selects, stores and cleans the workspace
     int fused_select;
     int nq_total;            // queries of the whole pass (the exchange's epoch goes out after the last one)
-    uint32_t* done_blocks;   // device counter, zero between launches
+    uint32_t* done_blocks;   // two device counters, zero between launches: [0] blocks that finished, [1] tiles dealt on demand
     uint32_t* host_flags;    // pinned host words that receive the pass's raised flags (sticky until the host clears them)
     int32_t* out_ids;        // [nq][k]
     float* out_topk_scores;  // [nq][k]

@@ -289,7 +289,7 @@ __global__ void __launch_bounds__(256) ws_reset_kernel(SelectWs ws, uint32_t* do
     }
     for (uint32_t i = threadIdx.x; i < ws.nb; i += blockDim.x) ws.bucket[(size_t)q * ws.nb + i] = 0;
     if (q == 0 && threadIdx.x < kNumFlags) ws.flags[threadIdx.x] = 0;
-    if (q == 0 && threadIdx.x == 0 && done_blocks != nullptr) *done_blocks = 0;
+    if (q == 0 && threadIdx.x == 0 && done_blocks != nullptr) done_blocks[0] = done_blocks[1] = 0;
 }
 
 cudaError_t launch_ws_reset(cudaStream_t st, const SelectWs& ws, int nq, uint32_t* done_blocks) {

@@ -34,7 +34,7 @@ __device__ __forceinline__ void bitonic_sort_desc(uint64_t* s, int n2) {
 //     threshold is a lower bound of the k-th best, so nothing that matters is dropped);
 //  2. if more than kSelSmemKeys survive, an 8-pass byte-wise radix select over the whole pool finds the
 //     exact k-th largest key (keys are unique) and the k keys >= it are compacted instead;
-//  3. bitonic sort, write ids and scores (and, sharded, store them into every rank's inbox); optionally write the
+//  3. sort (by rank when the survivors fit one per thread, else bitonic), write ids and scores (and, sharded, store them into every rank's inbox); optionally write the
 //     k keys back as the new pool, or leave the query's fill count and threshold at zero for the next pass.
 // smem: kSelSmemBytes bytes, 16-byte aligned.  Pool entries are read through L2 (other blocks wrote them).
 __device__ __forceinline__ void select_block(const SelectArgs& a, int q, unsigned char* smem) {
@@ -53,11 +53,16 @@ __device__ __forceinline__ void select_block(const SelectArgs& a, int q, unsigne
     __syncthreads();
     if (tid == 0) s_scal[0] = 0;
     __syncthreads();
-    for (uint32_t i = tid; i < total; i += blockDim.x) {
-        uint64_t key = __ldcg(pool + i);
-        if (key >= floor_key) {
-            uint32_t pos = atomicAdd(&s_scal[0], 1u);
-            if (pos < kSelSmemKeys) s_keys[pos] = key;
+    for (uint32_t i0 = tid; i0 < total; i0 += 4 * blockDim.x) {   // four independent loads at a time
+        uint64_t key[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) key[u] = (i0 + u * blockDim.x < total) ? __ldcg(pool + i0 + u * blockDim.x) : 0ull;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (i0 + u * blockDim.x < total && key[u] >= floor_key) {
+                uint32_t pos = atomicAdd(&s_scal[0], 1u);
+                if (pos < kSelSmemKeys) s_keys[pos] = key[u];
+            }
         }
     }
     __syncthreads();
@@ -106,10 +111,24 @@ __device__ __forceinline__ void select_block(const SelectArgs& a, int q, unsigne
         __syncthreads();
     }
 
-    int n2 = 1;
-    while ((uint32_t)n2 < n) n2 <<= 1;
-    for (int i = n + tid; i < n2; i += blockDim.x) s_keys[i] = 0;
-    bitonic_sort_desc(s_keys, n2);
+    if (n <= blockDim.x) {
+        // the usual case, a few hundred survivors at most: every thread ranks one key against all the others (keys are
+        // unique) and stores it at its rank
+        const uint64_t mine = ((uint32_t)tid < n) ? s_keys[tid] : 0ull;
+        uint32_t rank = 0;
+        if ((uint32_t)tid < n) {
+#pragma unroll 4
+            for (uint32_t j = 0; j < n; ++j) rank += (s_keys[j] > mine) ? 1u : 0u;
+        }
+        __syncthreads();
+        if ((uint32_t)tid < n) s_keys[rank] = mine;
+        __syncthreads();
+    } else {
+        int n2 = 1;
+        while ((uint32_t)n2 < n) n2 <<= 1;
+        for (int i = n + tid; i < n2; i += blockDim.x) s_keys[i] = 0;
+        bitonic_sort_desc(s_keys, n2);
+    }
 
     if (n < k && tid == 0) flags[kFlagInternal] = 1u;
     const float sign = (a.order == MANTA_B200_ORDER_SMALLEST) ? -1.0f : 1.0f;

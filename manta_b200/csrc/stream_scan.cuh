@@ -209,21 +209,42 @@ __global__ void __launch_bounds__(scan_warps(QT) * 32, 1) stream_scan_kernel(con
     const int Cs = kSpec ? scan_padded_stride(LPR * CPL, kSpec ? LPR : 1) : g.cstride;
     unsigned char* my_ring = ring + (size_t)warp * S * g.stage_bytes;
 
-    const int64_t nrows = a.row_end - a.row_begin;
-    const int64_t n_tiles = (nrows + R - 1) / R;
-    const int64_t gw = (int64_t)blockIdx.x * W + warp;
-    const int64_t nwarps = (int64_t)gridDim.x * W;
-    const int my_tiles = (gw < n_tiles) ? (int)((n_tiles - gw + nwarps - 1) / nwarps) : 0;
+    // tile numbers fit 32 bits: a candidate set has fewer than 2^31 rows
+    const int n_tiles = (int)((a.row_end - a.row_begin + R - 1) / R);
+    const int gw = (int)blockIdx.x * W + warp;
+    const int nwarps = (int)gridDim.x * W;
     const bool topk = a.mode == kModeTopk;
+    // How the tiles are dealt.  A long pass (kScanClaimMinTiles tiles per warp or more) gives every warp runs of kRun
+    // consecutive tiles: run r of warp gw is tiles (r * nwarps + gw) * kRun ... + kRun - 1 (part A, `own_a` tiles per warp).
+    // In a fused single-query top-k pass over f16 or q8 rows -- the passes bound by memory bandwidth, in which the SMs
+    // advance unevenly -- part A ends after about three quarters of the tiles and the rest is claimed from a device
+    // counter in runs of 8, 4, 2 and finally 1 tiles, so that the SMs the memory system serves more slowly end up with
+    // fewer tiles and every warp finishes within a tile or two of the others.  (Runs, because one address takes well
+    // under a billion atomic adds a second and the warps together finish more than a billion tiles a second.  The
+    // passes bound by instruction issue, several queries or q4 rows, advance evenly and measured 3-4 % slower with
+    // claimed tiles, whose runs scatter an SM's warps over the rows; they keep part A to the end.)  What part A
+    // leaves of any other pass, and all of a short pass, goes round robin, one tile at a time (part B).  The tiles a warp
+    // observes and reads again are always its own first ones.
+    constexpr int kRun = 8;
+    const int per_warp = n_tiles / nwarps;
+    const bool long_pass = per_warp >= kScanClaimMinTiles;
+    const bool claim_on = QT == 1 && !kQ4 && topk && a.fused_select && long_pass;
+    const int own_a = !long_pass ? 0 : ((claim_on ? max(kScanClaimMinTiles - 4, per_warp - per_warp / 4) : per_warp) & ~(kRun - 1));
+    const int a_end = own_a * nwarps;
+    const int static_end = claim_on ? a_end : n_tiles;
+    const int own_b = (gw < static_end - a_end) ? (static_end - a_end - gw + nwarps - 1) / nwarps : 0;
+    const int my_tiles = own_a + own_b;
+    const int n_claimable = n_tiles - static_end;
+    uint32_t* claim_counter = a.done_blocks + 1;
 
     // ---- the asynchronous copy of one tile: lane l copies chunks l, l + 32, ... of the tile's contiguous bytes
     // chunk i of the tile lands at ((i / C) * Cs + i % C) * 16 = (i + (i / C) * (Cs - C)) * 16; the division is a
     // multiply-high by ceil(2^32 / C), exact for every chunk index a tile can have
     const uint32_t c_magic = (uint32_t)((0x100000000ull + (uint32_t)C - 1u) / (uint32_t)C);
     const int c_pad = Cs - C;
-    auto issue = [&](int tile_local, int stage) {
-        if (tile_local >= 0 && tile_local < my_tiles) {
-            const int64_t first = a.row_begin + (gw + (int64_t)tile_local * nwarps) * R;
+    auto issue = [&](int tile, int stage) {
+        if (tile >= 0) {
+            const int64_t first = a.row_begin + (int64_t)tile * R;
             const int rows_here = (int)min((int64_t)R, a.row_end - first);
             const int n_chunks = rows_here * C;
             const unsigned char* src = cv.data + (size_t)first * cv.row_bytes;
@@ -266,14 +287,59 @@ __global__ void __launch_bounds__(scan_warps(QT) * 32, 1) stream_scan_kernel(con
     // consumed in append mode, then the T observed tiles are read again and appended, then the scan goes on.
     const int F = S - 1;
     int T = topk ? 0x3fffffff : 0;
-    auto tile_of = [&](int i) -> int {
-        if (i < T + F) return (i < my_tiles) ? i : -1;
+    // Position i of the warp's schedule: the warp's own tile number (>= 0), kNoTile, or kClaim (the tile comes from the
+    // shared counter).  Claims start once the warp's own tiles are used up, always after observation and replay.
+    constexpr int kNoTile = -1, kClaim = -2;
+    auto slot_of = [&](int i) -> int {
+        if (i < T + F) return (i < my_tiles) ? i : kNoTile;
         if (i < 2 * T + F) return i - (T + F);
-        return (i - T < my_tiles) ? i - T : -1;
+        return (i - T < my_tiles) ? i - T : (claim_on ? kClaim : kNoTile);
+    };
+    // A warp works through its run, and takes the next run an iteration before the copy that needs it is issued.  The
+    // length it asks for follows from where the counter will be by then: its last answer plus one run of every warp.
+    int claimed = 0, run_next = 0, run_end = 0, run_len = 0, counter_guess = 0;
+    bool claim_ready = false, dry = false;
+    auto take_run = [&]() {
+        const int left = n_claimable - counter_guess;
+        run_len = (left >= 16 * nwarps) ? 8 : (left >= 8 * nwarps) ? 4 : (left >= nwarps) ? 2 : 1;
+        if (lane == 0) claimed = (int)atomicAdd(claim_counter, (uint32_t)run_len);
+        claim_ready = true;
+    };
+    auto claim_ahead = [&](int i) {
+        if (claim_on && !claim_ready && !dry && run_next >= run_end && slot_of(i) == kClaim) take_run();
+    };
+    auto tile_at = [&](int i) -> int {
+        const int sl = slot_of(i);
+        if (sl >= 0) return (sl < own_a) ? (((sl / kRun) * nwarps + gw) * kRun + (sl % kRun)) : (a_end + gw + (sl - own_a) * nwarps);
+        if (sl == kNoTile || dry) return -1;
+        if (run_next >= run_end) {
+            if (!claim_ready) take_run();
+            claim_ready = false;
+            const int start = __shfl_sync(0xffffffffu, claimed, 0);
+            if (start < 0 || start >= n_claimable) {
+                dry = true;   // the counter only rises: every later claim is past the end too
+                return -1;
+            }
+            run_next = start;
+            run_end = min(start + run_len, n_claimable);
+            counter_guess = (int)min((int64_t)n_claimable, (int64_t)start + (int64_t)run_len * (1 + nwarps));
+        }
+        return static_end + run_next++;
+    };
+    // tiles in flight, oldest first (the ring holds S <= 3 stages)
+    int pend0 = -1, pend1 = -1, pend2 = -1;
+    auto push_tile = [&](int t) {
+        if (S == 2) pend1 = t;
+        else pend2 = t;
     };
 
     // start the stream before anything else, then prepare the queries while the first tiles are on their way
-    for (int p = 0; p < S - 1; ++p) issue(tile_of(p), p);
+    for (int p = 0; p < S - 1; ++p) {
+        const int t = tile_at(p);
+        issue(t, p);
+        if (p == 0) pend0 = t;
+        else pend1 = t;
+    }
     float* lo_norm_s = reinterpret_cast<float*>(hdr_s + QT);   // behind the headers, inside their 256 bytes
     prepare_queries_block<LAYOUT, QT>(a.queries, a.q0, a.qt, cv.cols, C, g.q_bytes, hdr_s, q_s, reinterpret_cast<float*>(s_stage), lo_norm_s);
     __syncthreads();
@@ -350,7 +416,7 @@ __global__ void __launch_bounds__(scan_warps(QT) * 32, 1) stream_scan_kernel(con
     int total = topk ? 0x3fffffff : max(my_tiles, F);
     uint32_t fresh = 0;            // fresh (not re-read) tiles consumed so far: drives the refresh duty
     uint32_t overflow_seen = 0;
-    for (int i = 0; i < total; ++i) {
+    for (int i = 0; i < total || (claim_on && !(dry && pend0 < 0 && pend1 < 0)); ++i) {
         if (topk) {
             // the bounds move fast only at the start: reread them every tile early on, every eighth tile later
             if (observing || i <= 16 || (i & 7) == 0) load_bounds();
@@ -384,16 +450,24 @@ __global__ void __launch_bounds__(scan_warps(QT) * 32, 1) stream_scan_kernel(con
         else if (S == 3) cp_async_wait<1>();
         else cp_async_wait<2>();
         __syncwarp();             // ... for every lane, and every lane is done with the stage refilled next
-        issue(tile_of(i + S - 1), next_stage);
+        {
+            const int t = tile_at(i + S - 1);
+            issue(t, next_stage);
+            push_tile(t);
+        }
+        claim_ahead(i + S);
         next_stage = stage;       // the stage consumed now is refilled in the next iteration
         stage = (stage + 1 == S) ? 0 : stage + 1;
         const int cur_stage = next_stage;
-        const int tile_local = tile_of(i);
-        if (tile_local < 0) continue;
+        const int tile = pend0;
+        pend0 = pend1;
+        pend1 = pend2;
+        pend2 = -1;
+        if (tile < 0) continue;
         const bool observe = i < T;
         const bool replay = i >= T + F && i < 2 * T + F;
         const unsigned char* st = my_ring + (size_t)cur_stage * g.stage_bytes;
-        const int64_t first = a.row_begin + (gw + (int64_t)tile_local * nwarps) * R;
+        const int64_t first = a.row_begin + (int64_t)tile * R;
         const int64_t my_row = first + r_in;
         const bool rv = leader && my_row < a.row_end;
 
@@ -786,9 +860,14 @@ __global__ void __launch_bounds__(scan_warps(QT) * 32, 1) stream_scan_kernel(con
         __syncthreads();
     }
     if (threadIdx.x == 0) {
-        *a.done_blocks = 0u;
+        a.done_blocks[0] = 0u;
+        a.done_blocks[1] = 0u;   // the tile counter
+        static_assert(kNumFlags == 4, "the flag words are read as one 16-byte load");
+        const uint4 fl = __ldcg(reinterpret_cast<const uint4*>(a.ws.flags));
+        const uint32_t fw[4] = {fl.x, fl.y, fl.z, fl.w};
+#pragma unroll
         for (int f = 0; f < kNumFlags; ++f) {
-            if (a.ws.flags[f] != 0u) {
+            if (fw[f] != 0u) {
                 a.host_flags[f] = 1u;   // sticky on the host until it reads and clears them
                 a.ws.flags[f] = 0u;
             }
