@@ -15,6 +15,7 @@
 // reports the failure (and the streaming kernel can redo the pass).
 #include <cuda.h>
 
+#include <cmath>
 #include <cstdio>
 #include <cstdlib>
 
@@ -58,9 +59,29 @@ struct KernelArgs {
     int filtered;                 // 0: everything enters the pool (small sets)
     int observe_tiles;            // tiles per CTA scored before the first bound exists (replayed at the end)
     int raw_chunks;               // q4: 128-byte chunks of packed nibbles per row (each becomes four f16 K chunks)
+    int hi_first;                 // q8: only the high planes are contracted (ncols = queries); see the kernel's note
+    const int8_t* plane_lo;       // q8, hi_first: low planes of this group's queries, [qn][plane_stride]
+    const float* lo_norms;        // q8, hi_first: their norms, rounded up a shade (written by build_b_kernel)
+    int plane_stride;
     int64_t row_begin;
     int64_t row_end;
 };
+
+// Exact int32 dot product of one q8 row with one low query plane (n16 16-byte pieces), computed by the whole warp: every
+// lane takes pieces lane, lane + 32, ... so that all loads of a pair are in flight together.  Used for the rare
+// (row, query) pair that passes the high-plane filter.
+__device__ __forceinline__ int lo_plane_dot_warp(const uint4* __restrict__ row, const uint4* __restrict__ lo, int n16, int lane) {
+    int acc = 0;
+#pragma unroll 2
+    for (int i = lane; i < n16; i += 32) {
+        const uint4 r = __ldg(row + i), q = __ldg(lo + i);
+        acc = __dp4a((int)r.x, (int)q.x, acc);
+        acc = __dp4a((int)r.y, (int)q.y, acc);
+        acc = __dp4a((int)r.z, (int)q.z, acc);
+        acc = __dp4a((int)r.w, (int)q.w, acc);
+    }
+    return __reduce_add_sync(0xffffffffu, acc);
+}
 
 // Scores of N consecutive queries for one candidate row (one lane).  METRIC is a compile-time constant so that
 // the evaluations are one basic block the compiler can interleave.
@@ -119,6 +140,7 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     uint32_t* pub_s = bmax_s + kMmaCols * 4;             // [qn][4][kBucketSlots]: last published values
     float* zq_s = (float*)(pub_s + kMmaCols * 4 * kBucketSlots);      // [kMmaCols]: pre-filter bound per query (+inf past qn)
     float* wq_s = zq_s + kMmaCols;                                    // [kMmaCols]: l2 only, weight of ||row||^2 in the bound
+    float* lo_s = wq_s + kMmaCols;                                    // [kMmaCols]: hi_first only, norm of the query's low plane (a shade high)
 
     const int64_t nrows = a.row_end - a.row_begin;
     const int n_tiles = (int)((nrows + kTileRows - 1) / kTileRows);
@@ -164,6 +186,9 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     for (int j = a.qn + threadIdx.x; j < kMmaCols; j += blockDim.x) {   // padding columns never pass
         zq_s[j] = INFINITY;
         wq_s[j] = 0.0f;
+    }
+    if constexpr (I8) {
+        for (int j = threadIdx.x; j < kMmaCols; j += blockDim.x) lo_s[j] = (a.hi_first && j < a.qn) ? a.lo_norms[j] : 0.0f;
     }
     if (warp == 1) tmem_alloc(tmem_slot, 512);
     tc_fence_before();
@@ -260,7 +285,14 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const int sub = (warp - 2) >> 2;        // this warp takes the 16-query chunks sub, sub + kEpiSubs, ...
             const float sign = (a.order == MANTA_B200_ORDER_SMALLEST) ? -1.0f : 1.0f;
             const bool want_scale = I8 && METRIC != MANTA_B200_METRIC_COSINE;
-            const bool want_stats = METRIC != MANTA_B200_METRIC_DOT;
+            // High planes first (q8, a.hi_first).  The contraction carries only I_hi; the low plane can move T = 254 * I_hi
+            // + I_lo by at most ||lo|| * ||codes of the row|| (Cauchy-Schwarz; the row's sum of squared codes is its stored
+            // statistic), so the pre-filter tests the upper bound of T, and a (row, query) pair that passes gets its I_lo
+            // from lo_plane_dot -- the same int32 the second plane's MMA would have produced, so scores are unchanged.
+            // While a warp only observes (no bound yet, nothing appended) it scores every row with the low plane at its
+            // worst: lower bounds of the scores, hence valid (slightly low) bucket maxima.
+            const bool hf = I8 && a.hi_first;
+            const bool want_stats = METRIC != MANTA_B200_METRIC_DOT || hf;
             // every (metric, order) has a pre-filter except "largest l2 distance", which takes the exact path throughout
             constexpr bool kL2 = METRIC == MANTA_B200_METRIC_L2_DISTANCE;
             const bool cheap = !(kL2 && a.order == MANTA_B200_ORDER_LARGEST);
@@ -318,6 +350,10 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 // l2: ||row||^2 as the filter adds it to the per-query constant
                 float dn2row = 0.0f;
                 if constexpr (kL2) dn2row = I8 ? __fmul_rn(__fmul_rn(sd, sd), (float)(int)stat) : __uint_as_float(stat);
+                // hi_first: what the low plane can add to T * rowcs for a query whose low plane has norm 1
+                const float rnorm = (hf && rv) ? sqrtf((float)(int)stat) * 1.000002f : 0.0f;   // norm of the row's codes, a shade high
+                const float rslack = rnorm * fabsf(rv ? rowc : 0.0f);
+                const uint4* row_codes = reinterpret_cast<const uint4*>(a.cv.data + (size_t)(rv ? row : a.row_begin) * a.cv.row_bytes);
                 // One finished score of this lane's row for query j: vote against the bound, keep the bucket maximum,
                 // append the passing rows with one reservation per warp.
                 auto offer = [&](int j, float g, uint32_t o) {
@@ -345,6 +381,7 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 // chunks of 16 queries for this lane's row
                 for (int c0 = sub * 16; c0 < a.qn; c0 += 16 * kEpiSubs) {
                     uint32_t groups = 0xFu;   // four-query groups of the chunk that need the exact evaluation
+                    uint32_t myhit = 0xFFFFu; // this lane's own row: queries of the chunk that passed the pre-filter
                     uint32_t vh[16], vl[16];
                     if (cheap) {
                         if constexpr (Q4) {
@@ -368,7 +405,7 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         } else {
                             tmem_ld16(t_row + c0, vh);
                             if constexpr (I8) {
-                                tmem_ld16(t_row + a.lo_off + c0, vl);
+                                if (!hf) tmem_ld16(t_row + a.lo_off + c0, vl);
                             } else {
 #pragma unroll
                                 for (int jj = 0; jj < 16; ++jj) vl[jj] = 0;
@@ -385,16 +422,23 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         uint32_t hit = 0;
 #pragma unroll
                         for (int jj = 0; jj < 16; ++jj) {
-                            float t;
-                            if constexpr (I8)
-                                t = __fmaf_rn((float)(int)vh[jj], 254.0f, (float)(int)vl[jj]);
-                            else
+                            float t, slack = srow;
+                            if constexpr (I8) {
+                                if (hf) {
+                                    t = __fmul_rn((float)(int)vh[jj], 254.0f);
+                                    slack = __fmaf_rn(lo_s[c0 + jj], rslack, srow);
+                                } else {
+                                    t = __fmaf_rn((float)(int)vh[jj], 254.0f, (float)(int)vl[jj]);
+                                }
+                            } else {
                                 t = __uint_as_float(vh[jj]);
+                            }
                             // l2 (smallest): dist <= B  <=>  dot >= (||q||^2 - B^2 + ||row||^2) / 2, in the units of T
                             float rhs = zq_s[c0 + jj];
                             if constexpr (kL2) rhs = __fmaf_rn(dn2row, wq_s[c0 + jj], rhs);
-                            hit |= (__fmaf_rn(t, rowcs, srow) >= rhs) ? (1u << jj) : 0u;
+                            hit |= (__fmaf_rn(t, rowcs, slack) >= rhs) ? (1u << jj) : 0u;
                         }
+                        myhit = hit;
                         hit = __reduce_or_sync(0xffffffffu, hit);
                         if (hit == 0u) continue;
                         groups = ((hit & 0x000Fu) ? 1u : 0u) | ((hit & 0x00F0u) ? 2u : 0u) | ((hit & 0x0F00u) ? 4u : 0u) |
@@ -426,19 +470,51 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                             } else {
                                 tmem_ld4(t_row + cg, h4);
                                 if constexpr (I8) {
-                                    tmem_ld4(t_row + a.lo_off + cg, l4);
+                                    if (!hf) tmem_ld4(t_row + a.lo_off + cg, l4);
                                 } else {
 #pragma unroll
                                     for (int jj = 0; jj < 4; ++jj) l4[jj] = 0;
                                 }
                                 tmem_ld_wait();
                             }
+                            uint32_t need = 0xFu;   // queries of the group this lane finishes for its row
+                            if constexpr (I8) {
+                                if (hf) {
+                                    need = 0u;
+#pragma unroll
+                                    for (int jj = 0; jj < 4; ++jj) {
+                                        l4[jj] = 0;
+                                        if (cg + jj >= a.qn) continue;
+                                        if (observe) {
+                                            // no bound yet, nothing is appended: the score with the low plane at its worst
+                                            // (finished by the same function, which is monotone in I_lo) is a valid lower
+                                            // bound of the row's score and so of the bucket maximum
+                                            const int worst = (int)ceilf(__fmul_rn(lo_s[cg + jj], rnorm)) + 1;
+                                            l4[jj] = (uint32_t)((rowcs >= 0.0f) ? -worst : worst);
+                                            need |= 1u << jj;
+                                            continue;
+                                        }
+                                        const bool mine = rv && ((myhit >> (4 * gq + jj)) & 1u);
+                                        // one pair at a time, the whole warp on each
+                                        uint32_t pend = __ballot_sync(0xffffffffu, mine);
+                                        const uint4* lo_q = reinterpret_cast<const uint4*>(a.plane_lo + (size_t)(cg + jj) * a.plane_stride);
+                                        while (pend != 0u) {
+                                            const int src = __ffs(pend) - 1;
+                                            pend &= pend - 1u;
+                                            const uint4* rsrc = reinterpret_cast<const uint4*>(__shfl_sync(0xffffffffu, (unsigned long long)row_codes, src));
+                                            const int dot = lo_plane_dot_warp(rsrc, lo_q, a.cv.cols >> 4, lane);
+                                            if (lane == src) l4[jj] = (uint32_t)dot;
+                                        }
+                                        if (mine) need |= 1u << jj;
+                                    }
+                                }
+                            }
                             float g[4];
                             uint32_t o[4];
                             score_n<I8, METRIC, 4>(h4, l4, stat, rinv, sd, hdr_s, cg, a.qn, rv, sign, g, o);
 #pragma unroll
                             for (int jj = 0; jj < 4; ++jj)
-                                if (cg + jj < a.qn) offer(cg + jj, g[jj], o[jj]);
+                                if (cg + jj < a.qn) offer(cg + jj, g[jj], ((need >> jj) & 1u) ? o[jj] : 0u);
                         }
                     }
                 }
@@ -641,7 +717,18 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 // Operand B: [ncols][kpad] bytes, K-major.  q8: rows 0..qn-1 are the high planes, lo_off.. the low planes.
 // f16: row j is query j as half bits.  Everything else is zero.
 __global__ void build_b_kernel(unsigned char* __restrict__ out, int ncols, int kpad, int layout, QueryPrep qp, int q0,
-                               int qn, int lo_off, int cols) {
+                               int qn, int lo_off, int cols, float* __restrict__ lo_norms) {
+    if (lo_norms != nullptr && layout == MANTA_B200_LAYOUT_Q8_ROW_F32) {
+        // norms of the low planes (high-planes-first passes), one warp per query, rounded up a shade
+        const int lane = threadIdx.x & 31;
+        for (int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); n < qn; n += gridDim.x * (blockDim.x >> 5)) {
+            const int8_t* lo = qp.plane_lo + (size_t)(q0 + n) * qp.plane_stride;
+            int acc = 0;
+            for (int c = lane; c < cols; c += 32) acc += (int)lo[c] * (int)lo[c];
+            acc = __reduce_add_sync(0xffffffffu, acc);
+            if (lane == 0) lo_norms[n] = sqrtf((float)acc) * 1.000002f;
+        }
+    }
     const size_t total = (size_t)ncols * kpad;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const int n = (int)(i / kpad), kb = (int)(i % kpad);
@@ -798,13 +885,12 @@ cudaError_t launch_mma_topk(cudaStream_t stream, int sm_count, MmaState** state,
     MmaState* st = *state;
     const CandView& cv = a.cv;
     const bool i8 = cv.layout == MANTA_B200_LAYOUT_Q8_ROW_F32;
-    const int group = mma_group_queries(cv);
     const bool q4 = cv.layout == MANTA_B200_LAYOUT_Q4_B32_F16;
     // q4: a 128-byte chunk of nibbles (256 codes) becomes four 128-byte K chunks of f16
     const int raw_chunks = (cv.row_bytes + kChunkBytes - 1) / kChunkBytes;
     const int kchunks = q4 ? 4 * raw_chunks : raw_chunks;
     const int kpad = kchunks * kChunkBytes;
-    const size_t b_bytes = (size_t)kMmaCols * kpad;
+    const size_t b_bytes = (size_t)kMmaCols * kpad + kMmaCols * sizeof(float);   // operand B, then the low-plane norms
     if (st->d_b_bytes < b_bytes) {
         cudaError_t e = cudaStreamSynchronize(stream);
         if (e != cudaSuccess) return e;
@@ -822,6 +908,17 @@ cudaError_t launch_mma_topk(cudaStream_t stream, int sm_count, MmaState** state,
     const int n_tiles = (int)((nrows + kTileRows - 1) / kTileRows);
     const int grid = sm_count < n_tiles ? sm_count : n_tiles;
     const int filtered = (nrows > (int64_t)a.ws.cap) ? 1 : 0;
+    // q8: a filtered pass with a pre-filter contracts the high planes only (twice the queries per pass, half the MMAs
+    // and tensor-memory reads); everything else carries both planes
+    // It pays when pairs that pass the filter are rare next to the rows streamed: a pass appends on the order of
+    // k * log(rows / k) keys per query, each of which now costs a round trip to L2 for the low plane's dot product.  Measured
+    // on 768-byte cosine rows: 10 M rows, k = 10 wins from 32 queries up (1.8x at 256); k = 100, or 2 M rows, or C5's
+    // k = 50 on 5 M rows lose 3 - 15 %.
+    const double rows_per_append = (double)nrows / ((double)a.k * log2((double)nrows / (double)a.k + 2.0));
+    const int hi_first = (i8 && filtered && !(a.metric == MANTA_B200_METRIC_L2_DISTANCE && a.order == MANTA_B200_ORDER_LARGEST) &&
+                          rows_per_append >= (a.nq > kMmaCols / 2 ? 8000.0 : 30000.0))
+                             ? 1 : 0;
+    const int group = hi_first ? kMmaCols : mma_group_queries(cv);
     int observe = (a.k + grid * 4 - 1) / (grid * 4);
     if (filtered && observe > kBucketSlots) {
         *why = "k exceeds the bucket capacity of the tensor-core pass for this grid";
@@ -835,9 +932,10 @@ cudaError_t launch_mma_topk(cudaStream_t stream, int sm_count, MmaState** state,
     for (int q0 = 0; q0 < a.nq; q0 += group) {
         const int qn = (a.nq - q0 < group) ? a.nq - q0 : group;
         const int qpad = (qn + 15) / 16 * 16;
-        const int ncols = i8 ? 2 * qpad : qpad;
-        const int lo_off = qpad;
-        build_b_kernel<<<128, 256, 0, stream>>>(st->d_b, ncols, kpad, cv.layout, a.qp, q0, qn, lo_off, cv.cols);
+        const int ncols = (i8 && !hi_first) ? 2 * qpad : qpad;
+        const int lo_off = hi_first ? ncols : qpad;   // hi_first: no row of operand B is a low plane
+        float* d_lo_norms = reinterpret_cast<float*>(st->d_b + (size_t)kMmaCols * kpad);
+        build_b_kernel<<<128, 256, 0, stream>>>(st->d_b, ncols, kpad, cv.layout, a.qp, q0, qn, lo_off, cv.cols, hi_first ? d_lo_norms : nullptr);
         count_launch();
         ++*launches;
         e = cudaGetLastError();
@@ -850,7 +948,7 @@ cudaError_t launch_mma_topk(cudaStream_t stream, int sm_count, MmaState** state,
 
         const size_t a_stage = (size_t)kTileRows * kChunkBytes, b_stage = (size_t)ncols * kChunkBytes;
         const size_t fixed = 1024 /*alignment slack*/ + 256 /*barriers*/ + sizeof(QueryHeader) * kMmaCols + 4 * kMmaCols +
-                             16 * kMmaCols + 16 * kMmaCols * kBucketSlots + 8 * kMmaCols;
+                             16 * kMmaCols + 16 * kMmaCols * kBucketSlots + 12 * kMmaCols;
         const size_t raw_ring = q4 ? (size_t)kRawStages * kRawStageBytes : 0;
         const size_t budget = kSmemLimit - fixed - raw_ring;
         // Operand B stays resident when it leaves room for at least four candidate stages: the ring then carries
@@ -884,6 +982,10 @@ cudaError_t launch_mma_topk(cudaStream_t stream, int sm_count, MmaState** state,
         ka.row_begin = a.row_begin;
         ka.row_end = a.row_end;
         ka.raw_chunks = raw_chunks;
+        ka.hi_first = hi_first;
+        ka.plane_lo = a.qp.plane_lo ? a.qp.plane_lo + (size_t)q0 * a.qp.plane_stride : nullptr;
+        ka.plane_stride = a.qp.plane_stride;
+        ka.lo_norms = d_lo_norms;
         e = launch_scan_variant(st, cv.layout, a.metric, grid, smem, stream, map_a, map_b, ka, why);
         if (e != cudaSuccess) return e;
         count_launch();
