@@ -511,6 +511,7 @@ def run_ours(args, wl: Workload):
                 hb["scores"] = torch.empty((nq, k), dtype=torch.float32).pin_memory()
             ln.stream.synchronize()
             hbs.append(hb)
+        hb = None  # the list holds the only references: hbs.clear() below must release the pinned buffers
 
     def enqueue_host_step(i):
         """Upload, shard pass, exchange + merge, download of step i on lane i % n_lanes; returns the lane index."""
