@@ -91,3 +91,31 @@ def test_embed_then_score_at_stated_size(rt):
     q = oracle.half_to_float(oracle.float_to_half(pooled))  # the scan reads the pooled rows rounded to f16
     deq = _dequantised("q8", rows, cols, True)
     _check(topk_parity_report("dot", q, deq, ids, scores, k, floor=EMBED_FLOOR), "embed + q8 dot 500k x 384, Q=128, k=50")
+
+
+# Long passes deal their tiles differently from short ones (runs of eight tiles per warp, then a round-robin remainder; a
+# fused single-query top-k pass hands out its last quarter on demand): every row must still be scored exactly once.  Narrow
+# rows keep the oracle cheap: 64-byte rows make 32-row tiles, so 1.3 M rows are 17 tiles for each of the 2,368 warps.
+LONG = [("q8", "dot", 1_300_003, 64), ("f16", "cosine", 1_300_003, 64), ("q4", "l2_distance", 1_300_003, 128)]
+
+
+@pytest.mark.parametrize("case", LONG, ids=lambda c: f"{c[0]}-{c[1]}-{c[2]}x{c[3]}")
+def test_every_row_of_a_long_pass_is_scored_once(rt, case):
+    from helpers import assert_scores_close, assert_topk_matches, make_rows, pack
+
+    layout, metric, rows, cols = case
+    rng = np.random.default_rng(rows + cols)
+    x = make_rows(rng, rows, cols, normalised=(layout != "q4"))
+    q = make_rows(rng, 2, cols)
+    data, scales, deq = pack(layout, x)
+    cands = rt.bind(layout, data, scales)
+    try:
+        got = rt.score(cands, metric, q)                      # all scores: fixed deal, runs + remainder
+        ids1, sc1 = rt.score_topk(cands, metric, q[:1], 25)   # fused single-query pass: part of it on demand (f16 / q8)
+        ids2, sc2 = rt.score_topk(cands, metric, q, 25, smallest=True)
+    finally:
+        cands.unbind()
+    ref = oracle.SCORE_FNS[metric](q, deq)
+    assert_scores_close(metric, q, deq, got, ref)
+    assert_topk_matches(metric, q[:1], deq, ids1, sc1, 25)
+    assert_topk_matches(metric, q, deq, ids2, sc2, 25, smallest=True)
