@@ -202,7 +202,6 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         if (warp == 0) {
             // ---------------- TMA producer ----------------
             if (lane == 0) {
-                uint32_t g = 0;
                 if (a.b_resident) {
                     // the query operand fits beside the candidate ring: one load, then only candidates stream
                     mbar_expect_tx(bfull, (uint32_t)a.kchunks * b_stage_bytes);
@@ -221,15 +220,20 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     }
                 }
                 const uint32_t stage_tx = (uint32_t)(kTileRows * kChunkBytes) + (a.b_resident ? 0u : b_stage_bytes);
-                for (int it = 0; !Q4 && it < n_iters && !*abort_s; ++it) {
+                // (stage and phase are counted, not divided out of g: these single-thread loops are latency chains)
+                int s = 0;
+                uint32_t ph = 0;
+                const int kchunks = a.kchunks;
+                const bool b_res = a.b_resident != 0;
+                bool ok = true;
+                for (int it = 0; !Q4 && ok && it < n_iters && !*abort_s; ++it) {
                     const int row0 = (int)(a.row_begin + (int64_t)tile_of(it) * kTileRows);
-                    for (int kc = 0; kc < a.kchunks; ++kc, ++g) {
-                        const int s = g % S;
-                        const uint32_t ph = (g / S) & 1u;
-                        if (!mbar_wait(&empty[s], ph ^ 1u, abort_s)) break;
+                    for (int kc = 0; kc < kchunks; ++kc) {
+                        if (!mbar_try_wait(&empty[s], ph ^ 1u) && !mbar_wait(&empty[s], ph ^ 1u, abort_s)) { ok = false; break; }
                         mbar_expect_tx(&full[s], stage_tx);
                         tma_load_2d(sA + (size_t)s * kTileRows * kChunkBytes, &map_a, kc * kChunkBytes, row0, &full[s]);
-                        if (!a.b_resident) tma_load_2d(sB + (size_t)s * b_stage_bytes, &map_b, kc * kChunkBytes, 0, &full[s]);
+                        if (!b_res) tma_load_2d(sB + (size_t)s * b_stage_bytes, &map_b, kc * kChunkBytes, 0, &full[s]);
+                        if (++s == S) { s = 0; ph ^= 1u; }
                     }
                 }
             }
@@ -238,38 +242,49 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             if (lane == 0) {
                 const uint32_t idesc = I8 ? ((2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(a.ncols >> 3) << 17) | ((uint32_t)(kTileRows >> 4) << 24))
                                           : ((1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(a.ncols >> 3) << 17) | ((uint32_t)(kTileRows >> 4) << 24));
-                uint32_t g = 0;
+                // The issuing thread is alone on its latency chain: between two MMAs nothing hides the latency of its own
+                // scalar instructions (measured: 67 cycles per back-to-back tcgen05.mma of up to 128 columns, 127 at 256, but
+                // 170 - 240 when every instruction is preceded by divisions, descriptor construction and a called wait).  So
+                // stage and phase are counters, descriptors are one base plus a multiple of the stage stride, and a wait that
+                // is already over costs one try_wait.
+                const uint64_t desc_a0 = smem_desc_sw128(smem_u32(sA));
+                const uint64_t desc_b0 = smem_desc_sw128(smem_u32(sB));
+                const uint32_t a_step = (uint32_t)(kTileRows * kChunkBytes) >> 4;   // descriptor address units (16 bytes) per stage
+                const uint32_t b_step = b_stage_bytes >> 4;
+                const int kchunks = a.kchunks;
+                const bool b_res = a.b_resident != 0;
+                const uint32_t ncols = (uint32_t)a.ncols;
+                int s = 0;
+                uint32_t ph = 0;
                 bool b_ok = true;
-                if (a.b_resident) {
+                if (b_res) {
                     b_ok = mbar_wait(bfull, 0u, abort_s);
                     tc_fence_after();
                 }
                 for (int it = 0; b_ok && it < n_iters && !*abort_s; ++it) {
                     const int acc = it & 1;
-                    if (!mbar_wait(&tempty[acc], ((uint32_t)(it >> 1) & 1u) ^ 1u, abort_s)) break;
+                    const uint32_t tph = ((uint32_t)(it >> 1) & 1u) ^ 1u;
+                    if (!mbar_try_wait(&tempty[acc], tph) && !mbar_wait(&tempty[acc], tph, abort_s)) break;
                     tc_fence_after();
                     const uint32_t d_tmem = tmem_base + (uint32_t)acc * kMmaCols;
                     bool ok = true;
-                    for (int kc = 0; kc < a.kchunks; ++kc, ++g) {
-                        const int s = g % S;
-                        const uint32_t ph = (g / S) & 1u;
-                        if (!mbar_wait(&full[s], ph, abort_s)) { ok = false; break; }
+                    for (int kc = 0; kc < kchunks; ++kc) {
+                        if (!mbar_try_wait(&full[s], ph) && !mbar_wait(&full[s], ph, abort_s)) { ok = false; break; }
                         tc_fence_after();
-                        const uint32_t a_addr = smem_u32(sA + (size_t)s * kTileRows * kChunkBytes);
-                        const uint32_t b_addr = smem_u32(sB + (size_t)(a.b_resident ? kc : s) * b_stage_bytes);
+                        const uint64_t da = desc_a0 + (uint64_t)((uint32_t)s * a_step);
+                        const uint64_t db = desc_b0 + (uint64_t)((uint32_t)(b_res ? kc : s) * b_step);
 #pragma unroll
-                        for (int ks = 0; ks < kChunkBytes / 32; ++ks) {
+                        for (int ks = 0; ks < kChunkBytes / 32; ++ks) {   // +2 descriptor units = 32 bytes of K
                             if constexpr (Q4) {
                                 // 32 bytes = 16 codes: two steps per block, each block into its own columns
                                 const uint32_t blk = (uint32_t)(kc * 2 + (ks >> 1));
-                                tc_mma<I8>(d_tmem + blk * (uint32_t)a.ncols, smem_desc_sw128(a_addr + ks * 32), smem_desc_sw128(b_addr + ks * 32),
-                                           idesc, (ks & 1) ? 1u : 0u);
+                                tc_mma<I8>(d_tmem + blk * ncols, da + (uint64_t)(ks * 2), db + (uint64_t)(ks * 2), idesc, (ks & 1) ? 1u : 0u);
                             } else {
-                                tc_mma<I8>(d_tmem, smem_desc_sw128(a_addr + ks * 32), smem_desc_sw128(b_addr + ks * 32), idesc,
-                                           (kc > 0 || ks > 0) ? 1u : 0u);
+                                tc_mma<I8>(d_tmem, da + (uint64_t)(ks * 2), db + (uint64_t)(ks * 2), idesc, (ks > 0) ? 1u : (kc > 0 ? 1u : 0u));
                             }
                         }
                         tc_commit(&empty[s]);   // frees the stage when these MMAs have read it
+                        if (++s == S) { s = 0; ph ^= 1u; }
                     }
                     if (!ok) break;
                     tc_commit(&tfull[acc]);     // accumulator complete
@@ -556,15 +571,14 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             // memory, and writes four operand stages of 64 f16 each.
             const int t = (warp - (2 + kEpiWarps + 1)) * 32 + lane;
             const __half2 off2 = __floats2half2_rn(1032.0f, 1032.0f);
-            uint32_t g = 0;
+            int s = 0, rs = 0;
+            uint32_t ph = 0, rph = 0;
             for (int it = 0; it < n_iters && !*abort_s; ++it) {
-                const int rs = it % kRawStages;
-                if (!mbar_wait(&rfull[rs], (uint32_t)(it / kRawStages) & 1u, abort_s)) break;
+                if (!mbar_try_wait(&rfull[rs], rph) && !mbar_wait(&rfull[rs], rph, abort_s)) break;
                 const unsigned char* raw = sRaw + (size_t)rs * kRawStageBytes + (size_t)t * kChunkBytes;
                 bool ok = true;
-                for (int kc = 0; kc < 4; ++kc, ++g) {
-                    const int s = g % S;
-                    if (!mbar_wait(&empty[s], ((g / S) & 1u) ^ 1u, abort_s)) { ok = false; break; }
+                for (int kc = 0; kc < 4; ++kc) {
+                    if (!mbar_try_wait(&empty[s], ph ^ 1u) && !mbar_wait(&empty[s], ph ^ 1u, abort_s)) { ok = false; break; }
                     unsigned char* dst = sA + (size_t)s * kTileRows * kChunkBytes + (size_t)t * kChunkBytes;
                     // 32 raw bytes = two 16-byte chunks (2kc, 2kc+1), each one block of 32 codes
 #pragma unroll
@@ -591,10 +605,12 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&full[s]);
+                    if (++s == S) { s = 0; ph ^= 1u; }
                 }
                 if (!ok) break;
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&rempty[rs]);
+                if (++rs == kRawStages) { rs = 0; rph ^= 1u; }
             }
         } else if (a.filtered && warp == 2 + kEpiWarps) {
             // ---------------- threshold refresher ----------------
