@@ -930,10 +930,11 @@ cudaError_t launch_mma_topk(cudaStream_t stream, int sm_count, MmaState** state,
     // and tensor-memory reads); everything else carries both planes
     // It pays when pairs that pass the filter are rare next to the rows streamed: a pass appends on the order of
     // k * log(rows / k) keys per query, each of which now costs a round trip to L2 for the low plane's dot product.  Measured
-    // on 768-byte cosine rows: 10 M rows, k = 10 wins from 32 queries up (1.8x at 256); k = 100, or 2 M rows, or C5's
-    // k = 50 on 5 M rows lose 3 - 15 %.
+    // on 768-byte cosine rows: 10 M rows, k = 10 wins from 64 queries up (1.6x at 256) and loses 2 - 3 % up to 32, where the
+    // second plane's columns cost the tensor core nothing (an MMA of up to 128 columns takes the same 67 cycles); k = 100,
+    // or 2 M rows, or C5's k = 50 on 5 M rows lose 3 - 15 %.
     const double rows_per_append = (double)nrows / ((double)a.k * log2((double)nrows / (double)a.k + 2.0));
-    const int hi_first = (i8 && filtered && !(a.metric == MANTA_B200_METRIC_L2_DISTANCE && a.order == MANTA_B200_ORDER_LARGEST) &&
+    const int hi_first = (a.nq > 32 && i8 && filtered && !(a.metric == MANTA_B200_METRIC_L2_DISTANCE && a.order == MANTA_B200_ORDER_LARGEST) &&
                           rows_per_append >= (a.nq > kMmaCols / 2 ? 8000.0 : 30000.0))
                              ? 1 : 0;
     const int group = hi_first ? kMmaCols : mma_group_queries(cv);
@@ -990,8 +991,10 @@ cudaError_t launch_mma_topk(cudaStream_t stream, int sm_count, MmaState** state,
         ka.kchunks = kchunks;
         ka.stages = stages;
         ka.b_resident = b_resident;
-        // Four epilogue warps per quadrant pay off when a tile carries many 16-query chunks and few K chunks.
-        ka.epi_subs = (qn >= 96 && kchunks <= 4) ? 4 : 2;
+        // Four epilogue warps per quadrant pay off when a tile carries many 16-query chunks and few K chunks, and for f16
+        // rows from 48 queries up (measured: C2 0.173 -> 0.165 ms, 256 queries 0.36 -> 0.29 ms); the q8 instantiations with
+        // four are short of registers (96 per thread) and measured slower at 768-byte rows.
+        ka.epi_subs = ((qn >= 96 && kchunks <= 4) || (!i8 && !q4 && qn >= 48)) ? 4 : 2;
         ka.metric = a.metric;
         ka.order = a.order;
         ka.k = a.k;
