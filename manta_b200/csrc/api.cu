@@ -100,6 +100,7 @@ struct MantaB200Runtime {
     bool async_static_pending = false;  // a sync == 0 allocation-free pass copied its flags to h_flags[12..15]
     MantaB200LaunchInfo last_launch{};  // configuration of the last pass's scan kernel
     bool ws_dirty = true;  // the selection workspace is not in the all-zero state a fused streaming pass starts from
+    int ws_dirty_nq = 0;   // ... for this many queries (a later pass with fewer queries must not leave the others' state behind)
 };
 
 static void prof_mark(MantaB200Runtime* rt, int which) {
@@ -149,7 +150,8 @@ static int ensure(MantaB200Runtime* rt, DevBuf& b, size_t bytes, char** err) {
     size_t want = bytes + bytes / 4 + 256;
     CU_TRY(cudaMalloc(&b.p, want));
     b.bytes = want;
-    rt->ws_dirty = true;   // fresh memory is not the zeroed workspace a fused streaming pass expects
+    // fresh memory is not the zeroed workspace a fused streaming pass expects: zero all of it once, whatever it is for
+    CU_TRY(cudaMemsetAsync(b.p, 0, want, rt->stream));
     return 0;
 }
 
@@ -718,6 +720,7 @@ static int mma_pass(MantaB200Runtime* rt, const CandView& cv, const void* d_quer
     QueryPrep qp;
     if (prepare_queries(rt, cv, d_queries, nq, ws, 1, &qp, err)) return 1;
     rt->ws_dirty = true;
+    rt->ws_dirty_nq = std::max(rt->ws_dirty_nq, nq);
     MmaArgs m;
     m.cv = cv;
     m.qp = qp;
@@ -776,8 +779,11 @@ static int score_topk_locked(MantaB200Runtime* rt, const MantaB200Candidates* se
     }
     if (streamed) {
         // one launch per group of four queries does everything: query preparation, scan, selection, clean-up
-        if (rt->ws_dirty && reset_ws(rt, ws, nq, err)) return 1;
+        // every query a dirty pass touched, not only the ones of this call: a two-query tensor-core pass followed by a
+        // one-query pass and then a two-query streaming pass must not find the second query's old threshold
+        if (rt->ws_dirty && reset_ws(rt, ws, std::max(nq, rt->ws_dirty_nq), err)) return 1;
         rt->ws_dirty = false;
+        rt->ws_dirty_nq = 0;
         FusedTail tail;
         tail.d_out_ids = d_out_ids;
         tail.d_out_scores = d_out_scores;
@@ -785,6 +791,7 @@ static int score_topk_locked(MantaB200Runtime* rt, const MantaB200Candidates* se
         prof_mark(rt, 0);
         if (stream_rows(rt, cv, d_queries, metric, order, k, 0, cv.rows, ws, nq, &tail, err)) {
             rt->ws_dirty = true;
+            rt->ws_dirty_nq = std::max(rt->ws_dirty_nq, nq);
             return 1;
         }
         prof_mark(rt, 1);
@@ -810,6 +817,7 @@ static int score_topk_locked(MantaB200Runtime* rt, const MantaB200Candidates* se
     cap = (uint32_t)(chunk + k);
     if (ensure_select_ws(rt, nq, cap, nb, &ws, err)) return 1;
     rt->ws_dirty = true;
+    rt->ws_dirty_nq = std::max(rt->ws_dirty_nq, nq);
     if (reset_ws(rt, ws, nq, err)) return 1;
     SelectArgs sa{};
     sa.nq = nq;

@@ -794,7 +794,12 @@ static int mma_group_queries(const CandView& cv) {
 }
 
 bool mma_supported(const CandView& cv, int nq, int metric) {
-    if (nq < 8) return false;               // small batches stream faster on the streaming kernel
+    // From two queries up the contraction beats the streaming kernel on f16 and q8 rows by 2 - 4x (four queries over 10 M x
+    // 768: 4.22 ms streamed, 1.12 ms here; the streaming kernel pays its dp4a work once per query, an MMA of up to 128
+    // columns costs the same 67 cycles whatever the column count).  One query stays on the streaming kernel (one launch
+    // per step, no start-up).  q4 rows pass through the converter warps, which bound the pass at about 1.35 ms per 12.5 M
+    // rows: worth it from eight queries.
+    if (nq < (cv.layout == MANTA_B200_LAYOUT_Q4_B32_F16 ? 8 : 2)) return false;
     if (cv.rows < kTileRows) return false;
     if (((uintptr_t)cv.data & 15) || (cv.row_bytes & 15)) return false;
     if (cv.layout == MANTA_B200_LAYOUT_Q4_B32_F16) {
