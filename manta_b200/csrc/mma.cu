@@ -937,10 +937,13 @@ cudaError_t launch_mma_topk(cudaStream_t stream, int sm_count, MmaState** state,
     // k * log(rows / k) keys per query, each of which now costs a round trip to L2 for the low plane's dot product.  Measured
     // on 768-byte cosine rows: 10 M rows, k = 10 wins from 64 queries up (1.6x at 256) and loses 2 - 3 % up to 32, where the
     // second plane's columns cost the tensor core nothing (an MMA of up to 128 columns takes the same 67 cycles); k = 100,
-    // or 2 M rows, or C5's k = 50 on 5 M rows lose 3 - 15 %.
+    // or 2 M rows, or C5's k = 50 on 5 M rows lose 3 - 15 %.  The more the second plane costs, the denser the appends may
+    // be: up to 64 queries it costs nothing (threshold 30,000 rows per append), up to 128 it doubles the MMA time (8,000:
+    // 128 queries, k = 50 over 10 M rows 2.11 -> 1.76 ms), beyond that it costs a second pass (3,000: 256 queries, k = 100
+    // 4.42 -> 3.09 ms).
     const double rows_per_append = (double)nrows / ((double)a.k * log2((double)nrows / (double)a.k + 2.0));
     const int hi_first = (a.nq > 32 && i8 && filtered && !(a.metric == MANTA_B200_METRIC_L2_DISTANCE && a.order == MANTA_B200_ORDER_LARGEST) &&
-                          rows_per_append >= (a.nq > kMmaCols / 2 ? 8000.0 : 30000.0))
+                          rows_per_append >= (a.nq > kMmaCols / 2 ? 3000.0 : a.nq > kMmaCols / 4 ? 8000.0 : 30000.0))
                              ? 1 : 0;
     const int group = hi_first ? kMmaCols : mma_group_queries(cv);
     int observe = (a.k + grid * 4 - 1) / (grid * 4);
