@@ -138,9 +138,10 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     uint32_t* thr_s = (uint32_t*)(hdr_s + kMmaCols);
     uint32_t* bmax_s = thr_s + kMmaCols;                 // [qn][4]: maxima of the current tile per epilogue warp
     uint32_t* pub_s = bmax_s + kMmaCols * 4;             // [qn][4][kBucketSlots]: last published values
-    float* zq_s = (float*)(pub_s + kMmaCols * 4 * kBucketSlots);      // [kMmaCols]: pre-filter bound per query (+inf past qn)
-    float* wq_s = zq_s + kMmaCols;                                    // [kMmaCols]: l2 only, weight of ||row||^2 in the bound
-    float* lo_s = wq_s + kMmaCols;                                    // [kMmaCols]: hi_first only, norm of the query's low plane (a shade high)
+    // [kMmaCols] pairs: .x pre-filter bound per query (+inf past qn), .y (hi_first only) norm of the query's low plane, a
+    // shade high -- side by side so that the filter fetches both with one shared-memory read
+    float2* zl_s = (float2*)(pub_s + kMmaCols * 4 * kBucketSlots);
+    float* wq_s = (float*)(zl_s + kMmaCols);                          // [kMmaCols]: l2 only, weight of ||row||^2 in the bound
 
     const int64_t nrows = a.row_end - a.row_begin;
     const int n_tiles = (int)((nrows + kTileRows - 1) / kTileRows);
@@ -171,7 +172,7 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     }
     for (int j = threadIdx.x; j < a.qn; j += blockDim.x) {
         hdr_s[j] = a.headers[a.q0 + j];
-        zq_s[j] = -INFINITY;   // no bound yet: every chunk takes the exact path
+        zl_s[j].x = -INFINITY;   // no bound yet: every chunk takes the exact path
         {
             // l2: 1 / (2 s_lo) for q8 (the filter works on T = dot / (row scale * s_lo)), 1/2 for f16, a shade low
             const float s2 = I8 ? 2.0f * hdr_s[j].s_lo : 2.0f;
@@ -184,11 +185,11 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         }
     }
     for (int j = a.qn + threadIdx.x; j < kMmaCols; j += blockDim.x) {   // padding columns never pass
-        zq_s[j] = INFINITY;
+        zl_s[j].x = INFINITY;
         wq_s[j] = 0.0f;
     }
     if constexpr (I8) {
-        for (int j = threadIdx.x; j < kMmaCols; j += blockDim.x) lo_s[j] = (a.hi_first && j < a.qn) ? a.lo_norms[j] : 0.0f;
+        for (int j = threadIdx.x; j < kMmaCols; j += blockDim.x) zl_s[j].y = (a.hi_first && j < a.qn) ? a.lo_norms[j] : 0.0f;
     }
     if (warp == 1) tmem_alloc(tmem_slot, 512);
     tc_fence_before();
@@ -360,10 +361,11 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 // row factor of the pre-filter; NaN for rows past the end makes every comparison false
                 float rowc = __int_as_float(0x7fc00000);
                 if (rv) rowc = (METRIC == MANTA_B200_METRIC_COSINE) ? rinv : (I8 ? sd : 1.0f);
-                // |T_f32 - T| and the 254 * s_lo != s_hi mismatch are below 4e-7 * 254 * |I_hi|, |I_hi| <= 127^2 * cols
-                const float srow = I8 ? rowc * (4e-7f * 254.0f * 16129.0f * (float)a.cv.cols) : 0.0f;
+                // |T_f32 - T| and the 254 * s_lo != s_hi mismatch (and, high planes first, the rounding of 254 * row factor) are below 5e-7 * 254 * |I_hi|, |I_hi| <= 127^2 * cols
+                const float srow = I8 ? rowc * (5e-7f * 254.0f * 16129.0f * (float)a.cv.cols) : 0.0f;
                 // "smallest" orders compare -score; the smallest l2 distance asks for a LARGE dot product, see below
                 const float rowcs = kL2 ? rowc : sign * rowc;
+                const float rowcs254 = __fmul_rn(rowcs, 254.0f);
                 // l2: ||row||^2 as the filter adds it to the per-query constant
                 float dn2row = 0.0f;
                 if constexpr (kL2) dn2row = I8 ? __fmul_rn(__fmul_rn(sd, sd), (float)(int)stat) : __uint_as_float(stat);
@@ -437,23 +439,28 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         // rounding of s_lo itself, z is lowered by a few ulps, so the test can only pass too often.
                         // Five arithmetic instructions per score; almost every chunk ends here.
                         uint32_t hit = 0;
+                        if (I8 && hf) {
+                            // high planes first: T's upper bound, 254 folded into the row factor (its rounding is inside srow)
 #pragma unroll
-                        for (int jj = 0; jj < 16; ++jj) {
-                            float t, slack = srow;
-                            if constexpr (I8) {
-                                if (hf) {
-                                    t = __fmul_rn((float)(int)vh[jj], 254.0f);
-                                    slack = __fmaf_rn(lo_s[c0 + jj], rslack, srow);
-                                } else {
-                                    t = __fmaf_rn((float)(int)vh[jj], 254.0f, (float)(int)vl[jj]);
-                                }
-                            } else {
-                                t = __uint_as_float(vh[jj]);
+                            for (int jj = 0; jj < 16; ++jj) {
+                                const float2 zl = zl_s[c0 + jj];
+                                float rhs = zl.x;
+                                if constexpr (kL2) rhs = __fmaf_rn(dn2row, wq_s[c0 + jj], rhs);
+                                hit |= (__fmaf_rn((float)(int)vh[jj], rowcs254, __fmaf_rn(zl.y, rslack, srow)) >= rhs) ? (1u << jj) : 0u;
                             }
-                            // l2 (smallest): dist <= B  <=>  dot >= (||q||^2 - B^2 + ||row||^2) / 2, in the units of T
-                            float rhs = zq_s[c0 + jj];
-                            if constexpr (kL2) rhs = __fmaf_rn(dn2row, wq_s[c0 + jj], rhs);
-                            hit |= (__fmaf_rn(t, rowcs, slack) >= rhs) ? (1u << jj) : 0u;
+                        } else {
+#pragma unroll
+                            for (int jj = 0; jj < 16; ++jj) {
+                                float t;
+                                if constexpr (I8)
+                                    t = __fmaf_rn((float)(int)vh[jj], 254.0f, (float)(int)vl[jj]);
+                                else
+                                    t = __uint_as_float(vh[jj]);
+                                // l2 (smallest): dist <= B  <=>  dot >= (||q||^2 - B^2 + ||row||^2) / 2, in the units of T
+                                float rhs = zl_s[c0 + jj].x;
+                                if constexpr (kL2) rhs = __fmaf_rn(dn2row, wq_s[c0 + jj], rhs);
+                                hit |= (__fmaf_rn(t, rowcs, srow) >= rhs) ? (1u << jj) : 0u;
+                            }
                         }
                         myhit = hit;
                         hit = __reduce_or_sync(0xffffffffu, hit);
@@ -506,7 +513,7 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                                             // no bound yet, nothing is appended: the score with the low plane at its worst
                                             // (finished by the same function, which is monotone in I_lo) is a valid lower
                                             // bound of the row's score and so of the bucket maximum
-                                            const int worst = (int)ceilf(__fmul_rn(lo_s[cg + jj], rnorm)) + 1;
+                                            const int worst = (int)ceilf(__fmul_rn(zl_s[cg + jj].y, rnorm)) + 1;
                                             l4[jj] = (uint32_t)((rowcs >= 0.0f) ? -worst : worst);
                                             need |= 1u << jj;
                                             continue;
@@ -715,7 +722,7 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                             }
                         }
                     }
-                    zq_s[jj] = c;
+                    zl_s[jj].x = c;
                 }
                 allset = __all_sync(0xffffffffu, allset);
                 if (allset && lane == 0) *thr_ready_s = 1u;
