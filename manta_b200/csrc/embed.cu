@@ -116,23 +116,89 @@ __global__ void __launch_bounds__(kEmbThreads) embed_pool_first_kernel(const __h
     float pooled[kEmbColsPerThread];
     double ss = 0.0;
     const float inv = count > 0 ? __fdiv_rn(1.0f, (float)count) : 0.0f;
+    if ((out_dim & 7) == 0) {
+        // The [1, dim] x [dim, out_dim] product, split over the warps by k: warp w takes k = w, w + 8, ...; a lane owns eight
+        // consecutive columns per group of 256 (one 16-byte load per k and group, a warp's loads contiguous), eight k in
+        // flight: 128 bytes per thread, 32 KB per SM.  The eight partial rows meet in shared memory and are added in warp
+        // order.  (One column per thread with a serial walk over k kept only eight 2-byte loads in flight per thread, and
+        // four 8-byte loads were hardly better: 50 us of latency per batch element either way.)
+        float* part = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(wts + seq) + 15) & ~(uintptr_t)15);   // [8][out_dim], 16-byte aligned
+        const int lane = tid & 31, warp = tid >> 5;
+        constexpr int kWarps = kEmbThreads / 32;
+        constexpr int kGroups = kEmbThreads * kEmbColsPerThread / 256;   // column groups of 256 at the widest projection
+        float acc[kGroups][8];
 #pragma unroll
-    for (int j = 0; j < kEmbColsPerThread; ++j) {
-        const int c = tid + j * kEmbThreads;
-        float acc = 0.0f;
-        if (c < out_dim) {
-            int k = 0;
-            for (; k + 8 <= dim; k += 8) {
-                float p[8];
+        for (int g = 0; g < kGroups; ++g)
 #pragma unroll
-                for (int u = 0; u < 8; ++u) p[u] = __half2float(proj[(size_t)(k + u) * out_dim + c]);
+            for (int e = 0; e < 8; ++e) acc[g][e] = 0.0f;
+        const int groups = (out_dim + 255) / 256;
+        for (int k0 = warp; k0 < dim; k0 += 8 * kWarps) {
 #pragma unroll
-                for (int u = 0; u < 8; ++u) acc = fmaf(hsum[k + u], p[u], acc);
+            for (int g = 0; g < kGroups; ++g) {
+                if (g < groups) {
+                    const int c = g * 256 + lane * 8;
+                    uint4 pv[8];
+                    float hv[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const int k = k0 + u * kWarps;
+                        const bool in = k < dim && c < out_dim;
+                        pv[u] = in ? __ldg(reinterpret_cast<const uint4*>(proj + (size_t)k * out_dim + c)) : make_uint4(0u, 0u, 0u, 0u);
+                        hv[u] = (k < dim) ? hsum[k] : 0.0f;
+                    }
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const uint32_t w4[4] = {pv[u].x, pv[u].y, pv[u].z, pv[u].w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float2 p2 = __half22float2(*reinterpret_cast<const __half2*>(&w4[e]));
+                            acc[g][2 * e] = fmaf(hv[u], p2.x, acc[g][2 * e]);
+                            acc[g][2 * e + 1] = fmaf(hv[u], p2.y, acc[g][2 * e + 1]);
+                        }
+                    }
+                }
             }
-            for (; k < dim; ++k) acc = fmaf(hsum[k], __half2float(proj[(size_t)k * out_dim + c]), acc);
         }
-        pooled[j] = __fmul_rn(acc, inv);
-        ss = __dadd_rn(ss, __dmul_rn((double)pooled[j], (double)pooled[j]));  // columns past out_dim hold 0
+#pragma unroll
+        for (int g = 0; g < kGroups; ++g) {
+            const int c = g * 256 + lane * 8;
+            if (g < groups && c < out_dim) {
+                float4* dst = reinterpret_cast<float4*>(part + (size_t)warp * out_dim + c);
+                dst[0] = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
+                dst[1] = make_float4(acc[g][4], acc[g][5], acc[g][6], acc[g][7]);
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int j = 0; j < kEmbColsPerThread; ++j) {
+            const int c = tid + j * kEmbThreads;
+            float a = 0.0f;
+            if (c < out_dim) {
+#pragma unroll
+                for (int w = 0; w < kEmbThreads / 32; ++w) a = __fadd_rn(a, part[(size_t)w * out_dim + c]);
+            }
+            pooled[j] = __fmul_rn(a, inv);
+            ss = __dadd_rn(ss, __dmul_rn((double)pooled[j], (double)pooled[j]));  // columns past out_dim hold 0
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < kEmbColsPerThread; ++j) {
+            const int c = tid + j * kEmbThreads;
+            float acc = 0.0f;
+            if (c < out_dim) {
+                int k = 0;
+                for (; k + 8 <= dim; k += 8) {
+                    float p[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) p[u] = __half2float(proj[(size_t)(k + u) * out_dim + c]);
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) acc = fmaf(hsum[k + u], p[u], acc);
+                }
+                for (; k < dim; ++k) acc = fmaf(hsum[k], __half2float(proj[(size_t)k * out_dim + c]), acc);
+            }
+            pooled[j] = __fmul_rn(acc, inv);
+            ss = __dadd_rn(ss, __dmul_rn((double)pooled[j], (double)pooled[j]));  // columns past out_dim hold 0
+        }
     }
     const float norm = WEIGHTED ? 0.0f : __double2float_rn(__dsqrt_rn(block_sum(ss, s_part)));   // 0: values stay as they are
 #pragma unroll
@@ -254,9 +320,9 @@ cudaError_t launch_embed_pooled(cudaStream_t st, const void* table_f16, int voca
                                 uint32_t* d_bad_flag) {
     if (out_dim > kEmbThreads * kEmbColsPerThread) return cudaErrorInvalidValue;
     const bool weighted = order != 0 && d_token_norms != nullptr;
-    const size_t smem = weighted ? (size_t)dim * 4 + (size_t)seq * 12
-                        : (order == 0) ? (size_t)dim * 4 + (size_t)seq * 4
-                                       : (size_t)kEmbRows * dim * 4 + (size_t)kEmbRows * out_dim * 4 + (size_t)seq * 4;
+    // pool-first kernel: token-row sum [dim], kept tokens, their positions and weights ([seq] each), eight partial rows
+    const size_t smem = (weighted || order == 0) ? (size_t)dim * 4 + (size_t)seq * 12 + (size_t)(kEmbThreads / 32) * out_dim * 4 + 16
+                                                 : (size_t)kEmbRows * dim * 4 + (size_t)kEmbRows * out_dim * 4 + (size_t)seq * 4;
     constexpr size_t kMaxSmem = 220 * 1024;
     if (smem > kMaxSmem) return cudaErrorInvalidValue;
     static bool configured[64] = {};
