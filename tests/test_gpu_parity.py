@@ -381,7 +381,7 @@ def test_a_later_pass_never_sees_another_querys_old_threshold(rt):
     """A tensor-core pass leaves thresholds and fill counts behind for ALL its queries; a streaming pass over fewer
     queries cleans up, and a streaming pass over more queries after that must still start from a clean workspace."""
     rng = np.random.default_rng(2024)
-    xf = make_rows(rng, 30000, 64)
+    xf = make_rows(rng, 40000, 64)
     cf, _ = _bind(rt, "f16", xf)
     xq = make_rows(rng, 30000, 64, normalised=False)
     cq, deq = _bind(rt, "q4", xq)
