@@ -280,7 +280,18 @@ def run_ours(args, wl: Workload):
         import torch.distributed as dist_mod
 
         dist = dist_mod
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        # stdout carries the one JSON line: whatever the communicator set-up prints there (NCCL's version banner) is sent
+        # to stderr for the duration of the set-up
+        sys.stdout.flush()
+        saved_stdout = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+            dist.barrier()   # the first collective creates the communicator
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved_stdout, 1)
+            os.close(saved_stdout)
     native.load()
     # One "lane" = a runtime (stream + scratch) with its own result buffers.  With more than one GPU two lanes
     # alternate steps, so that the selection, the all-gather and the merge of one step overlap the scan of the
