@@ -82,7 +82,7 @@ struct MantaB200Runtime {
     std::mutex mu;
     MantaB200Stats stats{};
     // grow-only device buffers
-    DevBuf queries, headers, qf32, plane_hi, plane_lo, pool, count, thr, bucket, flags, out_ids, out_scores, misc, embed_flag, batch_in, tok_norms;
+    DevBuf queries, headers, qf32, plane_hi, plane_lo, pool, count, thr, bucket, flags, out_ids, out_scores, misc, embed_flag, batch_in, tok_norms, lo_norm;
     // pinned host staging
     void* h_stage = nullptr;
     size_t h_stage_bytes = 0;
@@ -227,7 +227,7 @@ int manta_b200_runtime_destroy(MantaB200Runtime* rt, char** err) {
     cudaSetDevice(rt->device);
     cudaError_t e = cudaStreamSynchronize(rt->stream);
     DevBuf* bufs[] = {&rt->queries, &rt->headers, &rt->qf32, &rt->plane_hi, &rt->plane_lo, &rt->pool, &rt->count,
-                      &rt->thr, &rt->bucket, &rt->flags, &rt->out_ids, &rt->out_scores, &rt->misc, &rt->embed_flag, &rt->batch_in, &rt->tok_norms};
+                      &rt->thr, &rt->bucket, &rt->flags, &rt->out_ids, &rt->out_scores, &rt->misc, &rt->embed_flag, &rt->batch_in, &rt->tok_norms, &rt->lo_norm};
     for (DevBuf* b : bufs) free_buf(*b);
     mma_state_destroy(rt->mma);
     for (int i = 0; i < rt->prof_created; ++i) cudaEventDestroy(rt->prof_ev[i]);
@@ -574,7 +574,8 @@ static int prepare_queries(MantaB200Runtime* rt, const CandView& cv, const void*
     if (ensure(rt, rt->qf32, (size_t)nq * cv.cols * 4, err)) return 1;
     if (ensure(rt, rt->plane_hi, (size_t)nq * ps, err)) return 1;
     if (ensure(rt, rt->plane_lo, (size_t)nq * ps, err)) return 1;
-    launch_query_prep(rt->stream, d_queries, nq, cv.cols, cv.layout, ps, (QueryHeader*)rt->headers.p, (float*)rt->qf32.p,
+    if (ensure(rt, rt->lo_norm, (size_t)nq * 4, err)) return 1;
+    launch_query_prep(rt->stream, d_queries, nq, cv.cols, cv.layout, ps, (float*)rt->lo_norm.p, (QueryHeader*)rt->headers.p, (float*)rt->qf32.p,
                       (int8_t*)rt->plane_hi.p, (int8_t*)rt->plane_lo.p, ws, reset_ws);
     rt->stats.kernel_launches++;
     CU_TRY(cudaGetLastError());
@@ -583,6 +584,8 @@ static int prepare_queries(MantaB200Runtime* rt, const CandView& cv, const void*
     qp->plane_hi = (const int8_t*)rt->plane_hi.p;
     qp->plane_lo = (const int8_t*)rt->plane_lo.p;
     qp->plane_stride = ps;
+    qp->lo_norm = (const float*)rt->lo_norm.p;
+    qp->queries_f16 = d_queries;
     qp->nq = nq;
     return 0;
 }

@@ -15,10 +15,12 @@ struct QueryPrep {
     const int8_t* plane_hi;      // [nq][plane_stride]  (q8/q4 candidates)
     const int8_t* plane_lo;      // [nq][plane_stride]
     int plane_stride;            // bytes per query in a plane (multiple of 32)
+    const float* lo_norm;        // [nq] norm of the low plane, rounded up a shade (q8/q4 candidates)
+    const void* queries_f16;     // [nq][cols] the queries as they came
     int nq;
 };
 
-void launch_query_prep(cudaStream_t st, const void* d_queries_f16, int nq, int cols, int layout, int plane_stride,
+void launch_query_prep(cudaStream_t st, const void* d_queries_f16, int nq, int cols, int layout, int plane_stride, float* lo_norm,
                        QueryHeader* headers, float* qf32, int8_t* plane_hi, int8_t* plane_lo, const SelectWs& ws,
                        int reset_ws);
 void launch_row_stats(cudaStream_t st, const CandView& cv, void* stats);

@@ -53,6 +53,8 @@ struct KernelArgs {
     int stages;
     int epi_subs;                 // epilogue warps per tensor-memory quadrant (2 or 4): which instantiation runs
     int b_resident;               // operand B (all K chunks) is loaded once and stays in shared memory
+    int b_second_rows;            // > 0: operand B is read from the query planes themselves and its low planes are a second
+                                  // box of this many rows (map_b2) behind the high planes; 0: one box per chunk
     int metric;
     int order;
     int k;
@@ -111,7 +113,8 @@ __device__ __forceinline__ void score_n(const uint32_t (&vh)[N], const uint32_t 
 // unpack yields pairwise); operand B is built with the same order, and a contraction does not care.
 template <bool I8, int METRIC, int SUBS, bool Q4>
 __global__ void __launch_bounds__(mma_threads(SUBS, Q4), 1)
-mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const KernelArgs a) {
+mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                const __grid_constant__ CUtensorMap map_b2, const KernelArgs a) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int S = a.stages;
@@ -206,8 +209,11 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 if (a.b_resident) {
                     // the query operand fits beside the candidate ring: one load, then only candidates stream
                     mbar_expect_tx(bfull, (uint32_t)a.kchunks * b_stage_bytes);
-                    for (int kc = 0; kc < a.kchunks; ++kc)
+                    for (int kc = 0; kc < a.kchunks; ++kc) {
                         tma_load_2d(sB + (size_t)kc * b_stage_bytes, &map_b, kc * kChunkBytes, 0, bfull);
+                        if (a.b_second_rows > 0)
+                            tma_load_2d(sB + (size_t)kc * b_stage_bytes + (size_t)a.b_second_rows * kChunkBytes, &map_b2, kc * kChunkBytes, 0, bfull);
+                    }
                 }
                 if constexpr (Q4) {
                     // raw tiles: one 128 x 128-byte box of nibbles per tile; the converter warps make the operand stages
@@ -233,7 +239,11 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         if (!mbar_try_wait(&empty[s], ph ^ 1u) && !mbar_wait(&empty[s], ph ^ 1u, abort_s)) { ok = false; break; }
                         mbar_expect_tx(&full[s], stage_tx);
                         tma_load_2d(sA + (size_t)s * kTileRows * kChunkBytes, &map_a, kc * kChunkBytes, row0, &full[s]);
-                        if (!b_res) tma_load_2d(sB + (size_t)s * b_stage_bytes, &map_b, kc * kChunkBytes, 0, &full[s]);
+                        if (!b_res) {
+                            tma_load_2d(sB + (size_t)s * b_stage_bytes, &map_b, kc * kChunkBytes, 0, &full[s]);
+                            if (a.b_second_rows > 0)
+                                tma_load_2d(sB + (size_t)s * b_stage_bytes + (size_t)a.b_second_rows * kChunkBytes, &map_b2, kc * kChunkBytes, 0, &full[s]);
+                        }
                         if (++s == S) { s = 0; ph ^= 1u; }
                     }
                 }
@@ -850,43 +860,44 @@ static cudaError_t make_map(MmaState* st, CUtensorMap* map, const void* base, ui
 
 template <bool I8, int METRIC, int SUBS, bool Q4>
 static cudaError_t launch_scan_subs(MmaState* st, int slot, int grid, size_t smem, cudaStream_t stream, const CUtensorMap& map_a,
-                                    const CUtensorMap& map_b, const KernelArgs& ka, const char** why) {
+                                    const CUtensorMap& map_b, const CUtensorMap& map_b2, const KernelArgs& ka, const char** why) {
     const int idx = slot * 2 + (SUBS == 4 ? 1 : 0);
     if (!st->attr_set[idx]) {
         cudaError_t e = cudaFuncSetAttribute(mma_scan_kernel<I8, METRIC, SUBS, Q4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit);
         if (e != cudaSuccess) { *why = "cudaFuncSetAttribute"; return e; }
         st->attr_set[idx] = true;
     }
-    mma_scan_kernel<I8, METRIC, SUBS, Q4><<<grid, mma_threads(SUBS, Q4), smem, stream>>>(map_a, map_b, ka);
+    mma_scan_kernel<I8, METRIC, SUBS, Q4><<<grid, mma_threads(SUBS, Q4), smem, stream>>>(map_a, map_b, map_b2, ka);
     note_scan_launch("mma_scan_kernel", grid, mma_threads(SUBS, Q4), smem);
     return cudaSuccess;
 }
 
 template <bool I8, int METRIC, bool Q4 = false>
 static cudaError_t launch_scan_one(MmaState* st, int slot, int grid, size_t smem, cudaStream_t stream, const CUtensorMap& map_a,
-                                   const CUtensorMap& map_b, const KernelArgs& ka, const char** why) {
-    if (ka.epi_subs == 4) return launch_scan_subs<I8, METRIC, 4, Q4>(st, slot, grid, smem, stream, map_a, map_b, ka, why);
-    return launch_scan_subs<I8, METRIC, 2, Q4>(st, slot, grid, smem, stream, map_a, map_b, ka, why);
+                                   const CUtensorMap& map_b, const CUtensorMap& map_b2, const KernelArgs& ka, const char** why) {
+    if (ka.epi_subs == 4) return launch_scan_subs<I8, METRIC, 4, Q4>(st, slot, grid, smem, stream, map_a, map_b, map_b2, ka, why);
+    return launch_scan_subs<I8, METRIC, 2, Q4>(st, slot, grid, smem, stream, map_a, map_b, map_b2, ka, why);
 }
 
 // One instantiation per (layout, metric): the epilogue of each is straight-line code for its own metric.
 static cudaError_t launch_scan_variant(MmaState* st, int layout, int metric, int grid, size_t smem, cudaStream_t stream,
-                                       const CUtensorMap& map_a, const CUtensorMap& map_b, const KernelArgs& ka, const char** why) {
+                                       const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_b2, const KernelArgs& ka,
+                                       const char** why) {
     if (layout == MANTA_B200_LAYOUT_Q4_B32_F16) {
         switch (metric) {
-            case MANTA_B200_METRIC_DOT: return launch_scan_one<false, MANTA_B200_METRIC_DOT, true>(st, 6, grid, smem, stream, map_a, map_b, ka, why);
-            case MANTA_B200_METRIC_COSINE: return launch_scan_one<false, MANTA_B200_METRIC_COSINE, true>(st, 7, grid, smem, stream, map_a, map_b, ka, why);
-            default: return launch_scan_one<false, MANTA_B200_METRIC_L2_DISTANCE, true>(st, 8, grid, smem, stream, map_a, map_b, ka, why);
+            case MANTA_B200_METRIC_DOT: return launch_scan_one<false, MANTA_B200_METRIC_DOT, true>(st, 6, grid, smem, stream, map_a, map_b, map_b2, ka, why);
+            case MANTA_B200_METRIC_COSINE: return launch_scan_one<false, MANTA_B200_METRIC_COSINE, true>(st, 7, grid, smem, stream, map_a, map_b, map_b2, ka, why);
+            default: return launch_scan_one<false, MANTA_B200_METRIC_L2_DISTANCE, true>(st, 8, grid, smem, stream, map_a, map_b, map_b2, ka, why);
         }
     }
     const int slot = (layout == MANTA_B200_LAYOUT_Q8_ROW_F32 ? 0 : 3) + metric;
     switch (slot) {
-        case 0: return launch_scan_one<true, MANTA_B200_METRIC_DOT>(st, slot, grid, smem, stream, map_a, map_b, ka, why);
-        case 1: return launch_scan_one<true, MANTA_B200_METRIC_COSINE>(st, slot, grid, smem, stream, map_a, map_b, ka, why);
-        case 2: return launch_scan_one<true, MANTA_B200_METRIC_L2_DISTANCE>(st, slot, grid, smem, stream, map_a, map_b, ka, why);
-        case 3: return launch_scan_one<false, MANTA_B200_METRIC_DOT>(st, slot, grid, smem, stream, map_a, map_b, ka, why);
-        case 4: return launch_scan_one<false, MANTA_B200_METRIC_COSINE>(st, slot, grid, smem, stream, map_a, map_b, ka, why);
-        default: return launch_scan_one<false, MANTA_B200_METRIC_L2_DISTANCE>(st, slot, grid, smem, stream, map_a, map_b, ka, why);
+        case 0: return launch_scan_one<true, MANTA_B200_METRIC_DOT>(st, slot, grid, smem, stream, map_a, map_b, map_b2, ka, why);
+        case 1: return launch_scan_one<true, MANTA_B200_METRIC_COSINE>(st, slot, grid, smem, stream, map_a, map_b, map_b2, ka, why);
+        case 2: return launch_scan_one<true, MANTA_B200_METRIC_L2_DISTANCE>(st, slot, grid, smem, stream, map_a, map_b, map_b2, ka, why);
+        case 3: return launch_scan_one<false, MANTA_B200_METRIC_DOT>(st, slot, grid, smem, stream, map_a, map_b, map_b2, ka, why);
+        case 4: return launch_scan_one<false, MANTA_B200_METRIC_COSINE>(st, slot, grid, smem, stream, map_a, map_b, map_b2, ka, why);
+        default: return launch_scan_one<false, MANTA_B200_METRIC_L2_DISTANCE>(st, slot, grid, smem, stream, map_a, map_b, map_b2, ka, why);
     }
 }
 
@@ -968,17 +979,48 @@ cudaError_t launch_mma_topk(cudaStream_t stream, int sm_count, MmaState** state,
         const int qpad = (qn + 15) / 16 * 16;
         const int ncols = (i8 && !hi_first) ? 2 * qpad : qpad;
         const int lo_off = hi_first ? ncols : qpad;   // hi_first: no row of operand B is a low plane
-        float* d_lo_norms = reinterpret_cast<float*>(st->d_b + (size_t)kMmaCols * kpad);
-        build_b_kernel<<<128, 256, 0, stream>>>(st->d_b, ncols, kpad, cv.layout, a.qp, q0, qn, lo_off, cv.cols, hi_first ? d_lo_norms : nullptr);
-        count_launch();
-        ++*launches;
-        e = cudaGetLastError();
-        if (e != cudaSuccess) { *why = "operand B build launch"; return e; }
+        // Operand B.  f16 and q8 queries are already K-major rows in memory (the queries as they came; the int8 planes of the
+        // query preparation): the tensor maps read them where they lie, rows past the group and bytes past the row come
+        // back as zeros, and two planes are two boxes per chunk.  q4 rows (permuted f16 operand) and rows the TMA cannot
+        // address (pitch or base not a multiple of 16 bytes) go through build_b_kernel as before.
+        const float* d_lo_norms = a.qp.lo_norm ? a.qp.lo_norm + q0 : nullptr;
+        CUtensorMap map_b, map_b2;
+        int b_second_rows = 0;
+        const size_t f16_pitch = (size_t)cv.cols * 2;
+        const bool direct = !q4 && (i8 ? (a.qp.plane_hi != nullptr && a.qp.lo_norm != nullptr)
+                                       : (a.qp.queries_f16 != nullptr && (f16_pitch & 15) == 0 && ((uintptr_t)a.qp.queries_f16 & 15) == 0));
+        if (direct) {
+            if (i8) {
+                const size_t ps = (size_t)a.qp.plane_stride;
+                e = make_map(st, &map_b, a.qp.plane_hi + (size_t)q0 * ps, ps, (uint64_t)qn, ps, (uint32_t)(hi_first ? ncols : qpad), why);
+                if (e != cudaSuccess) return e;
+                if (!hi_first) {
+                    e = make_map(st, &map_b2, a.qp.plane_lo + (size_t)q0 * ps, ps, (uint64_t)qn, ps, (uint32_t)qpad, why);
+                    if (e != cudaSuccess) return e;
+                    b_second_rows = qpad;
+                } else {
+                    map_b2 = map_b;
+                }
+            } else {
+                e = make_map(st, &map_b, (const unsigned char*)a.qp.queries_f16 + (size_t)q0 * f16_pitch, f16_pitch, (uint64_t)qn, f16_pitch,
+                             (uint32_t)ncols, why);
+                if (e != cudaSuccess) return e;
+                map_b2 = map_b;
+            }
+        } else {
+            float* built_norms = reinterpret_cast<float*>(st->d_b + (size_t)kMmaCols * kpad);
+            build_b_kernel<<<128, 256, 0, stream>>>(st->d_b, ncols, kpad, cv.layout, a.qp, q0, qn, lo_off, cv.cols, hi_first ? built_norms : nullptr);
+            count_launch();
+            ++*launches;
+            e = cudaGetLastError();
+            if (e != cudaSuccess) { *why = "operand B build launch"; return e; }
+            if (hi_first) d_lo_norms = built_norms;
+            e = make_map(st, &map_b, st->d_b, (uint64_t)kpad, (uint64_t)ncols, (uint64_t)kpad, (uint32_t)ncols, why);
+            if (e != cudaSuccess) return e;
+            map_b2 = map_b;
+        }
         e = cudaMemsetAsync(st->d_ready, 0, 4, stream);
         if (e != cudaSuccess) { *why = "cudaMemsetAsync(ready)"; return e; }
-        CUtensorMap map_b;
-        e = make_map(st, &map_b, st->d_b, (uint64_t)kpad, (uint64_t)ncols, (uint64_t)kpad, (uint32_t)ncols, why);
-        if (e != cudaSuccess) return e;
 
         const size_t a_stage = (size_t)kTileRows * kChunkBytes, b_stage = (size_t)ncols * kChunkBytes;
         const size_t fixed = 1024 /*alignment slack*/ + 256 /*barriers*/ + sizeof(QueryHeader) * kMmaCols + 4 * kMmaCols +
@@ -1006,6 +1048,7 @@ cudaError_t launch_mma_topk(cudaStream_t stream, int sm_count, MmaState** state,
         ka.kchunks = kchunks;
         ka.stages = stages;
         ka.b_resident = b_resident;
+        ka.b_second_rows = b_second_rows;
         // Four epilogue warps per quadrant pay off when a tile carries many 16-query chunks and few K chunks, and for f16
         // rows from 48 queries up (measured: C2 0.173 -> 0.165 ms, 256 queries 0.36 -> 0.29 ms); the q8 instantiations with
         // four are short of registers (96 per thread) and measured slower at 768-byte rows.
@@ -1022,7 +1065,7 @@ cudaError_t launch_mma_topk(cudaStream_t stream, int sm_count, MmaState** state,
         ka.plane_lo = a.qp.plane_lo ? a.qp.plane_lo + (size_t)q0 * a.qp.plane_stride : nullptr;
         ka.plane_stride = a.qp.plane_stride;
         ka.lo_norms = d_lo_norms;
-        e = launch_scan_variant(st, cv.layout, a.metric, grid, smem, stream, map_a, map_b, ka, why);
+        e = launch_scan_variant(st, cv.layout, a.metric, grid, smem, stream, map_a, map_b, map_b2, ka, why);
         if (e != cudaSuccess) return e;
         count_launch();
         ++*launches;

@@ -17,11 +17,13 @@ namespace mb200 {
 __global__ void __launch_bounds__(256) query_prep_kernel(const __half* __restrict__ queries, int cols, int layout,
                                                          int plane_stride, QueryHeader* __restrict__ headers,
                                                          float* __restrict__ qf32, int8_t* __restrict__ plane_hi,
-                                                         int8_t* __restrict__ plane_lo, SelectWs ws, int reset_ws) {
+                                                         int8_t* __restrict__ plane_lo, float* __restrict__ lo_norm, SelectWs ws,
+                                                         int reset_ws) {
     const int q = blockIdx.x;
     const int tid = threadIdx.x;
     const __half* src = queries + (size_t)q * cols;
     __shared__ float s_red[8];
+    __shared__ int s_lsq[8];
     __shared__ float s_amax;
     __shared__ float s_sh, s_sl;
 
@@ -66,6 +68,7 @@ __global__ void __launch_bounds__(256) query_prep_kernel(const __half* __restric
     if (layout != MANTA_B200_LAYOUT_F16) {
         const float sh = s_sh, sl = s_sl;
         const bool zero = !(s_amax > 0.0f);
+        int lsq = 0;   // sum of the squared low-plane codes of this thread's elements
         for (int c = tid; c < plane_stride; c += blockDim.x) {
             // c indexes the plane in storage order; e is the query element stored there
             int e = c;
@@ -89,6 +92,17 @@ __global__ void __launch_bounds__(256) query_prep_kernel(const __half* __restric
             }
             plane_hi[(size_t)q * plane_stride + c] = hi;
             plane_lo[(size_t)q * plane_stride + c] = lo;
+            lsq += (int)lo * (int)lo;
+        }
+        // norm of the low plane, a shade high: what the plane can add to a dot product is at most this times the norm of
+        // the row's codes (the tensor-core pass bounds it that way when it contracts the high planes only)
+        lsq = __reduce_add_sync(0xffffffffu, lsq);
+        if ((tid & 31) == 0) s_lsq[tid >> 5] = lsq;
+        __syncthreads();
+        if (tid == 0 && lo_norm != nullptr) {
+            int tot = 0;
+            for (int w = 0; w < 8; ++w) tot += s_lsq[w];
+            lo_norm[q] = sqrtf((float)tot) * 1.000002f;
         }
     }
     if (layout != MANTA_B200_LAYOUT_F16) {
@@ -299,11 +313,11 @@ cudaError_t launch_ws_reset(cudaStream_t st, const SelectWs& ws, int nq, uint32_
 }
 
 // ---- launchers ----------------------------------------------------------------------------------------------
-void launch_query_prep(cudaStream_t st, const void* d_queries_f16, int nq, int cols, int layout, int plane_stride,
+void launch_query_prep(cudaStream_t st, const void* d_queries_f16, int nq, int cols, int layout, int plane_stride, float* lo_norm,
                        QueryHeader* headers, float* qf32, int8_t* plane_hi, int8_t* plane_lo, const SelectWs& ws,
                        int reset_ws) {
     query_prep_kernel<<<nq, 256, 0, st>>>((const __half*)d_queries_f16, cols, layout, plane_stride, headers, qf32,
-                                           plane_hi, plane_lo, ws, reset_ws);
+                                           plane_hi, plane_lo, lo_norm, ws, reset_ws);
     count_launch();
 }
 
