@@ -625,11 +625,11 @@ def run_ours(args, wl: Workload):
         algo_bytes = shard_rows * wl.row_bytes()
         achieved = algo_bytes / (scan_ms_per_pass * 1e-3) / 1e9
         # DRAM traffic per launch is not read live: it is the dram__bytes_read + dram__bytes_write of one ncu capture of
-        # the same kernel on a 2 M-row case (1.5480e9 B for 2e6 rows), scaled by rows -- every row is read exactly once,
-        # so traffic grows in proportion.
+        # the same kernel on a 2 M-row case (1.5521e9 B read + 4.0e6 B written for 2e6 rows), scaled by rows -- every row
+        # is read exactly once, so traffic grows in proportion.
         traffic, traffic_source = None, None
-        if wl.layout == "q8" and wl.metric == "cosine" and wl.cols == 768 and nq <= 4:
-            traffic = shard_rows * (1.544046e9 + 3.98e6) / 2e6
+        if wl.layout == "q8" and wl.metric == "cosine" and wl.cols == 768 and nq == 1:
+            traffic = shard_rows * (1.552110e9 + 4.0e6) / 2e6
             traffic_source = "from_profile: profiles/stream_scan_q8_cosine_2Mx768.md (ncu, 2 M rows), scaled by rows; not measured in this run"
         value = args.steps * nq / (total_ms * 1e-3)
         line = {
