@@ -1,6 +1,8 @@
 // Streaming scoring kernel: 1, 2 or 4 queries against packed candidate rows, every stored byte read once.
 //
-// Data movement.  A warp owns "tiles" of R consecutive rows (R a power of two, 1..32) and strides over the row range.
+// Data movement.  A warp works on "tiles" of R consecutive rows (R a power of two, 1..32).  Short passes deal the tiles
+// round robin; long ones give every warp runs of eight consecutive tiles, and a fused single-query pass over f16 or q8
+// rows hands out its last quarter on demand from a device counter (see the kernel).
 // The tile's bytes are contiguous in HBM; the 32 lanes copy them 16 bytes at a time, lane after lane, with
 // asynchronous copies (cp.async.cg, no registers held in flight) into the warp's own ring in shared memory (two
 // stages with 16 warps per block, three with 8), so every global access is a fully coalesced 512-byte warp request.
