@@ -1,14 +1,18 @@
-// tcgen05 tensor-core scoring pass: a batch of queries against packed q8 or f16 candidate rows as a dense
-// contraction.  One persistent CTA per SM; candidate tiles of 128 rows stream through a TMA-fed shared-memory
-// ring, tcgen05.mma accumulates [128 rows x N columns] in tensor memory (int32 for q8: columns are the two int8
-// planes of every query; f32 for f16), and four epilogue warps read the accumulators back (tcgen05.ld), finish
-// the scores with the same epilogue functions as the streaming kernel and filter them into the top-k pools.
+// tcgen05 tensor-core scoring pass: a batch of queries (two or more over f16 / q8 rows, eight or more over q4 rows)
+// against packed candidate rows as a dense contraction.  One persistent CTA per SM; candidate tiles of 128 rows stream
+// through a TMA-fed shared-memory ring, tcgen05.mma accumulates [128 rows x N columns] in tensor memory (int32 for q8:
+// the columns are the high int8 planes of up to 256 queries, or both planes of up to 128; f32 for f16 and q4), and the
+// epilogue warps read the accumulators back (tcgen05.ld), finish the scores with the same epilogue functions as the
+// streaming kernel and filter them into the top-k pools.  Operand B is read where the queries already lie (the f16 rows
+// as they came, the int8 planes of the query preparation); q4 rows get a built, permuted f16 operand.
 //
-// Warp roles (19 warps): 0 = TMA producer, 1 = MMA issuer (owns the tensor-memory allocation), 2..17 = epilogue
-// (four per 32-lane quadrant of tensor memory, each taking every fourth 16-query chunk), 18 = threshold refresher.
-// The epilogue is latency-bound (tensor-memory reads, dependent arithmetic), so it is spread over as many warps as
-// the register file allows: 608 threads x 104 registers.  To fit, the exact scoring of a chunk that passes the
-// cheap filter re-reads its accumulators four queries at a time instead of keeping sixteen finished scores live.
+// Warp roles: 0 = TMA producer, 1 = MMA issuer (owns the tensor-memory allocation), then SUBS = 2 or 4 epilogue warps per
+// 32-lane quadrant of tensor memory (each taking every SUBS-th 16-query chunk), one threshold refresher, and for q4 rows
+// four converter warps: 11 to 19 warps.  With four epilogue warps per quadrant (608 threads x 96 registers) the exact
+// scoring of a chunk that passes the cheap filter re-reads its accumulators four queries at a time instead of keeping
+// sixteen finished scores live.  The producer, the issuer and the converters are single threads (or one thread per row)
+// on their own latency chains: their loops count stages and phases instead of dividing, and build descriptors from one
+// base -- the issuer's own scalar instructions were what the tensor core used to wait for.
 //
 // Every wait in this file is bounded: a wait that runs out sets the abort flag of the CTA and the time-out flag
 // of the pass, every role leaves its loop, tensor memory is released and the kernel returns; the host then
