@@ -898,8 +898,6 @@ int manta_b200_score_topk(MantaB200Runtime* rt, const MantaB200Candidates* set, 
     const size_t qbytes = (size_t)nq * set->cv.cols * 2;
     const size_t obytes = (size_t)nq * k * 4;
     if (ensure(rt, rt->queries, qbytes, err)) return 1;
-    if (ensure(rt, rt->out_ids, obytes, err)) return 1;
-    if (ensure(rt, rt->out_scores, obytes, err)) return 1;
     const size_t qpad = (qbytes + 255) / 256 * 256, opad = (obytes + 255) / 256 * 256;
     if (ensure_host(rt, qpad + 2 * opad, err)) return 1;
     char* hq = (char*)rt->h_stage;
@@ -908,12 +906,11 @@ int manta_b200_score_topk(MantaB200Runtime* rt, const MantaB200Candidates* set, 
     memcpy(hq, queries, qbytes);
     CU_TRY(cudaMemcpyAsync(rt->queries.p, hq, qbytes, cudaMemcpyHostToDevice, rt->stream));
     rt->stats.h2d_bytes += qbytes;
-    int rc = score_topk_locked(rt, set, metric, order, rt->queries.p, nq, k, (int32_t*)rt->out_ids.p,
-                               (float*)rt->out_scores.p, 1, err);
+    // The selection writes ids and scores straight into the pinned staging buffer (device-addressable host memory): the
+    // synchronisation that reads the pass's flags is also the one that makes the results visible, no copy back, no second
+    // synchronisation.
+    int rc = score_topk_locked(rt, set, metric, order, rt->queries.p, nq, k, (int32_t*)hi, (float*)hs, 1, err);
     if (rc) return rc;
-    CU_TRY(cudaMemcpyAsync(hi, rt->out_ids.p, obytes, cudaMemcpyDeviceToHost, rt->stream));
-    CU_TRY(cudaMemcpyAsync(hs, rt->out_scores.p, obytes, cudaMemcpyDeviceToHost, rt->stream));
-    CU_TRY(cudaStreamSynchronize(rt->stream));
     memcpy(out_ids, hi, obytes);
     memcpy(out_scores, hs, obytes);
     rt->stats.d2h_bytes += 2 * obytes;
@@ -1148,7 +1145,7 @@ static int embed_device_locked(MantaB200Runtime* rt, const MantaB200Embedder* em
 
 // Uploads host tokens + mask (staged in rt->out_ids), then embeds into rt->queries (f16) and optionally rt->misc (f32).
 static int embed_locked(MantaB200Runtime* rt, const MantaB200Embedder* emb, const int32_t* tokens, const int32_t* mask, int batch,
-                        int seq, int pool_order, bool want_f32, char** err) {
+                        int seq, int pool_order, bool want_f32, char** err, int sync = 1) {
     const size_t tb = (size_t)batch * seq * 4;
     if (ensure(rt, rt->out_ids, 2 * tb, err)) return 1;
     if (ensure(rt, rt->queries, (size_t)batch * emb->out_dim * 2, err)) return 1;
@@ -1159,7 +1156,7 @@ static int embed_locked(MantaB200Runtime* rt, const MantaB200Embedder* emb, cons
     CU_TRY(cudaMemcpyAsync(d_mask, mask, tb, cudaMemcpyHostToDevice, rt->stream));
     rt->stats.h2d_bytes += 2 * tb;
     return embed_device_locked(rt, emb, d_tok, d_mask, batch, seq, pool_order, want_f32 ? (float*)rt->misc.p : nullptr, rt->queries.p,
-                               1, err);
+                               sync, err);
 }
 
 static int check_embed_args(const MantaB200Runtime* rt, const MantaB200Embedder* emb, const int32_t* tokens, const int32_t* mask,
@@ -1206,16 +1203,24 @@ int manta_b200_embed_score_topk(MantaB200Runtime* rt, const MantaB200Embedder* e
     CU_TRY(cudaSetDevice(rt->device));
     rt->stats.score_topk_calls++;
     const size_t obytes = (size_t)batch * k * 4;
-    // result buffers live in misc (out_ids holds the tokens until the embed kernel has run)
-    if (ensure(rt, rt->misc, 2 * obytes + 256, err)) return 1;
-    if (embed_locked(rt, emb, tokens, mask, batch, seq, pool_order, false, err)) return 1;
-    int32_t* d_ids = (int32_t*)rt->misc.p;
-    float* d_sc = (float*)((char*)rt->misc.p + (obytes + 255) / 256 * 256);
-    int rc = score_topk_locked(rt, set, metric, order, rt->queries.p, batch, k, d_ids, d_sc, 1, err);
+    // One synchronisation for the whole call: the embedding kernels are enqueued without one (their flag words are read
+    // below), and the selection writes ids and scores straight into the pinned staging buffer.
+    const size_t opad = (obytes + 255) / 256 * 256;
+    if (ensure_host(rt, 2 * opad, err)) return 1;
+    int32_t* h_ids = (int32_t*)rt->h_stage;
+    float* h_sc = (float*)((char*)rt->h_stage + opad);
+    if (embed_locked(rt, emb, tokens, mask, batch, seq, pool_order, false, err, 0)) return 1;
+    int rc = score_topk_locked(rt, set, metric, order, rt->queries.p, batch, k, h_ids, h_sc, 1, err);
+    // the stream is synchronised (or the pass failed to launch): the embedding kernels' report first
+    const bool embed_pending = rt->async_embed_pending;
+    rt->async_embed_pending = false;
+    if (embed_pending && rc == 0) {
+        if (rt->h_flags[10] == 2u) return fail(err, "embed: a bounded wait of the tensor-core projection ran out");
+        if (rt->h_flags[10]) return fail(err, "gather index %d out of range", (int32_t)rt->h_flags[11]);  // tensor_ops.go:803
+    }
     if (rc) return rc;
-    CU_TRY(cudaMemcpyAsync(out_ids, d_ids, obytes, cudaMemcpyDeviceToHost, rt->stream));
-    CU_TRY(cudaMemcpyAsync(out_scores, d_sc, obytes, cudaMemcpyDeviceToHost, rt->stream));
-    CU_TRY(cudaStreamSynchronize(rt->stream));
+    memcpy(out_ids, h_ids, obytes);
+    memcpy(out_scores, h_sc, obytes);
     rt->stats.d2h_bytes += 2 * obytes;
     return 0;
 }
