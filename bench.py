@@ -537,13 +537,15 @@ def run_ours(args, wl: Workload):
         if wl.embed:
             ln.rt.embed_device(emb, hb["s_tokens"], hb["s_mask"], nq, wl.embed[2], hb["s_q"], normalize_then_pool=bool(wl.embed_order), sync=False)
         if ln.px is not None:
-            ln.px.score_topk_merge(cands, wl.metric, hb["s_q"], nq, k, ln.m_ids, ln.m_scores, smallest=wl.smallest, sync=False)
+            # the merge writes the step's ids and scores straight into the pinned host buffers (device-addressable memory):
+            # the same bytes cross PCIe, without a copy operation behind the kernel
+            ln.px.score_topk_merge(cands, wl.metric, hb["s_q"], nq, k, hb["ids"], hb["scores"], smallest=wl.smallest, sync=False)
         else:
             ln.rt.score_topk_device(cands, wl.metric, hb["s_q"], nq, k, ln.d_ids, ln.d_scores, smallest=wl.smallest, sync=False)
             ln.merge(False)
-        with torch.cuda.stream(ln.stream):
-            hb["ids"].copy_(ln.m_ids, non_blocking=True)
-            hb["scores"].copy_(ln.m_scores, non_blocking=True)
+            with torch.cuda.stream(ln.stream):
+                hb["ids"].copy_(ln.m_ids, non_blocking=True)
+                hb["scores"].copy_(ln.m_scores, non_blocking=True)
         return li
 
     def finish_host_step(li):
@@ -577,6 +579,22 @@ def run_ours(args, wl: Workload):
     if world > 1:
         dist.all_reduce(te, op=dist.ReduceOp.MAX)
     e2e_s = float(te[0])
+
+    # The sharded end-to-end steps deliver their results in pinned host buffers: one more step (untimed) must hand back
+    # exactly what the device-resident path returns for the same queries.
+    e2e_verified = None
+    if world > 1 and lanes[0].px is not None and not wl.embed:
+        j = args.warmup + args.steps
+        ids_h, sc_h = finish_host_step(enqueue_host_step(j))
+        ids_h, sc_h = ids_h.copy(), sc_h.copy()
+        ln = lanes[j % n_lanes]
+        ln.px.score_topk_merge(cands, wl.metric, d_queries[j % nsets], nq, k, ln.m_ids, ln.m_scores, smallest=wl.smallest, sync=True)
+        same = bool(np.array_equal(ids_h, ln.m_ids.cpu().numpy()) and np.array_equal(sc_h, ln.m_scores.cpu().numpy()))
+        flag = torch.tensor([1 if same else 0], dtype=torch.int32, device="cuda")
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        e2e_verified = bool(int(flag.item()))
+        if not e2e_verified:
+            raise SystemExit("bench.py: the end-to-end step and the device-resident step disagree")
 
     # ---- CPU baseline + parity spot check on the same bounded sample (rank 0, N=1) ----------------------
     cpu = None
@@ -646,7 +664,7 @@ def run_ours(args, wl: Workload):
             "data": "synthetic",
             "config": {"workload": wl.describe(), "rows": wl.rows, "cols": wl.cols, "k": k, "queries_per_step": nq,
                        "layout": wl.layout, "shards": world, "note": wl.note, "lanes": n_lanes,
-                       "exchange": (args.exchange if world > 1 else None), "exchange_equals_nccl_path": exchange_verified,
+                       "exchange": (args.exchange if world > 1 else None), "exchange_equals_nccl_path": exchange_verified, "e2e_equals_device_path": e2e_verified,
                        "l2": f"inputs larger than L2: {algo_bytes / 1e9:.3f} GB scanned per pass and GPU" if algo_bytes > 2.5e8
                              else "inputs smaller than L2 (latency-bound configuration, not a roofline point)"},
             "candidates_dim_per_s": value * wl.rows * wl.cols,
